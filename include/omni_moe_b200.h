@@ -1,0 +1,175 @@
+/*
+ * C ABI of libomni_moe_b200.so: the OmniMoE layer-forward hot path on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream (passed as void*, a
+ * cudaStream_t), enqueues its kernels on that stream and returns at once:
+ *   0   the work was enqueued
+ *   <0  an argument was rejected (omni_last_error() gives the reason); nothing was enqueued
+ * No entry point allocates, frees, synchronises or throws.  Scratch memory is supplied by the
+ * caller (omni_*_workspace_bytes says how much).  Faults that can only be seen on the device
+ * (an expert index out of range, a wait inside a kernel that gave up) are written to the int32
+ * status word the caller passes; it stays 0 when all is well and the caller reads it when it
+ * chooses to synchronise.
+ *
+ * Each function names the interface of the reference project (HKUSTDial/omni-moe, paths relative
+ * to that project) whose work it takes over.
+ */
+#ifndef OMNI_MOE_B200_H
+#define OMNI_MOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define OMNI_API __attribute__((visibility("default")))
+#else
+#define OMNI_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of tensor arguments */
+enum { OMNI_F32 = 0, OMNI_BF16 = 1, OMNI_F16 = 2 };
+
+/* bits of the device status word */
+enum {
+  OMNI_ST_BAD_EXPERT_INDEX = 1,  /* an expert index was < 0 or >= num_experts; the pair was skipped */
+  OMNI_ST_WAIT_TIMEOUT = 2,      /* a bounded wait inside a kernel ran out; results are invalid */
+  OMNI_ST_BAD_TOKEN_INDEX = 4    /* a scheduled pair pointed outside the token range */
+};
+
+/* Library ABI version (major * 100 + minor). */
+OMNI_API int omni_version(void);
+
+/* Message of the last call on this host thread that returned < 0 ("" if none). */
+OMNI_API const char *omni_last_error(void);
+
+/*
+ * Product-key top-k over the sqrt(N) x sqrt(N) grid of log_probs_x[i] + log_probs_y[j].
+ * Replaces triton_omni_router_func (omni_moe/ops/triton/interface.py:32-51), i.e.
+ * OmniRouterFunc.forward / _omni_router_forward and its Triton kernel
+ * (omni_moe/ops/triton/omni_router.py:13-95,167-232), and the torch.exp that follows it in
+ * the module (omni_moe/modules/omni_moe.py:86).
+ *
+ *   log_probs_x/y  [T, sqrt_n] row-major, element type in_dtype
+ *   scores         [T, k] float32, sorted descending              (may not be NULL)
+ *   indices        [T, k] int32 (idx_is_i64 == 0) or int64: ix * sqrt_n + iy
+ *   weights        [T, k] float32 = exp(scores), or NULL
+ * Sums are formed in fp32.  Ties: higher score wins, then the lower index.
+ * Limits: 1 <= sqrt_n <= 1024, 1 <= k <= 128, k <= sqrt_n * sqrt_n.
+ */
+OMNI_API int omni_router_topk(const void *log_probs_x, const void *log_probs_y, int in_dtype,
+                     int64_t num_tokens, int sqrt_n, int k,
+                     float *scores, void *indices, int idx_is_i64, float *weights,
+                     void *stream);
+
+/*
+ * The same selection, starting from raw router-gate outputs: applies the eval-mode BatchNorm
+ * (as a per-column scale and shift), the per-axis log-softmax and the top-k in one kernel.
+ * Replaces, in OmniMoE.forward, router_norm_x/y, F.log_softmax, triton_omni_router_func and
+ * torch.exp (omni_moe/modules/omni_moe.py:70-86).
+ *
+ *   logits     [T, 2*sqrt_n] float32 with row stride ld_logits: columns [0, sqrt_n) are the
+ *              x axis, [sqrt_n, 2*sqrt_n) the y axis
+ *   bn_scale, bn_shift  [2*sqrt_n] float32: normalised = logit * scale + shift (NULL = identity)
+ *   log_probs_out  [T, 2*sqrt_n] float32 or NULL: the log-probabilities the selection used
+ */
+OMNI_API int omni_router_logits_topk(const float *logits, int64_t ld_logits,
+                            const float *bn_scale, const float *bn_shift,
+                            int64_t num_tokens, int sqrt_n, int k,
+                            float *scores, void *indices, int idx_is_i64, float *weights,
+                            float *log_probs_out, void *stream);
+
+/*
+ * Router gate GEMMs: logits[:, 0:sqrt_n] = x . gate_x^T, logits[:, sqrt_n:] = x . gate_y^T,
+ * bf16 operands, fp32 accumulation and output (tcgen05 tensor cores, operands by TMA).
+ * Replaces the two nn.Linear router gates (omni_moe/modules/omni_moe.py:47-52,70-71).
+ *
+ *   x        [T, H] bf16 row-major       gate_x, gate_y  [sqrt_n, H] bf16 row-major
+ *   logits   [T, 2*sqrt_n] float32 row-major
+ * Limits: H % 8 == 0, pointers 16-byte aligned.  status: device int32, see top of file.
+ */
+OMNI_API int omni_router_gate(const void *x, const void *gate_x, const void *gate_y,
+                     int64_t num_tokens, int hidden, int sqrt_n,
+                     float *logits, int32_t *status, void *stream);
+
+/*
+ * Expert-centric scheduling: stable sort of the T*k (token, expert) pairs by expert, with the
+ * CSR description of the expert segments.  Replaces get_scheduling_info, tail path
+ * (omni_moe/ops/triton/omni_scheduler.py:48-101): ~12 torch launches and one blocking .item().
+ *
+ *   indices          [T, k] int32 or int64 expert ids
+ *   weights          [T, k] routing weights, element size weight_elem_bytes (2 or 4), or NULL
+ *   sorted_pair_ids  [P] int32  the permutation: pairs ordered by (expert, pair id)   P = T*k
+ *   sorted_experts   [P] int32  expert id at each sorted position
+ *   token_ids        [P] int32  sorted_pair_ids / k, or NULL
+ *   sorted_weights   [P] weights in sorted order (same element size), or NULL
+ *   expert_ids       [min(P, N)] int32  distinct experts, ascending (first U entries valid), or NULL
+ *   offsets          [min(P, N) + 1] int32  segment starts, offsets[U] = P, or NULL
+ *   meta             [4] int32 device: {U, max pairs per expert, status word, reserved}
+ *   workspace        omni_schedule_workspace_bytes(P, N) bytes, 256-byte aligned
+ */
+OMNI_API size_t omni_schedule_workspace_bytes(int64_t num_pairs, int64_t num_experts);
+OMNI_API int omni_schedule(const void *indices, int idx_is_i64, const void *weights, int weight_elem_bytes,
+                  int64_t num_tokens, int k, int64_t num_experts,
+                  int32_t *sorted_pair_ids, int32_t *sorted_experts, int32_t *token_ids,
+                  void *sorted_weights, int32_t *expert_ids, int32_t *offsets, int32_t *meta,
+                  void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Routed experts, y[t] = sum_j w[t,j] * silu(x[t] . Up[e[t,j]]) * Down[e[t,j]], in two kernels:
+ * omni_expert_coef walks the pairs in expert order (each Up row is fetched once per run of
+ * pairs on that expert) and writes c[t,j] = w[t,j] * silu(x[t] . Up[e]) in fp32;
+ * omni_expert_combine forms y[t] = sum_j c[t,j] * Down[e[t,j]] per token, without atomics, so
+ * the result does not depend on execution order.
+ * Replace omni_expert_forward and its two Triton kernels
+ * (omni_moe/ops/triton/omni_expert.py:13-168,920-992) behind triton_omni_expert_func
+ * (omni_moe/ops/triton/interface.py:54-72).
+ *
+ *   x [T, H], up/down [N, H] bf16 row-major; weights [T, k] float32; indices [T, k] int32
+ *   sorted_pair_ids, sorted_experts: from omni_schedule
+ *   coef [T, k] float32
+ *   y [T, H] of out_dtype (OMNI_F32 or OMNI_BF16); residual [T, H] of the same type added in, or NULL
+ * Limits: H % 8 == 0, pointers 16-byte aligned.
+ */
+OMNI_API int omni_expert_coef(const void *x, const void *up, const float *weights,
+                     const int32_t *sorted_pair_ids, const int32_t *sorted_experts,
+                     int64_t num_tokens, int k, int hidden, int64_t num_experts,
+                     float *coef, int32_t *status, void *stream);
+OMNI_API int omni_expert_combine(const void *down, const float *coef, const int32_t *indices,
+                        int64_t num_tokens, int k, int hidden, int64_t num_experts,
+                        const void *residual, void *y, int out_dtype,
+                        int32_t *status, void *stream);
+
+/*
+ * Shared SwiGLU MLP, y = (silu(x Wg^T) * (x Wu^T)) Wd^T (+ residual), as two tcgen05 GEMMs: the
+ * first computes the gate and up projections of a tile side by side and applies silu(g)*u in
+ * its epilogue (the [T, I] gate and up activations never reach memory), the second applies the
+ * down projection and, if given, adds the fp32 residual before rounding to bf16.
+ * Replaces triton_omni_mlp_func (omni_moe/ops/triton/interface.py:7-29): three cuBLAS GEMMs and
+ * the Triton SwiGLU kernel (omni_moe/ops/triton/omni_mlp.py:103-177,252-303); with residual,
+ * also the final add of the module (omni_moe/modules/omni_moe.py:102).
+ *
+ *   x [T, H], gate_w/up_w [I, H], down_w [H, I]  bf16 row-major
+ *   act [T, I] bf16 scratch (caller-owned)     residual [T, H] float32 or NULL     y [T, H] bf16
+ * Limits: H % 8 == 0, I % 8 == 0, pointers 16-byte aligned.
+ */
+OMNI_API int omni_mlp_fwd(const void *x, const void *gate_w, const void *up_w, const void *down_w,
+                 int64_t num_tokens, int hidden, int intermediate,
+                 void *act, const float *residual, void *y,
+                 int32_t *status, void *stream);
+
+/* The two halves of omni_mlp_fwd, for callers that schedule them on different streams. */
+OMNI_API int omni_mlp_gate_up(const void *x, const void *gate_w, const void *up_w,
+                     int64_t num_tokens, int hidden, int intermediate,
+                     void *act, int32_t *status, void *stream);
+OMNI_API int omni_mlp_down(const void *act, const void *down_w,
+                  int64_t num_tokens, int hidden, int intermediate,
+                  const float *residual, void *y, int32_t *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMNI_MOE_B200_H */

@@ -1,0 +1,68 @@
+// Shared helpers for the sm_100a kernels of libomni_moe_b200.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/omni_moe_b200.h"
+
+namespace omni {
+
+// Records the message returned by omni_last_error() and yields the error code.
+int fail(int code, const char* fmt, ...);
+
+#define OMNI_REQUIRE(cond, ...)                      \
+  do {                                               \
+    if (!(cond)) return ::omni::fail(-1, __VA_ARGS__); \
+  } while (0)
+
+// Checks the launch itself (configuration errors show up here; kernels report through status words).
+int check_launch(const char* what);
+
+constexpr unsigned FULL_MASK = 0xffffffffu;
+
+__host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+__host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+__device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
+// Maps a float to an unsigned key whose integer order is the float order; -0.0 is first
+// folded into +0.0 so the two tie, as they do under a float comparison.
+__device__ __forceinline__ uint32_t float_to_key(float f) {
+  uint32_t u = __float_as_uint(__fadd_rn(f, 0.0f));
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+__device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
+
+// 128-bit read-only load of 8 bf16.
+__device__ __forceinline__ uint4 ldg128(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t v) {
+  // a bf16 is the upper half of an fp32
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+
+__device__ __forceinline__ uint32_t float2_to_bf16x2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL_MASK, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL_MASK, v, o));
+  return v;
+}
+
+}  // namespace omni

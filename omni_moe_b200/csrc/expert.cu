@@ -1,0 +1,246 @@
+// Routed experts: y[t] = sum_j w[t,j] * silu(x[t] . Up[e[t,j]]) * Down[e[t,j]].
+//
+// expert_coef_kernel    walks the pairs in expert order (the output of the scheduler).  A warp owns
+//                       a run of consecutive sorted positions, keeps the current expert's Up row in
+//                       registers and only refetches it when the expert changes, so each Up row
+//                       leaves HBM once; the token rows x[t] are re-read per pair, but x is k/4
+//                       times smaller than the touched part of the table and lives in L2.
+//                       Output: c[pair] = w * silu(x . up), fp32, at the pair's original place.
+// expert_combine_kernel is token-centric: a warp owns (token, column slab), loops over the token's
+//                       k pairs and accumulates c * Down[e] in fp32 registers, then writes the
+//                       row once.  No atomics, no zero fill, fixed summation order.
+// All row traffic is 128-bit loads, a warp reading 512 contiguous bytes per instruction.
+#include "common.cuh"
+
+namespace omni {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kRun = 16;  // sorted positions per warp in expert_coef_kernel
+
+__device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc) {
+  const uint32_t* pa = reinterpret_cast<const uint32_t*>(&a);
+  const uint32_t* pb = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fa = bf16x2_to_float2(pa[i]), fb = bf16x2_to_float2(pb[i]);
+    acc = __fmaf_rn(fa.x, fb.x, acc);
+    acc = __fmaf_rn(fa.y, fb.y, acc);
+  }
+  return acc;
+}
+
+// HV = 128-bit vectors per lane; covers HV * 256 columns per slab.
+template <int HV>
+__global__ void __launch_bounds__(kThreads) expert_coef_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const float* __restrict__ weights,
+    const int* __restrict__ perm, const int* __restrict__ sorted_experts, int64_t P, int64_t T, int k, int H,
+    int64_t N, float* __restrict__ coef, int* status) {
+  const int lane = lane_id();
+  const int64_t w0 = (static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5)) * kRun;
+  if (w0 >= P) return;
+  // lane i < kRun carries the metadata of sorted position w0 + i
+  int my_pair = -1, my_e = -1;
+  float my_g = 0.f;
+  if (lane < kRun && w0 + lane < P) {
+    my_pair = perm[w0 + lane];
+    my_e = sorted_experts[w0 + lane];
+    my_g = (my_pair >= 0 && my_pair < P) ? weights[my_pair] : 0.f;
+  }
+  const int count = (P - w0 < kRun) ? static_cast<int>(P - w0) : kRun;
+  const int slabs = ceil_div(H, HV * 256);
+  int cur_e = -1;
+  uint4 row[HV];
+  bool bad_e = false, bad_t = false;
+  for (int i = 0; i < count; ++i) {
+    const int pair = __shfl_sync(FULL_MASK, my_pair, i);
+    const int e = __shfl_sync(FULL_MASK, my_e, i);
+    const float g = __shfl_sync(FULL_MASK, my_g, i);
+    const int64_t t = pair / k;
+    if (e < 0 || e >= N) { bad_e = true; if (lane == 0 && pair >= 0 && pair < P) coef[pair] = 0.f; continue; }
+    if (pair < 0 || t >= T) { bad_t = true; continue; }
+    float acc = 0.f;
+    for (int s = 0; s < slabs; ++s) {
+      const int c0 = s * HV * 256 + lane * 8;
+      uint4 xv[HV];
+#pragma unroll
+      for (int v = 0; v < HV; ++v) {
+        const int c = c0 + v * 256;
+        xv[v] = c < H ? ldg128(x + t * H + c) : make_uint4(0, 0, 0, 0);
+      }
+      if (e != cur_e || slabs > 1) {
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const int c = c0 + v * 256;
+          row[v] = c < H ? ldg128(up + static_cast<int64_t>(e) * H + c) : make_uint4(0, 0, 0, 0);
+        }
+        cur_e = e;
+      }
+#pragma unroll
+      for (int v = 0; v < HV; ++v) acc = dot8(xv[v], row[v], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) coef[pair] = g * silu(acc);
+  }
+  if (bad_e && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+  if (bad_t && lane == 0) atomicOr(status, OMNI_ST_BAD_TOKEN_INDEX);
+}
+
+template <int HV, bool OUT_F32>
+__global__ void __launch_bounds__(kThreads) expert_combine_kernel(
+    const __nv_bfloat16* __restrict__ down, const float* __restrict__ coef, const int* __restrict__ indices,
+    int64_t T, int k, int H, int64_t N, int slabs, const void* __restrict__ residual, void* __restrict__ y, int* status) {
+  const int lane = lane_id();
+  const int64_t wid = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  const int64_t t = wid / slabs;
+  const int slab = static_cast<int>(wid - t * slabs);
+  if (t >= T) return;
+  const int c0 = slab * HV * 256 + lane * 8;
+  float acc[HV][8];
+#pragma unroll
+  for (int v = 0; v < HV; ++v)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[v][q] = 0.f;
+  bool bad = false;
+  for (int j0 = 0; j0 < k; j0 += 32) {
+    // lane l carries pair j0 + l of this token
+    int my_e = -1;
+    float my_c = 0.f;
+    if (j0 + lane < k) {
+      my_e = indices[t * k + j0 + lane];
+      my_c = coef[t * k + j0 + lane];
+      if (my_e < 0 || my_e >= N) { bad = true; my_e = -1; }
+    }
+    const int cnt = min(32, k - j0);
+    constexpr int UNR = HV >= 8 ? 2 : 4;  // rows in flight per step
+    for (int j = 0; j < cnt; j += UNR) {
+      uint4 dv[UNR][HV];
+      float c[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int e = __shfl_sync(FULL_MASK, my_e, (j + u) & 31);
+        c[u] = __shfl_sync(FULL_MASK, my_c, (j + u) & 31);
+        const bool on = (j + u < cnt) && e >= 0;
+        if (!on) c[u] = 0.f;
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const int col = c0 + v * 256;
+          dv[u][v] = (on && col < H) ? ldg128(down + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv[u][v]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = bf16x2_to_float2(pd[q]);
+            acc[v][2 * q] = __fmaf_rn(c[u], f.x, acc[v][2 * q]);
+            acc[v][2 * q + 1] = __fmaf_rn(c[u], f.y, acc[v][2 * q + 1]);
+          }
+        }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < HV; ++v) {
+    const int col = c0 + v * 256;
+    if (col >= H) continue;
+    const int64_t o = t * H + col;
+    if (OUT_F32) {
+      float4 a = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+      float4 b = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+      if (residual) {
+        const float4 ra = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o));
+        const float4 rb = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o + 4));
+        a.x += ra.x, a.y += ra.y, a.z += ra.z, a.w += ra.w;
+        b.x += rb.x, b.y += rb.y, b.z += rb.z, b.w += rb.w;
+      }
+      float* yo = reinterpret_cast<float*>(y) + o;
+      *reinterpret_cast<float4*>(yo) = a;
+      *reinterpret_cast<float4*>(yo + 4) = b;
+    } else {
+      if (residual) {
+        const uint4 rv = ldg128(reinterpret_cast<const __nv_bfloat16*>(residual) + o);
+        const uint32_t* pr = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = bf16x2_to_float2(pr[q]);
+          acc[v][2 * q] += f.x;
+          acc[v][2 * q + 1] += f.y;
+        }
+      }
+      uint4 o4;
+      o4.x = float2_to_bf16x2(acc[v][0], acc[v][1]);
+      o4.y = float2_to_bf16x2(acc[v][2], acc[v][3]);
+      o4.z = float2_to_bf16x2(acc[v][4], acc[v][5]);
+      o4.w = float2_to_bf16x2(acc[v][6], acc[v][7]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(y) + o) = o4;
+    }
+  }
+  if (bad && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace omni
+
+using namespace omni;
+
+extern "C" int omni_expert_coef(const void* x, const void* up, const float* weights, const int32_t* sorted_pair_ids,
+                                const int32_t* sorted_experts, int64_t num_tokens, int k, int hidden,
+                                int64_t num_experts, float* coef, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && num_experts >= 1, "bad sizes");
+  OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
+  const int64_t P = num_tokens * k;
+  if (P == 0) return 0;
+  OMNI_REQUIRE(x && up && weights && sorted_pair_ids && sorted_experts && coef && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(up), "x and up must be 16-byte aligned");
+  const auto* xb = static_cast<const __nv_bfloat16*>(x);
+  const auto* ub = static_cast<const __nv_bfloat16*>(up);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(ceil_div64(ceil_div64(P, kRun), kWarps));
+#define OMNI_COEF(HV)                                                                                         \
+  expert_coef_kernel<HV><<<grid, kThreads, 0, st>>>(xb, ub, weights, sorted_pair_ids, sorted_experts, P, num_tokens, \
+                                                   k, hidden, num_experts, coef, status)
+  if (hidden <= 256) OMNI_COEF(1);
+  else if (hidden <= 512) OMNI_COEF(2);
+  else if (hidden <= 1024) OMNI_COEF(4);
+  else if (hidden <= 2048) OMNI_COEF(8);
+  else OMNI_COEF(16);
+#undef OMNI_COEF
+  return check_launch("expert_coef_kernel");
+}
+
+extern "C" int omni_expert_combine(const void* down, const float* coef, const int32_t* indices, int64_t num_tokens,
+                                   int k, int hidden, int64_t num_experts, const void* residual, void* y,
+                                   int out_dtype, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && num_experts >= 1, "bad sizes");
+  OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
+  OMNI_REQUIRE(out_dtype == OMNI_F32 || out_dtype == OMNI_BF16, "out_dtype must be OMNI_F32 or OMNI_BF16");
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(down && coef && indices && y && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(down) && aligned16(y) && aligned16(residual), "down, y and residual must be 16-byte aligned");
+  const auto* db = static_cast<const __nv_bfloat16*>(down);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int hv = hidden <= 256 ? 1 : hidden <= 512 ? 2 : hidden <= 1024 ? 4 : 8;
+  const int slabs = ceil_div(hidden, hv * 256);
+  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens * slabs, kWarps));
+#define OMNI_COMB(HV)                                                                                              \
+  do {                                                                                                             \
+    if (out_dtype == OMNI_F32)                                                                                     \
+      expert_combine_kernel<HV, true><<<grid, kThreads, 0, st>>>(db, coef, indices, num_tokens, k, hidden, num_experts, \
+                                                                 slabs, residual, y, status);                        \
+    else                                                                                                           \
+      expert_combine_kernel<HV, false><<<grid, kThreads, 0, st>>>(db, coef, indices, num_tokens, k, hidden, num_experts, \
+                                                                  slabs, residual, y, status);                       \
+  } while (0)
+  if (hv == 1) OMNI_COMB(1);
+  else if (hv == 2) OMNI_COMB(2);
+  else if (hv == 4) OMNI_COMB(4);
+  else OMNI_COMB(8);
+#undef OMNI_COMB
+  return check_launch("expert_combine_kernel");
+}

@@ -1,0 +1,402 @@
+// Expert-centric scheduling: a stable least-significant-digit radix sort of the (token, expert)
+// pairs by expert id, followed by the CSR description of the expert segments.
+//
+// One digit pass = two kernels and no inter-block waiting:
+//   radix_count   every tile (a contiguous run of pairs) histograms its digit into shared memory
+//                 and writes its column of the [bins x tiles] count matrix; the block that
+//                 finishes last turns the matrix into exclusive prefixes (each warp scans bin
+//                 rows, then the bin totals are scanned) - "last block done", nobody spins.
+//   radix_scatter every tile ranks its pairs inside the tile with warp match operations
+//                 (order preserving) and writes key and pair id to
+//                 bin_base[digit] + tile_prefix[digit][tile] + rank.
+// Digits are at most 11 bits wide, so expert tables up to 2^22 rows need two passes.
+//
+// The segment description is two more kernels: count segment heads per tile (+ last-block
+// scan), then write expert ids / offsets / token ids / permuted weights (+ last-block maximum
+// segment length).
+#include "common.cuh"
+
+namespace omni {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxBits = 11;
+constexpr int kMaxBins = 1 << kMaxBits;
+
+// workspace header (int32 words)
+enum { HDR_TICKET0 = 0, HDR_WORDS = 16 };  // one ticket counter per kernel that uses "last block done"
+
+struct Plan {
+  int64_t P;
+  int passes, bits[3], ipt, tile, tiles;
+  size_t off_keysA, off_valsA, off_keysB, off_valsB, off_hist, off_binbase, off_tilecnt, total;
+};
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+Plan make_plan(int64_t P, int64_t N) {
+  Plan p{};
+  p.P = P;
+  int key_bits = 1;
+  while ((int64_t(1) << key_bits) < N) ++key_bits;
+  p.passes = ceil_div(key_bits, kMaxBits);
+  // distribute the bits evenly over the passes: the first passes get the ceiling
+  int left = key_bits;
+  for (int i = 0; i < p.passes; ++i) {
+    p.bits[i] = ceil_div(left, p.passes - i);
+    left -= p.bits[i];
+  }
+  p.ipt = (P >= int64_t(148) * 2 * kThreads * 16) ? 16 : 4;
+  p.tile = kThreads * p.ipt;
+  p.tiles = static_cast<int>(ceil_div64(P > 0 ? P : 1, p.tile));
+  size_t o = HDR_WORDS * sizeof(int32_t);
+  o = align_up(o, 256);
+  const size_t arr = align_up(static_cast<size_t>(P > 0 ? P : 1) * 4, 256);
+  p.off_keysA = o, o += arr;
+  p.off_valsA = o, o += arr;
+  p.off_keysB = o, o += arr;
+  p.off_valsB = o, o += arr;
+  p.off_hist = o, o += align_up(static_cast<size_t>(kMaxBins) * p.tiles * 4, 256);
+  p.off_binbase = o, o += align_up(static_cast<size_t>(kMaxBins) * 4, 256);
+  p.off_tilecnt = o, o += align_up(static_cast<size_t>(p.tiles + 1) * 4, 256);
+  p.total = o;
+  return p;
+}
+
+__device__ __forceinline__ int load_key(const void* keys, int is_i64, int64_t i) {
+  return is_i64 ? static_cast<int>(reinterpret_cast<const int64_t*>(keys)[i]) : reinterpret_cast<const int32_t*>(keys)[i];
+}
+
+// Block-wide exclusive scan of one int per thread; returns the exclusive prefix, total via reference.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* s_warp /*[kWarps]*/, int& total) {
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(FULL_MASK, inc, o);
+    if (lane >= o) inc += y;
+  }
+  if (lane == 31) s_warp[warp] = inc;
+  __syncthreads();
+  int wbase = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const int c = s_warp[w];
+    if (w < warp) wbase += c;
+    tot += c;
+  }
+  __syncthreads();
+  total = tot;
+  return wbase + inc - v;
+}
+
+// ---- pass kernel 1: per-tile digit histogram + last-block scan ----------------------------
+template <int IPT>
+__global__ void __launch_bounds__(kThreads) radix_count_kernel(
+    const void* keys, int key_is_i64, int64_t P, int shift, int bits, int check_range, int num_experts,
+    int* hist /*[bins][tiles]*/, int* bin_base /*[bins]*/, int* ticket, int* status) {
+  __shared__ int s_hist[kMaxBins];
+  __shared__ int s_scan[kWarps];
+  __shared__ int s_last;
+  const int bins = 1 << bits, tiles = gridDim.x, tile = blockIdx.x;
+  for (int b = threadIdx.x; b < bins; b += kThreads) s_hist[b] = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(tile) * (kThreads * IPT);
+  bool bad = false;
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int64_t p = base + i * kThreads + threadIdx.x;
+    if (p < P) {
+      const int e = load_key(keys, key_is_i64, p);
+      if (check_range && (e < 0 || e >= num_experts)) bad = true;
+      atomicAdd(&s_hist[(static_cast<unsigned>(e) >> shift) & (bins - 1)], 1);
+    }
+  }
+  if (bad) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+  __syncthreads();
+  for (int b = threadIdx.x; b < bins; b += kThreads) hist[static_cast<size_t>(b) * tiles + tile] = s_hist[b];
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == tiles - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // Last block: row-wise exclusive prefixes over tiles (one warp per bin row), totals to s_hist.
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  for (int b = warp; b < bins; b += kWarps) {
+    volatile int* row = hist + static_cast<size_t>(b) * tiles;
+    int carry = 0;
+    for (int t0 = 0; t0 < tiles; t0 += 32) {
+      const int t = t0 + lane;
+      const int v = t < tiles ? row[t] : 0;
+      int inc = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(FULL_MASK, inc, o);
+        if (lane >= o) inc += y;
+      }
+      if (t < tiles) row[t] = carry + inc - v;
+      carry += __shfl_sync(FULL_MASK, inc, 31);
+    }
+    if (lane == 0) s_hist[b] = carry;
+  }
+  __syncthreads();
+  // exclusive scan of the bin totals (bins <= 2048 = 8 per thread)
+  constexpr int PER = kMaxBins / kThreads;
+  int loc[PER], sum = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int b = threadIdx.x * PER + j;
+    loc[j] = b < bins ? s_hist[b] : 0;
+    sum += loc[j];
+  }
+  int total;
+  int run = block_exclusive_scan(sum, s_scan, total);
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int b = threadIdx.x * PER + j;
+    if (b < bins) bin_base[b] = run;
+    run += loc[j];
+  }
+  if (threadIdx.x == 0) *ticket = 0;  // ready for the next use of this counter
+}
+
+// ---- pass kernel 2: stable in-tile ranking + scatter --------------------------------------
+template <int IPT>
+__global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
+    const void* keys, int key_is_i64, const int* vals /*null: identity*/, int64_t P, int shift, int bits,
+    const int* hist, const int* bin_base, int* out_keys, int* out_vals) {
+  extern __shared__ uint16_t s_cnt[];  // [kWarps][bins]: pairs of each digit seen so far by each warp
+  const int bins = 1 << bits, tiles = gridDim.x, tile = blockIdx.x;
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  for (int b = threadIdx.x; b < kWarps * bins; b += kThreads) s_cnt[b] = 0;
+  __syncthreads();
+  // warp w owns the contiguous run [w * 32 * IPT, (w + 1) * 32 * IPT) of the tile, item i of lane
+  // l sits at offset i * 32 + l, so walking i upward visits the pairs in ascending pair order.
+  const int64_t wbase = static_cast<int64_t>(tile) * (kThreads * IPT) + warp * (32 * IPT);
+  uint16_t* cnt = s_cnt + warp * bins;
+  int key[IPT], val[IPT];
+  uint16_t rank[IPT];
+  const unsigned lt_mask = (1u << lane) - 1u;
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int64_t p = wbase + i * 32 + lane;
+    const bool ok = p < P;
+    key[i] = ok ? load_key(keys, key_is_i64, p) : 0;
+    val[i] = ok ? (vals ? vals[p] : static_cast<int>(p)) : 0;
+    const int d = ok ? ((static_cast<unsigned>(key[i]) >> shift) & (bins - 1)) : bins;  // bins = "none"
+    const unsigned peers = __match_any_sync(FULL_MASK, d);
+    const int before = ok ? cnt[d] : 0;
+    __syncwarp();
+    if (ok && (peers & lt_mask) == 0) cnt[d] = static_cast<uint16_t>(before + __popc(peers));
+    __syncwarp();
+    rank[i] = static_cast<uint16_t>(before + __popc(peers & lt_mask));
+  }
+  __syncthreads();
+  // per digit: exclusive prefix over the warps (warp order = pair order)
+  for (int b = threadIdx.x; b < bins; b += kThreads) {
+    int run = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = s_cnt[w * bins + b];
+      s_cnt[w * bins + b] = static_cast<uint16_t>(run);
+      run += c;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int64_t p = wbase + i * 32 + lane;
+    if (p < P) {
+      const int d = (static_cast<unsigned>(key[i]) >> shift) & (bins - 1);
+      const int dst = bin_base[d] + hist[static_cast<size_t>(d) * tiles + tile] + cnt[d] + rank[i];
+      out_keys[dst] = key[i];
+      out_vals[dst] = val[i];
+    }
+  }
+}
+
+// ---- segments kernel 1: heads per tile + last-block scan ------------------------------------
+template <int IPT>
+__global__ void __launch_bounds__(kThreads) segment_count_kernel(const int* sorted_keys, int64_t P, int* tile_cnt /*[tiles+1]*/,
+                                                                 int* ticket, int* meta) {
+  __shared__ int s_scan[kWarps];
+  __shared__ int s_last;
+  const int tiles = gridDim.x, tile = blockIdx.x;
+  const int64_t base = static_cast<int64_t>(tile) * (kThreads * IPT) + static_cast<int64_t>(threadIdx.x) * IPT;
+  int heads = 0;
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int64_t p = base + i;
+    if (p < P && (p == 0 || sorted_keys[p] != sorted_keys[p - 1])) ++heads;
+  }
+  int total;
+  block_exclusive_scan(heads, s_scan, total);
+  if (threadIdx.x == 0) {
+    tile_cnt[tile] = total;
+    __threadfence();
+    s_last = (atomicAdd(ticket, 1) == tiles - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // last block: exclusive scan of tile_cnt in place, U to meta[0]
+  volatile int* tc = tile_cnt;
+  int carry = 0;
+  for (int t0 = 0; t0 < tiles; t0 += kThreads) {
+    const int t = t0 + threadIdx.x;
+    const int v = t < tiles ? tc[t] : 0;
+    int tot;
+    const int ex = block_exclusive_scan(v, s_scan, tot);
+    if (t < tiles) tc[t] = carry + ex;
+    carry += tot;
+  }
+  if (threadIdx.x == 0) {
+    tc[tiles] = carry;
+    meta[0] = carry;
+    *ticket = 0;
+  }
+}
+
+// ---- segments kernel 2: write the description -------------------------------------------------
+template <int IPT>
+__global__ void __launch_bounds__(kThreads) segment_write_kernel(
+    const int* sorted_keys, const int* perm, int64_t P, int k, const void* weights, int wbytes,
+    const int* tile_cnt, int* token_ids, void* sorted_weights, int* expert_ids, int* offsets,
+    int* ticket, int* meta) {
+  __shared__ int s_scan[kWarps];
+  __shared__ int s_last;
+  const int tiles = gridDim.x, tile = blockIdx.x;
+  const int64_t base = static_cast<int64_t>(tile) * (kThreads * IPT) + static_cast<int64_t>(threadIdx.x) * IPT;
+  int keyv[IPT];
+  bool head[IPT];
+  int heads = 0;
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int64_t p = base + i;
+    head[i] = false;
+    if (p < P) {
+      keyv[i] = sorted_keys[p];
+      head[i] = (p == 0) || (keyv[i] != sorted_keys[p - 1]);
+      heads += head[i];
+      const int pr = perm[p];
+      if (token_ids) token_ids[p] = pr / k;
+      if (sorted_weights) {
+        if (wbytes == 4) reinterpret_cast<uint32_t*>(sorted_weights)[p] = reinterpret_cast<const uint32_t*>(weights)[pr];
+        else reinterpret_cast<uint16_t*>(sorted_weights)[p] = reinterpret_cast<const uint16_t*>(weights)[pr];
+      }
+    }
+  }
+  int total;
+  int r = tile_cnt[tile] + block_exclusive_scan(heads, s_scan, total);
+  if (offsets) {
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (head[i]) {
+        if (expert_ids) expert_ids[r] = keyv[i];
+        offsets[r] = static_cast<int>(base + i);
+        ++r;
+      }
+    }
+  }
+  if (!offsets) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == tiles - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // last block: offsets[U] = P and the longest segment
+  const int U = tile_cnt[tiles];
+  volatile int* off = offsets;
+  if (threadIdx.x == 0) off[U] = static_cast<int>(P);
+  __syncthreads();
+  int mx = 0;
+  for (int s = threadIdx.x; s < U; s += kThreads) mx = max(mx, off[s + 1] - off[s]);
+  mx = __reduce_max_sync(FULL_MASK, mx);
+  if (lane_id() == 0) s_scan[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 0; w < kWarps; ++w) mx = max(mx, s_scan[w]);
+    meta[1] = mx;
+    *ticket = 0;
+  }
+}
+
+template <int IPT>
+int run(const Plan& pl, const void* indices, int idx_is_i64, const void* weights, int wbytes, int k, int64_t N,
+        int* perm, int* sorted_experts, int* token_ids, void* sorted_weights, int* expert_ids, int* offsets,
+        int* meta, char* ws, cudaStream_t st) {
+  int* hdr = reinterpret_cast<int*>(ws);
+  int* keysA = reinterpret_cast<int*>(ws + pl.off_keysA);
+  int* valsA = reinterpret_cast<int*>(ws + pl.off_valsA);
+  int* keysB = reinterpret_cast<int*>(ws + pl.off_keysB);
+  int* valsB = reinterpret_cast<int*>(ws + pl.off_valsB);
+  int* hist = reinterpret_cast<int*>(ws + pl.off_hist);
+  int* binbase = reinterpret_cast<int*>(ws + pl.off_binbase);
+  int* tilecnt = reinterpret_cast<int*>(ws + pl.off_tilecnt);
+  cudaMemsetAsync(hdr, 0, HDR_WORDS * sizeof(int), st);
+  cudaMemsetAsync(meta, 0, 4 * sizeof(int), st);
+  const void* in_keys = indices;
+  int in_i64 = idx_is_i64;
+  const int* in_vals = nullptr;
+  int shift = 0;
+  for (int pass = 0; pass < pl.passes; ++pass) {
+    const bool last = pass == pl.passes - 1;
+    int* ok = last ? sorted_experts : (pass == 0 ? keysA : keysB);
+    int* ov = last ? perm : (pass == 0 ? valsA : valsB);
+    const int bits = pl.bits[pass];
+    radix_count_kernel<IPT><<<pl.tiles, kThreads, 0, st>>>(in_keys, in_i64, pl.P, shift, bits, pass == 0,
+                                                         static_cast<int>(N), hist, binbase, hdr + HDR_TICKET0, meta + 2);
+    const size_t smem = static_cast<size_t>(kWarps) * (size_t(1) << bits) * sizeof(uint16_t);
+    radix_scatter_kernel<IPT><<<pl.tiles, kThreads, smem, st>>>(in_keys, in_i64, in_vals, pl.P, shift, bits, hist, binbase, ok, ov);
+    in_keys = ok, in_i64 = 0, in_vals = ov;
+    shift += bits;
+  }
+  segment_count_kernel<IPT><<<pl.tiles, kThreads, 0, st>>>(sorted_experts, pl.P, tilecnt, hdr + HDR_TICKET0, meta);
+  segment_write_kernel<IPT><<<pl.tiles, kThreads, 0, st>>>(sorted_experts, perm, pl.P, k, weights, wbytes, tilecnt, token_ids,
+                                                         sorted_weights, expert_ids, offsets, hdr + HDR_TICKET0, meta);
+  return check_launch("omni_schedule kernels");
+}
+
+}  // namespace
+}  // namespace omni
+
+using namespace omni;
+
+extern "C" size_t omni_schedule_workspace_bytes(int64_t num_pairs, int64_t num_experts) {
+  if (num_pairs < 0 || num_experts < 1) return 0;
+  return make_plan(num_pairs, num_experts).total;
+}
+
+extern "C" int omni_schedule(const void* indices, int idx_is_i64, const void* weights, int weight_elem_bytes,
+                             int64_t num_tokens, int k, int64_t num_experts, int32_t* sorted_pair_ids,
+                             int32_t* sorted_experts, int32_t* token_ids, void* sorted_weights,
+                             int32_t* expert_ids, int32_t* offsets, int32_t* meta, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1, "num_tokens must be >= 0 and k >= 1");
+  OMNI_REQUIRE(num_experts >= 1 && num_experts <= (int64_t(1) << 30), "num_experts must be in [1, 2^30]");
+  const int64_t P = num_tokens * k;
+  OMNI_REQUIRE(P < (int64_t(1) << 31) - 65536, "too many (token, expert) pairs: %lld", static_cast<long long>(P));
+  OMNI_REQUIRE(meta, "meta must not be NULL");
+  OMNI_REQUIRE((sorted_weights == nullptr) || (weights != nullptr), "sorted_weights needs weights");
+  OMNI_REQUIRE(weights == nullptr || weight_elem_bytes == 2 || weight_elem_bytes == 4, "weight_elem_bytes must be 2 or 4");
+  OMNI_REQUIRE((expert_ids == nullptr) || (offsets != nullptr), "expert_ids needs offsets");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (P == 0) {
+    cudaMemsetAsync(meta, 0, 4 * sizeof(int), st);
+    if (offsets) cudaMemsetAsync(offsets, 0, sizeof(int), st);
+    return check_launch("omni_schedule (empty)");
+  }
+  OMNI_REQUIRE(indices && sorted_pair_ids && sorted_experts, "indices, sorted_pair_ids and sorted_experts must not be NULL");
+  const Plan pl = make_plan(P, num_experts);
+  OMNI_REQUIRE(workspace && workspace_bytes >= pl.total, "workspace too small: need %zu bytes", pl.total);
+  OMNI_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  char* ws = static_cast<char*>(workspace);
+  if (pl.ipt == 16)
+    return run<16>(pl, indices, idx_is_i64, weights, weight_elem_bytes, k, num_experts, sorted_pair_ids, sorted_experts,
+                   token_ids, sorted_weights, expert_ids, offsets, meta, ws, st);
+  return run<4>(pl, indices, idx_is_i64, weights, weight_elem_bytes, k, num_experts, sorted_pair_ids, sorted_experts,
+                token_ids, sorted_weights, expert_ids, offsets, meta, ws, st);
+}

@@ -1,0 +1,203 @@
+"""``OmniMoE`` layer backed by the sm_100a kernels.
+
+Constructor, parameter / buffer names and shapes, and ``forward(hidden_states)`` follow the
+reference module (omni_moe/modules/omni_moe.py:14-106), so a reference ``state_dict`` loads
+unchanged.  Forward only.
+
+Stream plan of one forward (eval mode), all enqueued without a host synchronisation:
+
+    main stream   gate/up GEMM + SwiGLU  ..............................  down GEMM (+ expert states) -> y
+    side stream   router gate GEMM -> BatchNorm/log-softmax/top-k -> schedule -> coefficients -> combine
+
+The expert branch has no dependency on the shared MLP until the final add, which is folded into the
+epilogue of the down projection.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from .. import _lib
+from ..ops.scheduler import workspace_bytes
+
+
+class OmniMoEConfig:
+    """Same five fields as the reference configuration (omni_moe/modules/omni_moe.py:14-27)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, hidden_act: str, num_experts: int,
+                 num_experts_per_token: int):
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.hidden_act = hidden_act
+        self.num_experts = num_experts
+        self.num_experts_per_token = num_experts_per_token
+
+
+class _Buffers:
+    """Per-(token count, device) scratch of a forward; allocated once and reused."""
+
+    def __init__(self, t, h, i, n_sqrt, n, k, dev):
+        f32 = dict(device=dev, dtype=torch.float32)
+        i32 = dict(device=dev, dtype=torch.int32)
+        p = t * k
+        self.logits = torch.empty((t, 2 * n_sqrt), **f32)
+        self.scores = torch.empty((t, k), **f32)
+        self.weights = torch.empty((t, k), **f32)
+        self.indices = torch.empty((t, k), **i32)
+        self.perm = torch.empty(max(p, 1), **i32)
+        self.sorted_experts = torch.empty(max(p, 1), **i32)
+        self.meta = torch.zeros(4, **i32)
+        self.coef = torch.empty((t, k), **f32)
+        self.expert_states = torch.empty((t, h), **f32)
+        self.act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
+        self.workspace = torch.empty(workspace_bytes(p, n), device=dev, dtype=torch.uint8)
+        self.status = torch.zeros(1, **i32)
+        self.side = torch.cuda.Stream(device=dev)
+        self.ev_in = torch.cuda.Event()
+        self.ev_side = torch.cuda.Event()
+
+
+class OmniMoE(nn.Module):
+    def __init__(self, config: OmniMoEConfig):
+        super().__init__()
+        if config.hidden_act not in ("silu", "swish"):
+            # the reference's kernels hard-code SiLU whatever hidden_act says; other names are refused here
+            raise ValueError(f"hidden_act={config.hidden_act!r} is not supported: the fused kernels implement SiLU")
+        self.hidden_size = config.hidden_size
+        self.intermediate_size = config.intermediate_size
+        self.num_experts = config.num_experts
+        self.num_expert_sqrt = math.floor(math.sqrt(self.num_experts))
+        self.top_k = config.num_experts_per_token
+
+        # shared expert
+        self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
+        # router gates and their (non-affine) normalisation
+        self.router_gate_x = nn.Linear(self.hidden_size, self.num_expert_sqrt, bias=False)
+        self.router_gate_y = nn.Linear(self.hidden_size, self.num_expert_sqrt, bias=False)
+        self.router_norm_x = nn.BatchNorm1d(self.num_expert_sqrt, affine=False)
+        self.router_norm_y = nn.BatchNorm1d(self.num_expert_sqrt, affine=False)
+        # routed experts: one up row and one down row per expert
+        self.up_embed = nn.Embedding(self.num_experts, self.hidden_size)
+        self.down_embed = nn.Embedding(self.num_experts, self.hidden_size)
+
+        self._buffers_cache: dict = {}
+        self._bn_cache = None
+        self.last_routing = None  # (scores, indices, weights) of the latest forward, for inspection
+
+    # ------------------------------------------------------------------------------------------
+    def _bf16_weight(self, p: torch.Tensor) -> torch.Tensor:
+        w = p.detach()
+        if w.dtype != torch.bfloat16:
+            w = w.to(torch.bfloat16)  # fp32 / fp16 modules: operands are rounded to bf16 per call
+        return w.contiguous()
+
+    def _bn_fold_eval(self):
+        """Eval-mode BatchNorm of both axes as one scale / shift pair per logit column."""
+        bx, by = self.router_norm_x, self.router_norm_y
+        key = (bx.running_mean._version, bx.running_var._version, by.running_mean._version, by.running_var._version,
+               bx.running_mean.data_ptr(), by.running_mean.data_ptr())
+        if self._bn_cache is None or self._bn_cache[0] != key:
+            mean = torch.cat([bx.running_mean, by.running_mean]).float()
+            var = torch.cat([bx.running_var, by.running_var]).float()
+            eps = torch.cat([torch.full_like(bx.running_var, bx.eps, dtype=torch.float32),
+                             torch.full_like(by.running_var, by.eps, dtype=torch.float32)])
+            scale = torch.rsqrt(var + eps)
+            self._bn_cache = (key, scale.contiguous(), (-mean * scale).contiguous())
+        return self._bn_cache[1], self._bn_cache[2]
+
+    def _bn_fold_train(self, logits: torch.Tensor):
+        """Training-mode BatchNorm: batch statistics over all tokens, running statistics updated as
+        nn.BatchNorm1d does (momentum average, unbiased variance)."""
+        n = self.num_expert_sqrt
+        t = logits.size(0)
+        var, mean = torch.var_mean(logits, dim=0, unbiased=False)
+        with torch.no_grad():
+            for bn, sl in ((self.router_norm_x, slice(0, n)), (self.router_norm_y, slice(n, 2 * n))):
+                if bn.track_running_stats:
+                    bn.num_batches_tracked += 1
+                    mom = bn.momentum if bn.momentum is not None else 1.0 / float(bn.num_batches_tracked)
+                    unbiased = var[sl] * (t / max(t - 1, 1))
+                    bn.running_mean.mul_(1 - mom).add_(mean[sl].to(bn.running_mean.dtype), alpha=mom)
+                    bn.running_var.mul_(1 - mom).add_(unbiased.to(bn.running_var.dtype), alpha=mom)
+        eps = torch.cat([torch.full((n,), self.router_norm_x.eps), torch.full((n,), self.router_norm_y.eps)]).to(var)
+        scale = torch.rsqrt(var + eps)
+        return scale.contiguous(), (-mean * scale).contiguous()
+
+    def _get_buffers(self, t: int, dev: torch.device) -> _Buffers:
+        key = (t, dev.index)
+        b = self._buffers_cache.get(key)
+        if b is None:
+            b = _Buffers(t, self.hidden_size, self.intermediate_size, self.num_expert_sqrt, self.num_experts,
+                         self.top_k, dev)
+            self._buffers_cache = {key: b}  # keep one set: shapes rarely alternate
+        return b
+
+    # ------------------------------------------------------------------------------------------
+    def forward(self, hidden_states: torch.Tensor, **kwargs) -> torch.Tensor:
+        _lib.require_cuda(hidden_states)
+        bsz, seq_len, _ = hidden_states.shape
+        in_dtype = hidden_states.dtype
+        x = hidden_states.detach().reshape(-1, self.hidden_size)
+        if x.dtype != torch.bfloat16:
+            x = x.to(torch.bfloat16)
+        x = x.contiguous()
+        t, h, i, n, k = x.size(0), self.hidden_size, self.intermediate_size, self.num_expert_sqrt, self.top_k
+        dev = x.device
+        y = torch.empty((t, h), device=dev, dtype=torch.bfloat16)
+        if t == 0:
+            return y.view(bsz, seq_len, h).to(in_dtype)
+        wg, wu, wd = (self._bf16_weight(p.weight) for p in (self.gate_proj, self.up_proj, self.down_proj))
+        kx, ky = self._bf16_weight(self.router_gate_x.weight), self._bf16_weight(self.router_gate_y.weight)
+        up_t, down_t = self._bf16_weight(self.up_embed.weight), self._bf16_weight(self.down_embed.weight)
+        b = self._get_buffers(t, dev)
+        lib = _lib.load()
+        chk = _lib.check
+        with torch.cuda.device(dev):
+            main = torch.cuda.current_stream()
+            b.ev_in.record(main)
+            # ---- expert branch on the side stream ----
+            with torch.cuda.stream(b.side):
+                b.side.wait_event(b.ev_in)
+                ss = b.side.cuda_stream
+                chk(lib.omni_router_gate(x.data_ptr(), kx.data_ptr(), ky.data_ptr(), t, h, n, b.logits.data_ptr(),
+                                         b.status.data_ptr(), ss))
+                if self.training:
+                    scale, shift = self._bn_fold_train(b.logits)
+                else:
+                    scale, shift = self._bn_fold_eval()
+                chk(lib.omni_router_logits_topk(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
+                                                b.scores.data_ptr(), b.indices.data_ptr(), 0, b.weights.data_ptr(),
+                                                None, ss))
+                chk(lib.omni_schedule(b.indices.data_ptr(), 0, None, 0, t, k, self.num_experts, b.perm.data_ptr(),
+                                      b.sorted_experts.data_ptr(), None, None, None, None, b.meta.data_ptr(),
+                                      b.workspace.data_ptr(), b.workspace.numel(), ss))
+                chk(lib.omni_expert_coef(x.data_ptr(), up_t.data_ptr(), b.weights.data_ptr(), b.perm.data_ptr(),
+                                         b.sorted_experts.data_ptr(), t, k, h, self.num_experts, b.coef.data_ptr(),
+                                         b.status.data_ptr(), ss))
+                chk(lib.omni_expert_combine(down_t.data_ptr(), b.coef.data_ptr(), b.indices.data_ptr(), t, k, h,
+                                            self.num_experts, None, b.expert_states.data_ptr(), _lib.OMNI_F32,
+                                            b.status.data_ptr(), ss))
+                b.ev_side.record(b.side)
+                for tns in (x, kx, ky, up_t, down_t, scale, shift):
+                    tns.record_stream(b.side)
+            # ---- shared MLP on the main stream ----
+            ms = main.cuda_stream
+            chk(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, b.act.data_ptr(),
+                                     b.status.data_ptr(), ms))
+            main.wait_event(b.ev_side)
+            chk(lib.omni_mlp_down(b.act.data_ptr(), wd.data_ptr(), t, h, i, b.expert_states.data_ptr(), y.data_ptr(),
+                                  b.status.data_ptr(), ms))
+        self.last_routing = (b.scores, b.indices, b.weights)
+        self.last_status = b.status
+        out = y.view(bsz, seq_len, h)
+        return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
+
+    def check_status(self) -> None:
+        """Synchronise and raise if any kernel of the latest forward reported a device-side fault."""
+        st = getattr(self, "last_status", None)
+        if st is not None:
+            _lib.check_status(st)

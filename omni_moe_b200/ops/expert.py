@@ -1,0 +1,74 @@
+"""Routed-expert op (reference: omni_moe/ops/triton/omni_expert.py:920-992, interface.py:54-72)."""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ._common import as_bf16, guard_no_grad
+from .scheduler import schedule
+
+
+def expert_forward(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor, weights: torch.Tensor,
+                   indices: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                   residual: torch.Tensor | None = None, status: torch.Tensor | None = None,
+                   workspace: torch.Tensor | None = None, return_coef: bool = False):
+    """``y[t] = sum_j w[t,j] * silu(x[t] . Up[e[t,j]]) * Down[e[t,j]]`` (+ residual).
+
+    ``x [T, H]``, ``up/down [N, H]`` bf16; ``weights [T, k]`` fp32; ``indices [T, k]`` int32.
+    Schedules the pairs by expert, computes the per-pair coefficients in expert order, then combines
+    per token.  ``out_dtype`` float32 or bfloat16; ``residual`` (same dtype as the output) is added in.
+    """
+    _lib.require_cuda(x, up_weight, down_weight, weights, indices)
+    assert x.dtype == up_weight.dtype == down_weight.dtype == torch.bfloat16
+    assert weights.dtype == torch.float32 and indices.dtype == torch.int32
+    assert out_dtype in (torch.float32, torch.bfloat16)
+    x, up_weight, down_weight = x.contiguous(), up_weight.contiguous(), down_weight.contiguous()
+    weights, indices = weights.contiguous(), indices.contiguous()
+    t, h = x.shape
+    n = up_weight.size(0)
+    k = indices.size(1)
+    dev = x.device
+    if status is None:
+        status = torch.zeros(1, device=dev, dtype=torch.int32)
+    y = torch.empty((t, h), device=dev, dtype=out_dtype)
+    if residual is not None:
+        assert residual.shape == y.shape and residual.dtype == out_dtype and residual.is_contiguous()
+    coef = torch.empty((t, k), device=dev, dtype=torch.float32)
+    if t == 0:
+        return (y, coef) if return_coef else y
+    if k == 0:
+        y.zero_() if residual is None else y.copy_(residual)
+        return (y, coef) if return_coef else y
+    sch = schedule(indices, n, segments=False, workspace=workspace)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        st = _lib.stream_ptr()
+        _lib.check(lib.omni_expert_coef(x.data_ptr(), up_weight.data_ptr(), weights.data_ptr(),
+                                        sch.sorted_pair_ids.data_ptr(), sch.sorted_experts.data_ptr(), t, k, h, n,
+                                        coef.data_ptr(), status.data_ptr(), st))
+        _lib.check(lib.omni_expert_combine(down_weight.data_ptr(), coef.data_ptr(), indices.data_ptr(), t, k, h, n,
+                                           _lib.ptr(residual), y.data_ptr(), _lib.dtype_code(out_dtype),
+                                           status.data_ptr(), st))
+    return (y, coef) if return_coef else y
+
+
+def omni_expert_func(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
+                     routing_weights: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """Drop-in for ``triton_omni_expert_func`` (omni_moe/ops/triton/interface.py:54-72).
+
+    :param x: (num_tokens, hidden_size)
+    :param up_weight, down_weight: (num_experts, hidden_size)
+    :param routing_weights: (num_tokens, num_experts_per_token)
+    :param indices: (num_tokens, num_experts_per_token) integer expert ids (duplicates allowed)
+    :return y: (num_tokens, hidden_size), dtype of ``x``
+
+    Operands are taken as bf16 (other float dtypes are rounded to bf16 first); the dot products,
+    the activation and the accumulation run in fp32.
+    """
+    assert x.dim() == 2 and up_weight.dim() == 2 and down_weight.shape == up_weight.shape
+    assert routing_weights.shape == indices.shape and indices.size(0) == x.size(0)
+    y = expert_forward(as_bf16(x), as_bf16(up_weight), as_bf16(down_weight), routing_weights.detach().float(),
+                       indices.to(torch.int32), out_dtype=torch.float32 if x.dtype == torch.float32 else torch.bfloat16)
+    y = y.to(x.dtype)
+    y, = guard_no_grad("omni_expert_func", (x, up_weight, down_weight, routing_weights), (y,))
+    return y

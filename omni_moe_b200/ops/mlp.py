@@ -1,0 +1,52 @@
+"""Shared SwiGLU MLP op (reference: omni_moe/ops/triton/interface.py:7-29, omni_mlp.py:252-303)."""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ._common import as_bf16, guard_no_grad
+
+
+def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
+                residual: torch.Tensor | None = None, status: torch.Tensor | None = None,
+                act: torch.Tensor | None = None) -> torch.Tensor:
+    """``(silu(x Wg^T) * (x Wu^T)) Wd^T (+ residual)`` on bf16 operands with two tcgen05 GEMMs.
+
+    ``residual``: optional fp32 ``[T, H]`` added before the result is rounded to bf16.
+    ``act``: optional bf16 ``[T, I]`` scratch for the activation.
+    """
+    _lib.require_cuda(x, gate_weight, up_weight, down_weight)
+    assert x.dtype == gate_weight.dtype == up_weight.dtype == down_weight.dtype == torch.bfloat16
+    x, gate_weight, up_weight, down_weight = (v.contiguous() for v in (x, gate_weight, up_weight, down_weight))
+    t, h = x.shape
+    i = gate_weight.size(0)
+    assert gate_weight.shape == up_weight.shape == (i, h) and down_weight.shape == (h, i)
+    dev = x.device
+    if status is None:
+        status = torch.zeros(1, device=dev, dtype=torch.int32)
+    if act is None:
+        act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
+    if residual is not None:
+        assert residual.shape == (t, h) and residual.dtype == torch.float32 and residual.is_contiguous()
+    y = torch.empty((t, h), device=dev, dtype=torch.bfloat16)
+    if t > 0:
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().omni_mlp_fwd(
+                x.data_ptr(), gate_weight.data_ptr(), up_weight.data_ptr(), down_weight.data_ptr(), t, h, i,
+                act.data_ptr(), _lib.ptr(residual), y.data_ptr(), status.data_ptr(), _lib.stream_ptr()))
+    return y
+
+
+def omni_mlp_func(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor,
+                  down_weight: torch.Tensor) -> torch.Tensor:
+    """Drop-in for ``triton_omni_mlp_func`` (omni_moe/ops/triton/interface.py:7-29).
+
+    :param x: (num_tokens, hidden_size)
+    :param gate_weight, up_weight: (intermediate_size, hidden_size)
+    :param down_weight: (hidden_size, intermediate_size)
+    :return y: (num_tokens, hidden_size), dtype of ``x``
+    """
+    assert x.dim() == 2
+    y = mlp_forward(as_bf16(x), as_bf16(gate_weight), as_bf16(up_weight), as_bf16(down_weight)).to(x.dtype)
+    y, = guard_no_grad("omni_mlp_func", (x, gate_weight, up_weight, down_weight), (y,))
+    return y

@@ -1,0 +1,117 @@
+"""Routed-expert kernels against the fp32 oracle (bf16 operands, rtol/atol 2e-2)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import omni_oracle as orc
+from _util import assert_close, bf16_round, gen, zipf_indices
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(t, h, n, k, seed, idx=None):
+    g = gen(seed)
+    x = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
+    up = (torch.randn(n, h, generator=g) * 0.1).bfloat16()
+    dn = (torch.randn(n, h, generator=g) * 0.1).bfloat16()
+    w = torch.randn(t, k, generator=g) * 0.1
+    if idx is None:
+        idx = torch.randint(0, n, (t, k), generator=g, dtype=torch.int32)  # duplicates allowed
+    return x, up, dn, w, idx
+
+
+@pytest.mark.parametrize("t,h,n,k", [(32, 64, 128, 8), (300, 256, 1024, 8), (257, 1024, 4096, 16), (64, 2048, 512, 32),
+                                       (40, 4096, 300, 64), (50, 72, 64, 6), (33, 1536, 200, 4), (20, 8192, 64, 2),
+                                       (1, 8, 1, 1)])
+def test_expert_matches_oracle(t, h, n, k):
+    from omni_moe_b200.ops import expert_forward
+    x, up, dn, w, idx = _inputs(t, h, n, k, t + h)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for out_dtype in (torch.float32, torch.bfloat16):
+        y, coef = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=out_dtype,
+                                 status=st, return_coef=True)
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        ey = orc.expert_forward(x, up, dn, w, idx)
+        ec = orc.expert_coefficients(x, up, w, idx)
+        assert_close(coef, ec, rtol=1e-3, atol=1e-4, what="coefficients")
+        if out_dtype == torch.float32:
+            assert_close(y, ey, rtol=1e-3, atol=1e-4, what="fp32 output")
+        else:
+            assert_close(y, ey, what="bf16 output")
+
+
+def test_expert_residual_and_determinism():
+    from omni_moe_b200.ops import expert_forward
+    x, up, dn, w, idx = _inputs(100, 512, 256, 8, 3)
+    res = torch.randn(100, 512, generator=gen(4))
+    a = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.float32, residual=res.cuda())
+    b = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.float32, residual=res.cuda())
+    assert torch.equal(a, b)  # no atomics: bit-identical from run to run
+    assert_close(a, orc.expert_forward(x, up, dn, w, idx) + res, rtol=1e-3, atol=1e-4)
+    rb = res.bfloat16()
+    c = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.bfloat16, residual=rb.cuda())
+    assert_close(c, orc.expert_forward(x, up, dn, w, idx) + rb.float())
+
+
+def test_expert_skewed_routing():
+    # hot experts: thousands of pairs on one expert, duplicates inside tokens
+    t, h, n, k = 2048, 256, 4096, 32
+    idx = zipf_indices(t, k, n, 1.1, 5)
+    x, up, dn, w, _ = _inputs(t, h, n, k, 6)
+    w = torch.distributions.Dirichlet(torch.ones(k)).sample((t,))
+    from omni_moe_b200.ops import expert_forward
+    y = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.bfloat16)
+    assert_close(y, orc.expert_forward(x, up, dn, w, idx))
+
+
+def test_expert_golden_mirror_and_drop_in(golden_dir):
+    g = np.load(os.path.join(golden_dir, "expert_mirror.npz"))
+    from omni_moe.ops.triton import triton_omni_expert_func
+    args = [torch.from_numpy(g[k]) for k in ("x", "up", "down", "w", "indices")]
+    # fp32 call: operands are rounded to bf16 inside, so compare with the reference output loosely ...
+    y = triton_omni_expert_func(*[a.cuda() for a in args])
+    assert y.dtype == torch.float32
+    assert_close(y, torch.from_numpy(g["y"]))
+    # ... and tightly against the oracle evaluated on the rounded operands
+    x, up, dn, w, idx = args
+    assert_close(y, orc.expert_forward(bf16_round(x), bf16_round(up), bf16_round(dn), w, idx), rtol=1e-3, atol=1e-4)
+    yb = triton_omni_expert_func(x.bfloat16().cuda(), up.bfloat16().cuda(), dn.bfloat16().cuda(), w.bfloat16().cuda(), idx.cuda())
+    assert yb.dtype == torch.bfloat16
+
+
+def test_expert_bad_index_is_reported_not_faulting():
+    from omni_moe_b200.ops import expert_forward
+    x, up, dn, w, idx = _inputs(16, 64, 32, 4, 8)
+    idx[3, 2] = 1000
+    idx[5, 0] = -7
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.float32, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) & 1
+    good = torch.ones(16, dtype=torch.bool)
+    good[3] = good[5] = False
+    ey = orc.expert_forward(x, up, dn, w, idx.clamp(0, 31))
+    assert_close(y[good.cuda()], ey[good], rtol=1e-3, atol=1e-4)
+
+
+def test_expert_stress_shape_properties():
+    # a slice of the skewed stress configuration (hidden 2048, 262144 experts, k = 32, Zipf 1.1):
+    # linearity in the routing weights and agreement with the oracle on sampled tokens
+    t, h, n, k = 4096, 2048, 262144, 32
+    g = gen(0)
+    x = torch.randn(t, h, generator=g).bfloat16()
+    up = (torch.randn(n, h, generator=g) * 0.02).bfloat16()
+    dn = (torch.randn(n, h, generator=g) * 0.02).bfloat16()
+    idx = zipf_indices(t, k, n, 1.1, 0)
+    w = torch.distributions.Dirichlet(torch.ones(k)).sample((t,))
+    from omni_moe_b200.ops import expert_forward
+    xc, uc, dc, ic = x.cuda(), up.cuda(), dn.cuda(), idx.cuda()
+    y1 = expert_forward(xc, uc, dc, w.cuda(), ic, out_dtype=torch.float32)
+    y2 = expert_forward(xc, uc, dc, (2 * w).cuda(), ic, out_dtype=torch.float32)
+    assert_close(y2, 2 * y1, rtol=1e-5, atol=1e-7, what="linearity in the weights")
+    sel = torch.arange(0, t, 64)
+    ey = orc.expert_forward(x[sel], up, dn, w[sel], idx[sel])
+    assert_close(y1[sel.cuda()], ey, rtol=1e-3, atol=1e-4)

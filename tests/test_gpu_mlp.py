@@ -1,0 +1,78 @@
+"""tcgen05 GEMM paths (router gate logits, shared SwiGLU MLP) against the fp32 oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import omni_oracle as orc
+from _util import assert_close, bf16_round, gen
+
+pytestmark = pytest.mark.gpu
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("t,h,n", [(128, 64, 64), (300, 256, 32), (1000, 1024, 64), (129, 72, 100), (4096, 1024, 64),
+                                     (513, 2048, 256), (64, 512, 1024), (1, 8, 1)])
+def test_router_gate_logits(t, h, n):
+    from omni_moe_b200 import _lib
+    g = gen(t + h)
+    x = torch.randn(t, h, generator=g).bfloat16()
+    kx = (torch.randn(n, h, generator=g) / h ** 0.5).bfloat16()
+    ky = (torch.randn(n, h, generator=g) / h ** 0.5).bfloat16()
+    xc, kxc, kyc = x.cuda(), kx.cuda(), ky.cuda()
+    z = torch.full((t, 2 * n), float("nan"), device="cuda")
+    st = _status()
+    _lib.check(_lib.load().omni_router_gate(xc.data_ptr(), kxc.data_ptr(), kyc.data_ptr(), t, h, n, z.data_ptr(),
+                                            st.data_ptr(), _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    ez = torch.cat([orc.router_logits(x, kx), orc.router_logits(x, ky)], 1)
+    assert_close(z, ez, rtol=1e-4, atol=1e-4, what="router logits")
+
+
+@pytest.mark.parametrize("t,h,i", [(128, 64, 128), (48, 64, 96), (300, 256, 1024), (1000, 1024, 4096), (77, 72, 200),
+                                     (4096, 1024, 4096), (130, 4096, 1408)])
+def test_mlp_matches_oracle(t, h, i):
+    from omni_moe_b200.ops import mlp_forward
+    g = gen(t + i)
+    x = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
+    wg = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wu = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wd = (torch.randn(h, i, generator=g) / i ** 0.5).bfloat16()
+    st = _status()
+    y = mlp_forward(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert_close(y, orc.mlp_forward(x, wg, wu, wd), what="mlp")
+    res = torch.randn(t, h, generator=g)
+    y2 = mlp_forward(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), residual=res.cuda(), status=st)
+    assert_close(y2, orc.mlp_forward(x, wg, wu, wd) + res, what="mlp + residual")
+    assert int(st.item()) == 0
+
+
+def test_mlp_golden_mirror_and_drop_in(golden_dir):
+    g = np.load(os.path.join(golden_dir, "mlp_mirror.npz"))
+    from omni_moe.ops.triton import triton_omni_mlp_func
+    x, wg, wu, wd = (torch.from_numpy(g[k]) for k in ("x", "gate", "up", "down"))
+    y = triton_omni_mlp_func(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
+    assert y.dtype == torch.float32 and y.shape == (48, 64)
+    assert_close(y, torch.from_numpy(g["y"]))
+    assert_close(y, orc.mlp_forward(bf16_round(x), bf16_round(wg), bf16_round(wu), bf16_round(wd)), rtol=1e-2, atol=1e-2)
+    yb = triton_omni_mlp_func(x.bfloat16().cuda(), wg.bfloat16().cuda(), wu.bfloat16().cuda(), wd.bfloat16().cuda())
+    assert yb.dtype == torch.bfloat16
+
+
+def test_mlp_repeatable():
+    from omni_moe_b200.ops import mlp_forward
+    g = gen(1)
+    x = torch.randn(512, 256, generator=g).bfloat16().cuda()
+    wg = (torch.randn(512, 256, generator=g) / 16).bfloat16().cuda()
+    wu = (torch.randn(512, 256, generator=g) / 16).bfloat16().cuda()
+    wd = (torch.randn(256, 512, generator=g) / 22).bfloat16().cuda()
+    a = mlp_forward(x, wg, wu, wd)
+    for _ in range(5):
+        assert torch.equal(a, mlp_forward(x, wg, wu, wd))
