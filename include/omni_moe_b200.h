@@ -108,7 +108,8 @@ OMNI_API int omni_router_gate(const void *x, const void *gate_x, const void *gat
  *   sorted_weights   [P] weights in sorted order (same element size), or NULL
  *   expert_ids       [min(P, N)] int32  distinct experts, ascending (first U entries valid), or NULL
  *   offsets          [min(P, N) + 1] int32  segment starts, offsets[U] = P, or NULL
- *   meta             [4] int32 device: {U, max pairs per expert, status word, reserved}
+ *   meta             [4] int32 device: {U, max pairs per expert, status word, reserved}; U and the
+ *                    maximum are only computed when one of token_ids / sorted_weights / offsets is given
  *   workspace        omni_schedule_workspace_bytes(P, N) bytes, 256-byte aligned
  */
 OMNI_API size_t omni_schedule_workspace_bytes(int64_t num_pairs, int64_t num_experts);

@@ -354,6 +354,7 @@ int run(const Plan& pl, const void* indices, int idx_is_i64, const void* weights
     in_keys = ok, in_i64 = 0, in_vals = ov;
     shift += bits;
   }
+  if (!offsets && !token_ids && !sorted_weights) return check_launch("omni_schedule kernels");  // permutation only
   segment_count_kernel<IPT><<<pl.tiles, kThreads, 0, st>>>(sorted_experts, pl.P, tilecnt, hdr + HDR_TICKET0, meta);
   segment_write_kernel<IPT><<<pl.tiles, kThreads, 0, st>>>(sorted_experts, perm, pl.P, k, weights, wbytes, tilecnt, token_ids,
                                                          sorted_weights, expert_ids, offsets, hdr + HDR_TICKET0, meta);

@@ -137,6 +137,65 @@ class OmniMoE(nn.Module):
         return b
 
     # ------------------------------------------------------------------------------------------
+    def _operands(self):
+        """bf16 views (or per-call bf16 copies, for fp32 / fp16 modules) of all weights."""
+        return tuple(self._bf16_weight(p.weight) for p in (
+            self.gate_proj, self.up_proj, self.down_proj, self.router_gate_x, self.router_gate_y,
+            self.up_embed, self.down_embed))
+
+    def _launch(self, x: torch.Tensor, y: torch.Tensor, b: _Buffers, record_streams: bool) -> None:
+        """Enqueue one forward: ``x [T, H]`` bf16 contiguous -> ``y [T, H]`` bf16.  Allocates nothing in
+        eval mode, so it can be captured in a CUDA graph."""
+        t, h, i, n, k = x.size(0), self.hidden_size, self.intermediate_size, self.num_expert_sqrt, self.top_k
+        wg, wu, wd, kx, ky, up_t, down_t = self._operands()
+        lib = _lib.load()
+        chk = _lib.check
+        main = torch.cuda.current_stream()
+        b.ev_in.record(main)
+        # ---- expert branch on the side stream ----
+        with torch.cuda.stream(b.side):
+            b.side.wait_event(b.ev_in)
+            ss = b.side.cuda_stream
+            chk(lib.omni_router_gate(x.data_ptr(), kx.data_ptr(), ky.data_ptr(), t, h, n, b.logits.data_ptr(),
+                                     b.status.data_ptr(), ss))
+            if self.training:
+                scale, shift = self._bn_fold_train(b.logits)
+            else:
+                scale, shift = self._bn_fold_eval()
+            chk(lib.omni_router_logits_topk(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
+                                            b.scores.data_ptr(), b.indices.data_ptr(), 0, b.weights.data_ptr(),
+                                            None, ss))
+            chk(lib.omni_schedule(b.indices.data_ptr(), 0, None, 0, t, k, self.num_experts, b.perm.data_ptr(),
+                                  b.sorted_experts.data_ptr(), None, None, None, None, b.meta.data_ptr(),
+                                  b.workspace.data_ptr(), b.workspace.numel(), ss))
+            chk(lib.omni_expert_coef(x.data_ptr(), up_t.data_ptr(), b.weights.data_ptr(), b.perm.data_ptr(),
+                                     b.sorted_experts.data_ptr(), t, k, h, self.num_experts, b.coef.data_ptr(),
+                                     b.status.data_ptr(), ss))
+            chk(lib.omni_expert_combine(down_t.data_ptr(), b.coef.data_ptr(), b.indices.data_ptr(), t, k, h,
+                                        self.num_experts, None, b.expert_states.data_ptr(), _lib.OMNI_F32,
+                                        b.status.data_ptr(), ss))
+            b.ev_side.record(b.side)
+            if record_streams:
+                for tns in (x, kx, ky, up_t, down_t, scale, shift):
+                    tns.record_stream(b.side)
+        # ---- shared MLP on the main stream ----
+        ms = main.cuda_stream
+        chk(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, b.act.data_ptr(),
+                                 b.status.data_ptr(), ms))
+        main.wait_event(b.ev_side)
+        chk(lib.omni_mlp_down(b.act.data_ptr(), wd.data_ptr(), t, h, i, b.expert_states.data_ptr(), y.data_ptr(),
+                              b.status.data_ptr(), ms))
+        self.last_routing = (b.scores, b.indices, b.weights)
+        self.last_status = b.status
+
+    #: kernels of this library launched by one forward at the given pass count of the scheduler
+    @staticmethod
+    def kernels_per_forward(num_experts: int) -> int:
+        bits = max(1, (num_experts - 1).bit_length())
+        passes = -(-bits // 11)
+        # router gate GEMM, top-k, 2 per radix pass, coefficients, combine, 2 MLP GEMMs
+        return 2 + 2 * passes + 2 + 2
+
     def forward(self, hidden_states: torch.Tensor, **kwargs) -> torch.Tensor:
         _lib.require_cuda(hidden_states)
         bsz, seq_len, _ = hidden_states.shape
@@ -145,59 +204,61 @@ class OmniMoE(nn.Module):
         if x.dtype != torch.bfloat16:
             x = x.to(torch.bfloat16)
         x = x.contiguous()
-        t, h, i, n, k = x.size(0), self.hidden_size, self.intermediate_size, self.num_expert_sqrt, self.top_k
+        t, h = x.size(0), self.hidden_size
         dev = x.device
         y = torch.empty((t, h), device=dev, dtype=torch.bfloat16)
         if t == 0:
             return y.view(bsz, seq_len, h).to(in_dtype)
-        wg, wu, wd = (self._bf16_weight(p.weight) for p in (self.gate_proj, self.up_proj, self.down_proj))
-        kx, ky = self._bf16_weight(self.router_gate_x.weight), self._bf16_weight(self.router_gate_y.weight)
-        up_t, down_t = self._bf16_weight(self.up_embed.weight), self._bf16_weight(self.down_embed.weight)
-        b = self._get_buffers(t, dev)
-        lib = _lib.load()
-        chk = _lib.check
         with torch.cuda.device(dev):
-            main = torch.cuda.current_stream()
-            b.ev_in.record(main)
-            # ---- expert branch on the side stream ----
-            with torch.cuda.stream(b.side):
-                b.side.wait_event(b.ev_in)
-                ss = b.side.cuda_stream
-                chk(lib.omni_router_gate(x.data_ptr(), kx.data_ptr(), ky.data_ptr(), t, h, n, b.logits.data_ptr(),
-                                         b.status.data_ptr(), ss))
-                if self.training:
-                    scale, shift = self._bn_fold_train(b.logits)
-                else:
-                    scale, shift = self._bn_fold_eval()
-                chk(lib.omni_router_logits_topk(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
-                                                b.scores.data_ptr(), b.indices.data_ptr(), 0, b.weights.data_ptr(),
-                                                None, ss))
-                chk(lib.omni_schedule(b.indices.data_ptr(), 0, None, 0, t, k, self.num_experts, b.perm.data_ptr(),
-                                      b.sorted_experts.data_ptr(), None, None, None, None, b.meta.data_ptr(),
-                                      b.workspace.data_ptr(), b.workspace.numel(), ss))
-                chk(lib.omni_expert_coef(x.data_ptr(), up_t.data_ptr(), b.weights.data_ptr(), b.perm.data_ptr(),
-                                         b.sorted_experts.data_ptr(), t, k, h, self.num_experts, b.coef.data_ptr(),
-                                         b.status.data_ptr(), ss))
-                chk(lib.omni_expert_combine(down_t.data_ptr(), b.coef.data_ptr(), b.indices.data_ptr(), t, k, h,
-                                            self.num_experts, None, b.expert_states.data_ptr(), _lib.OMNI_F32,
-                                            b.status.data_ptr(), ss))
-                b.ev_side.record(b.side)
-                for tns in (x, kx, ky, up_t, down_t, scale, shift):
-                    tns.record_stream(b.side)
-            # ---- shared MLP on the main stream ----
-            ms = main.cuda_stream
-            chk(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, b.act.data_ptr(),
-                                     b.status.data_ptr(), ms))
-            main.wait_event(b.ev_side)
-            chk(lib.omni_mlp_down(b.act.data_ptr(), wd.data_ptr(), t, h, i, b.expert_states.data_ptr(), y.data_ptr(),
-                                  b.status.data_ptr(), ms))
-        self.last_routing = (b.scores, b.indices, b.weights)
-        self.last_status = b.status
+            self._launch(x, y, self._get_buffers(t, dev), record_streams=True)
         out = y.view(bsz, seq_len, h)
         return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
+
+    def graphed(self, num_tokens: int, device=None) -> "GraphedOmniMoE":
+        """Capture one eval-mode forward for ``num_tokens`` tokens in a CUDA graph."""
+        return GraphedOmniMoE(self, num_tokens, device)
 
     def check_status(self) -> None:
         """Synchronise and raise if any kernel of the latest forward reported a device-side fault."""
         st = getattr(self, "last_status", None)
         if st is not None:
             _lib.check_status(st)
+
+
+class GraphedOmniMoE:
+    """One captured forward with static input / output buffers: ``x`` (bf16 ``[T, H]``) is the input
+    to fill, ``y`` the output of the latest ``replay()``.  The ~12 kernel launches and the two-stream
+    fork/join become one graph launch."""
+
+    def __init__(self, module: OmniMoE, num_tokens: int, device=None):
+        if module.training:
+            raise RuntimeError("graph capture is for eval mode (training-mode BatchNorm allocates and updates buffers)")
+        dev = torch.device(device) if device is not None else module.gate_proj.weight.device
+        if module.gate_proj.weight.dtype != torch.bfloat16:
+            raise RuntimeError("graph capture needs a bf16 module (module.to(torch.bfloat16)): "
+                               "other dtypes are converted per call, which a graph would freeze")
+        self.module = module
+        self.x = torch.zeros((num_tokens, module.hidden_size), device=dev, dtype=torch.bfloat16)
+        self.y = torch.zeros((num_tokens, module.hidden_size), device=dev, dtype=torch.bfloat16)
+        self.buffers = _Buffers(num_tokens, module.hidden_size, module.intermediate_size, module.num_expert_sqrt,
+                                module.num_experts, module.top_k, dev)
+        with torch.cuda.device(dev):
+            module._bn_fold_eval()
+            warm = torch.cuda.Stream()
+            warm.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(warm):
+                module._launch(self.x, self.y, self.buffers, record_streams=False)
+            torch.cuda.current_stream().wait_stream(warm)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                module._launch(self.x, self.y, self.buffers, record_streams=False)
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.y
+
+    def __call__(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        self.x.copy_(hidden_states.reshape(self.x.shape), non_blocking=True)
+        self.graph.replay()
+        return self.y.view(hidden_states.shape)
