@@ -8,29 +8,28 @@
 //   EPI_SWIGLU  B tile = 128 rows of Wg next to 128 rows of Wu; writes silu(g) * u as bf16
 //   EPI_RES     adds an optional fp32 residual, writes bf16 (down projection + expert states)
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer (one lane): fills a ring of shared-memory stages
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma and commits to the stage / accumulator barriers
-//   warps 2-5   epilogue: each owns the 32 TMEM lanes (= tile rows) its warp id selects
+//   warps 2-9   epilogue: a warp may read the 32 TMEM lanes (= tile rows) its warp id modulo 4 selects;
+//               two warps share a lane quarter and split the columns
 // Two accumulators alternate, so the epilogue of tile i overlaps the MMAs of tile i+1.
 //
 // Every mbarrier wait is bounded.  A wait that runs out sets OMNI_ST_WAIT_TIMEOUT in the status
 // word and raises a CTA-wide abort flag that turns all later waits into no-ops, so the kernel still
 // drains, frees its TMEM and returns; the results of such a launch are garbage and the host sees the flag.
+// The MLP GEMMs normally run the CTA-pair variant further down (cta_group::2).
 // No load in this file uses cluster multicast.
-#include <cuda.h>
+#include <cstdlib>
 
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace omni {
 namespace {
 
-constexpr int BM = 128;       // tile rows (UMMA M)
-constexpr int BK = 64;        // K per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;    // K per tcgen05.mma for 16-bit types
-constexpr int kThreads = 192;
-constexpr int kEpiWarps = 4;
-constexpr uint32_t kSpinLimit = 1u << 22;
+using namespace tc;
+constexpr int kEpiWarps = 8;  // two per TMEM lane quarter, each draining half of the columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 
 enum { EPI_F32 = 0, EPI_SWIGLU = 1, EPI_RES = 2 };
 
@@ -44,117 +43,22 @@ struct GemmArgs {
   const float* residual;  // EPI_RES
   int64_t ldr;
   int* status;
+  long long* prof;  // debug: per-CTA cycle counters (8 words per CTA), normally null
+  int knobs;        // debug: 1 = no TMA loads (MMAs run on stale tiles), 2 = no MMAs; normally 0
+  int grid_limit;   // debug: cap on CTAs (pairs for the pair kernel); 0 = none
 };
 
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and raises the abort flag) when it gives up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  if (*abort_flag) return false;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 128) {
-      __nanosleep(64);
-      if ((i & 1023) == 0 && *abort_flag) return false;
-    }
-  }
-  *abort_flag = 1;
-  atomicOr(status, OMNI_ST_WAIT_TIMEOUT);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// mbarrier arrives once all tcgen05.mma issued so far by this thread have completed
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 32 lanes x 32 columns of fp32: thread i of the warp gets row (lane base + i), columns [c, c+32)
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
-// swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading byte offset is
-// not used for swizzled K-major layouts, descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);  // start address, 16-byte units
-  d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (ignored)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset
-  d |= static_cast<uint64_t>(1) << 46;                      // version
-  d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, both K-major, M x N tile.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
-}
+// Cycle accounting for tuning: adds the cycles spent in `stmt` to `acc` when profiling is on.
+#define OMNI_TIMED(acc, stmt)                 \
+  do {                                        \
+    if (g.prof) {                             \
+      const long long t0_ = clock64();        \
+      stmt;                                   \
+      acc += clock64() - t0_;                 \
+    } else {                                  \
+      stmt;                                   \
+    }                                         \
+  } while (0)
 
 template <int BN>
 struct Cfg {
@@ -166,6 +70,81 @@ struct Cfg {
   static constexpr int kBarBytes = 1024;
   static constexpr int kSmem = kStages * kStage + kBarBytes + 1024;  // + slack to align the base to 1024
 };
+
+// Drains this warp's share of one accumulator tile: its 32 rows (TMEM lane quarter) and the column
+// chunks [c_begin, c_begin + 32 * NCH).  The TMEM load of chunk i+1 and the residual fetch of
+// chunk i are in flight while chunk i-1 is converted and stored.
+// taddr: TMEM address of column 0 of the accumulator in this warp's lane quarter; row: global row
+// of this thread; output columns start at col_tile and are clipped to col_lim.
+template <int BN, int EPI, int NCH>
+__device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile, int col_lim, int c_begin, const GemmArgs& g) {
+  uint32_t ra[32], rb[32];
+  tmem_ld32_async(taddr + c_begin, ra);
+  if (EPI == EPI_SWIGLU) tmem_ld32_async(taddr + BN / 2 + c_begin, rb);
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = c_begin + 32 * ch;
+    const int col0 = col_tile + c;
+    const bool live = row < g.M && col0 < col_lim;
+    const bool full = col0 + 32 <= col_lim;
+    float4 res[8];
+    const bool vec_res = EPI == EPI_RES && g.residual && live && full && (g.ldr & 3) == 0;
+    if (vec_res) {
+      const float* r = g.residual + static_cast<int64_t>(row) * g.ldr + col0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) res[i] = __ldg(reinterpret_cast<const float4*>(r) + i);
+    }
+    float v[32];
+    tmem_ld_wait(ra);
+    if (EPI == EPI_SWIGLU) {
+      tmem_ld_wait(rb);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = silu_fast(__uint_as_float(ra[i])) * __uint_as_float(rb[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
+    }
+    if (ch + 1 < NCH) {
+      tmem_ld32_async(taddr + c + 32, ra);
+      if (EPI == EPI_SWIGLU) tmem_ld32_async(taddr + BN / 2 + c + 32, rb);
+    }
+    if (!live) continue;
+    if (EPI == EPI_F32) {
+      float* o = reinterpret_cast<float*>(g.out) + static_cast<int64_t>(row) * g.ldo + col0;
+      if (full && (g.ldo & 3) == 0 && (col0 & 3) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      } else {
+        for (int i = 0; i < 32 && col0 + i < col_lim; ++i) o[i] = v[i];
+      }
+    } else {
+      if (EPI == EPI_RES && g.residual) {
+        if (vec_res) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            v[4 * i] += res[i].x, v[4 * i + 1] += res[i].y, v[4 * i + 2] += res[i].z, v[4 * i + 3] += res[i].w;
+        } else {
+          const float* r = g.residual + static_cast<int64_t>(row) * g.ldr + col0;
+          for (int i = 0; i < 32 && col0 + i < col_lim; ++i) v[i] += r[i];
+        }
+      }
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + static_cast<int64_t>(row) * g.ldo + col0;
+      if (full && (g.ldo & 7) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 p;
+          p.x = float2_to_bf16x2(v[i], v[i + 1]);
+          p.y = float2_to_bf16x2(v[i + 2], v[i + 3]);
+          p.z = float2_to_bf16x2(v[i + 4], v[i + 5]);
+          p.w = float2_to_bf16x2(v[i + 6], v[i + 7]);
+          *reinterpret_cast<uint4*>(o + i) = p;
+        }
+      } else {
+        for (int i = 0; i < 32 && col0 + i < col_lim; ++i) o[i] = __float2bfloat16_rn(v[i]);
+      }
+    }
+  }
+}
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
@@ -220,14 +199,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------------------
     if (lane == 0) {
+      long long p_wait = 0;
+      bool dead = false;
+      const long long p_t0 = clock64();
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
         const int axis = tn / g.tiles_n_axis, tj = tn - axis * g.tiles_n_axis;
         for (int kb = 0; kb < kblocks; ++kb) {
-          mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, g.status);
-          if (*abort_flag) break;
+          bool ok;
+          OMNI_TIMED(p_wait, ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, g.status));
+          if (!ok) { dead = true; break; }
           const uint32_t full = bar_full + 8 * stage;
           mbar_arrive_expect_tx(full, C::kStage);
           tma_load_2d(sA + stage * C::kStageA, &tm_a, kb * BK, tm * BM, full);
@@ -240,8 +223,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           }
           if (++stage == C::kStages) stage = 0, phase ^= 1;
         }
-        if (*abort_flag) break;
+        if (dead) break;
       }
+      if (g.prof) g.prof[blockIdx.x * 16 + 3] = p_wait, g.prof[blockIdx.x * 16 + 4] = clock64() - p_t0;
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------------------
@@ -250,18 +234,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
+      long long m_full = 0, m_tempty = 0;
+      bool dead = false;
+      const uint64_t adesc0 = make_smem_desc(sA), bdesc0 = make_smem_desc(sB);
+      const long long m_t0 = clock64();
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, g.status);
+        OMNI_TIMED(m_tempty, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, g.status));
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kblocks; ++kb) {
-          mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status);
-          if (*abort_flag) break;
+          bool ok;
+          OMNI_TIMED(m_full, ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status));
+          if (!ok) { dead = true; break; }
           tc_fence_after();
-          const uint64_t adesc = make_smem_desc(sA + stage * C::kStageA);
-          const uint64_t bdesc = make_smem_desc(sB + stage * C::kStageB);
+          // descriptors of consecutive stages differ only in the start-address field (16-byte units)
+          const uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * (C::kStageA >> 4));
+          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * (C::kStageB >> 4));
 #pragma unroll
           for (int ks = 0; ks < BK / UMMA_K; ++ks) {
             // advancing K by 16 bf16 = 32 bytes = 2 units of the start-address field
@@ -270,20 +260,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           umma_commit(bar_empty + 8 * stage);  // frees the stage when these MMAs have read it
           if (++stage == C::kStages) stage = 0, phase ^= 1;
         }
-        if (*abort_flag) break;
+        if (dead) break;
         umma_commit(bar_tfull + 8 * acc);  // accumulator complete
       }
+      if (g.prof) g.prof[blockIdx.x * 16 + 0] = m_full, g.prof[blockIdx.x * 16 + 1] = m_tempty, g.prof[blockIdx.x * 16 + 2] = clock64() - m_t0;
     }
   } else {
     // ------------------------------- epilogue -----------------------------------------------
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, +32) are the ones this warp may read
+    const int col_half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     int it = 0;
+    long long e_wait = 0, e_store = 0;
+    const long long e_t0 = clock64();
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
       const int axis = tn / g.tiles_n_axis, tj = tn - axis * g.tiles_n_axis;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status);
+      bool ok;
+      OMNI_TIMED(e_wait, ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status));
       tc_fence_after();
       if (!ok) break;
       const int row = tm * BM + quarter * 32 + lane;
@@ -291,61 +286,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       constexpr int OUTC = (EPI == EPI_SWIGLU) ? BN / 2 : BN;  // output columns of this tile
       const int col_tile = (EPI == EPI_F32 && g.dual) ? axis * g.N + tj * OUTC : tj * OUTC;
       const int col_lim = (EPI == EPI_F32 && g.dual) ? (axis + 1) * g.N : g.N;  // exclusive bound of valid columns
-#pragma unroll 1
-      for (int c = 0; c < OUTC; c += 32) {
-        float v[32];
-        tmem_ld32(taddr + c, v);
-        if (EPI == EPI_SWIGLU) {
-          float u[32];
-          tmem_ld32(taddr + BN / 2 + c, u);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = silu(v[i]) * u[i];
-        }
-        const int col0 = col_tile + c;
-        if (row < g.M && col0 < col_lim) {
-          const bool full = col0 + 32 <= col_lim;
-          if (EPI == EPI_F32) {
-            float* o = reinterpret_cast<float*>(g.out) + static_cast<int64_t>(row) * g.ldo + col0;
-            if (full && (g.ldo & 3) == 0 && (col0 & 3) == 0) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            } else {
-              for (int i = 0; i < 32 && col0 + i < col_lim; ++i) o[i] = v[i];
-            }
-          } else {
-            if (EPI == EPI_RES && g.residual) {
-              const float* r = g.residual + static_cast<int64_t>(row) * g.ldr + col0;
-              if (full && (g.ldr & 3) == 0) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                  const float4 rv = __ldg(reinterpret_cast<const float4*>(r + i));
-                  v[i] += rv.x, v[i + 1] += rv.y, v[i + 2] += rv.z, v[i + 3] += rv.w;
-                }
-              } else {
-                for (int i = 0; i < 32 && col0 + i < col_lim; ++i) v[i] += r[i];
-              }
-            }
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + static_cast<int64_t>(row) * g.ldo + col0;
-            if (full && (g.ldo & 7) == 0) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint4 p;
-                p.x = float2_to_bf16x2(v[i], v[i + 1]);
-                p.y = float2_to_bf16x2(v[i + 2], v[i + 3]);
-                p.z = float2_to_bf16x2(v[i + 4], v[i + 5]);
-                p.w = float2_to_bf16x2(v[i + 6], v[i + 7]);
-                *reinterpret_cast<uint4*>(o + i) = p;
-              }
-            } else {
-              for (int i = 0; i < 32 && col0 + i < col_lim; ++i) o[i] = __float2bfloat16_rn(v[i]);
-            }
-          }
-        }
-      }
+      OMNI_TIMED(e_store, (store_tile<BN, EPI, OUTC / 64>(taddr, row, col_tile, col_lim, col_half * (OUTC / 2), g)));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
     }
+    if (g.prof && warp == 2 && lane == 0)
+      g.prof[blockIdx.x * 16 + 5] = e_wait, g.prof[blockIdx.x * 16 + 6] = e_store, g.prof[blockIdx.x * 16 + 7] = clock64() - e_t0;
   }
 
   // ------------------------------- teardown -------------------------------------------------
@@ -360,6 +307,191 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair kernel: two CTAs of a cluster (two SMs) work on one 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA fetches its own 128 rows of A and its own half of the B tile
+// (128 of the 256 rows; for EPI_SWIGLU rank 0 holds the Wg rows and rank 1 the Wu rows), so a CTA
+// moves 32 KB per 64-wide K block instead of 48 KB and six stages fit in shared memory.
+// The accumulator of a CTA (its 128 rows x 256 columns) sits in its own TMEM.
+//   rank 0 (leader)  its MMA lane issues every MMA of the pair; the "full" barrier of a stage lives
+//                    here and counts the bytes of both CTAs' loads
+//   both ranks       producer lane loads the local tiles; epilogue warps drain the local accumulator
+// Stage-free and accumulator-ready signals reach both CTAs through the multicast form of
+// tcgen05.commit; accumulator-drained signals go to the leader with a remote mbarrier arrive.
+// ---------------------------------------------------------------------------------------------
+struct PairCfg {
+  static constexpr int BN = 256;
+  static constexpr int kStageA = BM * BK * 2;        // 16 KB: this CTA's 128 rows of A
+  static constexpr int kStageB = (BN / 2) * BK * 2;  // 16 KB: this CTA's half of B
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = 6;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmem = kStages * kStage + 1024 + 1024;
+};
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
+                     const __grid_constant__ CUtensorMap tm_b1, const GemmArgs g) {
+  using C = PairCfg;
+  constexpr int BN = C::BN;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t sA = base;
+  const uint32_t sB = base + C::kStages * C::kStageA;
+  uint8_t* bar_ptr = base_ptr + C::kStages * C::kStage;
+  const uint32_t bars = base + C::kStages * C::kStage;
+  const uint32_t bar_full = bars;
+  const uint32_t bar_empty = bars + 8 * C::kStages;
+  const uint32_t bar_tfull = bars + 16 * C::kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ptr + 16 * C::kStages + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 16 * C::kStages + 40);
+
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_tiles = g.tiles_m * g.tiles_n;  // tiles_m counts 256-row pair tiles here
+  const int kblocks = ceil_div(g.K, BK);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * kEpiWarps);  // epilogue warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tm_a);
+    prefetch_tmap(&tm_b0);
+    prefetch_tmap(&tm_b1);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) -------------------------------
+    if (lane == 0) {
+      long long p_wait = 0;
+      bool dead = false;
+      const long long p_t0 = clock64();
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t full_leader0 = mapa_shared(bar_full, 0);
+      for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+        const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
+        const int row_a = tm * (2 * BM) + static_cast<int>(rank) * BM;
+        const CUtensorMap* mb = (EPI == EPI_SWIGLU && rank == 1) ? &tm_b1 : &tm_b0;
+        const int row_b = (EPI == EPI_SWIGLU) ? tn * (BN / 2) : tn * BN + static_cast<int>(rank) * (BN / 2);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          bool ok;
+          OMNI_TIMED(p_wait, ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, g.status));
+          if (!ok) { dead = true; break; }
+          if (g.knobs & 1) {
+            if (leader) mbar_arrive(bar_full + 8 * stage);
+          } else {
+            if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::kStage);
+            const uint32_t full_leader = full_leader0 + 8 * stage;
+            tma_load_2d_pair(sA + stage * C::kStageA, &tm_a, kb * BK, row_a, full_leader);
+            tma_load_2d_pair(sB + stage * C::kStageB, mb, kb * BK, row_b, full_leader);
+          }
+          if (++stage == C::kStages) stage = 0, phase ^= 1;
+        }
+        if (dead) break;
+      }
+      if (g.prof) g.prof[blockIdx.x * 16 + 3] = p_wait, g.prof[blockIdx.x * 16 + 4] = clock64() - p_t0;
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader CTA only) ---------------------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc(2 * BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      long long m_full = 0, m_tempty = 0;
+      bool dead = false;
+      const uint64_t adesc0 = make_smem_desc(sA), bdesc0 = make_smem_desc(sB);
+      const long long m_t0 = clock64();
+      for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        OMNI_TIMED(m_tempty, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, g.status));
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          bool ok;
+          OMNI_TIMED(m_full, ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status));
+          if (!ok) { dead = true; break; }
+          tc_fence_after();
+          // descriptors of consecutive stages differ only in the start-address field (16-byte units)
+          const uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * (C::kStageA >> 4));
+          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * (C::kStageB >> 4));
+          if (!(g.knobs & 2)) {
+#pragma unroll
+            for (int ks = 0; ks < BK / UMMA_K; ++ks)
+              umma_bf16_pair(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, (kb | ks) != 0);
+          }
+          umma_commit_pair(bar_empty + 8 * stage, 3);  // both CTAs may refill this stage
+          if (++stage == C::kStages) stage = 0, phase ^= 1;
+        }
+        if (dead) break;
+        umma_commit_pair(bar_tfull + 8 * acc, 3);  // both CTAs may drain their accumulator
+      }
+      if (g.prof) g.prof[blockIdx.x * 16 + 0] = m_full, g.prof[blockIdx.x * 16 + 1] = m_tempty, g.prof[blockIdx.x * 16 + 2] = clock64() - m_t0;
+    }
+  } else {
+    // ------------------------------- epilogue (both CTAs) -----------------------------------
+    const int quarter = warp & 3;
+    const int col_half = (warp - 2) >> 2;
+    int it = 0;
+    long long e_wait = 0, e_store = 0;
+    const long long e_t0 = clock64();
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+      const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      bool ok;
+      OMNI_TIMED(e_wait, ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status));
+      tc_fence_after();
+      if (!ok) break;
+      const int row = tm * (2 * BM) + static_cast<int>(rank) * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      constexpr int OUTC = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+      OMNI_TIMED(e_store, (store_tile<BN, EPI, OUTC / 64>(taddr, row, tn * OUTC, g.N, col_half * (OUTC / 2), g)));
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
+    }
+    if (g.prof && warp == 2 && lane == 0)
+      g.prof[blockIdx.x * 16 + 5] = e_wait, g.prof[blockIdx.x * 16 + 6] = e_store, g.prof[blockIdx.x * 16 + 7] = clock64() - e_t0;
+  }
+
+  // ------------------------------- teardown -------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers or read its tiles
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::kTmemCols);
   }
 }
 
@@ -422,6 +554,35 @@ int launch(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, c
   return check_launch("gemm_kernel");
 }
 
+template <int EPI>
+int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const GemmArgs& g, cudaStream_t st) {
+  using C = PairCfg;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+      return fail(-2, "cannot raise the shared-memory limit to %d bytes", C::kSmem);
+    attr_set = true;
+  }
+  const int tiles = g.tiles_m * g.tiles_n;
+  const int max_pairs = sm_count() / 2;
+  int pairs = tiles < max_pairs ? tiles : max_pairs;
+  if (g.grid_limit > 0 && g.grid_limit < pairs) pairs = g.grid_limit;
+  gemm_pair_kernel<EPI><<<2 * pairs, kThreads, C::kSmem, st>>>(a, b0, b1, g);
+  return check_launch("gemm_pair_kernel");
+}
+
+// OMNI_MOE_B200_GEMM=1cta selects the single-CTA kernels for the MLP GEMMs (default: CTA pairs).
+bool use_pairs() {
+  static const bool v = [] {
+    const char* e = getenv("OMNI_MOE_B200_GEMM");
+    return !(e && e[0] == '1');
+  }();
+  return v;
+}
+
+long long* g_prof = nullptr;  // set by omni_debug_gemm_profile
+int g_knobs = 0, g_grid_limit = 0;
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -447,7 +608,7 @@ extern "C" int omni_router_gate(const void* x, const void* gate_x, const void* g
   g.tiles_m = ceil_div(g.M, BM);
   g.tiles_n_axis = ceil_div(sqrt_n, bn);
   g.tiles_n = 2 * g.tiles_n_axis;
-  g.out = logits, g.ldo = 2 * static_cast<int64_t>(sqrt_n), g.status = status;
+  g.out = logits, g.ldo = 2 * static_cast<int64_t>(sqrt_n), g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<64, EPI_F32>(ma, mx, my, g, st);
   if (bn == 128) return launch<128, EPI_F32>(ma, mx, my, g, st);
@@ -470,7 +631,11 @@ extern "C" int omni_mlp_gate_up(const void* x, const void* gate_w, const void* u
   g.M = static_cast<int>(num_tokens), g.N = intermediate, g.K = hidden, g.dual = 0;
   g.tiles_m = ceil_div(g.M, BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(intermediate, 128);
-  g.out = act, g.ldo = intermediate, g.status = status;
+  g.out = act, g.ldo = intermediate, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  if (use_pairs()) {
+    g.tiles_m = ceil_div(g.M, 2 * BM);
+    return launch_pair<EPI_SWIGLU>(ma, mg, mu, g, static_cast<cudaStream_t>(stream));
+  }
   return launch<256, EPI_SWIGLU>(ma, mg, mu, g, static_cast<cudaStream_t>(stream));
 }
 
@@ -482,7 +647,7 @@ extern "C" int omni_mlp_down(const void* act, const void* down_w, int64_t num_to
   if (num_tokens == 0) return 0;
   OMNI_REQUIRE(act && down_w && y && status, "NULL argument");
   OMNI_REQUIRE(aligned16(act) && aligned16(down_w) && aligned16(y) && aligned16(residual), "pointers must be 16-byte aligned");
-  const int bn = 128;
+  const int bn = 128;  // rows per B box: a whole tile of the single-CTA kernel, half a tile of the pair kernel
   CUtensorMap ma, mb;
   if (int e = make_map(&ma, act, num_tokens, intermediate, BM)) return e;
   if (int e = make_map(&mb, down_w, hidden, intermediate, bn)) return e;
@@ -490,7 +655,12 @@ extern "C" int omni_mlp_down(const void* act, const void* down_w, int64_t num_to
   g.M = static_cast<int>(num_tokens), g.N = hidden, g.K = intermediate, g.dual = 0;
   g.tiles_m = ceil_div(g.M, BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(hidden, bn);
-  g.out = y, g.ldo = hidden, g.residual = residual, g.ldr = hidden, g.status = status;
+  g.out = y, g.ldo = hidden, g.residual = residual, g.ldr = hidden, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  if (use_pairs()) {
+    g.tiles_m = ceil_div(g.M, 2 * BM);
+    g.tiles_n = g.tiles_n_axis = ceil_div(hidden, 256);
+    return launch_pair<EPI_RES>(ma, mb, mb, g, static_cast<cudaStream_t>(stream));
+  }
   return launch<128, EPI_RES>(ma, mb, mb, g, static_cast<cudaStream_t>(stream));
 }
 
@@ -500,3 +670,9 @@ extern "C" int omni_mlp_fwd(const void* x, const void* gate_w, const void* up_w,
   if (int e = omni_mlp_gate_up(x, gate_w, up_w, num_tokens, hidden, intermediate, act, status, stream)) return e;
   return omni_mlp_down(act, down_w, num_tokens, hidden, intermediate, residual, y, status, stream);
 }
+
+// Tuning aid, not part of the public header: while `buf` (device memory, 8 int64 per CTA) is set,
+// the GEMM kernels record cycle counters there: {MMA wait-for-operands, MMA wait-for-accumulator,
+// MMA total, producer wait-for-stage, producer total, epilogue wait, epilogue store, epilogue total}.
+extern "C" OMNI_API void omni_debug_gemm_profile(long long* buf) { g_prof = buf; }
+extern "C" OMNI_API void omni_debug_gemm_knobs(int knobs, int grid_limit) { g_knobs = knobs, g_grid_limit = grid_limit; }
