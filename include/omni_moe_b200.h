@@ -120,6 +120,34 @@ OMNI_API int omni_schedule(const void *indices, int idx_is_i64, const void *weig
                   void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * omni_schedule for callers that cannot hand over scratch memory.  (No counterpart in the reference
+ * project: this entry point exists for the embedding side.)
+ *
+ * Some hosts of this library may not allocate device memory themselves at the point where they
+ * schedule: a plugin that only receives the tensors its framework passes in, code running inside a
+ * memory-planned region where every buffer was fixed ahead of time, or a service whose allocator is
+ * owned by another component.  For them the radix-sort scratch is a fixed 6.5 MiB array inside the
+ * library image (every GPU that loads the library holds it until the process exits); this function
+ * never calls cudaMalloc, cudaFree or any allocating routine.  The caller still passes all inputs
+ * and outputs, with the meaning they have in omni_schedule.
+ *
+ * Limit: num_tokens * k <= omni_schedule_static_max_pairs() (262144); larger problems are refused
+ * with a message and nothing is enqueued.
+ * The first call on each device looks up the device address of the built-in array (with that
+ * device current); make that first call before any stream capture begins.
+ * All calls on a device share the one array, which keeps the previous call's contents: the counters
+ * that must start at zero are cleared at the start of each call, but two calls whose kernels overlap
+ * on the GPU (different streams without an ordering between them) race on it.  Keep calls on one
+ * stream, or order them with events.
+ */
+OMNI_API int64_t omni_schedule_static_max_pairs(void);
+OMNI_API int omni_schedule_static(const void *indices, int idx_is_i64, const void *weights, int weight_elem_bytes,
+                         int64_t num_tokens, int k, int64_t num_experts,
+                         int32_t *sorted_pair_ids, int32_t *sorted_experts, int32_t *token_ids,
+                         void *sorted_weights, int32_t *expert_ids, int32_t *offsets, int32_t *meta,
+                         void *stream);
+
+/*
  * Routed experts, y[t] = sum_j w[t,j] * silu(x[t] . Up[e[t,j]]) * Down[e[t,j]], in two kernels:
  * omni_expert_coef walks the pairs in expert order (each Up row is fetched once per run of
  * pairs on that expert) and writes c[t,j] = w[t,j] * silu(x[t] . Up[e]) in fp32;

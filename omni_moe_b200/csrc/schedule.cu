@@ -401,3 +401,59 @@ extern "C" int omni_schedule(const void* indices, int idx_is_i64, const void* we
   return run<4>(pl, indices, idx_is_i64, weights, weight_elem_bytes, k, num_experts, sorted_pair_ids, sorted_experts,
                 token_ids, sorted_weights, expert_ids, offsets, meta, ws, st);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Scheduling without caller-provided scratch
+// ---------------------------------------------------------------------------------------------
+namespace omni {
+namespace {
+
+constexpr int64_t kStaticMaxPairs = 262144;            // largest T*k the built-in scratch can sort
+constexpr size_t kStaticBytes = 6 * 1024 * 1024 + 512 * 1024;  // 6.5 MiB, held by every GPU that loads the library
+
+// The scratch lives in the library image, not on the heap.  In host code this name is only a handle
+// for the symbol: the device address has to be asked for with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_ptr[kMaxDevices] = {};
+
+// Device address of the built-in scratch on the current device (looked up once per device).
+int static_scratch(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(-2, "cannot identify the current CUDA device");
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) return fail(-2, "cudaGetSymbolAddress(built-in scratch) failed: %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+}  // namespace omni
+
+extern "C" int64_t omni_schedule_static_max_pairs(void) { return kStaticMaxPairs; }
+
+extern "C" int omni_schedule_static(const void* indices, int idx_is_i64, const void* weights, int weight_elem_bytes,
+                                    int64_t num_tokens, int k, int64_t num_experts, int32_t* sorted_pair_ids,
+                                    int32_t* sorted_experts, int32_t* token_ids, void* sorted_weights,
+                                    int32_t* expert_ids, int32_t* offsets, int32_t* meta, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1, "num_tokens must be >= 0 and k >= 1");
+  const int64_t P = num_tokens * k;
+  OMNI_REQUIRE(P <= kStaticMaxPairs,
+               "omni_schedule_static sorts at most %lld (token, expert) pairs with its built-in scratch, got %lld; "
+               "use omni_schedule with a caller-provided workspace",
+               static_cast<long long>(kStaticMaxPairs), static_cast<long long>(P));
+  OMNI_REQUIRE(num_experts >= 1 && num_experts <= (int64_t(1) << 30), "num_experts must be in [1, 2^30]");
+  OMNI_REQUIRE(make_plan(P, num_experts).total <= kStaticBytes, "built-in scratch too small for this problem");
+  void* ws = nullptr;
+  if (int e = static_scratch(&ws)) return e;
+  // Same kernels as omni_schedule; the counters that must start at zero are cleared on the stream
+  // at the start of every call, the rest of the scratch is overwritten before it is read.
+  return omni_schedule(indices, idx_is_i64, weights, weight_elem_bytes, num_tokens, k, num_experts, sorted_pair_ids,
+                       sorted_experts, token_ids, sorted_weights, expert_ids, offsets, meta, ws, kStaticBytes, stream);
+}
