@@ -160,7 +160,8 @@ OMNI_API int omni_schedule_static(const void *indices, int idx_is_i64, const voi
  *   x [T, H], up/down [N, H] bf16 row-major; weights [T, k] float32; indices [T, k] int32
  *   sorted_pair_ids, sorted_experts: from omni_schedule
  *   coef [T, k] float32
- *   y [T, H] of out_dtype (OMNI_F32 or OMNI_BF16); residual [T, H] of the same type added in, or NULL
+ *   y [T, H] of out_dtype (OMNI_F32 or OMNI_BF16); residual [T, H] of the same type added in, or NULL;
+ *   residual may be y itself (the sum is then added in place)
  * Limits: H % 8 == 0, pointers 16-byte aligned.
  */
 OMNI_API int omni_expert_coef(const void *x, const void *up, const float *weights,
@@ -171,6 +172,20 @@ OMNI_API int omni_expert_combine(const void *down, const float *coef, const int3
                         int64_t num_tokens, int k, int hidden, int64_t num_experts,
                         const void *residual, void *y, int out_dtype,
                         int32_t *status, void *stream);
+
+/*
+ * The same routed-expert sum in one token-centric kernel, for tables that stay resident in L2
+ * (2 * num_experts * hidden * 2 bytes well below the 126 MB L2): a warp holds its token's x row in
+ * registers and streams the k Up and Down rows of the token; no scheduling pass and no coefficient
+ * array are needed.  Replaces the same reference code as omni_expert_coef + omni_expert_combine
+ * (omni_moe/ops/triton/omni_expert.py:13-168,920-992).
+ *   coef  [T, k] float32 or NULL: if given, also receives w * silu(x . up) per pair
+ * Limits: hidden % 8 == 0 and hidden <= 2048.
+ */
+OMNI_API int omni_expert_fused(const void *x, const void *up, const void *down, const float *weights,
+                      const int32_t *indices, int64_t num_tokens, int k, int hidden, int64_t num_experts,
+                      const void *residual, void *y, int out_dtype, float *coef,
+                      int32_t *status, void *stream);
 
 /*
  * Shared SwiGLU MLP, y = (silu(x Wg^T) * (x Wu^T)) Wd^T (+ residual), as two tcgen05 GEMMs: the
@@ -189,6 +204,17 @@ OMNI_API int omni_mlp_fwd(const void *x, const void *gate_w, const void *up_w, c
                  int64_t num_tokens, int hidden, int intermediate,
                  void *act, const float *residual, void *y,
                  int32_t *status, void *stream);
+
+/*
+ * omni_mlp_gate_up and omni_router_gate in one launch: both multiply the same x, so the router
+ * sub-keys are appended to the gate/up GEMM as extra tile columns (fp32 logits out) and x is
+ * streamed once.  Replaces gate_proj / up_proj / the SwiGLU kernel and the two router gates
+ * (omni_moe/modules/omni_moe.py:70-71,96; omni_moe/ops/triton/interface.py:23-29).
+ */
+OMNI_API int omni_mlp_gate_up_router(const void *x, const void *gate_w, const void *up_w,
+                            const void *gate_x, const void *gate_y,
+                            int64_t num_tokens, int hidden, int intermediate, int sqrt_n,
+                            void *act, float *logits, int32_t *status, void *stream);
 
 /* The two halves of omni_mlp_fwd, for callers that schedule them on different streams. */
 OMNI_API int omni_mlp_gate_up(const void *x, const void *gate_w, const void *up_w,

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
 template <int HV, bool OUT_F32>
 __global__ void __launch_bounds__(kThreads) expert_combine_kernel(
     const __nv_bfloat16* __restrict__ down, const float* __restrict__ coef, const int* __restrict__ indices,
-    int64_t T, int k, int H, int64_t N, int slabs, const void* __restrict__ residual, void* __restrict__ y, int* status) {
+    int64_t T, int k, int H, int64_t N, int slabs, const void* residual, void* y, int* status) {
   const int lane = lane_id();
   const int64_t wid = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
   const int64_t t = wid / slabs;
@@ -152,8 +152,9 @@ __global__ void __launch_bounds__(kThreads) expert_combine_kernel(
       float4 a = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
       float4 b = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
       if (residual) {
-        const float4 ra = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o));
-        const float4 rb = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o + 4));
+        // plain loads: residual may be the output buffer itself (in-place add)
+        const float4 ra = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o);
+        const float4 rb = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o + 4);
         a.x += ra.x, a.y += ra.y, a.z += ra.z, a.w += ra.w;
         b.x += rb.x, b.y += rb.y, b.z += rb.z, b.w += rb.w;
       }
@@ -162,7 +163,129 @@ __global__ void __launch_bounds__(kThreads) expert_combine_kernel(
       *reinterpret_cast<float4*>(yo + 4) = b;
     } else {
       if (residual) {
-        const uint4 rv = ldg128(reinterpret_cast<const __nv_bfloat16*>(residual) + o);
+        const uint4 rv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(residual) + o);
+        const uint32_t* pr = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = bf16x2_to_float2(pr[q]);
+          acc[v][2 * q] += f.x;
+          acc[v][2 * q + 1] += f.y;
+        }
+      }
+      uint4 o4;
+      o4.x = float2_to_bf16x2(acc[v][0], acc[v][1]);
+      o4.y = float2_to_bf16x2(acc[v][2], acc[v][3]);
+      o4.z = float2_to_bf16x2(acc[v][4], acc[v][5]);
+      o4.w = float2_to_bf16x2(acc[v][6], acc[v][7]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(y) + o) = o4;
+    }
+  }
+  if (bad && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
+// Token-centric fusion of the two kernels above for tables that stay resident in L2: a warp owns one
+// token, holds its x row in registers and walks its k pairs with the Up and the Down row of UNR
+// pairs in flight; dot, SiLU, weight and the accumulation of c * Down happen in registers, nothing
+// is scheduled and no coefficient round-trips through memory.  Every row is read k times in total,
+// which is free while both tables live in L2 and wasteful once they do not (then the expert-ordered
+// pair of kernels above reads each Up row from HBM once).
+template <int HV, bool OUT_F32>
+__global__ void __launch_bounds__(kThreads) expert_fused_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
+    const float* __restrict__ weights, const int* __restrict__ indices, int64_t T, int k, int H, int64_t N,
+    const void* residual, void* y, float* __restrict__ coef, int* status) {
+  const int lane = lane_id();
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int c0 = lane * 8;
+  uint4 xv[HV];
+#pragma unroll
+  for (int v = 0; v < HV; ++v) {
+    const int col = c0 + v * 256;
+    xv[v] = col < H ? ldg128(x + t * H + col) : make_uint4(0, 0, 0, 0);
+  }
+  float acc[HV][8];
+#pragma unroll
+  for (int v = 0; v < HV; ++v)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[v][q] = 0.f;
+  bool bad = false;
+  constexpr int UNR = HV >= 8 ? 1 : 2;
+  for (int j0 = 0; j0 < k; j0 += 32) {
+    int my_e = -1;
+    float my_w = 0.f;
+    if (j0 + lane < k) {
+      my_e = indices[t * k + j0 + lane];
+      my_w = weights[t * k + j0 + lane];
+      if (my_e < 0 || my_e >= N) { bad = true; my_e = -1; }
+    }
+    const int cnt = min(32, k - j0);
+    for (int j = 0; j < cnt; j += UNR) {
+      uint4 uv[UNR][HV], dv[UNR][HV];
+      float w[UNR];
+      bool on[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int e = __shfl_sync(FULL_MASK, my_e, (j + u) & 31);
+        w[u] = __shfl_sync(FULL_MASK, my_w, (j + u) & 31);
+        on[u] = (j + u < cnt) && e >= 0;
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const int col = c0 + v * 256;
+          const bool ld = on[u] && col < H;
+          uv[u][v] = ld ? ldg128(up + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+          dv[u][v] = ld ? ldg128(down + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+        }
+      }
+      float dot[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        dot[u] = 0.f;
+#pragma unroll
+        for (int v = 0; v < HV; ++v) dot[u] = dot8(xv[v], uv[u][v], dot[u]);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) dot[u] += __shfl_xor_sync(FULL_MASK, dot[u], o);
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const float c = on[u] ? w[u] * silu(dot[u]) : 0.f;
+        if (coef && lane == 0 && j + u < cnt) coef[t * k + j0 + j + u] = c;
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv[u][v]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = bf16x2_to_float2(pd[q]);
+            acc[v][2 * q] = __fmaf_rn(c, f.x, acc[v][2 * q]);
+            acc[v][2 * q + 1] = __fmaf_rn(c, f.y, acc[v][2 * q + 1]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < HV; ++v) {
+    const int col = c0 + v * 256;
+    if (col >= H) continue;
+    const int64_t o = t * H + col;
+    if (OUT_F32) {
+      float4 a = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+      float4 b = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+      if (residual) {
+        // plain loads: residual may be the output buffer itself (in-place add)
+        const float4 ra = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o);
+        const float4 rb = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o + 4);
+        a.x += ra.x, a.y += ra.y, a.z += ra.z, a.w += ra.w;
+        b.x += rb.x, b.y += rb.y, b.z += rb.z, b.w += rb.w;
+      }
+      float* yo = reinterpret_cast<float*>(y) + o;
+      *reinterpret_cast<float4*>(yo) = a;
+      *reinterpret_cast<float4*>(yo + 4) = b;
+    } else {
+      if (residual) {
+        const uint4 rv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(residual) + o);
         const uint32_t* pr = reinterpret_cast<const uint32_t*>(&rv);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -243,4 +366,39 @@ extern "C" int omni_expert_combine(const void* down, const float* coef, const in
   else OMNI_COMB(8);
 #undef OMNI_COMB
   return check_launch("expert_combine_kernel");
+}
+
+extern "C" int omni_expert_fused(const void* x, const void* up, const void* down, const float* weights,
+                                 const int32_t* indices, int64_t num_tokens, int k, int hidden, int64_t num_experts,
+                                 const void* residual, void* y, int out_dtype, float* coef, int32_t* status,
+                                 void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && num_experts >= 1, "bad sizes");
+  OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
+  OMNI_REQUIRE(hidden <= 2048, "omni_expert_fused keeps a whole row in registers: hidden <= 2048, got %d "
+               "(use omni_schedule + omni_expert_coef + omni_expert_combine)", hidden);
+  OMNI_REQUIRE(out_dtype == OMNI_F32 || out_dtype == OMNI_BF16, "out_dtype must be OMNI_F32 or OMNI_BF16");
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(x && up && down && weights && indices && y && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(up) && aligned16(down) && aligned16(y) && aligned16(residual),
+               "x, up, down, y and residual must be 16-byte aligned");
+  const auto* xb = static_cast<const __nv_bfloat16*>(x);
+  const auto* ub = static_cast<const __nv_bfloat16*>(up);
+  const auto* db = static_cast<const __nv_bfloat16*>(down);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
+#define OMNI_FUSED(HV)                                                                                                 \
+  do {                                                                                                                 \
+    if (out_dtype == OMNI_F32)                                                                                         \
+      expert_fused_kernel<HV, true><<<grid, kThreads, 0, st>>>(xb, ub, db, weights, indices, num_tokens, k, hidden,    \
+                                                               num_experts, residual, y, coef, status);                 \
+    else                                                                                                               \
+      expert_fused_kernel<HV, false><<<grid, kThreads, 0, st>>>(xb, ub, db, weights, indices, num_tokens, k, hidden,   \
+                                                                num_experts, residual, y, coef, status);                \
+  } while (0)
+  if (hidden <= 256) OMNI_FUSED(1);
+  else if (hidden <= 512) OMNI_FUSED(2);
+  else if (hidden <= 1024) OMNI_FUSED(4);
+  else OMNI_FUSED(8);
+#undef OMNI_FUSED
+  return check_launch("expert_fused_kernel");
 }

@@ -42,6 +42,10 @@ struct GemmArgs {
   int64_t ldo;
   const float* residual;  // EPI_RES
   int64_t ldr;
+  // router tile columns of the fused gate/up + router-gate launch (pair kernel, EPI_SWIGLU only)
+  int router_tiles;       // tile columns holding router sub-keys (0 = none); they come first in tile order
+  int router_n;           // sqrt_n
+  float* logits;          // [M, 2 * sqrt_n]
   int* status;
   long long* prof;  // debug: per-CTA cycle counters (8 words per CTA), normally null
   int knobs;        // debug: 1 = no TMA loads (MMAs run on stale tiles), 2 = no MMAs; normally 0
@@ -332,10 +336,14 @@ struct PairCfg {
   static constexpr int kSmem = kStages * kStage + 1024 + 1024;
 };
 
-template <int EPI>
+template <int EPI, bool ROUTER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
-                     const __grid_constant__ CUtensorMap tm_b1, const GemmArgs g) {
+                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_r0,
+                     const __grid_constant__ CUtensorMap tm_r1, const GemmArgs g) {
+  // ROUTER: the first g.router_tiles tile columns multiply x by the router sub-keys instead of the MLP
+  // weights: rank 0 holds 128 rows of the x-axis keys, rank 1 the same rows of the y-axis keys, and the
+  // epilogue stores fp32 logits.  It rides along with the gate/up GEMM because it reads the same A.
   using C = PairCfg;
   constexpr int BN = C::BN;
   extern __shared__ uint8_t smem_raw[];
@@ -357,7 +365,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_tiles = g.tiles_m * g.tiles_n;  // tiles_m counts 256-row pair tiles here
+  const int rt = ROUTER ? g.router_tiles : 0;
+  const int num_tiles = g.tiles_m * (g.tiles_n + rt);  // tiles_m counts 256-row pair tiles here
   const int kblocks = ceil_div(g.K, BK);
 
   if (threadIdx.x == 0) {
@@ -395,10 +404,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       uint32_t phase = 0;
       const uint32_t full_leader0 = mapa_shared(bar_full, 0);
       for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-        const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
+        const int tm = tile % g.tiles_m, tn_all = tile / g.tiles_m;
+        const bool router_tile = ROUTER && tn_all < rt;
+        const int tn = router_tile ? tn_all : tn_all - rt;
         const int row_a = tm * (2 * BM) + static_cast<int>(rank) * BM;
-        const CUtensorMap* mb = (EPI == EPI_SWIGLU && rank == 1) ? &tm_b1 : &tm_b0;
-        const int row_b = (EPI == EPI_SWIGLU) ? tn * (BN / 2) : tn * BN + static_cast<int>(rank) * (BN / 2);
+        const CUtensorMap* mb = router_tile ? (rank == 1 ? &tm_r1 : &tm_r0)
+                                            : ((EPI == EPI_SWIGLU && rank == 1) ? &tm_b1 : &tm_b0);
+        const int row_b = (EPI == EPI_SWIGLU || router_tile) ? tn * (BN / 2) : tn * BN + static_cast<int>(rank) * (BN / 2);
         for (int kb = 0; kb < kblocks; ++kb) {
           bool ok;
           OMNI_TIMED(p_wait, ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, g.status));
@@ -463,7 +475,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     long long e_wait = 0, e_store = 0;
     const long long e_t0 = clock64();
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
-      const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
+      const int tm = tile % g.tiles_m, tn_all = tile / g.tiles_m;
+      const bool router_tile = ROUTER && tn_all < rt;
+      const int tn = router_tile ? tn_all : tn_all - rt;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       bool ok;
@@ -473,7 +487,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       const int row = tm * (2 * BM) + static_cast<int>(rank) * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       constexpr int OUTC = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
-      OMNI_TIMED(e_store, (store_tile<BN, EPI, OUTC / 64>(taddr, row, tn * OUTC, g.N, col_half * (OUTC / 2), g)));
+      if (router_tile) {
+        // accumulator columns [0, 128) are x-axis sub-keys tn*128.., [128, 256) the y-axis ones;
+        // the warps of column half h store axis h
+        GemmArgs gr = g;
+        gr.out = g.logits, gr.ldo = 2 * g.router_n;
+        const int col_tile = col_half * g.router_n + tn * (BN / 2);
+        store_tile<BN, EPI_F32, 4>(taddr + col_half * (BN / 2), row, col_tile, (col_half + 1) * g.router_n, 0, gr);
+      } else {
+        OMNI_TIMED(e_store, (store_tile<BN, EPI, OUTC / 64>(taddr, row, tn * OUTC, g.N, col_half * (OUTC / 2), g)));
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
@@ -554,20 +577,21 @@ int launch(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, c
   return check_launch("gemm_kernel");
 }
 
-template <int EPI>
-int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const GemmArgs& g, cudaStream_t st) {
+template <int EPI, bool ROUTER>
+int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const CUtensorMap& r0,
+                const CUtensorMap& r1, const GemmArgs& g, cudaStream_t st) {
   using C = PairCfg;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_pair_kernel<EPI, ROUTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
       return fail(-2, "cannot raise the shared-memory limit to %d bytes", C::kSmem);
     attr_set = true;
   }
-  const int tiles = g.tiles_m * g.tiles_n;
+  const int tiles = g.tiles_m * (g.tiles_n + (ROUTER ? g.router_tiles : 0));
   const int max_pairs = sm_count() / 2;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
   if (g.grid_limit > 0 && g.grid_limit < pairs) pairs = g.grid_limit;
-  gemm_pair_kernel<EPI><<<2 * pairs, kThreads, C::kSmem, st>>>(a, b0, b1, g);
+  gemm_pair_kernel<EPI, ROUTER><<<2 * pairs, kThreads, C::kSmem, st>>>(a, b0, b1, r0, r1, g);
   return check_launch("gemm_pair_kernel");
 }
 
@@ -634,9 +658,35 @@ extern "C" int omni_mlp_gate_up(const void* x, const void* gate_w, const void* u
   g.out = act, g.ldo = intermediate, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
   if (use_pairs()) {
     g.tiles_m = ceil_div(g.M, 2 * BM);
-    return launch_pair<EPI_SWIGLU>(ma, mg, mu, g, static_cast<cudaStream_t>(stream));
+    return launch_pair<EPI_SWIGLU, false>(ma, mg, mu, mg, mu, g, static_cast<cudaStream_t>(stream));
   }
   return launch<256, EPI_SWIGLU>(ma, mg, mu, g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int omni_mlp_gate_up_router(const void* x, const void* gate_w, const void* up_w, const void* gate_x,
+                                       const void* gate_y, int64_t num_tokens, int hidden, int intermediate,
+                                       int sqrt_n, void* act, float* logits, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && num_tokens < (int64_t(1) << 31) - 2 * BM, "num_tokens out of range");
+  OMNI_REQUIRE(hidden >= 8 && hidden % 8 == 0, "hidden must be a positive multiple of 8, got %d", hidden);
+  OMNI_REQUIRE(intermediate >= 8 && intermediate % 8 == 0, "intermediate must be a positive multiple of 8, got %d", intermediate);
+  OMNI_REQUIRE(sqrt_n >= 1, "sqrt_n must be >= 1");
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(x && gate_w && up_w && gate_x && gate_y && act && logits && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(gate_w) && aligned16(up_w) && aligned16(gate_x) && aligned16(gate_y) &&
+               aligned16(act) && aligned16(logits), "pointers must be 16-byte aligned");
+  CUtensorMap ma, mg, mu, mx, my;
+  if (int e = make_map(&ma, x, num_tokens, hidden, BM)) return e;
+  if (int e = make_map(&mg, gate_w, intermediate, hidden, 128)) return e;
+  if (int e = make_map(&mu, up_w, intermediate, hidden, 128)) return e;
+  if (int e = make_map(&mx, gate_x, sqrt_n, hidden, 128)) return e;
+  if (int e = make_map(&my, gate_y, sqrt_n, hidden, 128)) return e;
+  GemmArgs g{};
+  g.M = static_cast<int>(num_tokens), g.N = intermediate, g.K = hidden, g.dual = 0;
+  g.tiles_m = ceil_div(g.M, 2 * BM);
+  g.tiles_n = g.tiles_n_axis = ceil_div(intermediate, 128);
+  g.router_tiles = ceil_div(sqrt_n, 128), g.router_n = sqrt_n, g.logits = logits;
+  g.out = act, g.ldo = intermediate, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  return launch_pair<EPI_SWIGLU, true>(ma, mg, mu, mx, my, g, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int omni_mlp_down(const void* act, const void* down_w, int64_t num_tokens, int hidden, int intermediate,
@@ -659,7 +709,7 @@ extern "C" int omni_mlp_down(const void* act, const void* down_w, int64_t num_to
   if (use_pairs()) {
     g.tiles_m = ceil_div(g.M, 2 * BM);
     g.tiles_n = g.tiles_n_axis = ceil_div(hidden, 256);
-    return launch_pair<EPI_RES>(ma, mb, mb, g, static_cast<cudaStream_t>(stream));
+    return launch_pair<EPI_RES, false>(ma, mb, mb, mb, mb, g, static_cast<cudaStream_t>(stream));
   }
   return launch<128, EPI_RES>(ma, mb, mb, g, static_cast<cudaStream_t>(stream));
 }

@@ -74,8 +74,28 @@ __device__ __forceinline__ void axis_select(uint32_t (&key)[VPL], int kk, float*
   }
 }
 
+// Small rows (at most 64 entries, two per lane): rank every entry by counting the entries that beat
+// it.  The entries are made distinct by packing (score key, ~index) into 64 bits, so the ranks are a
+// permutation; there is no cross-lane dependency chain, only broadcast reads of shared memory.
+// Returns the rank of `mine` among the 64 packed entries in `all`.
+__device__ __forceinline__ int rank_among_64(const unsigned long long* all, unsigned long long mine) {
+  int rank = 0;
+  const ulonglong2* p = reinterpret_cast<const ulonglong2*>(all);
+#pragma unroll 8
+  for (int q = 0; q < 32; ++q) {
+    const ulonglong2 o = p[q];
+    rank += (o.x > mine) + (o.y > mine);
+  }
+  return rank;
+}
+
 template <int VPL, int CPL, bool PRE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) router_topk_kernel(const TopkArgs a) {
+  constexpr bool kSmallAxis = VPL == 2;   // n <= 64: rank by counting instead of selection rounds
+  constexpr bool kSmallCells = CPL == 2;  // <= 64 candidate cells: likewise
+  __shared__ __align__(16) unsigned long long s_pack[(kSmallAxis || kSmallCells) ? kWarpsPerBlock : 1][64];
+  __shared__ uint32_t s_rk[kSmallCells ? kWarpsPerBlock : 1][kSmallCells ? 64 : 1];
+  __shared__ uint32_t s_rf[kSmallCells ? kWarpsPerBlock : 1][kSmallCells ? 64 : 1];
   __shared__ float s_sx[kWarpsPerBlock][kMaxK], s_sy[kWarpsPerBlock][kMaxK];
   __shared__ int s_ix[kWarpsPerBlock][kMaxK], s_iy[kWarpsPerBlock][kMaxK];
   __shared__ uint16_t s_cell[kMaxCells];  // i | j << 8 for each cell of the pruned region
@@ -154,7 +174,26 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) router_topk_kernel(const 
         key[e] = c < n ? float_to_key(load_as_float(base, a.in_dtype, t * a.ld_in + c)) : 0u;
       }
     }
-    axis_select<VPL>(key, kk, axis == 0 ? sx : sy, axis == 0 ? ix : iy);
+    if constexpr (kSmallAxis) {
+      unsigned long long mine[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const uint32_t c = e * 32 + lane;
+        mine[e] = (static_cast<unsigned long long>(key[e]) << 32) | (0xffffffffu - c);
+        s_pack[warp][c] = mine[e];
+      }
+      __syncwarp();
+      float* so = axis == 0 ? sx : sy;
+      int* io = axis == 0 ? ix : iy;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int r = rank_among_64(s_pack[warp], mine[e]);
+        if (r < kk) so[r] = key_to_float(key[e]), io[r] = e * 32 + lane;
+      }
+      __syncwarp();
+    } else {
+      axis_select<VPL>(key, kk, axis == 0 ? sx : sy, axis == 0 ? ix : iy);
+    }
   }
   __syncwarp();
 
@@ -179,6 +218,28 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) router_topk_kernel(const 
 #pragma unroll
   for (int s = 0; s < kMaxK / 32; ++s) rkey[s] = 0, rflat[s] = 0;
   uint32_t last_key = 0;
+  if constexpr (kSmallCells) {
+    unsigned long long mine[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      // padding cells have key 0 and can never outrank a real one; real cells differ in `flat`
+      mine[q] = (static_cast<unsigned long long>(ckey[q]) << 32) | (0xffffffffu - cflat[q]);
+      s_pack[warp][q * 32 + lane] = mine[q];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int r = rank_among_64(s_pack[warp], mine[q]);
+      if (r < k && ckey[q] != 0) s_rk[warp][r] = ckey[q], s_rf[warp][r] = cflat[q];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int r = s * 32 + lane;
+      if (r < k) rkey[s] = s_rk[warp][r], rflat[s] = s_rf[warp][r];
+    }
+    last_key = s_rk[warp][k - 1];
+  } else
   for (int r = 0; r < k; ++r) {
     const uint32_t m = __reduce_max_sync(FULL_MASK, lmax);
     uint32_t mine = 0xffffffffu;
@@ -262,10 +323,24 @@ int launch_cpl(const TopkArgs& a, cudaStream_t st) {
   const unsigned grid = static_cast<unsigned>(ceil_div64(a.T, kWarpsPerBlock));
   const dim3 block(kWarpsPerBlock * 32);
   const int need = ceil_div(a.cells, 32);
-  if (need <= 2) router_topk_kernel<VPL, 2, PRE><<<grid, block, 0, st>>>(a);
-  else if (need <= 4) router_topk_kernel<VPL, 4, PRE><<<grid, block, 0, st>>>(a);
-  else if (need <= 10) router_topk_kernel<VPL, 10, PRE><<<grid, block, 0, st>>>(a);
-  else router_topk_kernel<VPL, 22, PRE><<<grid, block, 0, st>>>(a);
+  // An SM runs blocks of different kernels side by side only if they agree on its shared-memory /
+  // L1 split.  The GEMMs of the layer need the largest shared-memory split; asking for the same one
+  // here lets these small blocks run next to a GEMM block instead of waiting for the SM to drain.
+#define OMNI_TOPK_LAUNCH(CPL_)                                                                                  \
+  do {                                                                                                          \
+    static bool carveout_set = false;                                                                           \
+    if (!carveout_set) {                                                                                        \
+      cudaFuncSetAttribute(router_topk_kernel<VPL, CPL_, PRE>, cudaFuncAttributePreferredSharedMemoryCarveout,  \
+                           cudaSharedmemCarveoutMaxShared);                                                     \
+      carveout_set = true;                                                                                      \
+    }                                                                                                           \
+    router_topk_kernel<VPL, CPL_, PRE><<<grid, block, 0, st>>>(a);                                              \
+  } while (0)
+  if (need <= 2) OMNI_TOPK_LAUNCH(2);
+  else if (need <= 4) OMNI_TOPK_LAUNCH(4);
+  else if (need <= 10) OMNI_TOPK_LAUNCH(10);
+  else OMNI_TOPK_LAUNCH(22);
+#undef OMNI_TOPK_LAUNCH
   return check_launch("router_topk_kernel");
 }
 

@@ -4,13 +4,14 @@ Constructor, parameter / buffer names and shapes, and ``forward(hidden_states)``
 reference module (omni_moe/modules/omni_moe.py:14-106), so a reference ``state_dict`` loads
 unchanged.  Forward only.
 
-Stream plan of one forward (eval mode), all enqueued without a host synchronisation:
+One eval forward is five kernels (eight to ten when the expert tables are too large for L2 and the
+pairs are scheduled by expert first), enqueued without a host synchronisation:
 
-    main stream   gate/up GEMM + SwiGLU  ..............................  down GEMM (+ expert states) -> y
-    side stream   router gate GEMM -> BatchNorm/log-softmax/top-k -> schedule -> coefficients -> combine
+    main stream   gate/up GEMM + SwiGLU -> down GEMM ........................ -> routed experts (+= y)
+    side stream                            router gate GEMM -> BN/log-softmax/top-k
 
-The expert branch has no dependency on the shared MLP until the final add, which is folded into the
-epilogue of the down projection.
+The gate/up GEMM and the expert kernel fill the GPU on their own.  The down projection of the
+quick-start shape occupies 128 of the 148 SMs, so the two small router kernels run beside it.
 """
 from __future__ import annotations
 
@@ -20,6 +21,7 @@ import torch
 import torch.nn as nn
 
 from .. import _lib
+from ..ops.expert import use_fused_path
 from ..ops.scheduler import workspace_bytes
 
 
@@ -50,13 +52,12 @@ class _Buffers:
         self.sorted_experts = torch.empty(max(p, 1), **i32)
         self.meta = torch.zeros(4, **i32)
         self.coef = torch.empty((t, k), **f32)
-        self.expert_states = torch.empty((t, h), **f32)
         self.act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
         self.workspace = torch.empty(workspace_bytes(p, n), device=dev, dtype=torch.uint8)
         self.status = torch.zeros(1, **i32)
         self.side = torch.cuda.Stream(device=dev)
-        self.ev_in = torch.cuda.Event()
-        self.ev_side = torch.cuda.Event()
+        self.ev_fork = torch.cuda.Event()
+        self.ev_join = torch.cuda.Event()
 
 
 class OmniMoE(nn.Module):
@@ -143,58 +144,63 @@ class OmniMoE(nn.Module):
             self.gate_proj, self.up_proj, self.down_proj, self.router_gate_x, self.router_gate_y,
             self.up_embed, self.down_embed))
 
-    def _launch(self, x: torch.Tensor, y: torch.Tensor, b: _Buffers, record_streams: bool) -> None:
-        """Enqueue one forward: ``x [T, H]`` bf16 contiguous -> ``y [T, H]`` bf16.  Allocates nothing in
-        eval mode, so it can be captured in a CUDA graph."""
+    def _launch(self, x: torch.Tensor, y: torch.Tensor, b: _Buffers, record_streams: bool = False) -> None:
+        """Enqueue one forward on the current stream: ``x [T, H]`` bf16 contiguous -> ``y [T, H]`` bf16.
+        Allocates nothing in eval mode, so it can be captured in a CUDA graph."""
         t, h, i, n, k = x.size(0), self.hidden_size, self.intermediate_size, self.num_expert_sqrt, self.top_k
         wg, wu, wd, kx, ky, up_t, down_t = self._operands()
         lib = _lib.load()
         chk = _lib.check
         main = torch.cuda.current_stream()
-        b.ev_in.record(main)
-        # ---- expert branch on the side stream ----
+        st = main.cuda_stream
+        status = b.status.data_ptr()
+        # 1. gate/up projections + SwiGLU: fills every SM
+        chk(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, b.act.data_ptr(), status, st))
+        b.ev_fork.record(main)
+        # 2. side stream: router gates -> BatchNorm + log-softmax + product-key top-k.  Small kernels
+        #    that run on the SMs the down projection leaves free (and next to its CTAs).
         with torch.cuda.stream(b.side):
-            b.side.wait_event(b.ev_in)
+            b.side.wait_event(b.ev_fork)
             ss = b.side.cuda_stream
-            chk(lib.omni_router_gate(x.data_ptr(), kx.data_ptr(), ky.data_ptr(), t, h, n, b.logits.data_ptr(),
-                                     b.status.data_ptr(), ss))
-            if self.training:
-                scale, shift = self._bn_fold_train(b.logits)
-            else:
-                scale, shift = self._bn_fold_eval()
+            chk(lib.omni_router_gate(x.data_ptr(), kx.data_ptr(), ky.data_ptr(), t, h, n, b.logits.data_ptr(), status, ss))
+            scale, shift = self._bn_fold_train(b.logits) if self.training else self._bn_fold_eval()
             chk(lib.omni_router_logits_topk(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
-                                            b.scores.data_ptr(), b.indices.data_ptr(), 0, b.weights.data_ptr(),
-                                            None, ss))
+                                            b.scores.data_ptr(), b.indices.data_ptr(), 0, b.weights.data_ptr(), None, ss))
+            b.ev_join.record(b.side)
+            if record_streams:
+                for tns in (x, kx, ky, scale, shift):
+                    tns.record_stream(b.side)
+        # 3. main stream, meanwhile: down projection -> y
+        chk(lib.omni_mlp_down(b.act.data_ptr(), wd.data_ptr(), t, h, i, None, y.data_ptr(), status, st))
+        main.wait_event(b.ev_join)
+        # 4. routed experts, added onto y in place
+        if use_fused_path(self.num_experts, h):
+            # tables resident in L2: one token-centric kernel, no scheduling pass
+            chk(lib.omni_expert_fused(x.data_ptr(), up_t.data_ptr(), down_t.data_ptr(), b.weights.data_ptr(),
+                                      b.indices.data_ptr(), t, k, h, self.num_experts, y.data_ptr(), y.data_ptr(),
+                                      _lib.OMNI_BF16, None, status, st))
+        else:
+            # large tables: expert-centric schedule, each Up row leaves HBM once
             chk(lib.omni_schedule(b.indices.data_ptr(), 0, None, 0, t, k, self.num_experts, b.perm.data_ptr(),
                                   b.sorted_experts.data_ptr(), None, None, None, None, b.meta.data_ptr(),
-                                  b.workspace.data_ptr(), b.workspace.numel(), ss))
+                                  b.workspace.data_ptr(), b.workspace.numel(), st))
             chk(lib.omni_expert_coef(x.data_ptr(), up_t.data_ptr(), b.weights.data_ptr(), b.perm.data_ptr(),
                                      b.sorted_experts.data_ptr(), t, k, h, self.num_experts, b.coef.data_ptr(),
-                                     b.status.data_ptr(), ss))
+                                     status, st))
             chk(lib.omni_expert_combine(down_t.data_ptr(), b.coef.data_ptr(), b.indices.data_ptr(), t, k, h,
-                                        self.num_experts, None, b.expert_states.data_ptr(), _lib.OMNI_F32,
-                                        b.status.data_ptr(), ss))
-            b.ev_side.record(b.side)
-            if record_streams:
-                for tns in (x, kx, ky, up_t, down_t, scale, shift):
-                    tns.record_stream(b.side)
-        # ---- shared MLP on the main stream ----
-        ms = main.cuda_stream
-        chk(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, b.act.data_ptr(),
-                                 b.status.data_ptr(), ms))
-        main.wait_event(b.ev_side)
-        chk(lib.omni_mlp_down(b.act.data_ptr(), wd.data_ptr(), t, h, i, b.expert_states.data_ptr(), y.data_ptr(),
-                              b.status.data_ptr(), ms))
+                                        self.num_experts, y.data_ptr(), y.data_ptr(), _lib.OMNI_BF16, status, st))
         self.last_routing = (b.scores, b.indices, b.weights)
         self.last_status = b.status
 
-    #: kernels of this library launched by one forward at the given pass count of the scheduler
     @staticmethod
-    def kernels_per_forward(num_experts: int) -> int:
+    def kernels_per_forward(num_experts: int, hidden: int) -> int:
+        """Kernels of this library launched by one eval forward."""
+        if use_fused_path(num_experts, hidden):
+            return 5  # gate/up, router gates, top-k, down projection, fused experts
         bits = max(1, (num_experts - 1).bit_length())
         passes = -(-bits // 11)
-        # router gate GEMM, top-k, 2 per radix pass, coefficients, combine, 2 MLP GEMMs
-        return 2 + 2 * passes + 2 + 2
+        # gate/up, router gates, top-k, down projection, 2 per radix pass, coefficients, combine
+        return 4 + 2 * passes + 2
 
     def forward(self, hidden_states: torch.Tensor, **kwargs) -> torch.Tensor:
         _lib.require_cuda(hidden_states)
@@ -247,12 +253,12 @@ class GraphedOmniMoE:
             warm = torch.cuda.Stream()
             warm.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(warm):
-                module._launch(self.x, self.y, self.buffers, record_streams=False)
+                module._launch(self.x, self.y, self.buffers)
             torch.cuda.current_stream().wait_stream(warm)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):
-                module._launch(self.x, self.y, self.buffers, record_streams=False)
+                module._launch(self.x, self.y, self.buffers)
 
     def replay(self) -> torch.Tensor:
         self.graph.replay()

@@ -7,17 +7,37 @@ from .. import _lib
 from ._common import as_bf16, guard_no_grad
 from .scheduler import schedule
 
+L2_RESIDENT_TABLE_BYTES = 48 << 20  # both tables together; above this the expert-ordered path reads less HBM
+
+
+def use_fused_path(num_experts: int, hidden: int) -> bool:
+    """True when the token-centric single kernel is the better choice: the Up and Down tables
+    (2 * N * H bf16) stay resident in the 126 MB L2 next to the activations, and a row fits in
+    registers.  ``OMNI_MOE_B200_EXPERT=fused|scheduled`` overrides."""
+    import os
+    forced = os.environ.get("OMNI_MOE_B200_EXPERT", "")
+    if forced == "scheduled":
+        return False
+    if hidden > 2048:
+        return False
+    if forced == "fused":
+        return True
+    return 2 * num_experts * hidden * 2 <= L2_RESIDENT_TABLE_BYTES
+
 
 def expert_forward(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor, weights: torch.Tensor,
                    indices: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                    residual: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                   workspace: torch.Tensor | None = None, return_coef: bool = False):
+                   workspace: torch.Tensor | None = None, return_coef: bool = False, mode: str = "auto"):
     """``y[t] = sum_j w[t,j] * silu(x[t] . Up[e[t,j]]) * Down[e[t,j]]`` (+ residual).
 
     ``x [T, H]``, ``up/down [N, H]`` bf16; ``weights [T, k]`` fp32; ``indices [T, k]`` int32.
-    Schedules the pairs by expert, computes the per-pair coefficients in expert order, then combines
-    per token.  ``out_dtype`` float32 or bfloat16; ``residual`` (same dtype as the output) is added in.
+    ``mode="scheduled"``: schedules the pairs by expert, computes the per-pair coefficients in expert
+    order, then combines per token.  ``mode="fused"``: one token-centric kernel (tables resident in
+    L2, hidden <= 2048).  ``mode="auto"`` picks by table size (:func:`use_fused_path`).
+    ``out_dtype`` float32 or bfloat16; ``residual`` (same dtype as the output) is added in.
     """
+    assert mode in ("auto", "fused", "scheduled")
     _lib.require_cuda(x, up_weight, down_weight, weights, indices)
     assert x.dtype == up_weight.dtype == down_weight.dtype == torch.bfloat16
     assert weights.dtype == torch.float32 and indices.dtype == torch.int32
@@ -39,8 +59,17 @@ def expert_forward(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.
     if k == 0:
         y.zero_() if residual is None else y.copy_(residual)
         return (y, coef) if return_coef else y
-    sch = schedule(indices, n, segments=False, workspace=workspace)
     lib = _lib.load()
+    fused = use_fused_path(n, h) if mode == "auto" else mode == "fused"
+    if fused:
+        with torch.cuda.device(dev):
+            _lib.check(lib.omni_expert_fused(x.data_ptr(), up_weight.data_ptr(), down_weight.data_ptr(),
+                                             weights.data_ptr(), indices.data_ptr(), t, k, h, n, _lib.ptr(residual),
+                                             y.data_ptr(), _lib.dtype_code(out_dtype),
+                                             coef.data_ptr() if return_coef else None, status.data_ptr(),
+                                             _lib.stream_ptr()))
+        return (y, coef) if return_coef else y
+    sch = schedule(indices, n, segments=False, workspace=workspace)
     with torch.cuda.device(dev):
         st = _lib.stream_ptr()
         _lib.check(lib.omni_expert_coef(x.data_ptr(), up_weight.data_ptr(), weights.data_ptr(),

@@ -25,13 +25,19 @@ def _inputs(t, h, n, k, seed, idx=None):
 @pytest.mark.parametrize("t,h,n,k", [(32, 64, 128, 8), (300, 256, 1024, 8), (257, 1024, 4096, 16), (64, 2048, 512, 32),
                                        (40, 4096, 300, 64), (50, 72, 64, 6), (33, 1536, 200, 4), (20, 8192, 64, 2),
                                        (1, 8, 1, 1)])
-def test_expert_matches_oracle(t, h, n, k):
+@pytest.mark.parametrize("mode", ["scheduled", "fused"])
+def test_expert_matches_oracle(t, h, n, k, mode):
     from omni_moe_b200.ops import expert_forward
+    if mode == "fused" and h > 2048:
+        with pytest.raises(RuntimeError, match="hidden <= 2048"):
+            x, up, dn, w, idx = _inputs(4, h, 8, 2, 0)
+            expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), mode="fused")
+        return
     x, up, dn, w, idx = _inputs(t, h, n, k, t + h)
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
     for out_dtype in (torch.float32, torch.bfloat16):
         y, coef = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=out_dtype,
-                                 status=st, return_coef=True)
+                                 status=st, return_coef=True, mode=mode)
         torch.cuda.synchronize()
         assert int(st.item()) == 0
         ey = orc.expert_forward(x, up, dn, w, idx)
@@ -43,8 +49,11 @@ def test_expert_matches_oracle(t, h, n, k):
             assert_close(y, ey, what="bf16 output")
 
 
-def test_expert_residual_and_determinism():
-    from omni_moe_b200.ops import expert_forward
+@pytest.mark.parametrize("mode", ["scheduled", "fused"])
+def test_expert_residual_and_determinism(mode):
+    from functools import partial
+    from omni_moe_b200 import ops
+    expert_forward = partial(ops.expert_forward, mode=mode)
     x, up, dn, w, idx = _inputs(100, 512, 256, 8, 3)
     res = torch.randn(100, 512, generator=gen(4))
     a = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.float32, residual=res.cuda())
@@ -52,18 +61,28 @@ def test_expert_residual_and_determinism():
     assert torch.equal(a, b)  # no atomics: bit-identical from run to run
     assert_close(a, orc.expert_forward(x, up, dn, w, idx) + res, rtol=1e-3, atol=1e-4)
     rb = res.bfloat16()
+    inplace = rb.cuda().clone()   # residual and output may be one buffer
+    from omni_moe_b200 import _lib
+    lib, st = _lib.load(), torch.zeros(1, dtype=torch.int32, device="cuda")
+    xc, uc, dc, wc, ic = x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda()
+    if mode == "fused":
+        _lib.check(lib.omni_expert_fused(xc.data_ptr(), uc.data_ptr(), dc.data_ptr(), wc.data_ptr(), ic.data_ptr(), 100, 8,
+                                         512, 256, inplace.data_ptr(), inplace.data_ptr(), 1, None, st.data_ptr(),
+                                         _lib.stream_ptr()))
+        assert_close(inplace, orc.expert_forward(x, up, dn, w, idx) + rb.float())
     c = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.bfloat16, residual=rb.cuda())
     assert_close(c, orc.expert_forward(x, up, dn, w, idx) + rb.float())
 
 
-def test_expert_skewed_routing():
+@pytest.mark.parametrize("mode", ["scheduled", "fused"])
+def test_expert_skewed_routing(mode):
     # hot experts: thousands of pairs on one expert, duplicates inside tokens
     t, h, n, k = 2048, 256, 4096, 32
     idx = zipf_indices(t, k, n, 1.1, 5)
     x, up, dn, w, _ = _inputs(t, h, n, k, 6)
     w = torch.distributions.Dirichlet(torch.ones(k)).sample((t,))
     from omni_moe_b200.ops import expert_forward
-    y = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.bfloat16)
+    y = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.bfloat16, mode=mode)
     assert_close(y, orc.expert_forward(x, up, dn, w, idx))
 
 
@@ -82,13 +101,14 @@ def test_expert_golden_mirror_and_drop_in(golden_dir):
     assert yb.dtype == torch.bfloat16
 
 
-def test_expert_bad_index_is_reported_not_faulting():
+@pytest.mark.parametrize("mode", ["scheduled", "fused"])
+def test_expert_bad_index_is_reported_not_faulting(mode):
     from omni_moe_b200.ops import expert_forward
     x, up, dn, w, idx = _inputs(16, 64, 32, 4, 8)
     idx[3, 2] = 1000
     idx[5, 0] = -7
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
-    y = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.float32, status=st)
+    y = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), out_dtype=torch.float32, status=st, mode=mode)
     torch.cuda.synchronize()
     assert int(st.item()) & 1
     good = torch.ones(16, dtype=torch.bool)

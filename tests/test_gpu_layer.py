@@ -56,8 +56,10 @@ def test_layer_tiny_golden(golden_dir):
     _compare(m, x, near_tie_budget=0.02)
 
 
-def test_layer_config1_cpu_reference_shape():
+@pytest.mark.parametrize("expert_path", ["fused", "scheduled"])
+def test_layer_config1_cpu_reference_shape(expert_path, monkeypatch):
     from omni_moe.modules.omni_moe import OmniMoE, OmniMoEConfig
+    monkeypatch.setenv("OMNI_MOE_B200_EXPERT", expert_path)  # both routed-expert implementations
     torch.manual_seed(0)
     m = OmniMoE(OmniMoEConfig(256, 1024, "silu", 1024, 8))
     x = torch.randn(2, 256, 256)

@@ -76,3 +76,28 @@ def test_mlp_repeatable():
     a = mlp_forward(x, wg, wu, wd)
     for _ in range(5):
         assert torch.equal(a, mlp_forward(x, wg, wu, wd))
+
+
+@pytest.mark.parametrize("t,h,i,n", [(300, 256, 512, 32), (4096, 1024, 4096, 64), (129, 72, 200, 100), (64, 512, 256, 300)])
+def test_gate_up_with_router_tiles(t, h, i, n):
+    """The fused launch gives the activation of omni_mlp_gate_up and the logits of omni_router_gate."""
+    import torch.nn.functional as F
+    from omni_moe_b200 import _lib
+    g = gen(t + n)
+    x = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
+    wg = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wu = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    kx = (torch.randn(n, h, generator=g) / h ** 0.5).bfloat16()
+    ky = (torch.randn(n, h, generator=g) / h ** 0.5).bfloat16()
+    dev = [v.cuda() for v in (x, wg, wu, kx, ky)]
+    act = torch.full((t, i), float("nan"), device="cuda", dtype=torch.bfloat16)
+    logits = torch.full((t, 2 * n), float("nan"), device="cuda")
+    st = _status()
+    _lib.check(_lib.load().omni_mlp_gate_up_router(*[v.data_ptr() for v in dev], t, h, i, n, act.data_ptr(),
+                                                   logits.data_ptr(), st.data_ptr(), _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    xf = x.float()
+    assert_close(act, F.silu(xf @ wg.float().t()) * (xf @ wu.float().t()), what="activation")
+    ez = torch.cat([orc.router_logits(x, kx), orc.router_logits(x, ky)], 1)
+    assert_close(logits, ez, rtol=1e-4, atol=1e-4, what="router logits")
