@@ -310,7 +310,7 @@ def main():
             "e2e": {"value": tokens_total / (ms_e2e * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": CFG["tokens"] * CFG["hidden"] * 2, "d2h_bytes_per_step": CFG["tokens"] * CFG["hidden"] * 2,
                     "ms_per_step": ms_e2e / args.steps, "pipeline": f"{SLOTS} slots, one stream each"},
-            "gpu_launches": OmniMoE.kernels_per_forward(CFG["experts"], CFG["hidden"]) * args.steps,
+            "gpu_launches": OmniMoE.kernels_per_forward(CFG["experts"], CFG["hidden"], 64, CFG["top_k"]) * args.steps,
             "clocks": clocks,
             "roofline": {"kernel": "gemm_kernel<256, EPI_SWIGLU> (gate/up projections + SwiGLU)", "bound": "tensor",
                          "achieved": achieved, "peak": pk["tf"], "unit": "TFLOP/s", "frac": achieved / pk["tf"],

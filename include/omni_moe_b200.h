@@ -188,6 +188,26 @@ OMNI_API int omni_expert_fused(const void *x, const void *up, const void *down, 
                       int32_t *status, void *stream);
 
 /*
+ * Router selection and routed experts in one kernel, for the same regime as omni_expert_fused
+ * (tables resident in L2): the warp that owns a token applies the BatchNorm fold, the log-softmax
+ * and the product-key top-k to the token's router logits (as omni_router_logits_topk does, same
+ * results) and then gathers the k Up / Down rows.  Replaces, in OmniMoE.forward, router_norm_x/y,
+ * F.log_softmax, triton_omni_router_func, torch.exp and triton_omni_expert_func
+ * (omni_moe/modules/omni_moe.py:70-95).
+ *   logits [T, 2*sqrt_n] fp32 (row stride ld_logits); x, up, down bf16; y [T, H] bf16;
+ *   residual [T, H] bf16 or NULL, may be y itself
+ *   scores, indices (int32), weights [T, k]: the routing that was used, each may be NULL
+ * Limits: hidden % 8 == 0, hidden <= 2048, sqrt_n <= 256, k small enough that the pruned candidate
+ * region has at most 128 cells (k <= 32).
+ */
+OMNI_API int omni_route_expert_fused(const float *logits, int64_t ld_logits,
+                            const float *bn_scale, const float *bn_shift,
+                            const void *x, const void *up, const void *down,
+                            int64_t num_tokens, int sqrt_n, int k, int hidden, int64_t num_experts,
+                            const void *residual, void *y,
+                            float *scores, int32_t *indices, float *weights, void *stream);
+
+/*
  * Shared SwiGLU MLP, y = (silu(x Wg^T) * (x Wu^T)) Wd^T (+ residual), as two tcgen05 GEMMs: the
  * first computes the gate and up projections of a tile side by side and applies silu(g)*u in
  * its epilogue (the [T, I] gate and up activations never reach memory), the second applies the

@@ -40,6 +40,9 @@ SIGNATURES = {
                                     c_int, c_void_p, c_void_p]),
     "omni_expert_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64,
                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "omni_route_expert_fused": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                        c_int, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p]),
     "omni_mlp_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p]),
     "omni_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),

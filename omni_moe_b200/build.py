@@ -27,7 +27,7 @@ def _nvcc() -> str:
 
 def _deps():
     out = [os.path.join(CSRC, s) for s in SOURCES]
-    out.append(os.path.join(CSRC, "common.cuh"))
+    out += [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
     out.append(os.path.join(os.path.dirname(PKG), "include", "omni_moe_b200.h"))
     return out
 

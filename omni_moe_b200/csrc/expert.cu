@@ -10,7 +10,7 @@
 //                       k pairs and accumulates c * Down[e] in fp32 registers, then writes the
 //                       row once.  No atomics, no zero fill, fixed summation order.
 // All row traffic is 128-bit loads, a warp reading 512 contiguous bytes per instruction.
-#include "common.cuh"
+#include "router_select.cuh"
 
 namespace omni {
 namespace {
@@ -189,82 +189,64 @@ __global__ void __launch_bounds__(kThreads) expert_combine_kernel(
 // is scheduled and no coefficient round-trips through memory.  Every row is read k times in total,
 // which is free while both tables live in L2 and wasteful once they do not (then the expert-ordered
 // pair of kernels above reads each Up row from HBM once).
-template <int HV, bool OUT_F32>
-__global__ void __launch_bounds__(kThreads) expert_fused_kernel(
-    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
-    const float* __restrict__ weights, const int* __restrict__ indices, int64_t T, int k, int H, int64_t N,
-    const void* residual, void* y, float* __restrict__ coef, int* status) {
-  const int lane = lane_id();
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
-  if (t >= T) return;
-  const int c0 = lane * 8;
-  uint4 xv[HV];
-#pragma unroll
-  for (int v = 0; v < HV; ++v) {
-    const int col = c0 + v * 256;
-    xv[v] = col < H ? ldg128(x + t * H + col) : make_uint4(0, 0, 0, 0);
-  }
-  float acc[HV][8];
-#pragma unroll
-  for (int v = 0; v < HV; ++v)
-#pragma unroll
-    for (int q = 0; q < 8; ++q) acc[v][q] = 0.f;
-  bool bad = false;
+// Walks up to 32 pairs of one token: lane l carries pair l (expert my_e or -1, routing weight my_w).
+// The Up and Down rows of UNR pairs are in flight at a time; dot, SiLU, weight and the accumulation
+// of c * Down stay in registers.  coef_row, if not null, receives the cnt coefficients.
+template <int HV>
+__device__ __forceinline__ void gather_pairs(int my_e, float my_w, int cnt, int c0, int H, const uint4 (&xv)[HV],
+                                             const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
+                                             float (&acc)[HV][8], float* coef_row) {
   constexpr int UNR = HV >= 8 ? 1 : 2;
-  for (int j0 = 0; j0 < k; j0 += 32) {
-    int my_e = -1;
-    float my_w = 0.f;
-    if (j0 + lane < k) {
-      my_e = indices[t * k + j0 + lane];
-      my_w = weights[t * k + j0 + lane];
-      if (my_e < 0 || my_e >= N) { bad = true; my_e = -1; }
+  const int lane = lane_id();
+  for (int j = 0; j < cnt; j += UNR) {
+    uint4 uv[UNR][HV], dv[UNR][HV];
+    float w[UNR];
+    bool on[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int e = __shfl_sync(FULL_MASK, my_e, (j + u) & 31);
+      w[u] = __shfl_sync(FULL_MASK, my_w, (j + u) & 31);
+      on[u] = (j + u < cnt) && e >= 0;
+#pragma unroll
+      for (int v = 0; v < HV; ++v) {
+        const int col = c0 + v * 256;
+        const bool ld = on[u] && col < H;
+        uv[u][v] = ld ? ldg128(up + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+        dv[u][v] = ld ? ldg128(down + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+      }
     }
-    const int cnt = min(32, k - j0);
-    for (int j = 0; j < cnt; j += UNR) {
-      uint4 uv[UNR][HV], dv[UNR][HV];
-      float w[UNR];
-      bool on[UNR];
+    float dot[UNR];
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int e = __shfl_sync(FULL_MASK, my_e, (j + u) & 31);
-        w[u] = __shfl_sync(FULL_MASK, my_w, (j + u) & 31);
-        on[u] = (j + u < cnt) && e >= 0;
+    for (int u = 0; u < UNR; ++u) {
+      dot[u] = 0.f;
 #pragma unroll
-        for (int v = 0; v < HV; ++v) {
-          const int col = c0 + v * 256;
-          const bool ld = on[u] && col < H;
-          uv[u][v] = ld ? ldg128(up + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
-          dv[u][v] = ld ? ldg128(down + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
-        }
-      }
-      float dot[UNR];
+      for (int v = 0; v < HV; ++v) dot[u] = dot8(xv[v], uv[u][v], dot[u]);
+    }
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        dot[u] = 0.f;
+    for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-        for (int v = 0; v < HV; ++v) dot[u] = dot8(xv[v], uv[u][v], dot[u]);
-      }
+      for (int u = 0; u < UNR; ++u) dot[u] += __shfl_xor_sync(FULL_MASK, dot[u], o);
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1)
+    for (int u = 0; u < UNR; ++u) {
+      const float c = on[u] ? w[u] * silu(dot[u]) : 0.f;
+      if (coef_row && lane == 0 && j + u < cnt) coef_row[j + u] = c;
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) dot[u] += __shfl_xor_sync(FULL_MASK, dot[u], o);
+      for (int v = 0; v < HV; ++v) {
+        const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv[u][v]);
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const float c = on[u] ? w[u] * silu(dot[u]) : 0.f;
-        if (coef && lane == 0 && j + u < cnt) coef[t * k + j0 + j + u] = c;
-#pragma unroll
-        for (int v = 0; v < HV; ++v) {
-          const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv[u][v]);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 f = bf16x2_to_float2(pd[q]);
-            acc[v][2 * q] = __fmaf_rn(c, f.x, acc[v][2 * q]);
-            acc[v][2 * q + 1] = __fmaf_rn(c, f.y, acc[v][2 * q + 1]);
-          }
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = bf16x2_to_float2(pd[q]);
+          acc[v][2 * q] = __fmaf_rn(c, f.x, acc[v][2 * q]);
+          acc[v][2 * q + 1] = __fmaf_rn(c, f.y, acc[v][2 * q + 1]);
         }
       }
     }
   }
+}
+
+// Adds the optional residual row and writes one output row (fp32 or bf16).
+template <int HV, bool OUT_F32>
+__device__ __forceinline__ void store_row(float (&acc)[HV][8], int64_t t, int c0, int H, const void* residual, void* y) {
 #pragma unroll
   for (int v = 0; v < HV; ++v) {
     const int col = c0 + v * 256;
@@ -302,7 +284,88 @@ __global__ void __launch_bounds__(kThreads) expert_fused_kernel(
       *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(y) + o) = o4;
     }
   }
+}
+
+template <int HV>
+__device__ __forceinline__ void load_x_row(const __nv_bfloat16* __restrict__ x, int64_t t, int c0, int H, uint4 (&xv)[HV],
+                                           float (&acc)[HV][8]) {
+#pragma unroll
+  for (int v = 0; v < HV; ++v) {
+    const int col = c0 + v * 256;
+    xv[v] = col < H ? ldg128(x + t * H + col) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[v][q] = 0.f;
+  }
+}
+
+template <int HV, bool OUT_F32>
+__global__ void __launch_bounds__(kThreads) expert_fused_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
+    const float* __restrict__ weights, const int* __restrict__ indices, int64_t T, int k, int H, int64_t N,
+    const void* residual, void* y, float* __restrict__ coef, int* status) {
+  const int lane = lane_id();
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int c0 = lane * 8;
+  uint4 xv[HV];
+  float acc[HV][8];
+  load_x_row<HV>(x, t, c0, H, xv, acc);
+  bool bad = false;
+  for (int j0 = 0; j0 < k; j0 += 32) {
+    int my_e = -1;
+    float my_w = 0.f;
+    if (j0 + lane < k) {
+      my_e = indices[t * k + j0 + lane];
+      my_w = weights[t * k + j0 + lane];
+      if (my_e < 0 || my_e >= N) { bad = true; my_e = -1; }
+    }
+    gather_pairs<HV>(my_e, my_w, min(32, k - j0), c0, H, xv, up, down, acc, coef ? coef + t * k + j0 : nullptr);
+  }
+  store_row<HV, OUT_F32>(acc, t, c0, H, residual, y);
   if (bad && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
+// Router selection and routed experts in one kernel: the warp that owns a token first picks its k
+// experts from the token's router logits (BatchNorm fold, log-softmax, product-key top-k: see
+// router_select.cuh) and then gathers their rows.  The selection is arithmetic on a few hundred
+// values and runs in the shadow of other warps' row gathers, so it costs no extra pass over
+// memory and no launch.  Lane r % 32 ends the selection holding rank r, which is exactly the
+// layout gather_pairs wants.
+template <int HV, int VPL, int CPL>
+__global__ void __launch_bounds__(kThreads, HV <= 4 ? 2 : 1) expert_routed_kernel(
+    const sel::TopkArgs a, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up,
+    const __nv_bfloat16* __restrict__ down, int H, int64_t N, const void* residual, void* y) {
+  __shared__ sel::WarpScratch<VPL, CPL> s_warp[kWarps];
+  __shared__ sel::RegionTable s_region;
+  sel::build_region_table(s_region, a.kk, a.k, kWarps);
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (t >= a.T) return;
+  const int c0 = lane * 8, k = a.k;
+  uint4 xv[HV];
+  float acc[HV][8];
+  load_x_row<HV>(x, t, c0, H, xv, acc);  // in flight during the selection
+  uint32_t rkey[sel::kMaxK / 32], rflat[sel::kMaxK / 32];
+  sel::select_token<VPL, CPL, true>(a, t, s_warp[warp], s_region.cell, rkey, rflat);
+#pragma unroll
+  for (int s = 0; s < sel::kMaxK / 32; ++s) {
+    if (s * 32 >= k) break;
+    const int r = s * 32 + lane;
+    int my_e = -1;
+    float my_w = 0.f;
+    if (r < k) {
+      const float sc = key_to_float(rkey[s]);
+      my_w = expf(sc);
+      my_e = static_cast<int>(rflat[s]);  // < sqrt_n^2 <= N by construction
+      const int64_t o = t * k + r;
+      if (a.scores) a.scores[o] = sc;
+      if (a.indices) reinterpret_cast<int32_t*>(a.indices)[o] = my_e;
+      if (a.weights) a.weights[o] = my_w;
+      if (my_e >= N) my_e = -1;
+    }
+    gather_pairs<HV>(my_e, my_w, min(32, k - s * 32), c0, H, xv, up, down, acc, nullptr);
+  }
+  store_row<HV, false>(acc, t, c0, H, residual, y);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -401,4 +464,54 @@ extern "C" int omni_expert_fused(const void* x, const void* up, const void* down
   else OMNI_FUSED(8);
 #undef OMNI_FUSED
   return check_launch("expert_fused_kernel");
+}
+
+extern "C" int omni_route_expert_fused(const float* logits, int64_t ld_logits, const float* bn_scale,
+                                       const float* bn_shift, const void* x, const void* up, const void* down,
+                                       int64_t num_tokens, int sqrt_n, int k, int hidden, int64_t num_experts,
+                                       const void* residual, void* y, float* scores, int32_t* indices,
+                                       float* weights, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && hidden >= 8 && hidden % 8 == 0 && hidden <= 2048,
+               "hidden must be a multiple of 8 in [8, 2048], got %d", hidden);
+  OMNI_REQUIRE(sqrt_n >= 1 && sqrt_n <= 256, "omni_route_expert_fused: sqrt_n must be in [1, 256], got %d", sqrt_n);
+  OMNI_REQUIRE(k >= 1 && static_cast<int64_t>(k) <= static_cast<int64_t>(sqrt_n) * sqrt_n, "k out of range: %d", k);
+  OMNI_REQUIRE(static_cast<int64_t>(sqrt_n) * sqrt_n <= num_experts, "the tables have fewer than sqrt_n^2 rows");
+  OMNI_REQUIRE(ld_logits >= 2 * sqrt_n, "ld_logits %lld < 2*sqrt_n", static_cast<long long>(ld_logits));
+  OMNI_REQUIRE((bn_scale == nullptr) == (bn_shift == nullptr), "bn_scale and bn_shift must be given together");
+  sel::TopkArgs a{};
+  a.in_x = logits, a.in_dtype = OMNI_F32, a.ld_in = ld_logits, a.bn_scale = bn_scale, a.bn_shift = bn_shift;
+  a.T = num_tokens, a.n = sqrt_n, a.k = k, a.kk = sqrt_n < k ? sqrt_n : k;
+  a.cells = sel::region_cells(a.kk, k);
+  a.scores = scores, a.indices = indices, a.idx_is_i64 = 0, a.weights = weights;
+  OMNI_REQUIRE(a.cells <= 128, "omni_route_expert_fused: k = %d needs %d candidate cells, more than this kernel holds "
+               "(use omni_router_logits_topk + omni_expert_fused)", k, a.cells);
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(logits && x && up && down && y, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(up) && aligned16(down) && aligned16(y) && aligned16(residual),
+               "x, up, down, y and residual must be 16-byte aligned");
+  const auto* xb = static_cast<const __nv_bfloat16*>(x);
+  const auto* ub = static_cast<const __nv_bfloat16*>(up);
+  const auto* db = static_cast<const __nv_bfloat16*>(down);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
+#define OMNI_ROUTED(HV, VPL, CPL) \
+  expert_routed_kernel<HV, VPL, CPL><<<grid, kThreads, 0, st>>>(a, xb, ub, db, hidden, num_experts, residual, y)
+#define OMNI_ROUTED_HV(VPL, CPL)                  \
+  do {                                            \
+    if (hidden <= 256) OMNI_ROUTED(1, VPL, CPL);  \
+    else if (hidden <= 512) OMNI_ROUTED(2, VPL, CPL);  \
+    else if (hidden <= 1024) OMNI_ROUTED(4, VPL, CPL); \
+    else OMNI_ROUTED(8, VPL, CPL);                \
+  } while (0)
+  const bool small_cells = a.cells <= 64;
+  if (sqrt_n <= 64) {
+    if (small_cells) OMNI_ROUTED_HV(2, 2);
+    else OMNI_ROUTED_HV(2, 4);
+  } else {
+    if (small_cells) OMNI_ROUTED_HV(8, 2);
+    else OMNI_ROUTED_HV(8, 4);
+  }
+#undef OMNI_ROUTED_HV
+#undef OMNI_ROUTED
+  return check_launch("expert_routed_kernel");
 }

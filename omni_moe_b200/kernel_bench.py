@@ -1,0 +1,198 @@
+"""Per-kernel timings of the layer's stages against their rooflines.
+
+    python -m omni_moe_b200.kernel_bench [--config c2|c3|c4|c5|all] [--reps N]
+
+For each stage of a configuration the script launches the kernel through the C ABI inside a CUDA
+graph (several launches per replay, so host launch cost does not count), times replays with CUDA
+events and prints one JSON line: microseconds per launch, the algorithmic work of the launch and
+the fraction of the measured peak (HBM copy bandwidth or bf16 tensor throughput from
+MEASURED_PEAKS.json at the repository root; a stated fallback if the file is absent).
+
+Configurations (synthetic data, seeded):
+  c2  quick-start layer: T 4096, H 1024, I 4096, 64x64 experts, k 16
+  c3  router microbench: T 16384, H 2048, 256x256 experts, k 16
+  c4  skewed expert stress: T 32768, H 2048, 512x512 experts, k 32, Zipf(1.1) routing
+  c5  large table: T 65536, H 4096, I 11008, 1024x1024 experts, k 64 (needs ~25 GB of device memory)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import _lib
+from .ops.scheduler import workspace_bytes
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CONFIGS = {
+    "c2": dict(T=4096, H=1024, I=4096, n=64, k=16, zipf=None),
+    "c3": dict(T=16384, H=2048, I=0, n=256, k=16, zipf=None),
+    "c4": dict(T=32768, H=2048, I=0, n=512, k=32, zipf=1.1),
+    "c5": dict(T=65536, H=4096, I=11008, n=1024, k=64, zipf=None),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _randn_bf16(shape, std, dev, seed):
+    """Large bf16 normal tensors, generated on the device in slabs to bound temporary memory."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    out = torch.empty(shape, device=dev, dtype=torch.bfloat16)
+    rows = shape[0]
+    step = max(1, (64 << 20) // max(1, shape[1]))
+    for s in range(0, rows, step):
+        e = min(rows, s + step)
+        out[s:e] = (torch.randn((e - s, shape[1]), device=dev, generator=g) * std).to(torch.bfloat16)
+    return out
+
+
+def _zipf_indices(t, k, n_experts, s, seed, dev):
+    rng = np.random.default_rng(seed)
+    p = np.arange(1, n_experts + 1, dtype=np.float64) ** (-s)
+    cdf = np.cumsum(p / p.sum())
+    u = rng.random((t, k))
+    return torch.from_numpy(np.minimum(np.searchsorted(cdf, u), n_experts - 1).astype(np.int32)).to(dev)
+
+
+def time_graph(fn, launches=4, reps=10):
+    """Microseconds per launch of `fn(stream_ptr)`, measured over graph replays."""
+    fn(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(launches):
+                fn(s.cuda_stream)
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b) * 1e3 / launches)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def run_config(name: str, reps: int):
+    c = CONFIGS[name]
+    T, H, I, n, k = c["T"], c["H"], c["I"], c["n"], c["k"]
+    N, P = n * n, T * k
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hbm, tf, src = peaks()
+    lib = _lib.load()
+    chk = _lib.check
+    i32 = dict(device=dev, dtype=torch.int32)
+    f32 = dict(device=dev, dtype=torch.float32)
+    status = torch.zeros(1, **i32)
+    x = _randn_bf16((T, H), 1.0, dev, 0)
+    kx = _randn_bf16((n, H), H ** -0.5, dev, 1)
+    ky = _randn_bf16((n, H), H ** -0.5, dev, 2)
+    logits = torch.empty((T, 2 * n), **f32)
+    scores, weights = torch.empty((T, k), **f32), torch.empty((T, k), **f32)
+    indices = torch.empty((T, k), **i32)
+    out = []
+
+    def report(stage, us, bound, work, note=""):
+        if bound == "hbm":
+            ach = work / (us * 1e-6) / 1e9
+            line = dict(config=name, stage=stage, us=round(us, 2), bound="hbm", algorithmic_bytes=int(work),
+                        achieved_gbs=round(ach, 1), peak_gbs=hbm, frac=round(ach / hbm, 3))
+        else:
+            ach = work / (us * 1e-6) / 1e12
+            line = dict(config=name, stage=stage, us=round(us, 2), bound="tensor", flops=int(work),
+                        achieved_tflops=round(ach, 1), peak_tflops=tf, frac=round(ach / tf, 3))
+        line["peak_source"] = src
+        if note:
+            line["note"] = note
+        print(json.dumps(line), flush=True)
+        out.append(line)
+
+    # ---- router gates (tensor) -----------------------------------------------------------------
+    us = time_graph(lambda s: chk(lib.omni_router_gate(x.data_ptr(), kx.data_ptr(), ky.data_ptr(), T, H, n,
+                                                       logits.data_ptr(), status.data_ptr(), s)), reps=reps)
+    report("router_gate_gemm", us, "tensor", 4.0 * T * H * n)
+    # ---- BatchNorm / log-softmax / top-k (hbm) -------------------------------------------------
+    us = time_graph(lambda s: chk(lib.omni_router_logits_topk(logits.data_ptr(), 2 * n, None, None, T, n, k,
+                                                              scores.data_ptr(), indices.data_ptr(), 0,
+                                                              weights.data_ptr(), None, s)), reps=reps)
+    report("router_logits_topk", us, "hbm", 2.0 * T * n * 4 + T * k * 12)
+    # ---- routing for the expert stages ----------------------------------------------------------
+    if c["zipf"]:
+        indices.copy_(_zipf_indices(T, k, N, c["zipf"], 0, dev))
+        weights.copy_(torch.distributions.Dirichlet(torch.ones(k)).sample((T,)).to(dev))
+    U = int(torch.unique(indices).numel())
+    # ---- scheduling (hbm) ---------------------------------------------------------------------
+    ws = torch.empty(workspace_bytes(P, N), device=dev, dtype=torch.uint8)
+    perm, sorted_e = torch.empty(P, **i32), torch.empty(P, **i32)
+    meta = torch.zeros(4, **i32)
+    us = time_graph(lambda s: chk(lib.omni_schedule(indices.data_ptr(), 0, None, 0, T, k, N, perm.data_ptr(),
+                                                    sorted_e.data_ptr(), None, None, None, None, meta.data_ptr(),
+                                                    ws.data_ptr(), ws.numel(), s)), reps=reps)
+    report("schedule_permutation", us, "hbm", 20.0 * P + 8.0 * N, "bytes per the full description (20 P + 8 N)")
+    # ---- routed experts (hbm): algorithmic bytes = x in, y out, each touched Up/Down row once, schedule arrays
+    up = _randn_bf16((N, H), 0.02, dev, 3)
+    down = _randn_bf16((N, H), 0.02, dev, 4)
+    coef = torch.empty((T, k), **f32)
+    y = torch.empty((T, H), device=dev, dtype=torch.bfloat16)
+    alg = 4.0 * T * H + 4.0 * U * H + 12.0 * P
+    us_c = time_graph(lambda s: chk(lib.omni_expert_coef(x.data_ptr(), up.data_ptr(), weights.data_ptr(), perm.data_ptr(),
+                                                         sorted_e.data_ptr(), T, k, H, N, coef.data_ptr(),
+                                                         status.data_ptr(), s)), reps=reps)
+    us_b = time_graph(lambda s: chk(lib.omni_expert_combine(down.data_ptr(), coef.data_ptr(), indices.data_ptr(), T, k, H, N,
+                                                            None, y.data_ptr(), _lib.OMNI_BF16, status.data_ptr(), s)),
+                      reps=reps)
+    report("expert_coef", us_c, "hbm", 2.0 * T * H + 2.0 * U * H + 12.0 * P, f"U={U} distinct experts")
+    report("expert_combine", us_b, "hbm", 2.0 * T * H + 2.0 * U * H + 8.0 * P)
+    report("expert_coef+combine", us_c + us_b, "hbm", alg, f"gather traffic through L2: {2.0 * P * H * 2 / 2**30:.2f} GiB")
+    if H <= 2048:
+        us = time_graph(lambda s: chk(lib.omni_expert_fused(x.data_ptr(), up.data_ptr(), down.data_ptr(), weights.data_ptr(),
+                                                            indices.data_ptr(), T, k, H, N, None, y.data_ptr(),
+                                                            _lib.OMNI_BF16, None, status.data_ptr(), s)), reps=reps)
+        report("expert_fused", us, "hbm", alg - 12.0 * P + 8.0 * P)
+    # ---- shared MLP (tensor) --------------------------------------------------------------------
+    if I:
+        wg = _randn_bf16((I, H), H ** -0.5, dev, 5)
+        wu = _randn_bf16((I, H), H ** -0.5, dev, 6)
+        wd = _randn_bf16((H, I), I ** -0.5, dev, 7)
+        act = torch.empty((T, I), device=dev, dtype=torch.bfloat16)
+        us = time_graph(lambda s: chk(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), T, H, I,
+                                                           act.data_ptr(), status.data_ptr(), s)), reps=reps)
+        report("mlp_gate_up_swiglu", us, "tensor", 4.0 * T * H * I)
+        us = time_graph(lambda s: chk(lib.omni_mlp_down(act.data_ptr(), wd.data_ptr(), T, H, I, None, y.data_ptr(),
+                                                        status.data_ptr(), s)), reps=reps)
+        report("mlp_down", us, "tensor", 2.0 * T * H * I)
+    torch.cuda.synchronize()
+    if int(status.item()) or int(meta[2].item()):
+        raise RuntimeError("a kernel reported a device-side fault: " + _lib.status_message(int(status.item()) | int(meta[2].item())))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--config", default="c2", choices=[*CONFIGS, "all"])
+    ap.add_argument("--reps", type=int, default=10)
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("kernel_bench needs a CUDA device")
+    for name in (CONFIGS if args.config == "all" else [args.config]):
+        run_config(name, args.reps)
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

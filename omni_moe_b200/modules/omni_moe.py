@@ -4,11 +4,11 @@ Constructor, parameter / buffer names and shapes, and ``forward(hidden_states)``
 reference module (omni_moe/modules/omni_moe.py:14-106), so a reference ``state_dict`` loads
 unchanged.  Forward only.
 
-One eval forward is five kernels (eight to ten when the expert tables are too large for L2 and the
+One eval forward is four kernels (five when the router shape exceeds the fused kernel's limits, eight to ten when the expert tables are too large for L2 and the
 pairs are scheduled by expert first), enqueued without a host synchronisation:
 
     main stream   gate/up GEMM + SwiGLU -> down GEMM ........................ -> routed experts (+= y)
-    side stream                            router gate GEMM -> BN/log-softmax/top-k
+    side stream                            router gate GEMM                        (selection happens inside the expert kernel)
 
 The gate/up GEMM and the expert kernel fill the GPU on their own.  The down projection of the
 quick-start shape occupies 128 of the 148 SMs, so the two small router kernels run beside it.
@@ -21,7 +21,7 @@ import torch
 import torch.nn as nn
 
 from .. import _lib
-from ..ops.expert import use_fused_path
+from ..ops.expert import use_fused_path, use_routed_kernel
 from ..ops.scheduler import workspace_bytes
 
 
@@ -157,15 +157,17 @@ class OmniMoE(nn.Module):
         # 1. gate/up projections + SwiGLU: fills every SM
         chk(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, b.act.data_ptr(), status, st))
         b.ev_fork.record(main)
-        # 2. side stream: router gates -> BatchNorm + log-softmax + product-key top-k.  Small kernels
-        #    that run on the SMs the down projection leaves free (and next to its CTAs).
+        # 2. side stream: router gate GEMM.  It runs on the SMs the down projection leaves free.
+        routed = use_routed_kernel(self.num_experts, h, n, k)
         with torch.cuda.stream(b.side):
             b.side.wait_event(b.ev_fork)
             ss = b.side.cuda_stream
             chk(lib.omni_router_gate(x.data_ptr(), kx.data_ptr(), ky.data_ptr(), t, h, n, b.logits.data_ptr(), status, ss))
             scale, shift = self._bn_fold_train(b.logits) if self.training else self._bn_fold_eval()
-            chk(lib.omni_router_logits_topk(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
-                                            b.scores.data_ptr(), b.indices.data_ptr(), 0, b.weights.data_ptr(), None, ss))
+            if not routed:
+                chk(lib.omni_router_logits_topk(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
+                                                b.scores.data_ptr(), b.indices.data_ptr(), 0, b.weights.data_ptr(),
+                                                None, ss))
             b.ev_join.record(b.side)
             if record_streams:
                 for tns in (x, kx, ky, scale, shift):
@@ -174,8 +176,14 @@ class OmniMoE(nn.Module):
         chk(lib.omni_mlp_down(b.act.data_ptr(), wd.data_ptr(), t, h, i, None, y.data_ptr(), status, st))
         main.wait_event(b.ev_join)
         # 4. routed experts, added onto y in place
-        if use_fused_path(self.num_experts, h):
-            # tables resident in L2: one token-centric kernel, no scheduling pass
+        if routed:
+            # tables resident in L2: BatchNorm / log-softmax / top-k and the row gathers in one
+            # token-centric kernel
+            chk(lib.omni_route_expert_fused(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), x.data_ptr(),
+                                            up_t.data_ptr(), down_t.data_ptr(), t, n, k, h, self.num_experts,
+                                            y.data_ptr(), y.data_ptr(), b.scores.data_ptr(), b.indices.data_ptr(),
+                                            b.weights.data_ptr(), st))
+        elif use_fused_path(self.num_experts, h):
             chk(lib.omni_expert_fused(x.data_ptr(), up_t.data_ptr(), down_t.data_ptr(), b.weights.data_ptr(),
                                       b.indices.data_ptr(), t, k, h, self.num_experts, y.data_ptr(), y.data_ptr(),
                                       _lib.OMNI_BF16, None, status, st))
@@ -193,8 +201,10 @@ class OmniMoE(nn.Module):
         self.last_status = b.status
 
     @staticmethod
-    def kernels_per_forward(num_experts: int, hidden: int) -> int:
+    def kernels_per_forward(num_experts: int, hidden: int, sqrt_n: int = 0, k: int = 0) -> int:
         """Kernels of this library launched by one eval forward."""
+        if sqrt_n and use_routed_kernel(num_experts, hidden, sqrt_n, k):
+            return 4  # gate/up, router gates, down projection, router selection + experts
         if use_fused_path(num_experts, hidden):
             return 5  # gate/up, router gates, top-k, down projection, fused experts
         bits = max(1, (num_experts - 1).bit_length())

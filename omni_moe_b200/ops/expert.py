@@ -25,6 +25,48 @@ def use_fused_path(num_experts: int, hidden: int) -> bool:
     return 2 * num_experts * hidden * 2 <= L2_RESIDENT_TABLE_BYTES
 
 
+def region_cells(sqrt_n: int, k: int) -> int:
+    """Cells of the pruned candidate region of the router search: (i+1)(j+1) <= k in rank space."""
+    kk = min(sqrt_n, k)
+    return sum(min(kk, k // (i + 1)) for i in range(kk))
+
+
+def use_routed_kernel(num_experts: int, hidden: int, sqrt_n: int, k: int) -> bool:
+    """True when router selection and routed experts can run as the single fused kernel
+    (``omni_route_expert_fused``): the fused-expert regime plus its limits on the router shape."""
+    return (use_fused_path(num_experts, hidden) and sqrt_n <= 256 and 1 <= k <= sqrt_n * sqrt_n
+            and sqrt_n * sqrt_n <= num_experts and region_cells(sqrt_n, k) <= 128)
+
+
+def route_expert_fused(logits: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor, k: int,
+                       bn_scale: torch.Tensor | None = None, bn_shift: torch.Tensor | None = None,
+                       residual: torch.Tensor | None = None, return_routing: bool = True):
+    """Router selection from ``logits [T, 2*sqrt_n]`` (fp32) and the routed-expert sum in one kernel.
+
+    Returns ``y [T, H]`` bf16 (``residual`` added if given) and, if ``return_routing``,
+    ``(scores, indices, weights)`` as :func:`omni_moe_b200.ops.router_gate_topk` would give them.
+    """
+    _lib.require_cuda(logits, x, up_weight, down_weight)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
+    assert x.dtype == up_weight.dtype == down_weight.dtype == torch.bfloat16
+    x, up_weight, down_weight = x.contiguous(), up_weight.contiguous(), down_weight.contiguous()
+    t, h = x.shape
+    n = logits.size(1) // 2
+    dev = x.device
+    y = torch.empty((t, h), device=dev, dtype=torch.bfloat16)
+    if residual is not None:
+        assert residual.shape == y.shape and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+    scores = torch.empty((t, k), device=dev, dtype=torch.float32) if return_routing else None
+    indices = torch.empty((t, k), device=dev, dtype=torch.int32) if return_routing else None
+    weights = torch.empty((t, k), device=dev, dtype=torch.float32) if return_routing else None
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().omni_route_expert_fused(
+            logits.data_ptr(), logits.size(1), _lib.ptr(bn_scale), _lib.ptr(bn_shift), x.data_ptr(),
+            up_weight.data_ptr(), down_weight.data_ptr(), t, n, k, h, up_weight.size(0), _lib.ptr(residual),
+            y.data_ptr(), _lib.ptr(scores), _lib.ptr(indices), _lib.ptr(weights), _lib.stream_ptr()))
+    return (y, scores, indices, weights) if return_routing else y
+
+
 def expert_forward(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor, weights: torch.Tensor,
                    indices: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                    residual: torch.Tensor | None = None, status: torch.Tensor | None = None,

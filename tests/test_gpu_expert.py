@@ -135,3 +135,42 @@ def test_expert_stress_shape_properties():
     sel = torch.arange(0, t, 64)
     ey = orc.expert_forward(x[sel], up, dn, w[sel], idx[sel])
     assert_close(y1[sel.cuda()], ey, rtol=1e-3, atol=1e-4)
+
+
+@pytest.mark.parametrize("t,h,n,k", [(300, 256, 32, 8), (257, 1024, 64, 16), (100, 512, 100, 24), (64, 2048, 16, 32),
+                                       (130, 72, 200, 2), (50, 128, 8, 30)])
+def test_routed_kernel_equals_separate_router_and_expert_kernels(t, h, n, k):
+    """omni_route_expert_fused = omni_router_logits_topk followed by omni_expert_fused, bit for bit."""
+    from omni_moe_b200 import _lib
+    from omni_moe_b200.ops import expert_forward, route_expert_fused
+    g = gen(t + n + k)
+    N = n * n
+    x = (torch.randn(t, h, generator=g) * 0.5).bfloat16().cuda()
+    up = (torch.randn(N, h, generator=g) * 0.1).bfloat16().cuda()
+    dn = (torch.randn(N, h, generator=g) * 0.1).bfloat16().cuda()
+    logits = torch.randn(t, 2 * n, generator=g).cuda()
+    logits[::7] = 0.0  # some tokens where every score ties: exercises the exact re-scan inside the fused kernel
+    scale = (torch.rand(2 * n, generator=g) + 0.5).cuda()
+    shift = (torch.randn(2 * n, generator=g) * 0.1).cuda()
+    res = torch.randn(t, h, generator=g).bfloat16().cuda()
+    lib = _lib.load()
+    sc = torch.empty(t, k, device="cuda")
+    idx = torch.empty(t, k, device="cuda", dtype=torch.int32)
+    w = torch.empty(t, k, device="cuda")
+    lp = torch.empty(t, 2 * n, device="cuda")
+    _lib.check(lib.omni_router_logits_topk(logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
+                                           sc.data_ptr(), idx.data_ptr(), 0, w.data_ptr(), lp.data_ptr(), _lib.stream_ptr()))
+    y_ref = expert_forward(x, up, dn, w, idx, out_dtype=torch.bfloat16, residual=res, mode="fused")
+    y, sc2, idx2, w2 = route_expert_fused(logits, x, up, dn, k, scale, shift, residual=res)
+    torch.cuda.synchronize()
+    assert torch.equal(idx2, idx) and torch.equal(sc2, sc) and torch.equal(w2, w)
+    assert torch.equal(y, y_ref)
+    # and the selection is the oracle's, given the log-probs the kernel computed
+    es, ei = orc.router_topk(lp[:, :n].cpu().contiguous(), lp[:, n:].cpu().contiguous(), n, k)
+    np.testing.assert_array_equal(idx2.cpu().numpy(), ei)
+    # in place
+    y_in = res.clone()
+    _lib.check(lib.omni_route_expert_fused(logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), x.data_ptr(),
+                                           up.data_ptr(), dn.data_ptr(), t, n, k, h, N, y_in.data_ptr(), y_in.data_ptr(),
+                                           None, None, None, _lib.stream_ptr()))
+    assert torch.equal(y_in, y_ref)
