@@ -43,37 +43,91 @@ __device__ __forceinline__ float load_as_float(const void* base, int dtype, int6
   return __half2float(reinterpret_cast<const __half*>(base)[i]);
 }
 
-// Extracts the kk largest of a row spread over the warp (element e of lane l is sub-key e*32+l;
-// key 0 marks "absent").  Writes sorted scores and sub-key indices to shared memory.
-template <int VPL>
-__device__ __forceinline__ void axis_select(uint32_t (&key)[VPL], int kk, float* s_out, int* i_out) {
+// Sorted top-K of the E * 32 entries a warp holds in registers (entry = 32-bit key, larger wins, and a
+// 32-bit id that is unique among the entries, smaller wins on equal keys; key 0 = absent).
+//   1. radix select: a bitwise search for the K-th largest key tau (per step every lane counts its
+//      entries >= trial, one warp reduction adds the counts); only the bits in which the largest and
+//      the smallest key differ are searched;
+//   2. entries equal to tau are admitted by ascending id until K entries are in (a second bitwise
+//      search, on the ids, only when more entries tie at tau than there is room for);
+//   3. the K admitted entries are compacted into shared memory and ranked by counting.
+// out_key[r], out_id[r] receive rank r (AS_FLOAT: the key converted back to its float).
+template <int E, bool AS_FLOAT>
+__device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], const uint32_t (&id)[E], int K,
+                                                   unsigned long long* s_tmp /*[kMaxK]*/, uint32_t* out_key,
+                                                   uint32_t* out_id) {
   const int lane = lane_id();
-  uint32_t lmax = 0;
+  uint32_t kmax = 0, kmin = 0xffffffffu;
 #pragma unroll
-  for (int e = 0; e < VPL; ++e) lmax = max(lmax, key[e]);
-  for (int r = 0; r < kk; ++r) {
-    const uint32_t m = __reduce_max_sync(FULL_MASK, lmax);
-    uint32_t mine = 0xffffffffu;
-    if (lmax == m) {
-#pragma unroll
-      for (int e = VPL - 1; e >= 0; --e)
-        if (key[e] == m) mine = e * 32 + lane;
-    }
-    const uint32_t w = __reduce_min_sync(FULL_MASK, mine);
-    if (lane == 0) {
-      s_out[r] = key_to_float(m);
-      i_out[r] = static_cast<int>(w);
-    }
-    if ((w & 31u) == static_cast<uint32_t>(lane)) {
-      lmax = 0;
-#pragma unroll
-      for (int e = 0; e < VPL; ++e) {
-        if (e == static_cast<int>(w >> 5)) key[e] = 0;
-        lmax = max(lmax, key[e]);
-      }
-    }
-    __syncwarp();
+  for (int e = 0; e < E; ++e) {
+    kmax = max(kmax, key[e]);
+    if (key[e]) kmin = min(kmin, key[e]);
   }
+  kmax = __reduce_max_sync(FULL_MASK, kmax);
+  kmin = __reduce_min_sync(FULL_MASK, kmin);
+  const uint32_t diff = kmax ^ kmin;
+  uint32_t tau = kmax;
+  if (diff) {
+    const int hb = 31 - __clz(diff);  // highest bit in which present keys differ
+    tau = hb == 31 ? 0u : (kmax >> (hb + 1)) << (hb + 1);
+    for (int bit = hb; bit >= 0; --bit) {
+      const uint32_t trial = tau | (1u << bit);
+      int c = 0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) c += key[e] >= trial;
+      if (__reduce_add_sync(FULL_MASK, c) >= K) tau = trial;
+    }
+  }
+  int c_gt = 0, c_eq = 0;
+#pragma unroll
+  for (int e = 0; e < E; ++e) c_gt += key[e] > tau, c_eq += key[e] == tau;
+  c_gt = __reduce_add_sync(FULL_MASK, c_gt);
+  c_eq = __reduce_add_sync(FULL_MASK, c_eq);
+  const int room = K - c_gt;  // entries equal to tau that are admitted (>= 1)
+  uint32_t id_thr = 0xffffffffu;
+  if (c_eq > room) {
+    uint32_t lo = 0;  // becomes the room-th smallest id among the ties
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t trial = lo | (1u << bit);
+      int c = 0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) c += (key[e] == tau) && (id[e] < trial);
+      if (__reduce_add_sync(FULL_MASK, c) < room) lo = trial;
+    }
+    id_thr = lo;
+  }
+  const unsigned lt_mask = (1u << lane) - 1u;
+  int base = 0;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const bool in = key[e] > tau || (key[e] == tau && id[e] <= id_thr);
+    const unsigned m = __ballot_sync(FULL_MASK, in);
+    if (in) s_tmp[base + __popc(m & lt_mask)] = (static_cast<unsigned long long>(key[e]) << 32) | (0xffffffffu - id[e]);
+    base += __popc(m);
+  }
+  __syncwarp();
+  unsigned long long mine[kMaxK / 32];
+  int rank[kMaxK / 32];
+#pragma unroll
+  for (int q = 0; q < kMaxK / 32; ++q) {
+    const int r = q * 32 + lane;
+    mine[q] = r < K ? s_tmp[r] : 0ull;
+    rank[q] = 0;
+  }
+  for (int j = 0; j < K; ++j) {
+    const unsigned long long o = s_tmp[j];
+#pragma unroll
+    for (int q = 0; q < kMaxK / 32; ++q) rank[q] += o > mine[q];
+  }
+#pragma unroll
+  for (int q = 0; q < kMaxK / 32; ++q) {
+    if (q * 32 + lane < K) {
+      const uint32_t kq = static_cast<uint32_t>(mine[q] >> 32);
+      out_key[rank[q]] = AS_FLOAT ? __float_as_uint(key_to_float(kq)) : kq;
+      out_id[rank[q]] = 0xffffffffu - static_cast<uint32_t>(mine[q]);
+    }
+  }
+  __syncwarp();
 }
 
 // Small rows (at most 64 entries, two per lane): rank every entry by counting the entries that beat
@@ -95,9 +149,9 @@ __device__ __forceinline__ int rank_among_64(const unsigned long long* all, unsi
 // Shared memory of one warp.
 template <int VPL, int CPL>
 struct WarpScratch {
-  static constexpr bool kSmall = (VPL == 2) || (CPL == 2);
-  __align__(16) unsigned long long pack[kSmall ? 64 : 2];
-  uint32_t rk[CPL == 2 ? 64 : 1], rf[CPL == 2 ? 64 : 1];
+  static constexpr bool kAllSmall = (VPL == 2) && (CPL == 2);
+  __align__(16) unsigned long long pack[kAllSmall ? 64 : kMaxK];  // ranking scratch
+  uint32_t rk[CPL == 2 ? 64 : kMaxK], rf[CPL == 2 ? 64 : kMaxK];  // selected (score key, flat index) by rank
   float sx[kMaxK], sy[kMaxK];
   int ix[kMaxK], iy[kMaxK];
 };
@@ -207,14 +261,17 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpS
       }
       __syncwarp();
     } else {
-      axis_select<VPL>(key, kk, axis == 0 ? sx : sy, axis == 0 ? ix : iy);
+      uint32_t sub[VPL];
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) sub[e] = e * 32 + lane;
+      warp_select_sorted<VPL, true>(key, sub, kk, w.pack, reinterpret_cast<uint32_t*>(axis == 0 ? sx : sy),
+                                    reinterpret_cast<uint32_t*>(axis == 0 ? ix : iy));
     }
   }
   __syncwarp();
 
   // ---- pruned candidate search ----------------------------------------------------------
   uint32_t ckey[CPL], cflat[CPL];
-  uint32_t lmax = 0;
 #pragma unroll
   for (int q = 0; q < CPL; ++q) {
     const int c = q * 32 + lane;
@@ -227,7 +284,6 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpS
       ckey[q] = 0;
       cflat[q] = 0xffffffffu;
     }
-    lmax = max(lmax, ckey[q]);
   }
 #pragma unroll
   for (int s = 0; s < kMaxK / 32; ++s) rkey[s] = 0, rflat[s] = 0;
@@ -253,31 +309,14 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpS
       if (r < k) rkey[s] = w.rk[r], rflat[s] = w.rf[r];
     }
     last_key = w.rk[k - 1];
-  } else
-  for (int r = 0; r < k; ++r) {
-    const uint32_t m = __reduce_max_sync(FULL_MASK, lmax);
-    uint32_t mine = 0xffffffffu;
-    if (lmax == m) {
+  } else {
+    warp_select_sorted<CPL, false>(ckey, cflat, k, w.pack, w.rk, w.rf);
 #pragma unroll
-      for (int q = 0; q < CPL; ++q)
-        if (ckey[q] == m) mine = min(mine, cflat[q]);
+    for (int s = 0; s < kMaxK / 32; ++s) {
+      const int r = s * 32 + lane;
+      if (r < k) rkey[s] = w.rk[r], rflat[s] = w.rf[r];
     }
-    const uint32_t w = __reduce_min_sync(FULL_MASK, mine);
-    if (lane == (r & 31)) {
-#pragma unroll
-      for (int s = 0; s < kMaxK / 32; ++s)
-        if (s == (r >> 5)) rkey[s] = m, rflat[s] = w;
-    }
-    if (mine == w && lmax == m) {  // flat indices are unique, so exactly one lane owns the winner
-      lmax = 0;
-#pragma unroll
-      for (int q = 0; q < CPL; ++q) {
-        if (ckey[q] == m && cflat[q] == w) ckey[q] = 0;
-        lmax = max(lmax, ckey[q]);
-      }
-    }
-    last_key = m;
-    __syncwarp();
+    last_key = w.rk[k - 1];
   }
 
   // ---- did a cell outside the region tie with the k-th score? -----------------------------

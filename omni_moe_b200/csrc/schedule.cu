@@ -1,11 +1,11 @@
 // Expert-centric scheduling: a stable least-significant-digit radix sort of the (token, expert)
 // pairs by expert id, followed by the CSR description of the expert segments.
 //
-// One digit pass = two kernels and no inter-block waiting:
+// One digit pass = three kernels and no inter-block waiting:
 //   radix_count   every tile (a contiguous run of pairs) histograms its digit into shared memory
-//                 and writes its column of the [bins x tiles] count matrix; the block that
-//                 finishes last turns the matrix into exclusive prefixes (each warp scans bin
-//                 rows, then the bin totals are scanned) - "last block done", nobody spins.
+//                 and writes its column of the [bins x tiles] count matrix.
+//   radix_scan    one warp per bin row turns the row into exclusive prefixes over the tiles; the
+//                 block that finishes last scans the bin totals ("last block done", nobody spins).
 //   radix_scatter every tile ranks its pairs inside the tile with warp match operations
 //                 (order preserving) and writes key and pair id to
 //                 bin_base[digit] + tile_prefix[digit][tile] + rank.
@@ -58,7 +58,7 @@ Plan make_plan(int64_t P, int64_t N) {
   p.off_keysB = o, o += arr;
   p.off_valsB = o, o += arr;
   p.off_hist = o, o += align_up(static_cast<size_t>(kMaxBins) * p.tiles * 4, 256);
-  p.off_binbase = o, o += align_up(static_cast<size_t>(kMaxBins) * 4, 256);
+  p.off_binbase = o, o += align_up(static_cast<size_t>(2 * kMaxBins) * 4, 256);  // bin_base, bin_total
   p.off_tilecnt = o, o += align_up(static_cast<size_t>(p.tiles + 1) * 4, 256);
   p.total = o;
   return p;
@@ -91,14 +91,12 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* s_warp /*[kWarps
   return wbase + inc - v;
 }
 
-// ---- pass kernel 1: per-tile digit histogram + last-block scan ----------------------------
+// ---- pass kernel 1: per-tile digit histogram ---------------------------------------------------
 template <int IPT>
 __global__ void __launch_bounds__(kThreads) radix_count_kernel(
     const void* keys, int key_is_i64, int64_t P, int shift, int bits, int check_range, int num_experts,
-    int* hist /*[bins][tiles]*/, int* bin_base /*[bins]*/, int* ticket, int* status) {
+    int* hist /*[bins][tiles]*/, int* status) {
   __shared__ int s_hist[kMaxBins];
-  __shared__ int s_scan[kWarps];
-  __shared__ int s_last;
   const int bins = 1 << bits, tiles = gridDim.x, tile = blockIdx.x;
   for (int b = threadIdx.x; b < bins; b += kThreads) s_hist[b] = 0;
   __syncthreads();
@@ -116,53 +114,67 @@ __global__ void __launch_bounds__(kThreads) radix_count_kernel(
   if (bad) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
   __syncthreads();
   for (int b = threadIdx.x; b < bins; b += kThreads) hist[static_cast<size_t>(b) * tiles + tile] = s_hist[b];
+}
+
+// ---- pass kernel 2: exclusive prefixes of the count matrix ------------------------------------
+// One warp per bin row: every lane owns a contiguous chunk of the row, sums it (independent loads),
+// the lane sums are scanned across the warp, and the chunk is walked again to write the exclusive
+// prefixes.  The block that finishes last scans the bin totals into bin_base.
+__global__ void __launch_bounds__(kThreads) radix_scan_kernel(int* hist /*[bins][tiles]*/, int tiles, int bins,
+                                                             int* bin_total /*[bins]*/, int* bin_base /*[bins]*/,
+                                                             int* ticket) {
+  __shared__ int s_scan[kWarps];
+  __shared__ int s_last;
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  const int b = blockIdx.x * kWarps + warp;
+  if (b < bins) {
+    int* row = hist + static_cast<size_t>(b) * tiles;
+    const int per = ceil_div(tiles, 32);
+    const int lo = min(tiles, lane * per), hi = min(tiles, lo + per);
+    int sum = 0;
+    for (int t = lo; t < hi; ++t) sum += row[t];
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(FULL_MASK, inc, o);
+      if (lane >= o) inc += y;
+    }
+    int run = inc - sum;
+    for (int t = lo; t < hi; ++t) {
+      const int v = row[t];
+      row[t] = run;
+      run += v;
+    }
+    if (lane == 31) bin_total[b] = inc;
+  }
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == tiles - 1);
+  if (threadIdx.x == 0) s_last = (atomicAdd(ticket, 1) == static_cast<int>(gridDim.x) - 1);
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // Last block: row-wise exclusive prefixes over tiles (one warp per bin row), totals to s_hist.
-  const int lane = lane_id(), warp = threadIdx.x >> 5;
-  for (int b = warp; b < bins; b += kWarps) {
-    volatile int* row = hist + static_cast<size_t>(b) * tiles;
-    int carry = 0;
-    for (int t0 = 0; t0 < tiles; t0 += 32) {
-      const int t = t0 + lane;
-      const int v = t < tiles ? row[t] : 0;
-      int inc = v;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int y = __shfl_up_sync(FULL_MASK, inc, o);
-        if (lane >= o) inc += y;
-      }
-      if (t < tiles) row[t] = carry + inc - v;
-      carry += __shfl_sync(FULL_MASK, inc, 31);
-    }
-    if (lane == 0) s_hist[b] = carry;
-  }
-  __syncthreads();
   // exclusive scan of the bin totals (bins <= 2048 = 8 per thread)
   constexpr int PER = kMaxBins / kThreads;
+  volatile int* tot = bin_total;
   int loc[PER], sum = 0;
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
-    const int b = threadIdx.x * PER + j;
-    loc[j] = b < bins ? s_hist[b] : 0;
+    const int bb = threadIdx.x * PER + j;
+    loc[j] = bb < bins ? tot[bb] : 0;
     sum += loc[j];
   }
   int total;
   int run = block_exclusive_scan(sum, s_scan, total);
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
-    const int b = threadIdx.x * PER + j;
-    if (b < bins) bin_base[b] = run;
+    const int bb = threadIdx.x * PER + j;
+    if (bb < bins) bin_base[bb] = run;
     run += loc[j];
   }
   if (threadIdx.x == 0) *ticket = 0;  // ready for the next use of this counter
 }
 
-// ---- pass kernel 2: stable in-tile ranking + scatter --------------------------------------
+// ---- pass kernel 3: stable in-tile ranking + scatter --------------------------------------
 template <int IPT>
 __global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
     const void* keys, int key_is_i64, const int* vals /*null: identity*/, int64_t P, int shift, int bits,
@@ -335,6 +347,7 @@ int run(const Plan& pl, const void* indices, int idx_is_i64, const void* weights
   int* valsB = reinterpret_cast<int*>(ws + pl.off_valsB);
   int* hist = reinterpret_cast<int*>(ws + pl.off_hist);
   int* binbase = reinterpret_cast<int*>(ws + pl.off_binbase);
+  int* bintotal = binbase + kMaxBins;
   int* tilecnt = reinterpret_cast<int*>(ws + pl.off_tilecnt);
   cudaMemsetAsync(hdr, 0, HDR_WORDS * sizeof(int), st);
   cudaMemsetAsync(meta, 0, 4 * sizeof(int), st);
@@ -348,7 +361,9 @@ int run(const Plan& pl, const void* indices, int idx_is_i64, const void* weights
     int* ov = last ? perm : (pass == 0 ? valsA : valsB);
     const int bits = pl.bits[pass];
     radix_count_kernel<IPT><<<pl.tiles, kThreads, 0, st>>>(in_keys, in_i64, pl.P, shift, bits, pass == 0,
-                                                         static_cast<int>(N), hist, binbase, hdr + HDR_TICKET0, meta + 2);
+                                                         static_cast<int>(N), hist, meta + 2);
+    radix_scan_kernel<<<ceil_div(1 << bits, kWarps), kThreads, 0, st>>>(hist, pl.tiles, 1 << bits, bintotal, binbase,
+                                                                        hdr + HDR_TICKET0);
     const size_t smem = static_cast<size_t>(kWarps) * (size_t(1) << bits) * sizeof(uint16_t);
     radix_scatter_kernel<IPT><<<pl.tiles, kThreads, smem, st>>>(in_keys, in_i64, in_vals, pl.P, shift, bits, hist, binbase, ok, ov);
     in_keys = ok, in_i64 = 0, in_vals = ov;
