@@ -174,6 +174,27 @@ OMNI_API int omni_expert_combine(const void *down, const float *coef, const int3
                         int32_t *status, void *stream);
 
 /*
+ * The two routed-expert kernels for a GPU that holds only a slice of the expert tables (rows
+ * [lo, hi) of Up / Down) and works on a list of (token, local expert, weight) pairs that other GPUs
+ * dispatched to it, rather than on a [T, k] routing table.  The reference has no multi-GPU path;
+ * these do, per GPU, the work of omni_expert_forward (omni_moe/ops/triton/omni_expert.py:920-992).
+ *
+ * omni_expert_coef_pairs: c[p] = pair_weights[p] * silu(x[pair_tokens[p]] . Up[e[p]]), pairs walked in
+ *   expert order (sorted_pair_ids / sorted_experts from omni_schedule over the pairs' local expert ids).
+ * omni_expert_combine_segments: y[t] = sum over the pairs p in [token_offsets[t], token_offsets[t+1])
+ *   of coef[p] * Down[pair_experts[p]]  (+ residual); the pair list must be grouped by token.
+ *   Tokens without pairs get zeros (or the residual).
+ */
+OMNI_API int omni_expert_coef_pairs(const void *x, const void *up, const int32_t *pair_tokens,
+                           const float *pair_weights, const int32_t *sorted_pair_ids,
+                           const int32_t *sorted_experts, int64_t num_pairs, int64_t num_tokens,
+                           int hidden, int64_t num_experts, float *coef, int32_t *status, void *stream);
+OMNI_API int omni_expert_combine_segments(const void *down, const float *coef, const int32_t *pair_experts,
+                                 const int32_t *token_offsets, int64_t num_tokens, int hidden,
+                                 int64_t num_experts, const void *residual, void *y, int out_dtype,
+                                 int32_t *status, void *stream);
+
+/*
  * The same routed-expert sum in one token-centric kernel, for tables that stay resident in L2
  * (2 * num_experts * hidden * 2 bytes well below the 126 MB L2): a warp holds its token's x row in
  * registers and streams the k Up and Down rows of the token; no scheduling pass and no coefficient

@@ -38,6 +38,10 @@ SIGNATURES = {
                                  c_void_p, c_void_p, c_void_p]),
     "omni_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p, c_void_p,
                                     c_int, c_void_p, c_void_p]),
+    "omni_expert_coef_pairs": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,
+                                       c_int64, c_void_p, c_void_p, c_void_p]),
+    "omni_expert_combine_segments": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_void_p,
+                                             c_void_p, c_int, c_void_p, c_void_p]),
     "omni_expert_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64,
                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "omni_route_expert_fused": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

@@ -35,18 +35,23 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc)
 template <int HV>
 __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const float* __restrict__ weights,
-    const int* __restrict__ perm, const int* __restrict__ sorted_experts, int64_t P, int64_t T, int k, int H,
-    int64_t N, float* __restrict__ coef, int* status) {
+    const int* __restrict__ perm, const int* __restrict__ sorted_experts, const int* __restrict__ pair_tokens,
+    int64_t P, int64_t T, int k, int H, int64_t N, float* __restrict__ coef, int* status) {
+  // pair_tokens == nullptr: pairs come from a [T, k] routing table, pair p belongs to token p / k.
+  // Otherwise pair p belongs to token pair_tokens[p] (pairs received from other GPUs).
   const int lane = lane_id();
   const int64_t w0 = (static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5)) * kRun;
   if (w0 >= P) return;
   // lane i < kRun carries the metadata of sorted position w0 + i
-  int my_pair = -1, my_e = -1;
+  int my_pair = -1, my_e = -1, my_t = -1;
   float my_g = 0.f;
   if (lane < kRun && w0 + lane < P) {
     my_pair = perm[w0 + lane];
     my_e = sorted_experts[w0 + lane];
-    my_g = (my_pair >= 0 && my_pair < P) ? weights[my_pair] : 0.f;
+    if (my_pair >= 0 && my_pair < P) {
+      my_g = weights[my_pair];
+      my_t = pair_tokens ? pair_tokens[my_pair] : my_pair / k;
+    }
   }
   const int count = (P - w0 < kRun) ? static_cast<int>(P - w0) : kRun;
   const int slabs = ceil_div(H, HV * 256);
@@ -57,9 +62,9 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     const int pair = __shfl_sync(FULL_MASK, my_pair, i);
     const int e = __shfl_sync(FULL_MASK, my_e, i);
     const float g = __shfl_sync(FULL_MASK, my_g, i);
-    const int64_t t = pair / k;
+    const int64_t t = __shfl_sync(FULL_MASK, my_t, i);
     if (e < 0 || e >= N) { bad_e = true; if (lane == 0 && pair >= 0 && pair < P) coef[pair] = 0.f; continue; }
-    if (pair < 0 || t >= T) { bad_t = true; continue; }
+    if (pair < 0 || t < 0 || t >= T) { bad_t = true; continue; }
     float acc = 0.f;
     for (int s = 0; s < slabs; ++s) {
       const int c0 = s * HV * 256 + lane * 8;
@@ -286,6 +291,69 @@ __device__ __forceinline__ void store_row(float (&acc)[HV][8], int64_t t, int c0
   }
 }
 
+// Token-centric combine over a pair list grouped by token (CSR): token t owns the pairs
+// [offsets[t], offsets[t+1]) of pair_experts / coef.  Used where the number of pairs per token varies:
+// on a GPU that holds a slice of the expert tables and received only the pairs routed to its rows.
+template <int HV, bool OUT_F32>
+__global__ void __launch_bounds__(kThreads) expert_combine_segments_kernel(
+    const __nv_bfloat16* __restrict__ down, const float* __restrict__ coef, const int* __restrict__ pair_experts,
+    const int* __restrict__ offsets, int64_t T, int H, int64_t N, int slabs, const void* residual, void* y, int* status) {
+  const int lane = lane_id();
+  const int64_t wid = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  const int64_t t = wid / slabs;
+  const int slab = static_cast<int>(wid - t * slabs);
+  if (t >= T) return;
+  const int c0 = slab * HV * 256 + lane * 8;
+  float acc[HV][8];
+#pragma unroll
+  for (int v = 0; v < HV; ++v)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[v][q] = 0.f;
+  bool bad = false;
+  const int lo = offsets[t], hi = offsets[t + 1];
+  constexpr int UNR = HV >= 8 ? 2 : 4;
+  for (int j0 = lo; j0 < hi; j0 += 32) {
+    int my_e = -1;
+    float my_c = 0.f;
+    if (j0 + lane < hi) {
+      my_e = pair_experts[j0 + lane];
+      my_c = coef[j0 + lane];
+      if (my_e < 0 || my_e >= N) { bad = true; my_e = -1; }
+    }
+    const int cnt = min(32, hi - j0);
+    for (int j = 0; j < cnt; j += UNR) {
+      uint4 dv[UNR][HV];
+      float c[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int e = __shfl_sync(FULL_MASK, my_e, (j + u) & 31);
+        c[u] = __shfl_sync(FULL_MASK, my_c, (j + u) & 31);
+        const bool on = (j + u < cnt) && e >= 0;
+        if (!on) c[u] = 0.f;
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const int col = c0 + v * 256;
+          dv[u][v] = (on && col < H) ? ldg128(down + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv[u][v]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = bf16x2_to_float2(pd[q]);
+            acc[v][2 * q] = __fmaf_rn(c[u], f.x, acc[v][2 * q]);
+            acc[v][2 * q + 1] = __fmaf_rn(c[u], f.y, acc[v][2 * q + 1]);
+          }
+        }
+    }
+  }
+  store_row<HV, OUT_F32>(acc, t, c0, H, residual, y);
+  if (bad && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
 template <int HV>
 __device__ __forceinline__ void load_x_row(const __nv_bfloat16* __restrict__ x, int64_t t, int c0, int H, uint4 (&xv)[HV],
                                            float (&acc)[HV][8]) {
@@ -389,8 +457,8 @@ extern "C" int omni_expert_coef(const void* x, const void* up, const float* weig
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(ceil_div64(ceil_div64(P, kRun), kWarps));
 #define OMNI_COEF(HV)                                                                                         \
-  expert_coef_kernel<HV><<<grid, kThreads, 0, st>>>(xb, ub, weights, sorted_pair_ids, sorted_experts, P, num_tokens, \
-                                                   k, hidden, num_experts, coef, status)
+  expert_coef_kernel<HV><<<grid, kThreads, 0, st>>>(xb, ub, weights, sorted_pair_ids, sorted_experts, nullptr, P,     \
+                                                   num_tokens, k, hidden, num_experts, coef, status)
   if (hidden <= 256) OMNI_COEF(1);
   else if (hidden <= 512) OMNI_COEF(2);
   else if (hidden <= 1024) OMNI_COEF(4);
@@ -514,4 +582,64 @@ extern "C" int omni_route_expert_fused(const float* logits, int64_t ld_logits, c
 #undef OMNI_ROUTED_HV
 #undef OMNI_ROUTED
   return check_launch("expert_routed_kernel");
+}
+
+extern "C" int omni_expert_coef_pairs(const void* x, const void* up, const int32_t* pair_tokens, const float* pair_weights,
+                                      const int32_t* sorted_pair_ids, const int32_t* sorted_experts, int64_t num_pairs,
+                                      int64_t num_tokens, int hidden, int64_t num_experts, float* coef,
+                                      int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_pairs >= 0 && num_tokens >= 0 && hidden >= 8 && num_experts >= 1, "bad sizes");
+  OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
+  OMNI_REQUIRE(num_pairs < (int64_t(1) << 31), "too many pairs");
+  if (num_pairs == 0) return 0;
+  OMNI_REQUIRE(x && up && pair_tokens && pair_weights && sorted_pair_ids && sorted_experts && coef && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(up), "x and up must be 16-byte aligned");
+  const auto* xb = static_cast<const __nv_bfloat16*>(x);
+  const auto* ub = static_cast<const __nv_bfloat16*>(up);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(ceil_div64(ceil_div64(num_pairs, kRun), kWarps));
+#define OMNI_COEFP(HV)                                                                                               \
+  expert_coef_kernel<HV><<<grid, kThreads, 0, st>>>(xb, ub, pair_weights, sorted_pair_ids, sorted_experts, pair_tokens, \
+                                                   num_pairs, num_tokens, 1, hidden, num_experts, coef, status)
+  if (hidden <= 256) OMNI_COEFP(1);
+  else if (hidden <= 512) OMNI_COEFP(2);
+  else if (hidden <= 1024) OMNI_COEFP(4);
+  else if (hidden <= 2048) OMNI_COEFP(8);
+  else OMNI_COEFP(16);
+#undef OMNI_COEFP
+  return check_launch("expert_coef_kernel (pair list)");
+}
+
+extern "C" int omni_expert_combine_segments(const void* down, const float* coef, const int32_t* pair_experts,
+                                            const int32_t* token_offsets, int64_t num_tokens, int hidden,
+                                            int64_t num_experts, const void* residual, void* y, int out_dtype,
+                                            int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && hidden >= 8 && num_experts >= 1, "bad sizes");
+  OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
+  OMNI_REQUIRE(out_dtype == OMNI_F32 || out_dtype == OMNI_BF16, "out_dtype must be OMNI_F32 or OMNI_BF16");
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(down && token_offsets && y && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(down) && aligned16(y) && aligned16(residual), "down, y and residual must be 16-byte aligned");
+  const auto* db = static_cast<const __nv_bfloat16*>(down);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int hv = hidden <= 256 ? 1 : hidden <= 512 ? 2 : hidden <= 1024 ? 4 : 8;
+  const int slabs = ceil_div(hidden, hv * 256);
+  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens * slabs, kWarps));
+#define OMNI_COMBS(HV)                                                                                                \
+  do {                                                                                                                \
+    if (out_dtype == OMNI_F32)                                                                                        \
+      expert_combine_segments_kernel<HV, true><<<grid, kThreads, 0, st>>>(db, coef, pair_experts, token_offsets,      \
+                                                                          num_tokens, hidden, num_experts, slabs,     \
+                                                                          residual, y, status);                       \
+    else                                                                                                              \
+      expert_combine_segments_kernel<HV, false><<<grid, kThreads, 0, st>>>(db, coef, pair_experts, token_offsets,     \
+                                                                           num_tokens, hidden, num_experts, slabs,    \
+                                                                           residual, y, status);                      \
+  } while (0)
+  if (hv == 1) OMNI_COMBS(1);
+  else if (hv == 2) OMNI_COMBS(2);
+  else if (hv == 4) OMNI_COMBS(4);
+  else OMNI_COMBS(8);
+#undef OMNI_COMBS
+  return check_launch("expert_combine_segments_kernel");
 }

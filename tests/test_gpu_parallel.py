@@ -1,0 +1,97 @@
+"""Row-partitioned expert tables on the GPU: the pair-list kernels on one device (every rank's share
+computed in turn, no communication), and the whole partitioned layer on two devices over NCCL when
+two are present."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import omni_oracle as orc
+from _util import assert_close, gen, zipf_indices
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _received_for_rank(x, idx, w, part):
+    """What dispatch_pairs would deliver to part.rank if all tokens lived in one process."""
+    from omni_moe_b200.parallel import ReceivedPairs
+    t, k = idx.shape
+    flat = idx.reshape(-1)
+    mine = (part.owner(flat) == part.rank).nonzero().flatten()   # ascending pair id = ascending token id
+    tok = torch.div(mine, k, rounding_mode="floor").to(torch.int32)
+    off = torch.searchsorted(tok, torch.arange(t + 1, device=x.device, dtype=torch.int32)).to(torch.int32)
+    return ReceivedPairs(x, tok.contiguous(), (flat[mine] - part.lo).to(torch.int32).contiguous(),
+                         w.reshape(-1)[mine].float().contiguous(), off, [], [])
+
+
+@pytest.mark.parametrize("t,h,n,k,world,skew", [(200, 256, 1000, 8, 4, False), (64, 4096, 300, 16, 2, False),
+                                                  (512, 1024, 4096, 32, 8, True), (33, 72, 7, 4, 3, False)])
+def test_pair_list_kernels_sum_to_the_full_answer(t, h, n, k, world, skew):
+    from omni_moe_b200.parallel import ExpertPartition, local_partial_states
+    g = gen(t + n)
+    x = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
+    up = (torch.randn(n, h, generator=g) * 0.1).bfloat16()
+    dn = (torch.randn(n, h, generator=g) * 0.1).bfloat16()
+    w = torch.rand(t, k, generator=g)
+    idx = zipf_indices(t, k, n, 1.1, 1) if skew else torch.randint(0, n, (t, k), generator=g, dtype=torch.int32)
+    xc, uc, dc, wc, ic = x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda()
+    total = torch.zeros(t, h, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for r in range(world):
+        part = ExpertPartition(n, world, r)
+        recv = _received_for_rank(xc, ic, wc, part)
+        total += local_partial_states(recv, part.slice_rows(uc), part.slice_rows(dc), status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert_close(total, orc.expert_forward(x, up, dn, w, idx), rtol=1e-3, atol=1e-4)
+
+
+_CHILD = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["OMNI_ROOT"]); sys.path.insert(0, os.path.join(os.environ["OMNI_ROOT"], "tests"))
+from oracle import omni_oracle as orc
+from omni_moe_b200.modules.omni_moe import OmniMoE, OmniMoEConfig
+from omni_moe_b200.parallel import PartitionedOmniMoE, shard_tokens
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+torch.manual_seed(0)
+full = OmniMoE(OmniMoEConfig(256, 512, "silu", 1024, 8)).to(torch.bfloat16).eval()
+sd = {k: v.float() for k, v in full.state_dict().items()}
+x = torch.randn(1, 64 * world, 256).bfloat16()
+p = orc.params_from_state_dict(sd, 1024, 8)
+ey, _, _, _, ei = orc.layer_forward(p, x.float(), return_routing=True)
+m = PartitionedOmniMoE(full.cuda(), None)
+assert m.inner.up_embed.weight.shape[0] == 1024 // world
+xs = shard_tokens(x, rank, world).cuda().view(1, 64, 256)
+y = m(xs)
+m.inner.check_status()
+sl = slice(rank * 64, (rank + 1) * 64)
+same = (m.inner.last_routing[1].cpu().numpy() == ei[sl]).all(axis=1)
+assert same.mean() > 0.95, same.mean()
+a, e = y.float().cpu().view(64, 256)[same], ey.view(-1, 256)[sl][same]
+bad = (a - e).abs() > 2e-2 + 2e-2 * e.abs()
+assert not bad.any(), int(bad.sum())
+dist.barrier(); dist.destroy_process_group()
+print("rank", rank, "ok", flush=True)
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_partitioned_layer_two_gpus_nccl(tmp_path):
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, OMNI_ROOT=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout

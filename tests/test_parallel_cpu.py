@@ -1,0 +1,90 @@
+"""Exchange plumbing of the row-partitioned expert tables, on CPU ranks with the gloo backend.
+
+Two (and three) processes each own a slice of the tables and a shard of the tokens; the dispatch,
+the token-ordered receive lists and the combine are the real code of omni_moe_b200.parallel, the
+per-rank arithmetic is the oracle's.  The result must equal the oracle's single-process answer."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import omni_oracle as orc
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_local(recv, up_local, down_local):
+    """Step 3 with the oracle's arithmetic: per received pair w * silu(x . up) * down, summed per token."""
+    t_total, h = recv.x_all.shape
+    out = torch.zeros(t_total, h)
+    if recv.pair_tokens.numel():
+        tok = recv.pair_tokens.long()
+        e = recv.pair_experts.long()
+        s = (recv.x_all.float()[tok] * up_local.float()[e]).sum(-1)
+        c = torch.nn.functional.silu(s) * recv.pair_weights
+        out.index_add_(0, tok, c[:, None] * down_local.float()[e])
+        # the receive list is grouped by token and the offsets describe it
+        off = recv.token_offsets.long()
+        assert bool((tok[1:] >= tok[:-1]).all())
+        assert off[0] == 0 and off[-1] == tok.numel()
+        counts = torch.bincount(tok, minlength=t_total)
+        assert torch.equal(off[1:] - off[:-1], counts)
+    return out
+
+
+def _worker(rank, world, port, t_local, h, n, k, seed, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from omni_moe_b200.parallel import ExpertPartition, partitioned_expert_states, shard_tokens
+        g = torch.Generator().manual_seed(seed)
+        t = t_local * world
+        x = torch.randn(t, h, generator=g)
+        up = torch.randn(n, h, generator=g) * 0.1
+        down = torch.randn(n, h, generator=g) * 0.1
+        idx = torch.randint(0, n, (t, k), generator=g, dtype=torch.int32)
+        idx[:, 0] = idx[:, 1]          # duplicates inside a token
+        idx[0, :] = n - 1              # a token whose pairs all go to the last rank
+        w = torch.rand(t, k, generator=g)
+        part = ExpertPartition(n, world, rank)
+        sl = slice(rank * t_local, (rank + 1) * t_local)
+        assert torch.equal(shard_tokens(x, rank, world), x[sl])
+        got = partitioned_expert_states(x[sl], idx[sl], w[sl], part.slice_rows(up), part.slice_rows(down), part,
+                                        local_fn=_oracle_local)
+        expect = orc.expert_forward(x, up, down, w, idx)[sl]
+        ret[rank] = float((got - expect).abs().max())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,t_local,n", [(2, 12, 64), (3, 5, 50), (2, 8, 3)])
+def test_partitioned_dispatch_and_combine_gloo(world, t_local, n):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, t_local, 16, n, 6, 3, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)
+
+
+def test_expert_partition_arithmetic():
+    from omni_moe_b200.parallel import ExpertPartition
+    parts = [ExpertPartition(10, 4, r) for r in range(4)]
+    assert [(p.lo, p.hi) for p in parts] == [(0, 3), (3, 6), (6, 9), (9, 10)]
+    e = torch.arange(10)
+    assert parts[0].owner(e).tolist() == [0, 0, 0, 1, 1, 1, 2, 2, 2, 3]
+    t = torch.arange(20).view(10, 2)
+    assert torch.equal(parts[3].slice_rows(t), t[9:10])
