@@ -39,9 +39,9 @@ CFG = dict(hidden=1024, intermediate=4096, experts=4096, top_k=16, tokens=4096)
 WORKLOAD = "quick-start layer: hidden 1024, intermediate 4096, 4096 experts (64x64), top-k 16, x bf16 [1,4096,1024]"
 SLOTS = 4  # independent weight + activation sets rotated between steps (working set > L2)
 
-# DRAM bytes per launch of the gate/up GEMM kernel from the ncu capture summarised in
-# profiles/gemm_gate_up_quickstart.md (None until a capture exists)
-GATE_UP_DRAM_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) per launch of the gate/up GEMM kernel, from the ncu capture summarised
+# in profiles/gemm_pair_gate_up_quickstart.md (25.23 MB read + 0.65 MB written)
+GATE_UP_DRAM_BYTES_PER_LAUNCH = 25_889_280
 
 
 def peaks():
@@ -312,7 +312,7 @@ def main():
                     "ms_per_step": ms_e2e / args.steps, "pipeline": f"{SLOTS} slots, one stream each"},
             "gpu_launches": OmniMoE.kernels_per_forward(CFG["experts"], CFG["hidden"], 64, CFG["top_k"]) * args.steps,
             "clocks": clocks,
-            "roofline": {"kernel": "gemm_kernel<256, EPI_SWIGLU> (gate/up projections + SwiGLU)", "bound": "tensor",
+            "roofline": {"kernel": "gemm_pair_kernel<EPI_SWIGLU> (gate/up projections + SwiGLU, tcgen05 cta_group::2)", "bound": "tensor",
                          "achieved": achieved, "peak": pk["tf"], "unit": "TFLOP/s", "frac": achieved / pk["tf"],
                          "traffic": GATE_UP_DRAM_BYTES_PER_LAUNCH, "peak_source": pk["src"] + " (burst: kernel timed alone)",
                          "ms_per_launch": gemm_ms, "flops_per_launch": flops},
