@@ -64,6 +64,21 @@ struct GemmArgs {
     }                                         \
   } while (0)
 
+// Tile order.  Tiles are handed out in groups of kGroupM tile rows: inside a group the column index
+// advances slowest within a row block, so the CTAs running at any moment share a few A tiles and a few
+// B tiles, and a group's A rows stay in L2 while the whole width of B sweeps past them.  (With plain
+// row-fastest order a 65536-token activation matrix is re-read from HBM once per tile column.)
+constexpr int kGroupM = 8;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = kGroupM * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int rows = min(kGroupM, tiles_m - first_m);  // the last group may be short
+  const int in_group = tile - group * per_group;
+  tm = first_m + in_group % rows;
+  tn = in_group / rows;
+}
+
 template <int BN>
 struct Cfg {
   static constexpr int kStageA = BM * BK * 2;
@@ -209,7 +224,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
+        int tm, tn;
+        tile_coords(tile, g.tiles_m, g.tiles_n, tm, tn);
         const int axis = tn / g.tiles_n_axis, tj = tn - axis * g.tiles_n_axis;
         for (int kb = 0; kb < kblocks; ++kb) {
           bool ok;
@@ -277,7 +293,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     long long e_wait = 0, e_store = 0;
     const long long e_t0 = clock64();
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      const int tm = tile % g.tiles_m, tn = tile / g.tiles_m;
+      int tm, tn;
+      tile_coords(tile, g.tiles_m, g.tiles_n, tm, tn);
       const int axis = tn / g.tiles_n_axis, tj = tn - axis * g.tiles_n_axis;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -328,10 +345,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 // ---------------------------------------------------------------------------------------------
 struct PairCfg {
   static constexpr int BN = 256;
-  static constexpr int kStageA = BM * BK * 2;        // 16 KB: this CTA's 128 rows of A
-  static constexpr int kStageB = (BN / 2) * BK * 2;  // 16 KB: this CTA's half of B
+  // A stage holds kSub consecutive 64-wide K slices of both operands, so one barrier round trip
+  // (wait, commit) feeds 4 * kSub MMAs: the single issuing thread spends its time issuing.
+  static constexpr int kSub = 2;
+  static constexpr int kSliceA = BM * BK * 2;        // 16 KB: this CTA's 128 rows of A, one K slice
+  static constexpr int kSliceB = (BN / 2) * BK * 2;  // 16 KB: this CTA's half of B, one K slice
+  static constexpr int kStageA = kSub * kSliceA;
+  static constexpr int kStageB = kSub * kSliceB;
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = 6;
+  static constexpr int kStages = 6 / kSub;
   static constexpr int kTmemCols = 2 * BN;
   static constexpr int kSmem = kStages * kStage + 1024 + 1024;
 };
@@ -367,7 +389,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int rt = ROUTER ? g.router_tiles : 0;
   const int num_tiles = g.tiles_m * (g.tiles_n + rt);  // tiles_m counts 256-row pair tiles here
-  const int kblocks = ceil_div(g.K, BK);
+  const int kblocks = ceil_div(g.K, BK * C::kSub);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -404,7 +426,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       uint32_t phase = 0;
       const uint32_t full_leader0 = mapa_shared(bar_full, 0);
       for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-        const int tm = tile % g.tiles_m, tn_all = tile / g.tiles_m;
+        int tm, tn_all;
+        tile_coords(tile, g.tiles_m, g.tiles_n + rt, tm, tn_all);
         const bool router_tile = ROUTER && tn_all < rt;
         const int tn = router_tile ? tn_all : tn_all - rt;
         const int row_a = tm * (2 * BM) + static_cast<int>(rank) * BM;
@@ -420,8 +443,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           } else {
             if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::kStage);
             const uint32_t full_leader = full_leader0 + 8 * stage;
-            tma_load_2d_pair(sA + stage * C::kStageA, &tm_a, kb * BK, row_a, full_leader);
-            tma_load_2d_pair(sB + stage * C::kStageB, mb, kb * BK, row_b, full_leader);
+#pragma unroll
+            for (int sub = 0; sub < C::kSub; ++sub) {
+              const int kcol = (kb * C::kSub + sub) * BK;  // past K the box is zero-filled
+              tma_load_2d_pair(sA + stage * C::kStageA + sub * C::kSliceA, &tm_a, kcol, row_a, full_leader);
+              tma_load_2d_pair(sB + stage * C::kStageB + sub * C::kSliceB, mb, kcol, row_b, full_leader);
+            }
           }
           if (++stage == C::kStages) stage = 0, phase ^= 1;
         }
@@ -456,8 +483,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * (C::kStageB >> 4));
           if (!(g.knobs & 2)) {
 #pragma unroll
-            for (int ks = 0; ks < BK / UMMA_K; ++ks)
-              umma_bf16_pair(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, (kb | ks) != 0);
+            for (int sub = 0; sub < C::kSub; ++sub) {
+              const uint64_t ad = adesc + static_cast<uint64_t>(sub * (C::kSliceA >> 4));
+              const uint64_t bd = bdesc + static_cast<uint64_t>(sub * (C::kSliceB >> 4));
+#pragma unroll
+              for (int ks = 0; ks < BK / UMMA_K; ++ks)
+                umma_bf16_pair(d_tmem, ad + 2 * ks, bd + 2 * ks, idesc, (kb | sub | ks) != 0);
+            }
           }
           umma_commit_pair(bar_empty + 8 * stage, 3);  // both CTAs may refill this stage
           if (++stage == C::kStages) stage = 0, phase ^= 1;
@@ -475,7 +507,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     long long e_wait = 0, e_store = 0;
     const long long e_t0 = clock64();
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
-      const int tm = tile % g.tiles_m, tn_all = tile / g.tiles_m;
+      int tm, tn_all;
+      tile_coords(tile, g.tiles_m, g.tiles_n + rt, tm, tn_all);
       const bool router_tile = ROUTER && tn_all < rt;
       const int tn = router_tile ? tn_all : tn_all - rt;
       const int acc = it & 1;
