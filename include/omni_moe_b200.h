@@ -218,8 +218,7 @@ OMNI_API int omni_expert_fused(const void *x, const void *up, const void *down, 
  *   logits [T, 2*sqrt_n] fp32 (row stride ld_logits); x, up, down bf16; y [T, H] bf16;
  *   residual [T, H] bf16 or NULL, may be y itself
  *   scores, indices (int32), weights [T, k]: the routing that was used, each may be NULL
- * Limits: hidden % 8 == 0, hidden <= 2048, sqrt_n <= 256, k small enough that the pruned candidate
- * region has at most 128 cells (k <= 32).
+ * Limits: hidden % 8 == 0, hidden <= 2048, sqrt_n <= 256, k <= 32.
  */
 OMNI_API int omni_route_expert_fused(const float *logits, int64_t ld_logits,
                             const float *bn_scale, const float *bn_shift,

@@ -31,6 +31,33 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc)
   return acc;
 }
 
+// Packed fp32 pairs: Blackwell issues two FMAs per instruction on a register pair (fma.rn.f32x2), and
+// a bf16x2 word unpacks into exactly such a pair, so a row element costs 1 unpack op + 1/2 FMA issue.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+
+// x row unpacked to fp32 pairs once per token: xf[v][q] = elements (2q, 2q+1) of vector v.
+template <int HV>
+__device__ __forceinline__ void unpack_row(const uint4 (&xv)[HV], float2 (&xf)[HV][4]) {
+#pragma unroll
+  for (int v = 0; v < HV; ++v) {
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(&xv[v]);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) xf[v][q] = bf16x2_to_float2(p[q]);
+  }
+}
+__device__ __forceinline__ float2 dot8p(const float2 (&a)[4], const uint4& b, float2 acc) {
+  const uint32_t* pb = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc = fma2(a[i], bf16x2_to_float2(pb[i]), acc);
+  return acc;
+}
+__device__ __forceinline__ void axpy8p(float c, const uint4& d, float2 (&acc)[4]) {
+  const uint32_t* pd = reinterpret_cast<const uint32_t*>(&d);
+  const float2 c2 = make_float2(c, c);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = fma2(c2, bf16x2_to_float2(pd[i]), acc[i]);
+}
+
 // HV = 128-bit vectors per lane; covers HV * 256 columns per slab.
 template <int HV>
 __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
@@ -198,9 +225,9 @@ __global__ void __launch_bounds__(kThreads) expert_combine_kernel(
 // The Up and Down rows of UNR pairs are in flight at a time; dot, SiLU, weight and the accumulation
 // of c * Down stay in registers.  coef_row, if not null, receives the cnt coefficients.
 template <int HV>
-__device__ __forceinline__ void gather_pairs(int my_e, float my_w, int cnt, int c0, int H, const uint4 (&xv)[HV],
+__device__ __forceinline__ void gather_pairs(int my_e, float my_w, int cnt, int c0, int H, const float2 (&xf)[HV][4],
                                              const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
-                                             float (&acc)[HV][8], float* coef_row) {
+                                             float2 (&acc)[HV][4], float* coef_row) {
   constexpr int UNR = HV >= 8 ? 1 : 2;
   const int lane = lane_id();
   for (int j = 0; j < cnt; j += UNR) {
@@ -223,9 +250,10 @@ __device__ __forceinline__ void gather_pairs(int my_e, float my_w, int cnt, int 
     float dot[UNR];
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      dot[u] = 0.f;
+      float2 d2 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int v = 0; v < HV; ++v) dot[u] = dot8(xv[v], uv[u][v], dot[u]);
+      for (int v = 0; v < HV; ++v) d2 = dot8p(xf[v], uv[u][v], d2);
+      dot[u] = d2.x + d2.y;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
@@ -236,20 +264,26 @@ __device__ __forceinline__ void gather_pairs(int my_e, float my_w, int cnt, int 
       const float c = on[u] ? w[u] * silu(dot[u]) : 0.f;
       if (coef_row && lane == 0 && j + u < cnt) coef_row[j + u] = c;
 #pragma unroll
-      for (int v = 0; v < HV; ++v) {
-        const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv[u][v]);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 f = bf16x2_to_float2(pd[q]);
-          acc[v][2 * q] = __fmaf_rn(c, f.x, acc[v][2 * q]);
-          acc[v][2 * q + 1] = __fmaf_rn(c, f.y, acc[v][2 * q + 1]);
-        }
-      }
+      for (int v = 0; v < HV; ++v) axpy8p(c, dv[u][v], acc[v]);
     }
   }
 }
 
 // Adds the optional residual row and writes one output row (fp32 or bf16).
+template <int HV, bool OUT_F32>
+__device__ __forceinline__ void store_row(float (&acc)[HV][8], int64_t t, int c0, int H, const void* residual, void* y);
+
+// the same for accumulators kept as fp32 pairs
+template <int HV, bool OUT_F32>
+__device__ __forceinline__ void store_row(float2 (&acc2)[HV][4], int64_t t, int c0, int H, const void* residual, void* y) {
+  float acc[HV][8];
+#pragma unroll
+  for (int v = 0; v < HV; ++v)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[v][2 * q] = acc2[v][q].x, acc[v][2 * q + 1] = acc2[v][q].y;
+  store_row<HV, OUT_F32>(acc, t, c0, H, residual, y);
+}
+
 template <int HV, bool OUT_F32>
 __device__ __forceinline__ void store_row(float (&acc)[HV][8], int64_t t, int c0, int H, const void* residual, void* y) {
 #pragma unroll
@@ -356,13 +390,13 @@ __global__ void __launch_bounds__(kThreads) expert_combine_segments_kernel(
 
 template <int HV>
 __device__ __forceinline__ void load_x_row(const __nv_bfloat16* __restrict__ x, int64_t t, int c0, int H, uint4 (&xv)[HV],
-                                           float (&acc)[HV][8]) {
+                                           float2 (&acc)[HV][4]) {
 #pragma unroll
   for (int v = 0; v < HV; ++v) {
     const int col = c0 + v * 256;
     xv[v] = col < H ? ldg128(x + t * H + col) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int q = 0; q < 8; ++q) acc[v][q] = 0.f;
+    for (int q = 0; q < 4; ++q) acc[v][q] = make_float2(0.f, 0.f);
   }
 }
 
@@ -376,8 +410,9 @@ __global__ void __launch_bounds__(kThreads) expert_fused_kernel(
   if (t >= T) return;
   const int c0 = lane * 8;
   uint4 xv[HV];
-  float acc[HV][8];
+  float2 acc[HV][4], xf[HV][4];
   load_x_row<HV>(x, t, c0, H, xv, acc);
+  unpack_row<HV>(xv, xf);
   bool bad = false;
   for (int j0 = 0; j0 < k; j0 += 32) {
     int my_e = -1;
@@ -387,7 +422,7 @@ __global__ void __launch_bounds__(kThreads) expert_fused_kernel(
       my_w = weights[t * k + j0 + lane];
       if (my_e < 0 || my_e >= N) { bad = true; my_e = -1; }
     }
-    gather_pairs<HV>(my_e, my_w, min(32, k - j0), c0, H, xv, up, down, acc, coef ? coef + t * k + j0 : nullptr);
+    gather_pairs<HV>(my_e, my_w, min(32, k - j0), c0, H, xf, up, down, acc, coef ? coef + t * k + j0 : nullptr);
   }
   store_row<HV, OUT_F32>(acc, t, c0, H, residual, y);
   if (bad && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
@@ -410,29 +445,28 @@ __global__ void __launch_bounds__(kThreads, HV <= 4 ? 2 : 1) expert_routed_kerne
   const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
   if (t >= a.T) return;
   const int c0 = lane * 8, k = a.k;
-  uint4 xv[HV];
-  float acc[HV][8];
-  load_x_row<HV>(x, t, c0, H, xv, acc);  // in flight during the selection
   uint32_t rkey[sel::kMaxK / 32], rflat[sel::kMaxK / 32];
   sel::select_token<VPL, CPL, true>(a, t, s_warp[warp], s_region.cell, rkey, rflat);
-#pragma unroll
-  for (int s = 0; s < sel::kMaxK / 32; ++s) {
-    if (s * 32 >= k) break;
-    const int r = s * 32 + lane;
-    int my_e = -1;
-    float my_w = 0.f;
-    if (r < k) {
-      const float sc = key_to_float(rkey[s]);
-      my_w = expf(sc);
-      my_e = static_cast<int>(rflat[s]);  // < sqrt_n^2 <= N by construction
-      const int64_t o = t * k + r;
-      if (a.scores) a.scores[o] = sc;
-      if (a.indices) reinterpret_cast<int32_t*>(a.indices)[o] = my_e;
-      if (a.weights) a.weights[o] = my_w;
-      if (my_e >= N) my_e = -1;
-    }
-    gather_pairs<HV>(my_e, my_w, min(32, k - s * 32), c0, H, xv, up, down, acc, nullptr);
+  // k <= 32 here (checked by the host), so rank r lives in lane r
+  int my_e = -1;
+  float my_w = 0.f;
+  if (lane < k) {
+    const float sc = key_to_float(rkey[0]);
+    my_w = expf(sc);
+    my_e = static_cast<int>(rflat[0]);  // < sqrt_n^2 <= N by construction
+    const int64_t o = t * k + lane;
+    if (a.scores) a.scores[o] = sc;
+    if (a.indices) reinterpret_cast<int32_t*>(a.indices)[o] = my_e;
+    if (a.weights) a.weights[o] = my_w;
+    if (my_e >= N) my_e = -1;
   }
+  float2 acc[HV][4], xf[HV][4];
+  {
+    uint4 xv[HV];
+    load_x_row<HV>(x, t, c0, H, xv, acc);
+    unpack_row<HV>(xv, xf);
+  }
+  gather_pairs<HV>(my_e, my_w, k, c0, H, xf, up, down, acc, nullptr);
   store_row<HV, false>(acc, t, c0, H, residual, y);
 }
 
@@ -551,8 +585,8 @@ extern "C" int omni_route_expert_fused(const float* logits, int64_t ld_logits, c
   a.T = num_tokens, a.n = sqrt_n, a.k = k, a.kk = sqrt_n < k ? sqrt_n : k;
   a.cells = sel::region_cells(a.kk, k);
   a.scores = scores, a.indices = indices, a.idx_is_i64 = 0, a.weights = weights;
-  OMNI_REQUIRE(a.cells <= 128, "omni_route_expert_fused: k = %d needs %d candidate cells, more than this kernel holds "
-               "(use omni_router_logits_topk + omni_expert_fused)", k, a.cells);
+  OMNI_REQUIRE(k <= 32 && a.cells <= 128, "omni_route_expert_fused handles k <= 32 (got %d, %d candidate cells); "
+               "use omni_router_logits_topk + omni_expert_fused", k, a.cells);
   if (num_tokens == 0) return 0;
   OMNI_REQUIRE(logits && x && up && down && y, "NULL argument");
   OMNI_REQUIRE(aligned16(x) && aligned16(up) && aligned16(down) && aligned16(y) && aligned16(residual),

@@ -34,7 +34,7 @@ def region_cells(sqrt_n: int, k: int) -> int:
 def use_routed_kernel(num_experts: int, hidden: int, sqrt_n: int, k: int) -> bool:
     """True when router selection and routed experts can run as the single fused kernel
     (``omni_route_expert_fused``): the fused-expert regime plus its limits on the router shape."""
-    return (use_fused_path(num_experts, hidden) and sqrt_n <= 256 and 1 <= k <= sqrt_n * sqrt_n
+    return (use_fused_path(num_experts, hidden) and sqrt_n <= 256 and 1 <= k <= min(32, sqrt_n * sqrt_n)
             and sqrt_n * sqrt_n <= num_experts and region_cells(sqrt_n, k) <= 128)
 
 
