@@ -82,6 +82,8 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
   }
   const int count = (P - w0 < kRun) ? static_cast<int>(P - w0) : kRun;
   const int slabs = ceil_div(H, HV * 256);
+  // Up rows stream through once; the token rows are gathered k times and should keep their place in L2
+  const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
   int cur_e = -1;
   uint4 row[HV];
   bool bad_e = false, bad_t = false;
@@ -99,13 +101,13 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
 #pragma unroll
       for (int v = 0; v < HV; ++v) {
         const int c = c0 + v * 256;
-        xv[v] = c < H ? ldg128(x + t * H + c) : make_uint4(0, 0, 0, 0);
+        xv[v] = c < H ? ldg128_hint(x + t * H + c, pol_keep) : make_uint4(0, 0, 0, 0);
       }
       if (e != cur_e || slabs > 1) {
 #pragma unroll
         for (int v = 0; v < HV; ++v) {
           const int c = c0 + v * 256;
-          row[v] = c < H ? ldg128(up + static_cast<int64_t>(e) * H + c) : make_uint4(0, 0, 0, 0);
+          row[v] = c < H ? ldg128_hint(up + static_cast<int64_t>(e) * H + c, pol_stream) : make_uint4(0, 0, 0, 0);
         }
         cur_e = e;
       }

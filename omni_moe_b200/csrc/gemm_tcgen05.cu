@@ -655,6 +655,22 @@ extern "C" int omni_router_gate(const void* x, const void* gate_x, const void* g
   if (num_tokens == 0) return 0;
   OMNI_REQUIRE(x && gate_x && gate_y && logits && status, "NULL argument");
   OMNI_REQUIRE(aligned16(x) && aligned16(gate_x) && aligned16(gate_y) && aligned16(logits), "pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_pairs() && sqrt_n >= 128 && num_tokens >= 2 * BM * 16) {
+    // Wide router grids on many tokens: the CTA-pair kernel with router tiles only (rank 0 holds 128
+    // x-axis keys, rank 1 the same 128 y-axis keys of a tile column) runs at GEMM efficiency.
+    CUtensorMap ma, mx, my;
+    if (int e = make_map(&ma, x, num_tokens, hidden, BM)) return e;
+    if (int e = make_map(&mx, gate_x, sqrt_n, hidden, 128)) return e;
+    if (int e = make_map(&my, gate_y, sqrt_n, hidden, 128)) return e;
+    GemmArgs g{};
+    g.M = static_cast<int>(num_tokens), g.N = 0, g.K = hidden, g.dual = 0;
+    g.tiles_m = ceil_div(g.M, 2 * BM);
+    g.tiles_n = g.tiles_n_axis = 0;
+    g.router_tiles = ceil_div(sqrt_n, 128), g.router_n = sqrt_n, g.logits = logits;
+    g.out = nullptr, g.ldo = 0, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+    return launch_pair<EPI_SWIGLU, true>(ma, mx, my, mx, my, g, st);
+  }
   const int bn = sqrt_n <= 64 ? 64 : (sqrt_n <= 128 ? 128 : 256);
   CUtensorMap ma, mx, my;
   if (int e = make_map(&ma, x, num_tokens, hidden, BM)) return e;
@@ -666,7 +682,6 @@ extern "C" int omni_router_gate(const void* x, const void* gate_x, const void* g
   g.tiles_n_axis = ceil_div(sqrt_n, bn);
   g.tiles_n = 2 * g.tiles_n_axis;
   g.out = logits, g.ldo = 2 * static_cast<int64_t>(sqrt_n), g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<64, EPI_F32>(ma, mx, my, g, st);
   if (bn == 128) return launch<128, EPI_F32>(ma, mx, my, g, st);
   return launch<256, EPI_F32>(ma, mx, my, g, st);

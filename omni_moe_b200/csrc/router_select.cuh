@@ -221,7 +221,7 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpS
       float sum = 0.f;
 #pragma unroll
       for (int e = 0; e < VPL; ++e)
-        if (e * 32 + lane < n) sum += expf(v[e] - mx);
+        if (e * 32 + lane < n) sum += __expf(v[e] - mx);  // ex2-based: 2 ulp, the sum only shifts all log-probs
       sum = warp_sum(sum);
       const float lse = logf(sum);
 #pragma unroll

@@ -129,10 +129,22 @@ __global__ void __launch_bounds__(kThreads) radix_scan_kernel(int* hist /*[bins]
   const int b = blockIdx.x * kWarps + warp;
   if (b < bins) {
     int* row = hist + static_cast<size_t>(b) * tiles;
-    const int per = ceil_div(tiles, 32);
+    // chunk per lane, a multiple of 4 so that rows whose length is a multiple of 4 can move as int4
+    const int per = ceil_div(ceil_div(tiles, 32), 4) * 4;
     const int lo = min(tiles, lane * per), hi = min(tiles, lo + per);
+    const bool vec = (tiles & 3) == 0;  // then lo, hi and the row start are 16-byte aligned
     int sum = 0;
-    for (int t = lo; t < hi; ++t) sum += row[t];
+    if (vec) {
+      const int4* r4 = reinterpret_cast<const int4*>(row + lo);
+      const int n4 = (hi - lo) >> 2;
+#pragma unroll 8
+      for (int i = 0; i < n4; ++i) {
+        const int4 v = r4[i];
+        sum += v.x + v.y + v.z + v.w;
+      }
+    } else {
+      for (int t = lo; t < hi; ++t) sum += row[t];
+    }
     int inc = sum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -140,10 +152,23 @@ __global__ void __launch_bounds__(kThreads) radix_scan_kernel(int* hist /*[bins]
       if (lane >= o) inc += y;
     }
     int run = inc - sum;
-    for (int t = lo; t < hi; ++t) {
-      const int v = row[t];
-      row[t] = run;
-      run += v;
+    if (vec) {
+      int4* r4 = reinterpret_cast<int4*>(row + lo);
+      const int n4 = (hi - lo) >> 2;
+#pragma unroll 8
+      for (int i = 0; i < n4; ++i) {
+        const int4 v = r4[i];
+        int4 o;
+        o.x = run, o.y = run + v.x, o.z = o.y + v.y, o.w = o.z + v.z;
+        run = o.w + v.w;
+        r4[i] = o;
+      }
+    } else {
+      for (int t = lo; t < hi; ++t) {
+        const int v = row[t];
+        row[t] = run;
+        run += v;
+      }
     }
     if (lane == 31) bin_total[b] = inc;
   }
