@@ -1,0 +1,82 @@
+"""The shapes of the reference project's own test files (tests/test_router.py:103-110,
+tests/test_expert.py:183-186, tests/test_mlp.py:146-149), called through the reference's import
+paths, with the validation the reference leaves out or only prints: here a mismatch fails, and the
+router's indices are compared, not only its scores."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import omni_oracle as orc
+from _util import assert_close, gen
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("case", [(1024, 64, 16), (1024, 64, 32), (1024, 128, 16), (1024, 128, 32), (1024, 256, 16),
+                                  (1024, 256, 32)])
+def test_router_forward_reference_cases(case):
+    from omni_moe.ops.triton import triton_omni_router_func
+    num_tokens, num_keys, top_k = case
+    g = gen(0)
+    lx = torch.randn(num_tokens, num_keys, generator=g).bfloat16()   # the reference draws bf16 normals
+    ly = torch.randn(num_tokens, num_keys, generator=g).bfloat16()
+    scores, indices = triton_omni_router_func(lx.cuda(), ly.cuda(), num_keys, top_k)
+    assert scores.dtype == torch.bfloat16 and indices.dtype == torch.int32
+    es, ei = orc.router_topk(lx, ly, num_keys, top_k)
+    np.testing.assert_array_equal(indices.cpu().numpy(), ei)            # bit-exact experts, ties to the lower index
+    # scores: fp32 sums rounded once to the input dtype
+    assert torch.equal(scores.cpu(), torch.from_numpy(es).bfloat16())
+    # the mirror of the reference searches the full grid; pruning never changes the scores
+    fs, _ = orc.router_topk_full_grid(lx, ly, num_keys, top_k)
+    np.testing.assert_array_equal(es, fs)
+
+
+@pytest.mark.parametrize("num_experts", [1024, 4096, 16384, 65536])
+def test_expert_forward_reference_cases(num_experts):
+    from omni_moe.ops.triton import triton_omni_expert_func
+    num_tokens, hidden, top_k = 1024, 1024, 32
+    g = gen(0)
+    hs = (torch.randn(num_tokens, hidden, generator=g) * 0.5).bfloat16()
+    up = (torch.randn(num_experts, hidden, generator=g) * 0.1).bfloat16()
+    dn = (torch.randn(num_experts, hidden, generator=g) * 0.1).bfloat16()
+    rw = (torch.randn(num_tokens, top_k, generator=g) * 0.1).bfloat16()
+    idx = torch.randint(0, num_experts, (num_tokens, top_k), generator=g, dtype=torch.int32)  # duplicates allowed
+    y = triton_omni_expert_func(hs.cuda(), up.cuda(), dn.cuda(), rw.cuda(), idx.cuda())
+    assert y.dtype == torch.bfloat16 and y.shape == (num_tokens, hidden)
+    assert_close(y, orc.expert_forward(hs, up, dn, rw, idx), what="expert states")
+
+
+@pytest.mark.parametrize("intermediate", [1024, 4096, 16384, 65536])
+def test_mlp_forward_reference_cases(intermediate):
+    from omni_moe.ops.triton import triton_omni_mlp_func
+    num_tokens, hidden = 1024, 1024
+    g = gen(42)
+    hs = (torch.randn(num_tokens, hidden, generator=g) * 0.5).bfloat16()
+    wg = (torch.randn(intermediate, hidden, generator=g) * 0.1).bfloat16()
+    wu = (torch.randn(intermediate, hidden, generator=g) * 0.1).bfloat16()
+    wd = (torch.randn(hidden, intermediate, generator=g) * 0.1).bfloat16()
+    y = triton_omni_mlp_func(hs.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
+    assert y.dtype == torch.bfloat16
+    e = orc.mlp_forward(hs, wg, wu, wd)
+    # With the reference's N(0, 0.1) weights the [T, I] activation has entries of order 1 and the outputs
+    # are sums of thousands of them that largely cancel.  Rounding the activation to bf16 (which the
+    # reference does as well, omni_moe/ops/triton/omni_mlp.py:162-176) then leaves an absolute error of
+    # about sqrt(I) * 2^-9 * |act * w| whatever the size of the output element, so the error is judged
+    # against the scale of the output rather than element by element.
+    err = (y.float().cpu() - e).abs()
+    assert float(err.max()) <= 2e-2 * float(e.abs().max()) + 2e-2
+    assert float(err.mean()) <= 2e-2 * float(e.abs().mean())
+
+
+def test_readme_quick_start():
+    # README.md:58-79 of the reference: construct, move to the GPU in bf16, call on [1, 4096, 1024]
+    from omni_moe.modules.omni_moe import OmniMoE, OmniMoEConfig
+    torch.manual_seed(0)
+    config = OmniMoEConfig(hidden_size=1024, intermediate_size=4096, hidden_act="silu", num_experts=4096,
+                           num_experts_per_token=16)
+    layer = OmniMoE(config).to(torch.bfloat16).cuda()      # as constructed: training mode, batch statistics
+    x = torch.randn(1, 4096, 1024, device="cuda", dtype=torch.bfloat16)
+    y = layer(x)
+    layer.check_status()
+    assert y.shape == x.shape and y.dtype == torch.bfloat16 and bool(torch.isfinite(y).all())
+    assert int(layer.router_norm_x.num_batches_tracked) == 1
