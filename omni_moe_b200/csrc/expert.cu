@@ -87,6 +87,52 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
   int cur_e = -1;
   uint4 row[HV];
   bool bad_e = false, bad_t = false;
+  if (slabs == 1) {
+    // Common case, a whole row per lane set: the token row of pair i+1 is requested before pair i is
+    // computed, so a warp always has two gathers in flight.
+    const int c0 = lane * 8;
+    auto fetch_x = [&](int i, uint4 (&dst)[HV]) {
+      const int64_t t = __shfl_sync(FULL_MASK, my_t, i);
+      const bool ok = t >= 0 && t < T;
+#pragma unroll
+      for (int v = 0; v < HV; ++v) {
+        const int c = c0 + v * 256;
+        dst[v] = (ok && c < H) ? ldg128_hint(x + t * H + c, pol_keep) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    uint4 xcur[HV], xnext[HV];
+    fetch_x(0, xcur);
+    for (int i = 0; i < count; ++i) {
+      if (i + 1 < count) fetch_x(i + 1, xnext);
+      const int pair = __shfl_sync(FULL_MASK, my_pair, i);
+      const int e = __shfl_sync(FULL_MASK, my_e, i);
+      const float g = __shfl_sync(FULL_MASK, my_g, i);
+      const int64_t t = __shfl_sync(FULL_MASK, my_t, i);
+      const bool e_ok = e >= 0 && e < N, t_ok = pair >= 0 && t >= 0 && t < T;
+      if (!e_ok) {
+        bad_e = true;
+        if (lane == 0 && pair >= 0 && pair < P) coef[pair] = 0.f;
+      } else if (!t_ok) {
+        bad_t = true;
+      } else {
+        if (e != cur_e) {
+#pragma unroll
+          for (int v = 0; v < HV; ++v) {
+            const int c = c0 + v * 256;
+            row[v] = c < H ? ldg128_hint(up + static_cast<int64_t>(e) * H + c, pol_stream) : make_uint4(0, 0, 0, 0);
+          }
+          cur_e = e;
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int v = 0; v < HV; ++v) acc = dot8(xcur[v], row[v], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) coef[pair] = g * silu(acc);
+      }
+#pragma unroll
+      for (int v = 0; v < HV; ++v) xcur[v] = xnext[v];
+    }
+  } else
   for (int i = 0; i < count; ++i) {
     const int pair = __shfl_sync(FULL_MASK, my_pair, i);
     const int e = __shfl_sync(FULL_MASK, my_e, i);
