@@ -184,6 +184,28 @@ __device__ __forceinline__ void build_region_table(RegionTable& rt, int kk, int 
 
 // Selects the k experts of token t.  On return lane (r % 32) holds, in slot r / 32, the score key
 // (see float_to_key) and the flat expert index of rank r.
+// The same ranking on the 32-bit keys alone (half the compare work).  Entries with equal keys get
+// equal ranks, so the caller must check that the ranks it uses are distinct and fall back to the
+// packed 64-bit ranking when they are not.
+__device__ __forceinline__ int rank32_among_64(const uint32_t* all, uint32_t mine) {
+  int rank = 0;
+  const uint4* p = reinterpret_cast<const uint4*>(all);
+#pragma unroll
+  for (int q = 0; q < 16; ++q) {
+    const uint4 o = p[q];
+    rank += (o.x > mine) + (o.y > mine) + (o.z > mine) + (o.w > mine);
+  }
+  return rank;
+}
+// True if, over the warp, exactly `want` of the given ranks are below `want` and they are all
+// different (want <= 32): then the `want` best entries are strictly ordered by key alone.
+__device__ __forceinline__ bool ranks_distinct(int r0, int r1, int want) {
+  const unsigned bits = (r0 < want ? 1u << r0 : 0u) | (r1 < want ? 1u << r1 : 0u);
+  const unsigned mask = __reduce_or_sync(FULL_MASK, bits);
+  const int cnt = __reduce_add_sync(FULL_MASK, (r0 < want) + (r1 < want));
+  return cnt == want && __popc(mask) == want;
+}
+
 template <int VPL, int CPL, bool PRE>
 __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpScratch<VPL, CPL>& w,
                                              const uint16_t* cell_table, uint32_t (&rkey)[kMaxK / 32],
@@ -244,22 +266,37 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpS
       }
     }
     if constexpr (kSmallAxis) {
-      unsigned long long mine[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const uint32_t c = e * 32 + lane;
-        mine[e] = (static_cast<unsigned long long>(key[e]) << 32) | (0xffffffffu - c);
-        w.pack[c] = mine[e];
-      }
-      __syncwarp();
       float* so = axis == 0 ? sx : sy;
       int* io = axis == 0 ? ix : iy;
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int r = rank_among_64(w.pack, mine[e]);
-        if (r < kk) so[r] = key_to_float(key[e]), io[r] = e * 32 + lane;
+      bool done = false;
+      if (kk <= 32) {  // fast path: rank on the keys alone, valid when no tie touches the best kk
+        uint32_t* k32 = reinterpret_cast<uint32_t*>(w.pack);
+        k32[lane] = key[0], k32[32 + lane] = key[1];
+        __syncwarp();
+        const int r0 = rank32_among_64(k32, key[0]), r1 = rank32_among_64(k32, key[1]);
+        done = ranks_distinct(r0, r1, kk);
+        if (done) {
+          if (r0 < kk) so[r0] = key_to_float(key[0]), io[r0] = lane;
+          if (r1 < kk) so[r1] = key_to_float(key[1]), io[r1] = 32 + lane;
+        }
+        __syncwarp();
       }
-      __syncwarp();
+      if (!done) {
+        unsigned long long mine[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t c = e * 32 + lane;
+          mine[e] = (static_cast<unsigned long long>(key[e]) << 32) | (0xffffffffu - c);
+          w.pack[c] = mine[e];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int r = rank_among_64(w.pack, mine[e]);
+          if (r < kk) so[r] = key_to_float(key[e]), io[r] = e * 32 + lane;
+        }
+        __syncwarp();
+      }
     } else {
       uint32_t sub[VPL];
 #pragma unroll
@@ -289,20 +326,35 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpS
   for (int s = 0; s < kMaxK / 32; ++s) rkey[s] = 0, rflat[s] = 0;
   uint32_t last_key = 0;
   if constexpr (kSmallCells) {
-    unsigned long long mine[2];
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      // padding cells have key 0 and can never outrank a real one; real cells differ in `flat`
-      mine[q] = (static_cast<unsigned long long>(ckey[q]) << 32) | (0xffffffffu - cflat[q]);
-      w.pack[q * 32 + lane] = mine[q];
+    bool done = false;
+    if (k <= 32) {  // fast path on the score keys alone (see the axis selection above)
+      uint32_t* k32 = reinterpret_cast<uint32_t*>(w.pack);
+      k32[lane] = ckey[0], k32[32 + lane] = ckey[1];
+      __syncwarp();
+      const int r0 = rank32_among_64(k32, ckey[0]), r1 = rank32_among_64(k32, ckey[1]);
+      done = ranks_distinct(r0, r1, k);
+      if (done) {
+        if (r0 < k) w.rk[r0] = ckey[0], w.rf[r0] = cflat[0];
+        if (r1 < k) w.rk[r1] = ckey[1], w.rf[r1] = cflat[1];
+      }
+      __syncwarp();
     }
-    __syncwarp();
+    if (!done) {
+      unsigned long long mine[2];
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      const int r = rank_among_64(w.pack, mine[q]);
-      if (r < k && ckey[q] != 0) w.rk[r] = ckey[q], w.rf[r] = cflat[q];
+      for (int q = 0; q < 2; ++q) {
+        // padding cells have key 0 and can never outrank a real one; real cells differ in `flat`
+        mine[q] = (static_cast<unsigned long long>(ckey[q]) << 32) | (0xffffffffu - cflat[q]);
+        w.pack[q * 32 + lane] = mine[q];
+      }
+      __syncwarp();
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int r = rank_among_64(w.pack, mine[q]);
+        if (r < k && ckey[q] != 0) w.rk[r] = ckey[q], w.rf[r] = cflat[q];
+      }
+      __syncwarp();
     }
-    __syncwarp();
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       const int r = s * 32 + lane;
