@@ -169,25 +169,37 @@ def time_e2e(slots, steps, warmup, dist_on, dev):
 
 
 def time_gate_up(slots, reps):
-    """Average duration of the dominant kernel alone (CUDA events on its stream, slots rotated)."""
+    """Average duration of the dominant kernel alone: `SLOTS` launches (one per weight set) captured in a
+    CUDA graph so that host launch cost does not count, replays timed with CUDA events on the replay
+    stream."""
     from omni_moe_b200 import _lib
     lib = _lib.load()
     t, h, i = CFG["tokens"], CFG["hidden"], CFG["intermediate"]
 
-    def launch(s):
+    def launch(s, stream_ptr):
         m, b, g = s["module"], s["graph"].buffers, s["graph"]
         _lib.check(lib.omni_mlp_gate_up(g.x.data_ptr(), m.gate_proj.weight.data_ptr(), m.up_proj.weight.data_ptr(), t, h, i,
-                                        b.act.data_ptr(), b.status.data_ptr(), torch.cuda.current_stream().cuda_stream))
-    for r in range(4):
-        launch(slots[r % SLOTS])
+                                        b.act.data_ptr(), b.status.data_ptr(), stream_ptr))
+    for s in slots:
+        launch(s, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
-    for r, (a, b) in enumerate(evs):
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for s in slots:
+                launch(s, side.cuda_stream)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(max(reps // SLOTS, 3)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        launch(slots[r % SLOTS])
+        graph.replay()
         b.record()
-    torch.cuda.synchronize()
-    return statistics.mean(a.elapsed_time(b) for a, b in evs)
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) / SLOTS)
+    return statistics.mean(times)
 
 
 def _oracle_setup(sample_tokens: int):

@@ -1,6 +1,7 @@
 // Error reporting shared by all entry points of libomni_moe_b200.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -15,6 +16,14 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
   return code;
+}
+
+bool pdl_enabled() {
+  static const bool v = [] {
+    const char* e = getenv("OMNI_MOE_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return v;
 }
 
 int check_launch(const char* what) {

@@ -23,6 +23,29 @@ int check_launch(const char* what);
 
 constexpr unsigned FULL_MASK = 0xffffffffu;
 
+// Programmatic dependent launch.  A kernel launched with launch_after_predecessor() may start while the
+// kernel before it on the stream is still running; pdl_wait() blocks until that kernel has completed
+// and its memory is visible, so everything before pdl_wait() (shared-memory set-up, TMEM allocation,
+// descriptor prefetch) overlaps the predecessor's tail.  pdl_launch_dependents() lets the next kernel
+// start early.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launches `kernel` so that it may overlap the tail of the previous kernel on `st` (see pdl_wait).
+// OMNI_MOE_B200_PDL=0 turns the overlap off (ordinary stream order).
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after_predecessor(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                            Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 

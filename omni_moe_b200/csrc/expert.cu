@@ -489,6 +489,7 @@ __global__ void __launch_bounds__(kThreads, HV <= 4 ? 2 : 1) expert_routed_kerne
   __shared__ sel::WarpScratch<VPL, CPL> s_warp[kWarps];
   __shared__ sel::RegionTable s_region;
   sel::build_region_table(s_region, a.kk, a.k, kWarps);
+  pdl_wait();  // everything above is shared-memory set-up; the logits and y come from earlier kernels
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
   if (t >= a.T) return;
@@ -645,7 +646,8 @@ extern "C" int omni_route_expert_fused(const float* logits, int64_t ld_logits, c
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
 #define OMNI_ROUTED(HV, VPL, CPL) \
-  expert_routed_kernel<HV, VPL, CPL><<<grid, kThreads, 0, st>>>(a, xb, ub, db, hidden, num_experts, residual, y)
+  launch_after_predecessor(expert_routed_kernel<HV, VPL, CPL>, dim3(grid), dim3(kThreads), 0, st, a, xb, ub, db, hidden, \
+                           num_experts, residual, y)
 #define OMNI_ROUTED_HV(VPL, CPL)                  \
   do {                                            \
     if (hidden <= 256) OMNI_ROUTED(1, VPL, CPL);  \

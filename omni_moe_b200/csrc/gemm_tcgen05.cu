@@ -415,6 +415,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();  // the next kernel on the stream may set itself up while this one computes
+  pdl_wait();               // the kernel before this one has completed: its outputs may be read now
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) -------------------------------
@@ -624,7 +626,7 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& 
   const int max_pairs = sm_count() / 2;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
   if (g.grid_limit > 0 && g.grid_limit < pairs) pairs = g.grid_limit;
-  gemm_pair_kernel<EPI, ROUTER><<<2 * pairs, kThreads, C::kSmem, st>>>(a, b0, b1, r0, r1, g);
+  launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, g);
   return check_launch("gemm_pair_kernel");
 }
 
