@@ -88,6 +88,7 @@ def main():
         layer = PartitionedOmniMoE.__new__(PartitionedOmniMoE)   # the tables are already slices: skip the cutting
         torch.nn.Module.__init__(layer)
         layer.group, layer.part, layer.inner = None, part, inner
+        layer._side, layer.partial_dtype = None, torch.bfloat16
         run = lambda: layer(x)
     else:
         inner = build_module(cfg, dev)

@@ -209,10 +209,16 @@ class PartitionedOmniMoE(torch.nn.Module):
         # the full tables are dropped: this rank keeps only its rows
         module.up_embed.weight = torch.nn.Parameter(up, requires_grad=False)
         module.down_embed.weight = torch.nn.Parameter(down, requires_grad=False)
+        self._side = None
+        #: dtype of the per-rank partial sums that are reduce-scattered: bfloat16 halves the bytes on
+        #: NVLink at the cost of one rounding per rank; float32 keeps the single-GPU accuracy
+        self.partial_dtype = torch.bfloat16
 
     @torch.no_grad()
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
-        from .ops.mlp import mlp_forward
+        """Streams: the gate/up GEMM of the shared MLP (which needs only x) runs on a side stream while
+        the main stream routes, exchanges pairs and token rows, computes this rank's partial expert
+        states and reduce-scatters them; the down projection then adds the reduced states."""
         from .ops.router import router_gate_topk
         m = self.inner
         if m.training:
@@ -220,13 +226,32 @@ class PartitionedOmniMoE(torch.nn.Module):
         _lib.require_cuda(hidden_states)
         shape = hidden_states.shape
         x = hidden_states.detach().reshape(-1, m.hidden_size).to(torch.bfloat16).contiguous()
+        t, h, i = x.size(0), m.hidden_size, m.intermediate_size
+        dev = x.device
         wg, wu, wd, kx, ky, up_l, down_l = m._operands()
         scale, shift = m._bn_fold_eval()
-        status = torch.zeros(1, device=x.device, dtype=torch.int32)
-        scores, indices, weights = router_gate_topk(x, kx, ky, m.top_k, scale, shift, status=status)
-        states = partitioned_expert_states(x, indices, weights, up_l, down_l, self.part, self.group,
-                                           local_fn=lambda r, u, d: local_partial_states(r, u, d, status=status))
-        y = mlp_forward(x, wg, wu, wd, residual=states, status=status)
+        status = torch.zeros(1, device=dev, dtype=torch.int32)
+        lib = _lib.load()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=dev)
+        act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
+        y = torch.empty((t, h), device=dev, dtype=torch.bfloat16)
+        with torch.cuda.device(dev):
+            main = torch.cuda.current_stream()
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                _lib.check(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, act.data_ptr(),
+                                                status.data_ptr(), self._side.cuda_stream))
+                for tns in (x, wg, wu, act):
+                    tns.record_stream(self._side)
+            scores, indices, weights = router_gate_topk(x, kx, ky, m.top_k, scale, shift, status=status)
+            states = partitioned_expert_states(
+                x, indices, weights, up_l, down_l, self.part, self.group,
+                local_fn=lambda r, u, d: local_partial_states(r, u, d, out_dtype=self.partial_dtype, status=status))
+            states = states.float()  # [T_local, H]: the down-projection epilogue adds fp32
+            main.wait_stream(self._side)
+            _lib.check(lib.omni_mlp_down(act.data_ptr(), wd.data_ptr(), t, h, i, states.data_ptr(), y.data_ptr(),
+                                         status.data_ptr(), main.cuda_stream))
         m.last_routing = (scores, indices, weights)
         m.last_status = status
         return y.view(shape).to(hidden_states.dtype)
