@@ -295,6 +295,13 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=dev)
 
+    cpu_line = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        # first, while the process may still run on every host core (the placement below narrows that)
+        rate, cores, sample = cpu_oracle_rate()
+        cpu_line = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+    from omni_moe_b200.host import bind_near_gpu
+    placement = bind_near_gpu(local_rank)   # before the pinned host buffers are allocated
     slots = build_slots(dev)
     from omni_moe_b200.modules.omni_moe import OmniMoE
     sampler = ClockSampler(local_rank)
@@ -321,7 +328,8 @@ def main():
                        "launch": "one CUDA graph per step"},
             "e2e": {"value": tokens_total / (ms_e2e * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": CFG["tokens"] * CFG["hidden"] * 2, "d2h_bytes_per_step": CFG["tokens"] * CFG["hidden"] * 2,
-                    "ms_per_step": ms_e2e / args.steps, "pipeline": f"{SLOTS} slots, one stream each"},
+                    "ms_per_step": ms_e2e / args.steps, "pipeline": f"{SLOTS} slots, one stream each",
+                    "host_placement": placement["reason"]},
             "gpu_launches": OmniMoE.kernels_per_forward(CFG["experts"], CFG["hidden"], 64, CFG["top_k"]) * args.steps,
             "clocks": clocks,
             "roofline": {"kernel": "gemm_pair_kernel<EPI_SWIGLU> (gate/up projections + SwiGLU, tcgen05 cta_group::2)", "bound": "tensor",
@@ -329,9 +337,8 @@ def main():
                          "traffic": GATE_UP_DRAM_BYTES_PER_LAUNCH, "peak_source": pk["src"] + " (burst: kernel timed alone)",
                          "ms_per_launch": gemm_ms, "flops_per_launch": flops},
         }
-        if world == 1 and not args.no_cpu_baseline:
-            rate, cores, sample = cpu_oracle_rate()
-            line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        if cpu_line is not None:
+            line["cpu_baseline"] = cpu_line
         print(json.dumps(line), flush=True)
     if dist_on:
         torch.distributed.barrier()
