@@ -264,6 +264,49 @@ OMNI_API int omni_mlp_down(const void *act, const void *down_w,
                   int64_t num_tokens, int hidden, int intermediate,
                   const float *residual, void *y, int32_t *status, void *stream);
 
+/*
+ * ---- backward of the three operators --------------------------------------------------------
+ *
+ * Backward of the router op, scores[t,j] = lpx[t, ix] + lpy[t, iy] with indices[t,j] = ix*sqrt_n + iy:
+ * every score gradient is added to one column of each axis.  Replaces _omni_router_backward and its
+ * Triton kernel (omni_moe/ops/triton/omni_router.py:104-164,235-274), without atomics: the sums
+ * come out the same on every run.
+ *   dscores [T, k] float32; indices [T, k] int32 or int64; dlog_probs_x / _y [T, sqrt_n] float32,
+ *   fully written (columns no expert touches get 0).  sqrt_n <= 1024.
+ */
+OMNI_API int omni_router_bwd(const float *dscores, const void *indices, int idx_is_i64, int64_t num_tokens,
+                    int sqrt_n, int k, float *dlog_probs_x, float *dlog_probs_y, int32_t *status,
+                    void *stream);
+
+/*
+ * Backward of the routed-expert op, replacing omni_expert_backward and its Triton kernels
+ * (omni_moe/ops/triton/omni_expert.py:380-917,1067-1277).  Per pair p = (t, j), e = indices[t,j],
+ * g = weights[t,j]:  S = x[t].Up[e],  h = silu(S),  dA = dy[t].Down[e],
+ *   dg[t,j] = dA*h,   cdown[t,j] = g*h,   ds[t,j] = dA*g*silu'(S)
+ *   dx[t]   = sum_j ds[t,j] * Up[e]          -> omni_expert_combine(up, ds, indices, ...)
+ *   dUp[e]  = sum_{p on e} ds[p] * x[t_p],   dDown[e] = sum_{p on e} cdown[p] * dy[t_p]
+ *
+ * omni_expert_bwd_dots: token-centric; writes ds, cdown, dg ([T, k] float32 each).
+ * omni_expert_bwd_rows: expert-centric over the schedule of the same indices (omni_schedule with
+ *   expert_ids / offsets / meta requested): one gradient row per touched expert, pairs summed in
+ *   ascending pair order in fp32, no atomics.  compact = 0: row e of d_up / d_down ([N, H], rows of
+ *   untouched experts are NOT written: zero the tables first); compact = 1: row s of [U, H] for
+ *   segment s, expert expert_ids[s] (the reference returns dense zero-filled tables,
+ *   omni_expert.py:1097-1098; compact rows avoid 2*N*H bytes of zeros for large tables).
+ *   num_segments: device pointer to U (meta[0] of omni_schedule); max_segments: host bound on U
+ *   (min(T*k, N)) that sizes the launch.  out_dtype: OMNI_F32 or OMNI_BF16.
+ * Limits: H % 8 == 0, 16-byte aligned pointers.
+ */
+OMNI_API int omni_expert_bwd_dots(const void *x, const void *up, const void *down, const void *dy,
+                         const float *weights, const int32_t *indices, int64_t num_tokens, int k,
+                         int hidden, int64_t num_experts, float *ds, float *cdown, float *dg,
+                         int32_t *status, void *stream);
+OMNI_API int omni_expert_bwd_rows(const void *x, const void *dy, const float *ds, const float *cdown,
+                         const int32_t *sorted_pair_ids, const int32_t *expert_ids,
+                         const int32_t *offsets, const int32_t *num_segments, int64_t max_segments,
+                         int64_t num_tokens, int k, int hidden, int compact, void *d_up, void *d_down,
+                         int out_dtype, int32_t *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

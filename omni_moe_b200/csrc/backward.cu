@@ -1,0 +1,290 @@
+// Backward passes of the router op and of the routed-expert op.
+//
+// Router (scores[t,j] = lpx[t, ix] + lpy[t, iy]):
+//   dlpx[t, ix] += dscores[t,j],  dlpy[t, iy] += dscores[t,j]
+//   router_bwd_kernel: one warp per token, the two gradient rows live in shared memory; the lane
+//   (column mod 32) owns a column, so the adds of one column happen in program order of one lane:
+//   no atomics, the same bits on every run.
+//
+// Routed experts, per pair p = (t, j), e = indices[t, j], g = weights[t, j]:
+//   S  = x[t] . Up[e]            h = silu(S)          dA = dY[t] . Down[e]
+//   dg = dA * h                  c = g * h            dS = dA * g * silu'(S)
+//   dX[t]    += dS * Up[e]       (token-centric: the forward's combine kernel with Up and dS)
+//   dUp[e]   += dS * x[t]        dDown[e] += c * dY[t]      (expert-centric, needs the schedule)
+//   expert_bwd_dots_kernel  token-centric, one warp per token: both dot products of every pair, then
+//                           dS, c and dg at the pair's place in the [T, k] tables.
+//   expert_bwd_rows_kernel  one warp per expert segment of the schedule: walks the segment's pairs in
+//                           sorted (= ascending pair id) order and accumulates both gradient rows in
+//                           fp32 registers, 1024 columns at a time; each touched row is written once.
+//                           Rows no pair touches are not written (the caller zero-fills a dense table
+//                           or asks for compact rows, one per segment).
+#include "common.cuh"
+
+namespace omni {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kWarps = kThreads / 32;
+
+// ------------------------------------------------------------------------------------------------
+// router
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) router_bwd_kernel(const float* __restrict__ dscores, const void* __restrict__ indices,
+                                                              int idx_is_i64, int64_t T, int n, int k, float* __restrict__ dlx,
+                                                              float* __restrict__ dly, int* __restrict__ status) {
+  extern __shared__ float s_rows[];  // per warp: n floats for the x axis, n for the y axis
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (t >= T) return;
+  float* sx = s_rows + static_cast<size_t>(warp) * 2 * n;
+  float* sy = sx + n;
+  for (int c = lane; c < 2 * n; c += 32) sx[c] = 0.f;
+  __syncwarp();
+  bool bad = false;
+  for (int j0 = 0; j0 < k; j0 += 32) {
+    const int j = j0 + lane;
+    int64_t e = -1;
+    float d = 0.f;
+    if (j < k) {
+      e = idx_is_i64 ? reinterpret_cast<const int64_t*>(indices)[t * k + j] : reinterpret_cast<const int32_t*>(indices)[t * k + j];
+      d = dscores[t * k + j];
+      if (e < 0 || e >= static_cast<int64_t>(n) * n) bad = true, e = -1;
+    }
+    const int ix = e < 0 ? -1 : static_cast<int>(e / n);
+    const int iy = e < 0 ? -1 : static_cast<int>(e - static_cast<int64_t>(ix) * n);
+    const int cnt = min(32, k - j0);
+    for (int i = 0; i < cnt; ++i) {
+      const int bx = __shfl_sync(FULL_MASK, ix, i), by = __shfl_sync(FULL_MASK, iy, i);
+      const float bd = __shfl_sync(FULL_MASK, d, i);
+      if (bx >= 0) {
+        if ((bx & 31) == lane) sx[bx] += bd;
+        if ((by & 31) == lane) sy[by] += bd;
+      }
+    }
+  }
+  __syncwarp();
+  for (int c = lane; c < n; c += 32) {
+    dlx[t * n + c] = sx[c];
+    dly[t * n + c] = sy[c];
+  }
+  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
+// ------------------------------------------------------------------------------------------------
+// routed experts
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float2 dot8f(const uint4& a, const uint4& b, float2 acc) {
+  const uint32_t* pa = reinterpret_cast<const uint32_t*>(&a);
+  const uint32_t* pb = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc = __ffma2_rn(bf16x2_to_float2(pa[i]), bf16x2_to_float2(pb[i]), acc);
+  return acc;
+}
+__device__ __forceinline__ void axpy8f(float c, const uint4& d, float2 (&acc)[4]) {
+  const uint32_t* pd = reinterpret_cast<const uint32_t*>(&d);
+  const float2 c2 = make_float2(c, c);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = __ffma2_rn(c2, bf16x2_to_float2(pd[i]), acc[i]);
+}
+
+// One warp per token.  The token's x and dY rows are read through L1 (every pair of the token reads
+// them again), the expert rows are streamed past it.
+__global__ void __launch_bounds__(kThreads) expert_bwd_dots_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
+    const __nv_bfloat16* __restrict__ dy, const float* __restrict__ weights, const int32_t* __restrict__ indices, int64_t T,
+    int k, int H, int64_t N, float* __restrict__ ds, float* __restrict__ cdown, float* __restrict__ dg, int* __restrict__ status) {
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (t >= T) return;
+  const __nv_bfloat16* xr = x + t * H;
+  const __nv_bfloat16* dyr = dy + t * H;
+  bool bad = false;
+  for (int j0 = 0; j0 < k; j0 += 32) {
+    const int j = j0 + lane;
+    int my_e = -1;
+    float my_g = 0.f;
+    if (j < k) {
+      my_e = indices[t * k + j];
+      my_g = weights[t * k + j];
+      if (my_e < 0 || my_e >= N) bad = true, my_e = -1;
+    }
+    const int cnt = min(32, k - j0);
+    float my_ds = 0.f, my_c = 0.f, my_dg = 0.f;
+    for (int i = 0; i < cnt; ++i) {
+      const int e = __shfl_sync(FULL_MASK, my_e, i);
+      if (e < 0) continue;  // warp-uniform
+      const __nv_bfloat16* ur = up + static_cast<int64_t>(e) * H;
+      const __nv_bfloat16* dr = down + static_cast<int64_t>(e) * H;
+      float2 s2 = make_float2(0.f, 0.f), a2 = make_float2(0.f, 0.f);
+      for (int c0 = lane * 8; c0 < H; c0 += 1024) {
+        uint4 uv[4], dv[4], xv[4], gv[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = c0 + v * 256;
+          const bool ld = col < H;
+          uv[v] = ld ? ldg128(ur + col) : make_uint4(0, 0, 0, 0);
+          dv[v] = ld ? ldg128(dr + col) : make_uint4(0, 0, 0, 0);
+          xv[v] = ld ? *reinterpret_cast<const uint4*>(xr + col) : make_uint4(0, 0, 0, 0);
+          gv[v] = ld ? *reinterpret_cast<const uint4*>(dyr + col) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          s2 = dot8f(xv[v], uv[v], s2);
+          a2 = dot8f(gv[v], dv[v], a2);
+        }
+      }
+      const float S = warp_sum(s2.x + s2.y);
+      const float dA = warp_sum(a2.x + a2.y);
+      if (lane == i) {
+        const float sig = 1.0f / (1.0f + __expf(-S));
+        const float h = S * sig;
+        my_dg = dA * h;
+        my_c = my_g * h;
+        my_ds = dA * my_g * (sig * (1.0f + S * (1.0f - sig)));
+      }
+    }
+    if (j < k) {
+      ds[t * k + j] = my_ds;
+      cdown[t * k + j] = my_c;
+      dg[t * k + j] = my_dg;
+    }
+  }
+  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
+template <bool OUT_F32>
+__device__ __forceinline__ void store8(void* base, int64_t off, const float2 (&a)[4]) {
+  if (OUT_F32) {
+    float* o = reinterpret_cast<float*>(base) + off;
+    *reinterpret_cast<float4*>(o) = make_float4(a[0].x, a[0].y, a[1].x, a[1].y);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(a[2].x, a[2].y, a[3].x, a[3].y);
+  } else {
+    uint4 p;
+    p.x = float2_to_bf16x2(a[0].x, a[0].y), p.y = float2_to_bf16x2(a[1].x, a[1].y);
+    p.z = float2_to_bf16x2(a[2].x, a[2].y), p.w = float2_to_bf16x2(a[3].x, a[3].y);
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + off) = p;
+  }
+}
+
+// One warp per segment s of the schedule (expert expert_ids[s], sorted positions offsets[s] .. offsets[s+1]).
+template <bool OUT_F32>
+__global__ void __launch_bounds__(kThreads) expert_bwd_rows_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ ds,
+    const float* __restrict__ cdown, const int32_t* __restrict__ sorted_pair_ids, const int32_t* __restrict__ expert_ids,
+    const int32_t* __restrict__ offsets, const int32_t* __restrict__ num_segments, int64_t T, int k, int H, int compact,
+    void* __restrict__ d_up, void* __restrict__ d_down, int* __restrict__ status) {
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (s >= *num_segments) return;
+  const int begin = offsets[s], end = offsets[s + 1];
+  const int64_t row = compact ? s : static_cast<int64_t>(expert_ids[s]);
+  bool bad = false;
+  for (int c0 = lane * 8; c0 < H + lane * 8; c0 += 1024) {  // every lane makes the same number of trips
+    float2 au[4][4], ad[4][4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) au[v][q] = make_float2(0.f, 0.f), ad[v][q] = make_float2(0.f, 0.f);
+    for (int p0 = begin; p0 < end; p0 += 32) {
+      // lane l carries pair p0 + l of the segment
+      const int p = p0 + lane;
+      int my_t = -1;
+      float my_s = 0.f, my_c = 0.f;
+      if (p < end) {
+        const int pid = sorted_pair_ids[p];
+        const int64_t tok = pid / k;
+        if (pid < 0 || tok >= T) bad = true;
+        else my_t = static_cast<int>(tok), my_s = ds[pid], my_c = cdown[pid];
+      }
+      const int cnt = min(32, end - p0);
+      for (int i = 0; i < cnt; ++i) {
+        const int tok = __shfl_sync(FULL_MASK, my_t, i);
+        const float cs = __shfl_sync(FULL_MASK, my_s, i), cc = __shfl_sync(FULL_MASK, my_c, i);
+        if (tok < 0) continue;
+        const __nv_bfloat16* xr = x + static_cast<int64_t>(tok) * H;
+        const __nv_bfloat16* gr = dy + static_cast<int64_t>(tok) * H;
+        uint4 xv[4], gv[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = c0 + v * 256;
+          const bool ld = col < H;
+          xv[v] = ld ? ldg128(xr + col) : make_uint4(0, 0, 0, 0);
+          gv[v] = ld ? ldg128(gr + col) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          axpy8f(cs, xv[v], au[v]);
+          axpy8f(cc, gv[v], ad[v]);
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int col = c0 + v * 256;
+      if (col < H) {
+        store8<OUT_F32>(d_up, row * H + col, au[v]);
+        store8<OUT_F32>(d_down, row * H + col, ad[v]);
+      }
+    }
+  }
+  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_TOKEN_INDEX);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace omni
+
+using namespace omni;
+
+extern "C" int omni_router_bwd(const float* dscores, const void* indices, int idx_is_i64, int64_t num_tokens, int sqrt_n,
+                               int k, float* dlog_probs_x, float* dlog_probs_y, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && sqrt_n >= 1 && sqrt_n <= 1024 && k >= 0, "bad sizes (sqrt_n in [1, 1024])");
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(dlog_probs_x && dlog_probs_y && status && (k == 0 || (dscores && indices)), "NULL argument");
+  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
+  const size_t smem = static_cast<size_t>(kWarps) * 2 * sqrt_n * sizeof(float);
+  router_bwd_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(dscores, indices, idx_is_i64, num_tokens, sqrt_n,
+                                                                                k, dlog_probs_x, dlog_probs_y, status);
+  return check_launch("router_bwd_kernel");
+}
+
+extern "C" int omni_expert_bwd_dots(const void* x, const void* up, const void* down, const void* dy, const float* weights,
+                                    const int32_t* indices, int64_t num_tokens, int k, int hidden, int64_t num_experts,
+                                    float* ds, float* cdown, float* dg, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && num_experts >= 1, "bad sizes");
+  OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(x && up && down && dy && weights && indices && ds && cdown && dg && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(up) && aligned16(down) && aligned16(dy), "x, up, down and dy must be 16-byte aligned");
+  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
+  expert_bwd_dots_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(up), static_cast<const __nv_bfloat16*>(down),
+      static_cast<const __nv_bfloat16*>(dy), weights, indices, num_tokens, k, hidden, num_experts, ds, cdown, dg, status);
+  return check_launch("expert_bwd_dots_kernel");
+}
+
+extern "C" int omni_expert_bwd_rows(const void* x, const void* dy, const float* ds, const float* cdown,
+                                    const int32_t* sorted_pair_ids, const int32_t* expert_ids, const int32_t* offsets,
+                                    const int32_t* num_segments, int64_t max_segments, int64_t num_tokens, int k, int hidden,
+                                    int compact, void* d_up, void* d_down, int out_dtype, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && max_segments >= 0, "bad sizes");
+  OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
+  OMNI_REQUIRE(out_dtype == OMNI_F32 || out_dtype == OMNI_BF16, "out_dtype must be OMNI_F32 or OMNI_BF16");
+  OMNI_REQUIRE(max_segments < (int64_t(1) << 31), "too many segments");
+  if (num_tokens == 0 || max_segments == 0) return 0;
+  OMNI_REQUIRE(x && dy && ds && cdown && sorted_pair_ids && expert_ids && offsets && num_segments && d_up && d_down && status,
+               "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(dy) && aligned16(d_up) && aligned16(d_down), "x, dy, d_up and d_down must be 16-byte aligned");
+  const unsigned grid = static_cast<unsigned>(ceil_div64(max_segments, kWarps));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const auto* xb = static_cast<const __nv_bfloat16*>(x);
+  const auto* gb = static_cast<const __nv_bfloat16*>(dy);
+  if (out_dtype == OMNI_F32)
+    expert_bwd_rows_kernel<true><<<grid, kThreads, 0, st>>>(xb, gb, ds, cdown, sorted_pair_ids, expert_ids, offsets, num_segments,
+                                                            num_tokens, k, hidden, compact, d_up, d_down, status);
+  else
+    expert_bwd_rows_kernel<false><<<grid, kThreads, 0, st>>>(xb, gb, ds, cdown, sorted_pair_ids, expert_ids, offsets, num_segments,
+                                                             num_tokens, k, hidden, compact, d_up, d_down, status);
+  return check_launch("expert_bwd_rows_kernel");
+}

@@ -1,0 +1,152 @@
+"""Autograd functions of the three operators: forward through the forward kernels, backward through
+the kernels of ``csrc/backward.cu`` and the GEMMs of ``csrc/gemm_tcgen05.cu``.
+
+Reference counterparts: ``OmniRouterFunc`` (omni_moe/ops/triton/omni_router.py:277-305),
+``OmniExpertFunc`` (omni_moe/ops/triton/omni_expert.py:1280-1360) and ``TritonSwiGLUFunc`` with the
+three ``nn.functional.linear`` calls around it (omni_moe/ops/triton/omni_mlp.py:359-375,
+interface.py:7-29).  Gradients come back in the dtype of the corresponding input.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ._common import as_bf16
+from .scheduler import schedule
+
+
+def _status(dev) -> torch.Tensor:
+    return torch.zeros(1, device=dev, dtype=torch.int32)
+
+
+# ------------------------------------------------------------------------------------------------
+# router
+# ------------------------------------------------------------------------------------------------
+def router_backward(dscores: torch.Tensor, indices: torch.Tensor, num_expert_sqrt: int):
+    """``(dlog_probs_x, dlog_probs_y)`` fp32 ``[T, sqrt_n]`` from ``dscores [T, k]`` and the selected indices."""
+    _lib.require_cuda(dscores, indices)
+    assert dscores.shape == indices.shape and indices.dtype in (torch.int32, torch.int64)
+    t, k = indices.shape
+    dev = indices.device
+    ds = dscores.detach().float().contiguous()
+    indices = indices.contiguous()
+    dlx = torch.empty((t, num_expert_sqrt), device=dev, dtype=torch.float32)
+    dly = torch.empty((t, num_expert_sqrt), device=dev, dtype=torch.float32)
+    status = _status(dev)
+    if t > 0:
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().omni_router_bwd(ds.data_ptr(), indices.data_ptr(), int(indices.dtype == torch.int64), t,
+                                                   num_expert_sqrt, k, dlx.data_ptr(), dly.data_ptr(), status.data_ptr(),
+                                                   _lib.stream_ptr()))
+    return dlx, dly
+
+
+class RouterFunction(torch.autograd.Function):
+    """scores, indices = top-k of lpx[i] + lpy[j]; d/dlpx[ix] += dscore, d/dlpy[iy] += dscore."""
+
+    @staticmethod
+    def forward(ctx, log_probs_x, log_probs_y, num_expert_sqrt, k):
+        from .router import router_topk
+        scores, indices = router_topk(log_probs_x, log_probs_y, num_expert_sqrt, k)
+        ctx.save_for_backward(indices)
+        ctx.n = num_expert_sqrt
+        ctx.dtypes = (log_probs_x.dtype, log_probs_y.dtype)
+        ctx.mark_non_differentiable(indices)
+        return scores.to(log_probs_x.dtype), indices
+
+    @staticmethod
+    def backward(ctx, dscores, _dindices):
+        (indices,) = ctx.saved_tensors
+        dlx, dly = router_backward(dscores, indices, ctx.n)
+        return dlx.to(ctx.dtypes[0]), dly.to(ctx.dtypes[1]), None, None
+
+
+# ------------------------------------------------------------------------------------------------
+# routed experts
+# ------------------------------------------------------------------------------------------------
+def expert_backward(dy: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
+                    weights: torch.Tensor, indices: torch.Tensor, grad_dtype: torch.dtype = torch.bfloat16,
+                    compact: bool = False, need_tables: bool = True):
+    """Backward of ``y[t] = sum_j g[t,j] * silu(x[t].Up[e]) * Down[e]`` for bf16 operands.
+
+    Returns ``(dx [T,H] grad_dtype, d_up, d_down, dg [T,k] fp32, expert_ids)``.  With ``compact=False``
+    ``d_up / d_down`` are dense ``[N, H]`` tables (zero rows for untouched experts) and ``expert_ids`` is
+    None; with ``compact=True`` they hold one row per touched expert, ``expert_ids[s]`` names the
+    expert of row ``s`` and rows beyond the number of touched experts are unspecified
+    (``expert_ids`` is cut to the valid length, which costs one host read).
+    """
+    _lib.require_cuda(dy, x, up_weight, down_weight, weights, indices)
+    assert x.dtype == up_weight.dtype == down_weight.dtype == dy.dtype == torch.bfloat16
+    assert weights.dtype == torch.float32 and indices.dtype == torch.int32
+    assert grad_dtype in (torch.float32, torch.bfloat16)
+    x, up_weight, down_weight, dy = x.contiguous(), up_weight.contiguous(), down_weight.contiguous(), dy.contiguous()
+    weights, indices = weights.contiguous(), indices.contiguous()
+    t, h = x.shape
+    n = up_weight.size(0)
+    k = indices.size(1)
+    dev = x.device
+    f32 = dict(device=dev, dtype=torch.float32)
+    ds, cdown, dg = torch.empty((t, k), **f32), torch.empty((t, k), **f32), torch.empty((t, k), **f32)
+    dx = torch.empty((t, h), device=dev, dtype=grad_dtype)
+    status = _status(dev)
+    lib = _lib.load()
+    d_up = d_down = expert_ids = None
+    if t == 0 or k == 0:
+        dx.zero_()
+        if need_tables and not compact:
+            d_up = torch.zeros((n, h), device=dev, dtype=grad_dtype)
+            d_down = torch.zeros((n, h), device=dev, dtype=grad_dtype)
+        return dx, d_up, d_down, dg, expert_ids
+    with torch.cuda.device(dev):
+        st = _lib.stream_ptr()
+        _lib.check(lib.omni_expert_bwd_dots(x.data_ptr(), up_weight.data_ptr(), down_weight.data_ptr(), dy.data_ptr(),
+                                            weights.data_ptr(), indices.data_ptr(), t, k, h, n, ds.data_ptr(),
+                                            cdown.data_ptr(), dg.data_ptr(), status.data_ptr(), st))
+        # dx[t] = sum_j ds[t,j] * Up[e[t,j]]: the forward's token-centric combine with the Up table
+        _lib.check(lib.omni_expert_combine(up_weight.data_ptr(), ds.data_ptr(), indices.data_ptr(), t, k, h, n, None,
+                                           dx.data_ptr(), _lib.dtype_code(grad_dtype), status.data_ptr(), st))
+    if need_tables:
+        sch = schedule(indices, n, segments=True)
+        cap = sch.expert_ids.numel()
+        rows = cap if compact else n
+        alloc = torch.empty if compact else torch.zeros
+        d_up = alloc((rows, h), device=dev, dtype=grad_dtype)
+        d_down = alloc((rows, h), device=dev, dtype=grad_dtype)
+        with torch.cuda.device(dev):
+            _lib.check(lib.omni_expert_bwd_rows(x.data_ptr(), dy.data_ptr(), ds.data_ptr(), cdown.data_ptr(),
+                                                sch.sorted_pair_ids.data_ptr(), sch.expert_ids.data_ptr(),
+                                                sch.offsets.data_ptr(), sch.meta.data_ptr(), cap, t, k, h, int(compact),
+                                                d_up.data_ptr(), d_down.data_ptr(), _lib.dtype_code(grad_dtype),
+                                                status.data_ptr(), _lib.stream_ptr()))
+        if compact:
+            u = int(sch.meta[0].item())
+            d_up, d_down, expert_ids = d_up[:u], d_down[:u], sch.expert_ids[:u]
+    return dx, d_up, d_down, dg, expert_ids
+
+
+class ExpertFunction(torch.autograd.Function):
+    """Routed-expert sum with gradients for x, both tables and the routing weights."""
+
+    @staticmethod
+    def forward(ctx, x, up_weight, down_weight, routing_weights, indices):
+        from .expert import expert_forward
+        xb, ub, db = as_bf16(x), as_bf16(up_weight), as_bf16(down_weight)
+        g = routing_weights.detach().float().contiguous()
+        idx = indices.to(torch.int32).contiguous()
+        y = expert_forward(xb, ub, db, g, idx, out_dtype=torch.float32 if x.dtype == torch.float32 else torch.bfloat16)
+        ctx.save_for_backward(xb, ub, db, g, idx)
+        ctx.dtypes = (x.dtype, up_weight.dtype, down_weight.dtype, routing_weights.dtype)
+        return y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xb, ub, db, g, idx = ctx.saved_tensors
+        need_tables = ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
+        all_f32 = all(d == torch.float32 for d in ctx.dtypes[:3])
+        dx, d_up, d_down, dg, _ = expert_backward(as_bf16(dy), xb, ub, db, g, idx,
+                                                  grad_dtype=torch.float32 if all_f32 else torch.bfloat16,
+                                                  need_tables=need_tables)
+        return (dx.to(ctx.dtypes[0]) if ctx.needs_input_grad[0] else None,
+                d_up.to(ctx.dtypes[1]) if ctx.needs_input_grad[1] else None,
+                d_down.to(ctx.dtypes[2]) if ctx.needs_input_grad[2] else None,
+                dg.to(ctx.dtypes[3]) if ctx.needs_input_grad[3] else None, None)

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import as_bf16, guard_no_grad
+from ._common import as_bf16
 from .scheduler import schedule
 
 L2_RESIDENT_TABLE_BYTES = 48 << 20  # both tables together; above this the expert-ordered path reads less HBM
@@ -138,8 +138,9 @@ def omni_expert_func(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torc
     """
     assert x.dim() == 2 and up_weight.dim() == 2 and down_weight.shape == up_weight.shape
     assert routing_weights.shape == indices.shape and indices.size(0) == x.size(0)
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (x, up_weight, down_weight, routing_weights)):
+        from .autograd import ExpertFunction
+        return ExpertFunction.apply(x, up_weight, down_weight, routing_weights, indices)
     y = expert_forward(as_bf16(x), as_bf16(up_weight), as_bf16(down_weight), routing_weights.detach().float(),
                        indices.to(torch.int32), out_dtype=torch.float32 if x.dtype == torch.float32 else torch.bfloat16)
-    y = y.to(x.dtype)
-    y, = guard_no_grad("omni_expert_func", (x, up_weight, down_weight, routing_weights), (y,))
-    return y
+    return y.to(x.dtype)

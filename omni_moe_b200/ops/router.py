@@ -4,7 +4,6 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import guard_no_grad
 
 
 def _assert_router_inputs(lx, ly, num_expert_sqrt, k):
@@ -93,7 +92,8 @@ def omni_router_func(router_logits_x: torch.Tensor, router_logits_y: torch.Tenso
     :return indices: (num_tokens, num_experts_per_token) int32, ``ix * num_expert_sqrt + iy``
     """
     _assert_router_inputs(router_logits_x, router_logits_y, num_expert_sqrt, num_experts_per_token)
+    if torch.is_grad_enabled() and (router_logits_x.requires_grad or router_logits_y.requires_grad):
+        from .autograd import RouterFunction
+        return RouterFunction.apply(router_logits_x, router_logits_y, num_expert_sqrt, num_experts_per_token)
     scores, indices = router_topk(router_logits_x, router_logits_y, num_expert_sqrt, num_experts_per_token)
-    scores = scores.to(router_logits_x.dtype)
-    scores, = guard_no_grad("omni_router_func", (router_logits_x, router_logits_y), (scores,))
-    return scores, indices
+    return scores.to(router_logits_x.dtype), indices

@@ -272,3 +272,49 @@ def params_from_state_dict(sd: dict, num_experts: int, top_k: int) -> LayerParam
         up_embed=sd["up_embed.weight"], down_embed=sd["down_embed.weight"],
         num_experts=num_experts, top_k=top_k,
     )
+
+
+# ------------------------------------------------------------------------------------------------
+# Backward references.  The reference's tests obtain gradients by running torch autograd through the
+# PyTorch mirrors of the three operators (tests/test_router.py:36-50,73-95,
+# tests/test_expert.py and tests/test_mlp.py backward factories); these functions do the same in
+# fp32 on the CPU.
+# ------------------------------------------------------------------------------------------------
+def router_backward(dscores, indices, num_expert_sqrt: int):
+    """Gradients of ``scores[t,j] = lpx[t, ix] + lpy[t, iy]`` with respect to both log-prob tables:
+    every score gradient is added to column ``ix`` of the x axis and ``iy`` of the y axis
+    (what autograd yields for the topk / gather chain of tests/test_router.py:8-22; the reference's
+    kernel: omni_moe/ops/triton/omni_router.py:104-164)."""
+    ds = torch.as_tensor(dscores).double()
+    idx = torch.as_tensor(indices).long()
+    t = idx.size(0)
+    dlx = torch.zeros(t, num_expert_sqrt, dtype=torch.float64)
+    dly = torch.zeros(t, num_expert_sqrt, dtype=torch.float64)
+    dlx.scatter_add_(1, idx // num_expert_sqrt, ds)
+    dly.scatter_add_(1, idx % num_expert_sqrt, ds)
+    return dlx.float(), dly.float()
+
+
+def expert_backward(x, up_w, down_w, routing_w, indices, dy):
+    """``(dx, d_up, d_down, dg)`` of :func:`expert_forward` by autograd in fp32 (small cases only:
+    the dense table gradients are materialised)."""
+    x = torch.as_tensor(x).float().clone().requires_grad_(True)
+    up = torch.as_tensor(up_w).float().clone().requires_grad_(True)
+    dn = torch.as_tensor(down_w).float().clone().requires_grad_(True)
+    g = torch.as_tensor(routing_w).float().clone().requires_grad_(True)
+    idx = torch.as_tensor(indices).long()
+    sc = torch.matmul(up[idx], x.unsqueeze(-1)).squeeze(-1)
+    y = torch.matmul((F.silu(sc) * g).unsqueeze(-2), dn[idx]).squeeze(-2)
+    y.backward(torch.as_tensor(dy).float())
+    return x.grad, up.grad, dn.grad, g.grad
+
+
+def mlp_backward(x, gate_w, up_w, down_w, dy):
+    """``(dx, d_gate_w, d_up_w, d_down_w)`` of :func:`mlp_forward` by autograd in fp32."""
+    x = torch.as_tensor(x).float().clone().requires_grad_(True)
+    wg = torch.as_tensor(gate_w).float().clone().requires_grad_(True)
+    wu = torch.as_tensor(up_w).float().clone().requires_grad_(True)
+    wd = torch.as_tensor(down_w).float().clone().requires_grad_(True)
+    y = F.linear(F.silu(F.linear(x, wg)) * F.linear(x, wu), wd)
+    y.backward(torch.as_tensor(dy).float())
+    return x.grad, wg.grad, wu.grad, wd.grad

@@ -1,0 +1,111 @@
+"""Backward of the three operators against fp32 autograd through the oracle's restatement of the
+reference's PyTorch mirrors (the way the reference's own tests obtain reference gradients).
+
+Bars: router gradients are sums of the given fp32 score gradients in a fixed order -> compared at
+1e-6 relative; gradients of bf16 operands are compared at rtol/atol 2e-2 of the gradient's scale
+against the fp32 oracle run on the same bf16-rounded operands.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import omni_oracle as orc
+from _util import gen
+
+pytestmark = pytest.mark.gpu
+
+
+def _scaled_close(actual, expected, what, rtol=2e-2, atol_frac=2e-2):
+    a, e = actual.detach().float().cpu(), expected.detach().float().cpu()
+    scale = float(e.abs().max()) or 1.0
+    bad = (a - e).abs() > atol_frac * scale + rtol * e.abs()
+    assert not bad.any(), (f"{what}: {int(bad.sum())}/{bad.numel()} outside tolerance; max abs err "
+                           f"{float((a - e).abs().max()):.4g} at scale {scale:.4g}")
+
+
+@pytest.mark.parametrize("t,n,k,idt", [(64, 16, 4, torch.int32), (300, 64, 16, torch.int32), (129, 256, 32, torch.int64),
+                                         (40, 1024, 64, torch.int32), (7, 5, 25, torch.int64), (0, 8, 2, torch.int32)])
+def test_router_backward_matches_oracle(t, n, k, idt):
+    from omni_moe_b200.ops.autograd import router_backward
+    g = gen(t + n)
+    # duplicates inside a token are legal for the scatter (they cannot come out of a top-k, the kernel does not care)
+    idx = torch.randint(0, n * n, (t, k), generator=g).to(idt)
+    ds = torch.randn(t, k, generator=g)
+    dlx, dly = router_backward(ds.cuda(), idx.cuda(), n)
+    ex, ey = orc.router_backward(ds, idx, n)
+    torch.testing.assert_close(dlx.cpu(), ex, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(dly.cpu(), ey, rtol=1e-6, atol=1e-6)
+    if t:
+        again = router_backward(ds.cuda(), idx.cuda(), n)
+        assert torch.equal(again[0], dlx) and torch.equal(again[1], dly), "the scatter must be deterministic"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_router_op_autograd(dtype):
+    from omni_moe.ops.triton import triton_omni_router_func
+    t, n, k = 200, 64, 16
+    g = gen(3)
+    lx = torch.log_softmax(torch.randn(t, n, generator=g), -1).to(dtype)
+    ly = torch.log_softmax(torch.randn(t, n, generator=g), -1).to(dtype)
+    cx, cy = lx.cuda().requires_grad_(True), ly.cuda().requires_grad_(True)
+    scores, idx = triton_omni_router_func(cx, cy, n, k)
+    assert scores.dtype == dtype and not idx.requires_grad
+    wgt = torch.randn(t, k, generator=g)
+    (scores.float() * wgt.cuda()).sum().backward()
+    ex, ey = orc.router_backward(wgt.to(dtype).float(), idx.cpu(), n)
+    assert cx.grad.dtype == dtype
+    torch.testing.assert_close(cx.grad.float().cpu(), ex.to(dtype).float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(cy.grad.float().cpu(), ey.to(dtype).float(), rtol=1e-2, atol=1e-2)
+
+
+def _expert_inputs(t, h, n, k, seed):
+    g = gen(seed)
+    x = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
+    up = (torch.randn(n, h, generator=g) * (2.0 / h ** 0.5)).bfloat16()
+    dn = (torch.randn(n, h, generator=g) * 0.1).bfloat16()
+    w = torch.rand(t, k, generator=g) * 0.2
+    idx = torch.randint(0, n, (t, k), generator=g, dtype=torch.int32)
+    dy = (torch.randn(t, h, generator=g) * 0.3).bfloat16()
+    return x, up, dn, w, idx, dy
+
+
+@pytest.mark.parametrize("t,h,n,k", [(32, 64, 16, 4), (300, 256, 512, 8), (257, 1024, 4096, 16), (64, 2048, 128, 32),
+                                       (40, 4096, 300, 64), (50, 72, 64, 6), (20, 8192, 64, 2), (1, 8, 1, 1)])
+@pytest.mark.parametrize("grad_dtype", [torch.float32, torch.bfloat16])
+def test_expert_backward_matches_oracle(t, h, n, k, grad_dtype):
+    from omni_moe_b200.ops.autograd import expert_backward
+    x, up, dn, w, idx, dy = _expert_inputs(t, h, n, k, t + h)
+    dx, d_up, d_dn, dg, _ = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=grad_dtype)
+    ex, eu, ed, eg = orc.expert_backward(x.float(), up.float(), dn.float(), w, idx, dy.float())
+    tol = dict(rtol=2e-3, atol_frac=2e-3) if grad_dtype == torch.float32 else {}
+    _scaled_close(dx, ex, "dx", **tol)
+    _scaled_close(d_up, eu, "d_up", **tol)
+    _scaled_close(d_dn, ed, "d_down", **tol)
+    _scaled_close(dg, eg, "dg", rtol=2e-3, atol_frac=2e-3)
+    untouched = torch.ones(n, dtype=torch.bool)
+    untouched[idx.long().unique()] = False
+    assert not d_up.cpu()[untouched].any() and not d_dn.cpu()[untouched].any()
+    # compact rows = the touched rows of the dense tables, in ascending expert order
+    dx2, cu, cd, dg2, ids = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(),
+                                            grad_dtype=grad_dtype, compact=True)
+    assert torch.equal(ids.cpu().long(), idx.long().unique())
+    assert torch.equal(cu, d_up[ids.long()]) and torch.equal(cd, d_dn[ids.long()])
+    assert torch.equal(dx2, dx) and torch.equal(dg2, dg), "two runs must agree bit for bit"
+
+
+def test_expert_op_autograd_skewed():
+    """Through the drop-in op with autograd, on a routing table where one expert owns most pairs."""
+    from omni_moe.ops.triton import triton_omni_expert_func
+    t, h, n, k = 512, 256, 64, 8
+    x, up, dn, w, idx, dy = _expert_inputs(t, h, n, k, 11)
+    idx[:, :6] = 3
+    cx, cu, cd = (v.cuda().requires_grad_(True) for v in (x, up, dn))
+    cw = w.bfloat16().cuda().requires_grad_(True)
+    y = triton_omni_expert_func(cx, cu, cd, cw, idx.cuda())
+    y.backward(dy.cuda())
+    ex, eu, ed, eg = orc.expert_backward(x.float(), up.float(), dn.float(), w.bfloat16().float(), idx, dy.float())
+    _scaled_close(cx.grad, ex, "dx")
+    _scaled_close(cu.grad, eu, "d_up")
+    _scaled_close(cd.grad, ed, "d_down")
+    _scaled_close(cw.grad, eg, "dg")
+    assert cu.grad.dtype == torch.bfloat16 and cw.grad.dtype == torch.bfloat16
