@@ -307,6 +307,29 @@ OMNI_API int omni_expert_bwd_rows(const void *x, const void *dy, const float *ds
                          int64_t num_tokens, int k, int hidden, int compact, void *d_up, void *d_down,
                          int out_dtype, int32_t *status, void *stream);
 
+/*
+ * Building blocks of the MLP backward (the reference differentiates its MLP through three
+ * nn.functional.linear calls and TritonSwiGLUFunc.backward, omni_moe/ops/triton/interface.py:7-29,
+ * omni_moe/ops/triton/omni_mlp.py:181-249,306-375).
+ *
+ * omni_gemm_bf16_nt: out[m, n] = sum_k a[m, k] * b[n, k]; a [m, k], b [n, k] bf16 row-major (both
+ *   with the contraction dimension contiguous), fp32 accumulation on the tcgen05 tensor cores, out
+ *   bf16 with row stride ldo >= n.  k % 8 == 0; pointers 16-byte aligned.
+ * omni_transpose_bf16: out[c, r] = in[r, c] for an in [rows, cols] with row stride ld_in; out is
+ *   [cols, out_cols] with row stride ldo, out_cols >= rows, and its columns rows..out_cols-1 are
+ *   zero-filled (padding that keeps rows 16-byte aligned when `rows`, a token count, is not a
+ *   multiple of 8).  cols, ld_in, out_cols, ldo even.
+ * omni_swiglu_bwd: gate_up [T, 2I] = (gate | up) pre-activations, dact [T, I] ->
+ *   dgate_up [T, 2I] = (dact*up*silu'(gate) | dact*silu(gate)) and, if act != NULL,
+ *   act [T, I] = silu(gate)*up.  All bf16, arithmetic in fp32.  I % 8 == 0.
+ */
+OMNI_API int omni_gemm_bf16_nt(const void *a, const void *b, int64_t m, int64_t n, int64_t k, void *out,
+                      int64_t ldo, int32_t *status, void *stream);
+OMNI_API int omni_transpose_bf16(const void *in, int64_t rows, int64_t cols, int64_t ld_in, void *out,
+                        int64_t out_cols, int64_t ldo, void *stream);
+OMNI_API int omni_swiglu_bwd(const void *gate_up, const void *dact, int64_t num_tokens, int intermediate,
+                    void *dgate_up, void *act, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

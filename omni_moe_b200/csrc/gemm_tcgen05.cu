@@ -764,6 +764,31 @@ extern "C" int omni_mlp_down(const void* act, const void* down_w, int64_t num_to
   return launch<128, EPI_RES>(ma, mb, mb, g, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int omni_gemm_bf16_nt(const void* a, const void* b, int64_t m, int64_t n, int64_t k, void* out, int64_t ldo,
+                                 int32_t* status, void* stream) {
+  OMNI_REQUIRE(m >= 0 && m < (int64_t(1) << 31) - 2 * BM, "m out of range");
+  OMNI_REQUIRE(n >= 0 && n < (int64_t(1) << 31) - 256, "n out of range");
+  OMNI_REQUIRE(k >= 8 && k % 8 == 0 && k < (int64_t(1) << 31) - 256, "k must be a positive multiple of 8, got %lld", static_cast<long long>(k));
+  OMNI_REQUIRE(ldo >= n, "ldo %lld < n", static_cast<long long>(ldo));
+  if (m == 0 || n == 0) return 0;
+  OMNI_REQUIRE(a && b && out && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(a) && aligned16(b) && aligned16(out), "pointers must be 16-byte aligned");
+  CUtensorMap ma, mb;
+  if (int e = make_map(&ma, a, m, k, BM)) return e;
+  if (int e = make_map(&mb, b, n, k, 128)) return e;
+  GemmArgs g{};
+  g.M = static_cast<int>(m), g.N = static_cast<int>(n), g.K = static_cast<int>(k), g.dual = 0;
+  g.out = out, g.ldo = ldo, g.residual = nullptr, g.ldr = 0, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  if (use_pairs()) {
+    g.tiles_m = ceil_div(g.M, 2 * BM);
+    g.tiles_n = g.tiles_n_axis = ceil_div(g.N, 256);
+    return launch_pair<EPI_RES, false>(ma, mb, mb, mb, mb, g, static_cast<cudaStream_t>(stream));
+  }
+  g.tiles_m = ceil_div(g.M, BM);
+  g.tiles_n = g.tiles_n_axis = ceil_div(g.N, 128);
+  return launch<128, EPI_RES>(ma, mb, mb, g, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int omni_mlp_fwd(const void* x, const void* gate_w, const void* up_w, const void* down_w, int64_t num_tokens,
                             int hidden, int intermediate, void* act, const float* residual, void* y, int32_t* status,
                             void* stream) {

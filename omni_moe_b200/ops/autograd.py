@@ -150,3 +150,113 @@ class ExpertFunction(torch.autograd.Function):
                 d_up.to(ctx.dtypes[1]) if ctx.needs_input_grad[1] else None,
                 d_down.to(ctx.dtypes[2]) if ctx.needs_input_grad[2] else None,
                 dg.to(ctx.dtypes[3]) if ctx.needs_input_grad[3] else None, None)
+
+
+# ------------------------------------------------------------------------------------------------
+# shared SwiGLU MLP
+# ------------------------------------------------------------------------------------------------
+def _pad8(v: int) -> int:
+    return (v + 7) // 8 * 8
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None):
+    """``a [m, k] @ b [n, k]^T`` for bf16 row-major operands (fp32 accumulation, bf16 result).
+    ``out`` may be a column slice of a wider row-major matrix (its row stride is honoured)."""
+    _lib.require_cuda(a, b)
+    assert a.dtype == b.dtype == torch.bfloat16 and a.dim() == b.dim() == 2 and a.size(1) == b.size(1)
+    assert a.is_contiguous() and b.is_contiguous()
+    m, k = a.shape
+    n = b.size(0)
+    if out is None:
+        out = torch.empty((m, n), device=a.device, dtype=torch.bfloat16)
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16 and out.stride(1) == 1
+    if status is None:
+        status = _status(a.device)
+    if m and n:
+        with torch.cuda.device(a.device):
+            _lib.check(_lib.load().omni_gemm_bf16_nt(a.data_ptr(), b.data_ptr(), m, n, k, out.data_ptr(), out.stride(0),
+                                                     status.data_ptr(), _lib.stream_ptr()))
+    return out
+
+
+def transpose_padded(src: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``src [r, c]`` bf16 (row stride honoured) -> ``[c, pad8(r)]`` with zero padding columns, or into
+    ``out``, a ``[c, >= r]`` column slice of a wider row-major matrix."""
+    assert src.dtype == torch.bfloat16 and src.dim() == 2 and src.stride(1) == 1
+    r, c = src.shape
+    if out is None:
+        out = torch.empty((c, _pad8(r)), device=src.device, dtype=torch.bfloat16)
+    assert out.dtype == torch.bfloat16 and out.size(0) == c and out.size(1) >= r and out.stride(1) == 1
+    if c:
+        with torch.cuda.device(src.device):
+            _lib.check(_lib.load().omni_transpose_bf16(src.data_ptr(), r, c, src.stride(0), out.data_ptr(), out.size(1),
+                                                       out.stride(0), _lib.stream_ptr()))
+    return out
+
+
+def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor,
+                 down_weight: torch.Tensor, need_weight_grads: bool = True):
+    """Backward of ``y = (silu(x Wg^T) * (x Wu^T)) Wd^T`` on bf16 operands.
+
+    The forward keeps only x (its fused kernel never writes gate / up); they are recomputed here,
+    rounded to bf16 as the reference does before the activation.  Six GEMMs on the tensor cores:
+    gate, up, dact = dy Wd, dx = (dgate | dup) (Wg ; Wu), dWd = dy^T act, (dWg ; dWu) = (dgate | dup)^T x.
+    Returns ``(dx, d_gate_weight, d_up_weight, d_down_weight)`` in bf16.
+    """
+    _lib.require_cuda(dy, x, gate_weight, up_weight, down_weight)
+    for v in (dy, x, gate_weight, up_weight, down_weight):
+        assert v.dtype == torch.bfloat16
+    dy, x = dy.contiguous(), x.contiguous()
+    wg, wu, wd = gate_weight.contiguous(), up_weight.contiguous(), down_weight.contiguous()
+    t, h = x.shape
+    i = wg.size(0)
+    dev = x.device
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    status = _status(dev)
+    if t == 0:
+        z = torch.zeros
+        return (torch.empty((0, h), **bf), z((i, h), **bf), z((i, h), **bf), z((h, i), **bf))
+    lib = _lib.load()
+    # gate | up pre-activations
+    gu = torch.empty((t, 2 * i), **bf)
+    gemm_nt(x, wg, gu[:, :i], status)
+    gemm_nt(x, wu, gu[:, i:], status)
+    # dact = dy @ Wd   (Wd is [H, I]: its transpose has the contraction dimension contiguous)
+    dact = gemm_nt(dy, transpose_padded(wd), None, status)
+    dgu = torch.empty((t, 2 * i), **bf)
+    act = torch.empty((t, i), **bf) if need_weight_grads else None
+    with torch.cuda.device(dev):
+        _lib.check(lib.omni_swiglu_bwd(gu.data_ptr(), dact.data_ptr(), t, i, dgu.data_ptr(), _lib.ptr(act), _lib.stream_ptr()))
+    # dx = dgate @ Wg + dup @ Wu = dgu @ (Wg ; Wu): B operand [H, 2I] = (Wg^T | Wu^T)
+    wgu_t = torch.empty((h, 2 * i), **bf)
+    transpose_padded(wg, wgu_t[:, :i])
+    transpose_padded(wu, wgu_t[:, i:])
+    dx = gemm_nt(dgu, wgu_t, None, status)
+    d_wg = d_wu = d_wd = None
+    if need_weight_grads:
+        dy_t, act_t, x_t, dgu_t = (transpose_padded(v) for v in (dy, act, x, dgu))   # [*, pad8(T)]
+        d_wd = gemm_nt(dy_t, act_t, None, status)              # [H, I]
+        d_wgu = gemm_nt(dgu_t, x_t, None, status)              # [2I, H]
+        d_wg, d_wu = d_wgu[:i], d_wgu[i:]
+    return dx, d_wg, d_wu, d_wd
+
+
+class MlpFunction(torch.autograd.Function):
+    """Shared SwiGLU MLP with gradients for x and the three weight matrices."""
+
+    @staticmethod
+    def forward(ctx, x, gate_weight, up_weight, down_weight):
+        from .mlp import mlp_forward
+        xb, wg, wu, wd = as_bf16(x), as_bf16(gate_weight), as_bf16(up_weight), as_bf16(down_weight)
+        y = mlp_forward(xb, wg, wu, wd)
+        ctx.save_for_backward(xb, wg, wu, wd)
+        ctx.dtypes = (x.dtype, gate_weight.dtype, up_weight.dtype, down_weight.dtype)
+        return y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xb, wg, wu, wd = ctx.saved_tensors
+        need_w = any(ctx.needs_input_grad[1:])
+        dx, d_wg, d_wu, d_wd = mlp_backward(as_bf16(dy), xb, wg, wu, wd, need_weight_grads=need_w)
+        cast = lambda g, j: g.to(ctx.dtypes[j]) if (g is not None and ctx.needs_input_grad[j]) else None
+        return cast(dx, 0), cast(d_wg, 1), cast(d_wu, 2), cast(d_wd, 3)

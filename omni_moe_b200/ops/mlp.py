@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import as_bf16, guard_no_grad
+from ._common import as_bf16
 
 
 def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
@@ -47,6 +47,7 @@ def omni_mlp_func(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.T
     :return y: (num_tokens, hidden_size), dtype of ``x``
     """
     assert x.dim() == 2
-    y = mlp_forward(as_bf16(x), as_bf16(gate_weight), as_bf16(up_weight), as_bf16(down_weight)).to(x.dtype)
-    y, = guard_no_grad("omni_mlp_func", (x, gate_weight, up_weight, down_weight), (y,))
-    return y
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (x, gate_weight, up_weight, down_weight)):
+        from .autograd import MlpFunction
+        return MlpFunction.apply(x, gate_weight, up_weight, down_weight)
+    return mlp_forward(as_bf16(x), as_bf16(gate_weight), as_bf16(up_weight), as_bf16(down_weight)).to(x.dtype)

@@ -109,3 +109,63 @@ def test_expert_op_autograd_skewed():
     _scaled_close(cd.grad, ed, "d_down")
     _scaled_close(cw.grad, eg, "dg")
     assert cu.grad.dtype == torch.bfloat16 and cw.grad.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("r,c", [(64, 64), (257, 72), (1, 8), (300, 1026), (4096, 1024)])
+def test_transpose_padded(r, c):
+    from omni_moe_b200.ops.autograd import transpose_padded
+    src = torch.randn(r, c, generator=gen(r + c)).bfloat16()
+    out = transpose_padded(src.cuda()).cpu()
+    rp = (r + 7) // 8 * 8
+    assert out.shape == (c, rp)
+    assert torch.equal(out[:, :r], src.t()) and not out[:, r:].any()
+    wide = torch.full((c, 2 * rp + 8), 7.0, dtype=torch.bfloat16, device="cuda")
+    transpose_padded(src.cuda(), wide[:, 8:8 + rp])
+    assert torch.equal(wide[:, 8:8 + r].cpu(), src.t()) and bool((wide[:, :8] == 7).all()) and bool((wide[:, 8 + rp:] == 7).all())
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 200, 72), (1, 8, 8), (4096, 1024, 4096), (1000, 8192, 264), (513, 24, 1032)])
+def test_gemm_nt_matches_fp32(m, n, k):
+    from omni_moe_b200.ops.autograd import gemm_nt
+    g = gen(m + n + k)
+    a = (torch.randn(m, k, generator=g) * 0.5).bfloat16()
+    b = (torch.randn(n, k, generator=g) * (1.0 / k ** 0.5)).bfloat16()
+    out = gemm_nt(a.cuda(), b.cuda())
+    ref = a.float() @ b.float().t()
+    _scaled_close(out, ref, "gemm_nt", rtol=1e-2, atol_frac=4e-3)
+
+
+@pytest.mark.parametrize("t,h,i", [(64, 64, 128), (300, 256, 1024), (257, 1024, 4096), (1000, 72, 264), (1, 8, 8)])
+def test_mlp_backward_matches_oracle(t, h, i):
+    from omni_moe_b200.ops.autograd import mlp_backward
+    g = gen(t + h + i)
+    x = (torch.randn(t, h, generator=g)).bfloat16()
+    wg = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wu = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wd = (torch.randn(h, i, generator=g) / i ** 0.5).bfloat16()
+    dy = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
+    dx, dwg, dwu, dwd = mlp_backward(dy.cuda(), x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
+    ex, eg, eu, ed = orc.mlp_backward(x.float(), wg.float(), wu.float(), wd.float(), dy.float())
+    # intermediates (gate, up, dact, dgate, dup) are rounded to bf16 between the GEMMs, as in the reference's bf16 path
+    _scaled_close(dx, ex, "dx", rtol=3e-2, atol_frac=2e-2)
+    _scaled_close(dwg, eg, "d_gate_weight", rtol=3e-2, atol_frac=2e-2)
+    _scaled_close(dwu, eu, "d_up_weight", rtol=3e-2, atol_frac=2e-2)
+    _scaled_close(dwd, ed, "d_down_weight", rtol=3e-2, atol_frac=2e-2)
+
+
+def test_mlp_op_autograd():
+    from omni_moe.ops.triton import triton_omni_mlp_func
+    t, h, i = 200, 128, 512
+    g = gen(5)
+    x = torch.randn(t, h, generator=g).bfloat16()
+    wg = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wu = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wd = (torch.randn(h, i, generator=g) / i ** 0.5).bfloat16()
+    dy = torch.randn(t, h, generator=g).bfloat16()
+    cx, cg, cu, cd = (v.cuda().requires_grad_(True) for v in (x, wg, wu, wd))
+    y = triton_omni_mlp_func(cx, cg, cu, cd)
+    y.backward(dy.cuda())
+    ex, eg, eu, ed = orc.mlp_backward(x.float(), wg.float(), wu.float(), wd.float(), dy.float())
+    for got, exp, name in ((cx.grad, ex, "dx"), (cg.grad, eg, "dwg"), (cu.grad, eu, "dwu"), (cd.grad, ed, "dwd")):
+        assert got.dtype == torch.bfloat16
+        _scaled_close(got, exp, name, rtol=3e-2, atol_frac=2e-2)
