@@ -2,7 +2,9 @@
 
 Constructor, parameter / buffer names and shapes, and ``forward(hidden_states)`` follow the
 reference module (omni_moe/modules/omni_moe.py:14-106), so a reference ``state_dict`` loads
-unchanged.  Forward only.
+unchanged.  Under ``torch.no_grad()`` (or with nothing requiring gradients) the forward is the fused
+launch sequence below; when gradients are needed it is composed from the three differentiable
+operators, like the reference's own forward.
 
 One eval forward is four kernels (five when the router shape exceeds the fused kernel's limits, eight to ten when the expert tables are too large for L2 and the
 pairs are scheduled by expert first), enqueued without a host synchronisation:
@@ -212,8 +214,36 @@ class OmniMoE(nn.Module):
         # gate/up, router gates, top-k, down projection, 2 per radix pass, coefficients, combine
         return 4 + 2 * passes + 2
 
+    def _needs_grad(self, hidden_states: torch.Tensor) -> bool:
+        """The differentiable composition is used when gradients can be asked for: the input carries a
+        graph, or the module is in training mode with trainable parameters.  An eval-mode module called
+        on a plain tensor takes the fused inference path even outside ``torch.no_grad()``."""
+        if not torch.is_grad_enabled():
+            return False
+        return hidden_states.requires_grad or (self.training and any(p.requires_grad for p in self.parameters()))
+
+    def _forward_autograd(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        """Differentiable forward, composed like the reference module (omni_moe/modules/omni_moe.py:60-106):
+        router gates, BatchNorm and log-softmax are torch modules / functions (as they are in the
+        reference), the three operators run the kernels of this library and carry their own backward."""
+        from ..ops import omni_expert_func, omni_mlp_func, omni_router_func
+        bsz, seq_len, _ = hidden_states.shape
+        x = hidden_states.reshape(-1, self.hidden_size)
+        logits_x = self.router_norm_x(self.router_gate_x(x))
+        logits_y = self.router_norm_y(self.router_gate_y(x))
+        log_probs_x = torch.nn.functional.log_softmax(logits_x, dim=-1)
+        log_probs_y = torch.nn.functional.log_softmax(logits_y, dim=-1)
+        scores, indices = omni_router_func(log_probs_x, log_probs_y, self.num_expert_sqrt, self.top_k)
+        routing_weights = torch.exp(scores)
+        experts_states = omni_expert_func(x, self.up_embed.weight, self.down_embed.weight, routing_weights, indices)
+        shared = omni_mlp_func(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
+        self.last_routing = (scores.detach(), indices, routing_weights.detach())
+        return (shared + experts_states).view(bsz, seq_len, -1)
+
     def forward(self, hidden_states: torch.Tensor, **kwargs) -> torch.Tensor:
         _lib.require_cuda(hidden_states)
+        if self._needs_grad(hidden_states):
+            return self._forward_autograd(hidden_states)
         bsz, seq_len, _ = hidden_states.shape
         in_dtype = hidden_states.dtype
         x = hidden_states.detach().reshape(-1, self.hidden_size)

@@ -318,3 +318,38 @@ def mlp_backward(x, gate_w, up_w, down_w, dy):
     y = F.linear(F.silu(F.linear(x, wg)) * F.linear(x, wu), wd)
     y.backward(torch.as_tensor(dy).float())
     return x.grad, wg.grad, wu.grad, wd.grad
+
+
+def layer_gradients(p: "LayerParams", hidden_states, indices, dy, training: bool):
+    """Gradients of the whole layer (omni_moe/modules/omni_moe.py:60-106) for FIXED routing indices,
+    by fp32 autograd: returns ``(y, dict name -> gradient)`` with the reference's parameter names plus
+    ``"x"``.  The selection itself is not differentiable, so the indices are an input here; BatchNorm
+    uses batch statistics when ``training`` (biased variance, as nn.BatchNorm1d normalises) and the
+    running statistics otherwise."""
+    x = torch.as_tensor(hidden_states).float().reshape(-1, p.gate_proj.shape[1]).clone().requires_grad_(True)
+    names = ["gate_proj.weight", "up_proj.weight", "down_proj.weight", "router_gate_x.weight", "router_gate_y.weight",
+             "up_embed.weight", "down_embed.weight"]
+    vals = [p.gate_proj, p.up_proj, p.down_proj, p.router_gate_x, p.router_gate_y, p.up_embed, p.down_embed]
+    w = {n: torch.as_tensor(v).float().clone().requires_grad_(True) for n, v in zip(names, vals)}
+    idx = torch.as_tensor(indices).long()
+    n = p.sqrt_n
+    eps = 1e-5  # nn.BatchNorm1d default, omni_moe/modules/omni_moe.py:53-54
+
+    def norm(z, mean, var):
+        if training:
+            var_b, mean_b = torch.var_mean(z, dim=0, unbiased=False)
+            return (z - mean_b) / torch.sqrt(var_b + eps)
+        return (z - torch.as_tensor(mean).float()) / torch.sqrt(torch.as_tensor(var).float() + eps)
+
+    lpx = F.log_softmax(norm(F.linear(x, w["router_gate_x.weight"]), p.norm_x_mean, p.norm_x_var), dim=-1)
+    lpy = F.log_softmax(norm(F.linear(x, w["router_gate_y.weight"]), p.norm_y_mean, p.norm_y_var), dim=-1)
+    scores = lpx.gather(1, idx // n) + lpy.gather(1, idx % n)
+    g = torch.exp(scores)
+    sc = torch.matmul(w["up_embed.weight"][idx], x.unsqueeze(-1)).squeeze(-1)
+    experts = torch.matmul((F.silu(sc) * g).unsqueeze(-2), w["down_embed.weight"][idx]).squeeze(-2)
+    shared = F.linear(F.silu(F.linear(x, w["gate_proj.weight"])) * F.linear(x, w["up_proj.weight"]), w["down_proj.weight"])
+    y = shared + experts
+    y.backward(torch.as_tensor(dy).float().reshape(y.shape))
+    grads = {k: v.grad for k, v in w.items()}
+    grads["x"] = x.grad
+    return y.detach(), grads

@@ -169,3 +169,34 @@ def test_mlp_op_autograd():
     for got, exp, name in ((cx.grad, ex, "dx"), (cg.grad, eg, "dwg"), (cu.grad, eu, "dwu"), (cd.grad, ed, "dwd")):
         assert got.dtype == torch.bfloat16
         _scaled_close(got, exp, name, rtol=3e-2, atol_frac=2e-2)
+
+
+@pytest.mark.parametrize("training", [True, False])
+def test_layer_gradients_match_oracle(training):
+    """The module's differentiable forward + backward against fp32 autograd with the same routing."""
+    from omni_moe.modules.omni_moe import OmniMoE, OmniMoEConfig
+    torch.manual_seed(0)
+    h, i, n_exp, k, t = 128, 256, 256, 8, 384
+    m = OmniMoE(OmniMoEConfig(h, i, "silu", n_exp, k)).to(torch.bfloat16)
+    with torch.no_grad():
+        m.up_embed.weight.mul_(0.2)     # N(0,1) rows would saturate the SiLU of a 128-wide dot product
+        m.down_embed.weight.mul_(0.2)
+    sd = {kk: (v.float().clone() if v.is_floating_point() else v.clone()) for kk, v in m.state_dict().items()}
+    p = orc.params_from_state_dict(sd, n_exp, k)
+    m = m.cuda()
+    m.train(training)
+    x = torch.randn(1, t, h, generator=gen(1)).bfloat16()
+    dy = (torch.randn(1, t, h, generator=gen(2)) * 0.1).bfloat16()
+    cx = x.cuda().requires_grad_(True)
+    y = m(cx)
+    assert y.requires_grad and y.dtype == torch.bfloat16
+    y.backward(dy.cuda())
+    scores, indices, weights = m.last_routing
+    ey, eg = orc.layer_gradients(p, x.float(), indices.cpu(), dy.float(), training)
+    _scaled_close(y.reshape(-1, h), ey, "y", rtol=3e-2, atol_frac=2e-2)
+    got = {name: prm.grad for name, prm in m.named_parameters()}
+    got["x"] = cx.grad.reshape(-1, h)
+    for name, exp in eg.items():
+        # router-gate gradients pass through bf16 log-probs, scores and BatchNorm: looser
+        loose = name.startswith("router_gate")
+        _scaled_close(got[name], exp, name, rtol=1e-1 if loose else 4e-2, atol_frac=6e-2 if loose else 3e-2)

@@ -80,3 +80,8 @@ def test_readme_quick_start():
     layer.check_status()
     assert y.shape == x.shape and y.dtype == torch.bfloat16 and bool(torch.isfinite(y).all())
     assert int(layer.router_norm_x.num_batches_tracked) == 1
+    # as constructed the layer is trainable: one backward reaches every parameter
+    y.float().square().mean().backward()
+    for name, p in layer.named_parameters():
+        assert p.grad is not None and p.grad.shape == p.shape and bool(torch.isfinite(p.grad).all()), name
+        assert bool(p.grad.any()), name
