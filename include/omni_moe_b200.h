@@ -320,15 +320,25 @@ OMNI_API int omni_expert_bwd_rows(const void *x, const void *dy, const float *ds
  *   zero-filled (padding that keeps rows 16-byte aligned when `rows`, a token count, is not a
  *   multiple of 8).  cols, ld_in, out_cols, ldo even.
  * omni_swiglu_bwd: gate_up [T, 2I] = (gate | up) pre-activations, dact [T, I] ->
- *   dgate_up [T, 2I] = (dact*up*silu'(gate) | dact*silu(gate)) and, if act != NULL,
- *   act [T, I] = silu(gate)*up.  All bf16, arithmetic in fp32.  I % 8 == 0.
+ *   dgate_up [T, 2I] = (dact*up*silu'(gate) | dact*silu(gate)) and, if dgate_up_t / act_t are given,
+ *   the transposed copies the weight-gradient GEMMs contract over: dgate_up_t [2I, ld_t] and
+ *   act_t [I, ld_t] with act = silu(gate)*up, columns T..ld_t-1 zero-filled.
+ *   All bf16, arithmetic in fp32.  I % 8 == 0, ld_t even.
  */
+/*
+ * omni_mlp_gate_up_save: omni_mlp_gate_up that also writes the pre-activations for the backward:
+ *   gate_up [T, 2I] bf16 = (x Wg^T | x Wu^T), rounded from the fp32 accumulators (the reference's
+ *   TritonSwiGLUFunc saves gate and up the same way, omni_moe/ops/triton/omni_mlp.py:359-375).
+ */
+OMNI_API int omni_mlp_gate_up_save(const void *x, const void *gate_w, const void *up_w, int64_t num_tokens,
+                          int hidden, int intermediate, void *act, void *gate_up, int32_t *status,
+                          void *stream);
 OMNI_API int omni_gemm_bf16_nt(const void *a, const void *b, int64_t m, int64_t n, int64_t k, void *out,
                       int64_t ldo, int32_t *status, void *stream);
 OMNI_API int omni_transpose_bf16(const void *in, int64_t rows, int64_t cols, int64_t ld_in, void *out,
                         int64_t out_cols, int64_t ldo, void *stream);
 OMNI_API int omni_swiglu_bwd(const void *gate_up, const void *dact, int64_t num_tokens, int intermediate,
-                    void *dgate_up, void *act, void *stream);
+                    void *dgate_up, void *dgate_up_t, void *act_t, int64_t ld_t, void *stream);
 
 #ifdef __cplusplus
 }

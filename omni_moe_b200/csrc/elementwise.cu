@@ -38,41 +38,73 @@ __global__ void __launch_bounds__(256) transpose_bf16_kernel(const uint16_t* __r
 }
 
 // gu [T, 2I] = (gate | up) pre-activations, dact [T, I]:
-//   act = silu(gate) * up,  dgate = dact * up * silu'(gate),  dup = dact * silu(gate);  dgu = (dgate | dup)
+//   act = silu(gate) * up,  dgate = dact * up * silu'(gate),  dup = dact * silu(gate)
+// Outputs: dgu [T, 2I] = (dgate | dup) for the input-gradient GEMM and, for the weight-gradient GEMMs
+// that contract over tokens, the transposed copies dgu_t [2I, ld_t] and act_t [I, ld_t] (columns
+// T..ld_t-1 zero).  A block owns a 64-token x 64-column tile; the transposes go through shared memory.
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dact,
                                                          int64_t T, int I, __nv_bfloat16* __restrict__ dgu,
-                                                         __nv_bfloat16* __restrict__ act) {
-  const int vec_per_row = I / 8;
-  const int64_t total = T * vec_per_row;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t t = i / vec_per_row;
-    const int c = static_cast<int>(i - t * vec_per_row) * 8;
-    const uint4 gv = ldg128(gu + t * 2 * I + c), uv = ldg128(gu + t * 2 * I + I + c), dv = ldg128(dact + t * I + c);
-    const uint32_t* pg = reinterpret_cast<const uint32_t*>(&gv);
-    const uint32_t* pu = reinterpret_cast<const uint32_t*>(&uv);
-    const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv);
-    uint32_t og[4], ou[4], oa[4];
+                                                         uint16_t* __restrict__ dgu_t, uint16_t* __restrict__ act_t, int64_t ld_t) {
+  __shared__ uint16_t s_dg[kTile][kTile + 2], s_du[kTile][kTile + 2], s_ac[kTile][kTile + 2];
+  const int64_t r0 = static_cast<int64_t>(blockIdx.x) * kTile;
+  const int c0 = blockIdx.y * kTile;
+  const int tr = threadIdx.x >> 3, tc = (threadIdx.x & 7) * 8;  // 32 rows x 8 column groups of 8
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const float2 g = bf16x2_to_float2(pg[q]), u = bf16x2_to_float2(pu[q]), d = bf16x2_to_float2(pd[q]);
-      float rg[2], ru[2], ra[2];
-      const float gg[2] = {g.x, g.y}, uu[2] = {u.x, u.y}, dd[2] = {d.x, d.y};
+  for (int half = 0; half < 2; ++half) {
+    const int r = tr + 32 * half;
+    const int64_t t = r0 + r;
+    const int c = c0 + tc;
+    uint32_t og[4] = {0, 0, 0, 0}, ou[4] = {0, 0, 0, 0}, oa[4] = {0, 0, 0, 0};
+    if (t < T && c < I) {
+      const uint4 gv = ldg128(gu + t * 2 * I + c), uv = ldg128(gu + t * 2 * I + I + c), dv = ldg128(dact + t * I + c);
+      const uint32_t* pg = reinterpret_cast<const uint32_t*>(&gv);
+      const uint32_t* pu = reinterpret_cast<const uint32_t*>(&uv);
+      const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv);
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float sig = 1.0f / (1.0f + __expf(-gg[e]));
-        const float sl = gg[e] * sig;
-        ra[e] = sl * uu[e];
-        rg[e] = dd[e] * uu[e] * (sig * (1.0f + gg[e] * (1.0f - sig)));
-        ru[e] = dd[e] * sl;
+      for (int q = 0; q < 4; ++q) {
+        const float2 g = bf16x2_to_float2(pg[q]), u = bf16x2_to_float2(pu[q]), d = bf16x2_to_float2(pd[q]);
+        float rg[2], ru[2], ra[2];
+        const float gg[2] = {g.x, g.y}, uu[2] = {u.x, u.y}, dd[2] = {d.x, d.y};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float sig = 1.0f / (1.0f + __expf(-gg[e]));
+          const float sl = gg[e] * sig;
+          ra[e] = sl * uu[e];
+          rg[e] = dd[e] * uu[e] * (sig * (1.0f + gg[e] * (1.0f - sig)));
+          ru[e] = dd[e] * sl;
+        }
+        og[q] = float2_to_bf16x2(rg[0], rg[1]);
+        ou[q] = float2_to_bf16x2(ru[0], ru[1]);
+        oa[q] = float2_to_bf16x2(ra[0], ra[1]);
       }
-      og[q] = float2_to_bf16x2(rg[0], rg[1]);
-      ou[q] = float2_to_bf16x2(ru[0], ru[1]);
-      oa[q] = float2_to_bf16x2(ra[0], ra[1]);
+      *reinterpret_cast<uint4*>(dgu + t * 2 * I + c) = make_uint4(og[0], og[1], og[2], og[3]);
+      *reinterpret_cast<uint4*>(dgu + t * 2 * I + I + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
     }
-    *reinterpret_cast<uint4*>(dgu + t * 2 * I + c) = make_uint4(og[0], og[1], og[2], og[3]);
-    *reinterpret_cast<uint4*>(dgu + t * 2 * I + I + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-    if (act) *reinterpret_cast<uint4*>(act + t * I + c) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    if (dgu_t) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        s_dg[r][tc + 2 * q] = static_cast<uint16_t>(og[q] & 0xffffu), s_dg[r][tc + 2 * q + 1] = static_cast<uint16_t>(og[q] >> 16);
+        s_du[r][tc + 2 * q] = static_cast<uint16_t>(ou[q] & 0xffffu), s_du[r][tc + 2 * q + 1] = static_cast<uint16_t>(ou[q] >> 16);
+        s_ac[r][tc + 2 * q] = static_cast<uint16_t>(oa[q] & 0xffffu), s_ac[r][tc + 2 * q + 1] = static_cast<uint16_t>(oa[q] >> 16);
+      }
+    }
+  }
+  if (!dgu_t) return;
+  __syncthreads();
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t gr = r0 + 2 * tx;  // token pair
+  if (gr >= ld_t) return;
+#pragma unroll
+  for (int i = 0; i < kTile / 8; ++i) {
+    const int c = ty + 8 * i;
+    const int gc = c0 + c;
+    if (gc >= I) continue;
+    const uint32_t vg = static_cast<uint32_t>(s_dg[2 * tx][c]) | (static_cast<uint32_t>(s_dg[2 * tx + 1][c]) << 16);
+    const uint32_t vu = static_cast<uint32_t>(s_du[2 * tx][c]) | (static_cast<uint32_t>(s_du[2 * tx + 1][c]) << 16);
+    const uint32_t va = static_cast<uint32_t>(s_ac[2 * tx][c]) | (static_cast<uint32_t>(s_ac[2 * tx + 1][c]) << 16);
+    *reinterpret_cast<uint32_t*>(dgu_t + static_cast<int64_t>(gc) * ld_t + gr) = vg;
+    *reinterpret_cast<uint32_t*>(dgu_t + (static_cast<int64_t>(I) + gc) * ld_t + gr) = vu;
+    *reinterpret_cast<uint32_t*>(act_t + static_cast<int64_t>(gc) * ld_t + gr) = va;
   }
 }
 
@@ -99,16 +131,20 @@ extern "C" int omni_transpose_bf16(const void* in, int64_t rows, int64_t cols, i
 }
 
 extern "C" int omni_swiglu_bwd(const void* gate_up, const void* dact, int64_t num_tokens, int intermediate, void* dgate_up,
-                               void* act, void* stream) {
+                               void* dgate_up_t, void* act_t, int64_t ld_t, void* stream) {
   OMNI_REQUIRE(num_tokens >= 0 && intermediate >= 8 && intermediate % 8 == 0, "intermediate must be a positive multiple of 8");
+  OMNI_REQUIRE((dgate_up_t == nullptr) == (act_t == nullptr), "dgate_up_t and act_t must be given together");
+  OMNI_REQUIRE(dgate_up_t == nullptr || (ld_t >= num_tokens && ld_t % 2 == 0), "ld_t must be even and >= num_tokens");
   if (num_tokens == 0) return 0;
   OMNI_REQUIRE(gate_up && dact && dgate_up, "NULL argument");
-  OMNI_REQUIRE(aligned16(gate_up) && aligned16(dact) && aligned16(dgate_up) && aligned16(act), "pointers must be 16-byte aligned");
-  const int64_t total = num_tokens * (intermediate / 8);
-  const int64_t blocks = ceil_div64(total, 256);
-  const unsigned grid = static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16);
-  swiglu_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  OMNI_REQUIRE(aligned16(gate_up) && aligned16(dact) && aligned16(dgate_up) && aligned16(dgate_up_t) && aligned16(act_t),
+               "pointers must be 16-byte aligned");
+  // with transposed outputs the token tiles also cover the padding columns num_tokens..ld_t-1 (zeros)
+  const int64_t gx = ceil_div64(dgate_up_t ? ld_t : num_tokens, kTile);
+  const int64_t gy = ceil_div64(intermediate, kTile);
+  OMNI_REQUIRE(gy <= 65535, "intermediate too large for one launch");
+  swiglu_bwd_kernel<<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gate_up), static_cast<const __nv_bfloat16*>(dact), num_tokens, intermediate,
-      static_cast<__nv_bfloat16*>(dgate_up), static_cast<__nv_bfloat16*>(act));
+      static_cast<__nv_bfloat16*>(dgate_up), static_cast<uint16_t*>(dgate_up_t), static_cast<uint16_t*>(act_t), ld_t);
   return check_launch("swiglu_bwd_kernel");
 }

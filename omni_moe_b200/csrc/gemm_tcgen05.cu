@@ -42,6 +42,8 @@ struct GemmArgs {
   int64_t ldo;
   const float* residual;  // EPI_RES
   int64_t ldr;
+  void* gu_out;           // EPI_SWIGLU: if set, [M, 2N] bf16 that also receives the gate | up pre-activations
+  int64_t ldgu;
   // router tile columns of the fused gate/up + router-gate launch (pair kernel, EPI_SWIGLU only)
   int router_tiles;       // tile columns holding router sub-keys (0 = none); they come first in tile order
   int router_n;           // sqrt_n
@@ -122,6 +124,35 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
+    }
+    if (EPI == EPI_SWIGLU && g.gu_out != nullptr && live) {
+      // training: keep the pre-activations for the backward (gate in columns [0, N), up in [N, 2N))
+      __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(g.gu_out) + static_cast<int64_t>(row) * g.ldgu + col0;
+      __nv_bfloat16* ou = og + g.N;
+      if (full && (g.ldgu & 7) == 0 && (g.N & 7) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 pg, pu;
+          pg.x = float2_to_bf16x2(__uint_as_float(ra[i]), __uint_as_float(ra[i + 1]));
+          pg.y = float2_to_bf16x2(__uint_as_float(ra[i + 2]), __uint_as_float(ra[i + 3]));
+          pg.z = float2_to_bf16x2(__uint_as_float(ra[i + 4]), __uint_as_float(ra[i + 5]));
+          pg.w = float2_to_bf16x2(__uint_as_float(ra[i + 6]), __uint_as_float(ra[i + 7]));
+          pu.x = float2_to_bf16x2(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1]));
+          pu.y = float2_to_bf16x2(__uint_as_float(rb[i + 2]), __uint_as_float(rb[i + 3]));
+          pu.z = float2_to_bf16x2(__uint_as_float(rb[i + 4]), __uint_as_float(rb[i + 5]));
+          pu.w = float2_to_bf16x2(__uint_as_float(rb[i + 6]), __uint_as_float(rb[i + 7]));
+          *reinterpret_cast<uint4*>(og + i) = pg;
+          *reinterpret_cast<uint4*>(ou + i) = pu;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {  // static indices: the accumulator registers must not move to local memory
+          if (col0 + i < col_lim) {
+            og[i] = __float2bfloat16_rn(__uint_as_float(ra[i]));
+            ou[i] = __float2bfloat16_rn(__uint_as_float(rb[i]));
+          }
+        }
+      }
     }
     if (ch + 1 < NCH) {
       tmem_ld32_async(taddr + c + 32, ra);
@@ -711,6 +742,27 @@ extern "C" int omni_mlp_gate_up(const void* x, const void* gate_w, const void* u
     return launch_pair<EPI_SWIGLU, false>(ma, mg, mu, mg, mu, g, static_cast<cudaStream_t>(stream));
   }
   return launch<256, EPI_SWIGLU>(ma, mg, mu, g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int omni_mlp_gate_up_save(const void* x, const void* gate_w, const void* up_w, int64_t num_tokens, int hidden,
+                                     int intermediate, void* act, void* gate_up, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && num_tokens < (int64_t(1) << 31) - 2 * BM, "num_tokens out of range");
+  OMNI_REQUIRE(hidden >= 8 && hidden % 8 == 0, "hidden must be a positive multiple of 8, got %d", hidden);
+  OMNI_REQUIRE(intermediate >= 8 && intermediate % 8 == 0, "intermediate must be a positive multiple of 8, got %d", intermediate);
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(x && gate_w && up_w && act && gate_up && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(gate_w) && aligned16(up_w) && aligned16(act) && aligned16(gate_up), "pointers must be 16-byte aligned");
+  CUtensorMap ma, mg, mu;
+  if (int e = make_map(&ma, x, num_tokens, hidden, BM)) return e;
+  if (int e = make_map(&mg, gate_w, intermediate, hidden, 128)) return e;
+  if (int e = make_map(&mu, up_w, intermediate, hidden, 128)) return e;
+  GemmArgs g{};
+  g.M = static_cast<int>(num_tokens), g.N = intermediate, g.K = hidden, g.dual = 0;
+  g.tiles_m = ceil_div(g.M, 2 * BM);
+  g.tiles_n = g.tiles_n_axis = ceil_div(intermediate, 128);
+  g.out = act, g.ldo = intermediate, g.gu_out = gate_up, g.ldgu = 2 * static_cast<int64_t>(intermediate);
+  g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  return launch_pair<EPI_SWIGLU, false>(ma, mg, mu, mg, mu, g, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int omni_mlp_gate_up_router(const void* x, const void* gate_w, const void* up_w, const void* gate_x,

@@ -231,8 +231,10 @@ class OmniMoE(nn.Module):
         x = hidden_states.reshape(-1, self.hidden_size)
         logits_x = self.router_norm_x(self.router_gate_x(x))
         logits_y = self.router_norm_y(self.router_gate_y(x))
-        log_probs_x = torch.nn.functional.log_softmax(logits_x, dim=-1)
-        log_probs_y = torch.nn.functional.log_softmax(logits_y, dim=-1)
+        # log-probabilities, scores and routing weights stay in fp32 (the reference keeps the module dtype):
+        # bf16 log-probs tie massively, and ties are what makes a selection irreproducible
+        log_probs_x = torch.nn.functional.log_softmax(logits_x, dim=-1, dtype=torch.float32)
+        log_probs_y = torch.nn.functional.log_softmax(logits_y, dim=-1, dtype=torch.float32)
         scores, indices = omni_router_func(log_probs_x, log_probs_y, self.num_expert_sqrt, self.top_k)
         routing_weights = torch.exp(scores)
         experts_states = omni_expert_func(x, self.up_embed.weight, self.down_embed.weight, routing_weights, indices)

@@ -195,12 +195,13 @@ def transpose_padded(src: torch.Tensor, out: torch.Tensor | None = None) -> torc
 
 
 def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor,
-                 down_weight: torch.Tensor, need_weight_grads: bool = True):
+                 down_weight: torch.Tensor, need_weight_grads: bool = True, gate_up: torch.Tensor | None = None):
     """Backward of ``y = (silu(x Wg^T) * (x Wu^T)) Wd^T`` on bf16 operands.
 
-    The forward keeps only x (its fused kernel never writes gate / up); they are recomputed here,
-    rounded to bf16 as the reference does before the activation.  Six GEMMs on the tensor cores:
-    gate, up, dact = dy Wd, dx = (dgate | dup) (Wg ; Wu), dWd = dy^T act, (dWg ; dWu) = (dgate | dup)^T x.
+    ``gate_up [T, 2I]`` bf16 are the pre-activations saved by the training forward
+    (``mlp_forward(..., gate_up=...)``); without them they are recomputed here with two more GEMMs.
+    GEMMs on the tensor cores: dact = dy Wd, dx = (dgate | dup) (Wg ; Wu), dWd = dy^T act,
+    (dWg ; dWu) = (dgate | dup)^T x.
     Returns ``(dx, d_gate_weight, d_up_weight, d_down_weight)`` in bf16.
     """
     _lib.require_cuda(dy, x, gate_weight, up_weight, down_weight)
@@ -218,15 +219,22 @@ def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, u
         return (torch.empty((0, h), **bf), z((i, h), **bf), z((i, h), **bf), z((h, i), **bf))
     lib = _lib.load()
     # gate | up pre-activations
-    gu = torch.empty((t, 2 * i), **bf)
-    gemm_nt(x, wg, gu[:, :i], status)
-    gemm_nt(x, wu, gu[:, i:], status)
+    if gate_up is not None:
+        assert gate_up.shape == (t, 2 * i) and gate_up.dtype == torch.bfloat16 and gate_up.is_contiguous()
+        gu = gate_up
+    else:
+        gu = torch.empty((t, 2 * i), **bf)
+        gemm_nt(x, wg, gu[:, :i], status)
+        gemm_nt(x, wu, gu[:, i:], status)
     # dact = dy @ Wd   (Wd is [H, I]: its transpose has the contraction dimension contiguous)
     dact = gemm_nt(dy, transpose_padded(wd), None, status)
     dgu = torch.empty((t, 2 * i), **bf)
-    act = torch.empty((t, i), **bf) if need_weight_grads else None
+    tp = _pad8(t)
+    dgu_t = torch.empty((2 * i, tp), **bf) if need_weight_grads else None
+    act_t = torch.empty((i, tp), **bf) if need_weight_grads else None
     with torch.cuda.device(dev):
-        _lib.check(lib.omni_swiglu_bwd(gu.data_ptr(), dact.data_ptr(), t, i, dgu.data_ptr(), _lib.ptr(act), _lib.stream_ptr()))
+        _lib.check(lib.omni_swiglu_bwd(gu.data_ptr(), dact.data_ptr(), t, i, dgu.data_ptr(), _lib.ptr(dgu_t), _lib.ptr(act_t),
+                                       tp, _lib.stream_ptr()))
     # dx = dgate @ Wg + dup @ Wu = dgu @ (Wg ; Wu): B operand [H, 2I] = (Wg^T | Wu^T)
     wgu_t = torch.empty((h, 2 * i), **bf)
     transpose_padded(wg, wgu_t[:, :i])
@@ -234,7 +242,7 @@ def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, u
     dx = gemm_nt(dgu, wgu_t, None, status)
     d_wg = d_wu = d_wd = None
     if need_weight_grads:
-        dy_t, act_t, x_t, dgu_t = (transpose_padded(v) for v in (dy, act, x, dgu))   # [*, pad8(T)]
+        dy_t, x_t = transpose_padded(dy), transpose_padded(x)   # [H, pad8(T)]
         d_wd = gemm_nt(dy_t, act_t, None, status)              # [H, I]
         d_wgu = gemm_nt(dgu_t, x_t, None, status)              # [2I, H]
         d_wg, d_wu = d_wgu[:i], d_wgu[i:]
@@ -248,15 +256,16 @@ class MlpFunction(torch.autograd.Function):
     def forward(ctx, x, gate_weight, up_weight, down_weight):
         from .mlp import mlp_forward
         xb, wg, wu, wd = as_bf16(x), as_bf16(gate_weight), as_bf16(up_weight), as_bf16(down_weight)
-        y = mlp_forward(xb, wg, wu, wd)
-        ctx.save_for_backward(xb, wg, wu, wd)
+        gu = torch.empty((xb.size(0), 2 * wg.size(0)), device=xb.device, dtype=torch.bfloat16)
+        y = mlp_forward(xb, wg, wu, wd, gate_up=gu)
+        ctx.save_for_backward(xb, wg, wu, wd, gu)
         ctx.dtypes = (x.dtype, gate_weight.dtype, up_weight.dtype, down_weight.dtype)
         return y.to(x.dtype)
 
     @staticmethod
     def backward(ctx, dy):
-        xb, wg, wu, wd = ctx.saved_tensors
+        xb, wg, wu, wd, gu = ctx.saved_tensors
         need_w = any(ctx.needs_input_grad[1:])
-        dx, d_wg, d_wu, d_wd = mlp_backward(as_bf16(dy), xb, wg, wu, wd, need_weight_grads=need_w)
+        dx, d_wg, d_wu, d_wd = mlp_backward(as_bf16(dy), xb, wg, wu, wd, need_weight_grads=need_w, gate_up=gu)
         cast = lambda g, j: g.to(ctx.dtypes[j]) if (g is not None and ctx.needs_input_grad[j]) else None
         return cast(dx, 0), cast(d_wg, 1), cast(d_wu, 2), cast(d_wd, 3)

@@ -9,11 +9,13 @@ from ._common import as_bf16
 
 def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
                 residual: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                act: torch.Tensor | None = None) -> torch.Tensor:
+                act: torch.Tensor | None = None, gate_up: torch.Tensor | None = None) -> torch.Tensor:
     """``(silu(x Wg^T) * (x Wu^T)) Wd^T (+ residual)`` on bf16 operands with two tcgen05 GEMMs.
 
     ``residual``: optional fp32 ``[T, H]`` added before the result is rounded to bf16.
     ``act``: optional bf16 ``[T, I]`` scratch for the activation.
+    ``gate_up``: optional bf16 ``[T, 2I]`` that receives the pre-activations ``(x Wg^T | x Wu^T)`` (kept
+    for the backward in training).
     """
     _lib.require_cuda(x, gate_weight, up_weight, down_weight)
     assert x.dtype == gate_weight.dtype == up_weight.dtype == down_weight.dtype == torch.bfloat16
@@ -29,11 +31,20 @@ def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Ten
     if residual is not None:
         assert residual.shape == (t, h) and residual.dtype == torch.float32 and residual.is_contiguous()
     y = torch.empty((t, h), device=dev, dtype=torch.bfloat16)
+    if gate_up is not None:
+        assert gate_up.shape == (t, 2 * i) and gate_up.dtype == torch.bfloat16 and gate_up.is_contiguous()
     if t > 0:
+        lib = _lib.load()
         with torch.cuda.device(dev):
-            _lib.check(_lib.load().omni_mlp_fwd(
-                x.data_ptr(), gate_weight.data_ptr(), up_weight.data_ptr(), down_weight.data_ptr(), t, h, i,
-                act.data_ptr(), _lib.ptr(residual), y.data_ptr(), status.data_ptr(), _lib.stream_ptr()))
+            st = _lib.stream_ptr()
+            if gate_up is None:
+                _lib.check(lib.omni_mlp_gate_up(x.data_ptr(), gate_weight.data_ptr(), up_weight.data_ptr(), t, h, i,
+                                                act.data_ptr(), status.data_ptr(), st))
+            else:
+                _lib.check(lib.omni_mlp_gate_up_save(x.data_ptr(), gate_weight.data_ptr(), up_weight.data_ptr(), t, h, i,
+                                                     act.data_ptr(), gate_up.data_ptr(), status.data_ptr(), st))
+            _lib.check(lib.omni_mlp_down(act.data_ptr(), down_weight.data_ptr(), t, h, i, _lib.ptr(residual), y.data_ptr(),
+                                         status.data_ptr(), st))
     return y
 
 

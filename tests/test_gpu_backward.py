@@ -146,6 +146,16 @@ def test_mlp_backward_matches_oracle(t, h, i):
     dy = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
     dx, dwg, dwu, dwd = mlp_backward(dy.cuda(), x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
     ex, eg, eu, ed = orc.mlp_backward(x.float(), wg.float(), wu.float(), wd.float(), dy.float())
+    # the training forward saves gate | up from its epilogue: same values as x Wg^T, x Wu^T rounded to bf16
+    from omni_moe_b200.ops import mlp_forward
+    gu = torch.empty(t, 2 * i, dtype=torch.bfloat16, device="cuda")
+    y = mlp_forward(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), gate_up=gu)
+    _scaled_close(gu[:, :i], x.float() @ wg.float().t(), "saved gate", rtol=1e-2, atol_frac=4e-3)
+    _scaled_close(gu[:, i:], x.float() @ wu.float().t(), "saved up", rtol=1e-2, atol_frac=4e-3)
+    assert torch.equal(y, mlp_forward(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())), "saving must not change the output"
+    dx2, _, _, dwd2 = mlp_backward(dy.cuda(), x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), gate_up=gu)
+    _scaled_close(dx2, ex, "dx (saved gate/up)", rtol=3e-2, atol_frac=2e-2)
+    _scaled_close(dwd2, ed, "d_down_weight (saved gate/up)", rtol=3e-2, atol_frac=2e-2)
     # intermediates (gate, up, dact, dgate, dup) are rounded to bf16 between the GEMMs, as in the reference's bf16 path
     _scaled_close(dx, ex, "dx", rtol=3e-2, atol_frac=2e-2)
     _scaled_close(dwg, eg, "d_gate_weight", rtol=3e-2, atol_frac=2e-2)
