@@ -112,12 +112,33 @@ class OmniMoE(nn.Module):
             self._bn_cache = (key, scale.contiguous(), (-mean * scale).contiguous())
         return self._bn_cache[1], self._bn_cache[2]
 
+    def sync_batch_statistics(self, group=None, enabled: bool = True) -> "OmniMoE":
+        """Training-mode BatchNorm over the tokens of every rank of ``group`` (default: all ranks), for
+        data-parallel training where a batch is sharded over GPUs.  Covers the fused (no-grad) forward;
+        for the differentiable forward convert the two norm layers with
+        ``torch.nn.SyncBatchNorm.convert_sync_batchnorm`` - the fused forward then follows their group."""
+        self._bn_sync = (group,) if enabled else None
+        return self
+
+    def _bn_group(self):
+        """None = local statistics; otherwise a 1-tuple holding the process group (None inside = world)."""
+        if getattr(self, "_bn_sync", None) is not None:
+            return self._bn_sync
+        if isinstance(self.router_norm_x, nn.SyncBatchNorm):
+            return (self.router_norm_x.process_group,)
+        return None
+
     def _bn_fold_train(self, logits: torch.Tensor):
-        """Training-mode BatchNorm: batch statistics over all tokens, running statistics updated as
-        nn.BatchNorm1d does (momentum average, unbiased variance)."""
+        """Training-mode BatchNorm: batch statistics over all tokens (of all ranks, when synchronised),
+        running statistics updated as nn.BatchNorm1d does (momentum average, unbiased variance)."""
         n = self.num_expert_sqrt
-        t = logits.size(0)
-        var, mean = torch.var_mean(logits, dim=0, unbiased=False)
+        grp = self._bn_group()
+        if grp is None:
+            t = logits.size(0)
+            var, mean = torch.var_mean(logits, dim=0, unbiased=False)
+        else:
+            from ..parallel import synced_batch_statistics
+            mean, var, t = synced_batch_statistics(logits, grp[0])
         with torch.no_grad():
             for bn, sl in ((self.router_norm_x, slice(0, n)), (self.router_norm_y, slice(n, 2 * n))):
                 if bn.track_running_stats:

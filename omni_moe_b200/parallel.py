@@ -42,6 +42,35 @@ import torch.distributed as dist
 from . import _lib
 
 
+def synced_batch_statistics(z: torch.Tensor, group=None):
+    """Mean and biased variance of every column of ``z [T_local, C]`` over the tokens of ALL ranks of
+    ``group``, plus the global token count: what training-mode BatchNorm of the router logits needs
+    when the tokens of a batch are sharded over GPUs (the reference normalises over the whole batch
+    on one GPU, omni_moe/modules/omni_moe.py:53-54,70-71).
+
+    Each rank sends ``2C + 1`` floats (its column means, its sums of squared deviations, its count);
+    the per-rank moments are merged with the pairwise formula for combining variances, so nothing is
+    lost to cancellation as it would be in a global sum of squares.  Without an initialised process
+    group (or with a group of one) these are the local statistics.
+    """
+    t = z.size(0)
+    zf = z.float()
+    var_l, mean_l = torch.var_mean(zf, dim=0, unbiased=False) if t > 0 else (torch.zeros_like(zf[0:0].sum(0)),) * 2
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return mean_l, var_l, t
+    c = z.size(1)
+    packed = torch.cat([mean_l, var_l * t, torch.tensor([float(t)], device=z.device)])
+    world = dist.get_world_size(group)
+    gathered = torch.empty(world * (2 * c + 1), device=z.device, dtype=torch.float32)
+    dist.all_gather_into_tensor(gathered, packed.contiguous(), group=group)
+    gathered = gathered.view(world, 2 * c + 1)
+    means, m2s, counts = gathered[:, :c], gathered[:, c:2 * c], gathered[:, 2 * c:]
+    total = counts.sum()
+    mean = (means * counts).sum(0) / total
+    m2 = m2s.sum(0) + (counts * (means - mean) ** 2).sum(0)
+    return mean, m2 / total, int(total.item())
+
+
 def shard_tokens(hidden_states: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     """Contiguous token shard of ``[T, H]`` (or ``[B, S, H]`` flattened) for ``rank``; T must divide evenly."""
     x = hidden_states.reshape(-1, hidden_states.shape[-1])

@@ -95,3 +95,57 @@ def test_partitioned_layer_two_gpus_nccl(tmp_path):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
+
+
+_CHILD_BN = r"""
+import os, sys, copy, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["OMNI_ROOT"])
+from omni_moe_b200.modules.omni_moe import OmniMoE, OmniMoEConfig
+from omni_moe_b200.parallel import shard_tokens
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+torch.manual_seed(0)
+base = OmniMoE(OmniMoEConfig(256, 512, "silu", 1024, 8)).to(torch.bfloat16)
+x = torch.randn(1, 96 * world, 256).bfloat16()
+# one GPU, whole batch
+whole = copy.deepcopy(base).cuda().train()
+with torch.no_grad():
+    y_whole = whole(x.cuda())
+# token-sharded replicas with synchronised batch statistics: fused (no-grad) forward
+dp = copy.deepcopy(base).cuda().train().sync_batch_statistics()
+xs = shard_tokens(x, rank, world).cuda().view(1, 96, 256)
+with torch.no_grad():
+    y = dp(xs)
+for a, b in ((dp.router_norm_x, whole.router_norm_x), (dp.router_norm_y, whole.router_norm_y)):
+    assert torch.allclose(a.running_mean, b.running_mean, atol=1e-5), (a.running_mean - b.running_mean).abs().max()
+    assert torch.allclose(a.running_var, b.running_var, rtol=1e-4, atol=1e-6), (a.running_var - b.running_var).abs().max()
+sl = slice(rank * 96, (rank + 1) * 96)
+same = (dp.last_routing[1] == whole.last_routing[1][sl]).all(dim=1)
+assert same.float().mean() > 0.97, float(same.float().mean())
+assert torch.allclose(y.view(96, 256)[same].float(), y_whole.view(-1, 256)[sl][same].float(), rtol=2e-2, atol=2e-2)
+# differentiable forward: torch's SyncBatchNorm in place of the two norm layers
+sdp = torch.nn.SyncBatchNorm.convert_sync_batchnorm(copy.deepcopy(base)).cuda().train()
+ys = sdp(xs)
+ys.float().square().mean().backward()
+assert torch.allclose(sdp.router_norm_x.running_mean.float(), whole.router_norm_x.running_mean.float(), atol=2e-2)
+assert all(p.grad is not None for p in sdp.parameters())
+dist.barrier(); dist.destroy_process_group()
+print("rank", rank, "ok", flush=True)
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_training_batchnorm_synchronised_over_two_gpus(tmp_path):
+    """Token-sharded replicas in training mode normalise the router logits with the statistics of the whole batch."""
+    script = tmp_path / "child_bn.py"
+    script.write_text(_CHILD_BN)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, OMNI_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout

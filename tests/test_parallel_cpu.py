@@ -88,3 +88,44 @@ def test_expert_partition_arithmetic():
     assert parts[0].owner(e).tolist() == [0, 0, 0, 1, 1, 1, 2, 2, 2, 3]
     t = torch.arange(20).view(10, 2)
     assert torch.equal(parts[3].slice_rows(t), t[9:10])
+
+
+def _stats_worker(rank, world, port, counts, c, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from omni_moe_b200.parallel import synced_batch_statistics
+        g = torch.Generator().manual_seed(5)
+        z = torch.randn(sum(counts), c, generator=g) * 3.0 + 100.0     # a large common offset: cancellation would show
+        lo = sum(counts[:rank])
+        mean, var, total = synced_batch_statistics(z[lo:lo + counts[rank]])
+        ev, em = torch.var_mean(z.double(), dim=0, unbiased=False)
+        ret[rank] = (float((mean.double() - em).abs().max()), float((var.double() - ev).abs().max() / ev.max()), total)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("counts", [(7, 9), (1, 30, 5)])
+def test_synced_batch_statistics_gloo(counts):
+    """Batch statistics of router logits sharded unevenly over ranks = statistics of the whole batch."""
+    world, port = len(counts), _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_stats_worker, args=(r, world, port, counts, 12, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    for r in range(world):
+        dm, dv, total = ret[r]
+        assert dm < 1e-4 and dv < 1e-5 and total == sum(counts), (r, ret[r])
+
+
+def test_synced_batch_statistics_without_process_group():
+    from omni_moe_b200.parallel import synced_batch_statistics
+    z = torch.randn(50, 6)
+    mean, var, total = synced_batch_statistics(z)
+    ev, em = torch.var_mean(z, dim=0, unbiased=False)
+    assert torch.allclose(mean, em) and torch.allclose(var, ev) and total == 50
