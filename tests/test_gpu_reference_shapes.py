@@ -85,3 +85,67 @@ def test_readme_quick_start():
     for name, p in layer.named_parameters():
         assert p.grad is not None and p.grad.shape == p.shape and bool(torch.isfinite(p.grad).all()), name
         assert bool(p.grad.any()), name
+
+
+def _grad_close(actual, expected, what, rtol=3e-2, atol_frac=2e-2):
+    a, e = actual.detach().float().cpu(), expected.detach().float().cpu()
+    scale = float(e.abs().max()) or 1.0
+    bad = (a - e).abs() > atol_frac * scale + rtol * e.abs()
+    assert not bad.any(), f"{what}: {int(bad.sum())}/{bad.numel()} outside tolerance, max err {float((a - e).abs().max()):.4g} at scale {scale:.4g}"
+
+
+@pytest.mark.parametrize("case", [(1024, 64, 16), (1024, 64, 32), (1024, 128, 16), (1024, 128, 32), (1024, 256, 16),
+                                  (1024, 256, 32)])
+def test_router_backward_reference_cases(case):
+    # tests/test_router.py:73-95 of the reference: loss = scores.sum(); loss.backward()
+    from omni_moe.ops.triton import triton_omni_router_func
+    num_tokens, num_keys, top_k = case
+    g = gen(0)
+    lx = torch.randn(num_tokens, num_keys, generator=g).bfloat16()
+    ly = torch.randn(num_tokens, num_keys, generator=g).bfloat16()
+    cx, cy = lx.cuda().requires_grad_(True), ly.cuda().requires_grad_(True)
+    scores, indices = triton_omni_router_func(cx, cy, num_keys, top_k)
+    scores.sum().backward()
+    ex, ey = orc.router_backward(torch.ones(num_tokens, top_k), indices.cpu(), num_keys)
+    # sums of ones: small integers, exact in bf16
+    assert torch.equal(cx.grad.float().cpu(), ex) and torch.equal(cy.grad.float().cpu(), ey)
+
+
+@pytest.mark.parametrize("num_experts", [1024, 4096, 16384, 65536])
+def test_expert_backward_reference_cases(num_experts):
+    # tests/test_expert.py backward factory: loss = expert(...).sum(); gradients for x, both tables and the weights
+    from omni_moe.ops.triton import triton_omni_expert_func
+    num_tokens, hidden, top_k = 1024, 1024, 32
+    g = gen(0)
+    hs = (torch.randn(num_tokens, hidden, generator=g) * 0.5).bfloat16()
+    up = (torch.randn(num_experts, hidden, generator=g) * 0.1).bfloat16()
+    dn = (torch.randn(num_experts, hidden, generator=g) * 0.1).bfloat16()
+    rw = (torch.randn(num_tokens, top_k, generator=g) * 0.1).bfloat16()
+    idx = torch.randint(0, num_experts, (num_tokens, top_k), generator=g, dtype=torch.int32)
+    chs, cup, cdn, crw = (v.cuda().requires_grad_(True) for v in (hs, up, dn, rw))
+    triton_omni_expert_func(chs, cup, cdn, crw, idx.cuda()).sum().backward()
+    ex, eu, ed, eg = orc.expert_backward(hs, up, dn, rw, idx, torch.ones(num_tokens, hidden))
+    _grad_close(chs.grad, ex, "dx")
+    _grad_close(cup.grad, eu, "d_up")
+    _grad_close(cdn.grad, ed, "d_down")
+    _grad_close(crw.grad, eg, "d_routing_weights")
+
+
+@pytest.mark.parametrize("intermediate", [1024, 4096, 16384])
+def test_mlp_backward_reference_cases(intermediate):
+    # tests/test_mlp.py backward factory; the 65536-wide case is left to the forward test (its fp32 CPU
+    # reference gradients take minutes)
+    from omni_moe.ops.triton import triton_omni_mlp_func
+    num_tokens, hidden = 1024, 1024
+    g = gen(42)
+    hs = (torch.randn(num_tokens, hidden, generator=g) * 0.5).bfloat16()
+    wg = (torch.randn(intermediate, hidden, generator=g) * 0.02).bfloat16()
+    wu = (torch.randn(intermediate, hidden, generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(hidden, intermediate, generator=g) * 0.02).bfloat16()
+    chs, cg, cu, cd = (v.cuda().requires_grad_(True) for v in (hs, wg, wu, wd))
+    triton_omni_mlp_func(chs, cg, cu, cd).sum().backward()
+    ex, eg, eu, ed = orc.mlp_backward(hs, wg, wu, wd, torch.ones(num_tokens, hidden))
+    _grad_close(chs.grad, ex, "dx")
+    _grad_close(cg.grad, eg, "d_gate_weight")
+    _grad_close(cu.grad, eu, "d_up_weight")
+    _grad_close(cd.grad, ed, "d_down_weight")
