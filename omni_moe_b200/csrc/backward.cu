@@ -172,11 +172,12 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_rows_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ ds,
     const float* __restrict__ cdown, const int32_t* __restrict__ sorted_pair_ids, const int32_t* __restrict__ expert_ids,
     const int32_t* __restrict__ offsets, const int32_t* __restrict__ num_segments, int64_t T, int k, int H, int compact,
-    void* __restrict__ d_up, void* __restrict__ d_down, int* __restrict__ status) {
+    int long_threshold, void* __restrict__ d_up, void* __restrict__ d_down, int* __restrict__ status) {
   const int warp = threadIdx.x >> 5, lane = lane_id();
   const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
   if (s >= *num_segments) return;
   const int begin = offsets[s], end = offsets[s + 1];
+  if (end - begin > long_threshold) return;  // handled by the two long-segment kernels
   const int64_t row = compact ? s : static_cast<int64_t>(expert_ids[s]);
   bool bad = false;
   for (int c0 = lane * 8; c0 < H + lane * 8; c0 += 1024) {  // every lane makes the same number of trips
@@ -230,6 +231,144 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_rows_kernel(
   if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_TOKEN_INDEX);
 }
 
+// ---- long segments ----------------------------------------------------------------------------
+// An expert that receives thousands of pairs (skewed routing) would keep one warp busy for
+// milliseconds.  Segments longer than kLongBlock pairs are therefore summed in two levels:
+//   expert_bwd_rows_long_kernel    block b owns the sorted positions [b*kLongBlock, (b+1)*kLongBlock).
+//                                  At most two long segments meet it (the one covering its first position
+//                                  and the one covering its last); for each, the block's 8 warps sum their
+//                                  64 positions apiece, combine through shared memory in warp order and
+//                                  store one fp32 partial row pair in slot 2b (segment covers the block's
+//                                  first position) or 2b+1.
+//   expert_bwd_rows_reduce_kernel  one warp per long segment adds its partials in block order and writes
+//                                  the gradient rows.
+// Fixed assignment and fixed order: the sums are reproducible.
+constexpr int kLongBlock = 512;
+constexpr int kLongThreads = 256;
+constexpr int kLongCols = 256;  // columns per pass: one 128-bit load per lane
+
+// index of the segment containing sorted position p: largest s with offsets[s] <= p
+__device__ __forceinline__ int segment_of(const int32_t* __restrict__ offsets, int U, int p) {
+  int lo = 0, hi = U - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (offsets[mid] <= p) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(kLongThreads) expert_bwd_rows_long_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ ds,
+    const float* __restrict__ cdown, const int32_t* __restrict__ sorted_pair_ids, const int32_t* __restrict__ offsets,
+    const int32_t* __restrict__ num_segments, int64_t P, int64_t T, int k, int H, float* __restrict__ scratch,
+    int* __restrict__ status) {
+  __shared__ float s_part[kLongThreads / 32][2][kLongCols];
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const int U = *num_segments;
+  if (U <= 0) return;
+  const int64_t lo = static_cast<int64_t>(blockIdx.x) * kLongBlock;
+  if (lo >= P) return;
+  const int64_t hi = (lo + kLongBlock < P) ? lo + kLongBlock : P;
+  const int s_first = segment_of(offsets, U, static_cast<int>(lo));
+  const int s_last = segment_of(offsets, U, static_cast<int>(hi - 1));
+  bool bad = false;
+  for (int which = 0; which < 2; ++which) {
+    if (which == 1 && s_last == s_first) break;
+    const int s = which == 0 ? s_first : s_last;
+    const int begin = offsets[s], end = offsets[s + 1];
+    if (end - begin <= kLongBlock) continue;  // block-uniform
+    const int a = begin > lo ? begin : static_cast<int>(lo);
+    const int c = end < hi ? end : static_cast<int>(hi);
+    float* slot = scratch + (2 * static_cast<int64_t>(blockIdx.x) + which) * 2 * H;
+    // this warp's positions: a + warp*64 + {lane, lane+32}
+    int my_t[2];
+    float my_s[2], my_c[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int p = a + warp * 64 + u * 32 + lane;
+      my_t[u] = -1, my_s[u] = 0.f, my_c[u] = 0.f;
+      if (p < c) {
+        const int pid = sorted_pair_ids[p];
+        const int64_t tok = pid / k;
+        if (pid < 0 || tok >= T) bad = true;
+        else my_t[u] = static_cast<int>(tok), my_s[u] = ds[pid], my_c[u] = cdown[pid];
+      }
+    }
+    const int cnt = max(0, min(64, c - (a + warp * 64)));
+    for (int c0 = 0; c0 < H; c0 += kLongCols) {
+      const int col = c0 + lane * 8;
+      float2 au[4], ad[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) au[q] = make_float2(0.f, 0.f), ad[q] = make_float2(0.f, 0.f);
+      for (int i0 = 0; i0 < cnt; i0 += 4) {
+        uint4 xv[4], gv[4];
+        float cs[4], cc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u;
+          const int src = i & 31;
+          const int tok = (i < 32) ? __shfl_sync(FULL_MASK, my_t[0], src) : __shfl_sync(FULL_MASK, my_t[1], src);
+          cs[u] = (i < 32) ? __shfl_sync(FULL_MASK, my_s[0], src) : __shfl_sync(FULL_MASK, my_s[1], src);
+          cc[u] = (i < 32) ? __shfl_sync(FULL_MASK, my_c[0], src) : __shfl_sync(FULL_MASK, my_c[1], src);
+          const bool ld = i < cnt && tok >= 0 && col < H;
+          xv[u] = ld ? ldg128(x + static_cast<int64_t>(tok) * H + col) : make_uint4(0, 0, 0, 0);
+          gv[u] = ld ? ldg128(dy + static_cast<int64_t>(tok) * H + col) : make_uint4(0, 0, 0, 0);
+          if (!ld) cs[u] = 0.f, cc[u] = 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          axpy8f(cs[u], xv[u], au);
+          axpy8f(cc[u], gv[u], ad);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        s_part[warp][0][lane * 8 + 2 * q] = au[q].x, s_part[warp][0][lane * 8 + 2 * q + 1] = au[q].y;
+        s_part[warp][1][lane * 8 + 2 * q] = ad[q].x, s_part[warp][1][lane * 8 + 2 * q + 1] = ad[q].y;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int tb = 0; tb < 2; ++tb) {
+        const int cc2 = threadIdx.x;  // kLongThreads == kLongCols: one column per thread
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kLongThreads / 32; ++w) sum += s_part[w][tb][cc2];
+        if (c0 + cc2 < H) slot[tb * H + c0 + cc2] = sum;
+      }
+      __syncthreads();
+    }
+  }
+  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_TOKEN_INDEX);
+}
+
+template <bool OUT_F32>
+__global__ void __launch_bounds__(kThreads) expert_bwd_rows_reduce_kernel(
+    const float* __restrict__ scratch, const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ offsets,
+    const int32_t* __restrict__ num_segments, int H, int compact, void* __restrict__ d_up, void* __restrict__ d_down) {
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (s >= *num_segments) return;
+  const int begin = offsets[s], end = offsets[s + 1];
+  if (end - begin <= kLongBlock) return;
+  const int b0 = begin / kLongBlock, b1 = (end - 1) / kLongBlock;
+  const int64_t row = compact ? s : static_cast<int64_t>(expert_ids[s]);
+  for (int c0 = lane * 8; c0 < H; c0 += 256) {
+    float2 au[4], ad[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) au[q] = make_float2(0.f, 0.f), ad[q] = make_float2(0.f, 0.f);
+    for (int b = b0; b <= b1; ++b) {
+      const int which = (b == b0 && begin > b0 * kLongBlock) ? 1 : 0;
+      const float* slot = scratch + (2 * static_cast<int64_t>(b) + which) * 2 * H;
+      const float4 u0 = *reinterpret_cast<const float4*>(slot + c0), u1 = *reinterpret_cast<const float4*>(slot + c0 + 4);
+      const float4 d0 = *reinterpret_cast<const float4*>(slot + H + c0), d1 = *reinterpret_cast<const float4*>(slot + H + c0 + 4);
+      au[0].x += u0.x, au[0].y += u0.y, au[1].x += u0.z, au[1].y += u0.w, au[2].x += u1.x, au[2].y += u1.y, au[3].x += u1.z, au[3].y += u1.w;
+      ad[0].x += d0.x, ad[0].y += d0.y, ad[1].x += d0.z, ad[1].y += d0.w, ad[2].x += d1.x, ad[2].y += d1.y, ad[3].x += d1.z, ad[3].y += d1.w;
+    }
+    store8<OUT_F32>(d_up, row * H + c0, au);
+    store8<OUT_F32>(d_down, row * H + c0, ad);
+  }
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -264,27 +403,52 @@ extern "C" int omni_expert_bwd_dots(const void* x, const void* up, const void* d
   return check_launch("expert_bwd_dots_kernel");
 }
 
+extern "C" size_t omni_expert_bwd_rows_scratch_bytes(int64_t num_pairs, int hidden) {
+  if (num_pairs <= 0 || hidden <= 0) return 0;
+  return static_cast<size_t>(2 * ceil_div64(num_pairs, kLongBlock)) * 2 * static_cast<size_t>(hidden) * sizeof(float);
+}
+
 extern "C" int omni_expert_bwd_rows(const void* x, const void* dy, const float* ds, const float* cdown,
                                     const int32_t* sorted_pair_ids, const int32_t* expert_ids, const int32_t* offsets,
                                     const int32_t* num_segments, int64_t max_segments, int64_t num_tokens, int k, int hidden,
-                                    int compact, void* d_up, void* d_down, int out_dtype, int32_t* status, void* stream) {
+                                    int compact, void* d_up, void* d_down, int out_dtype, void* scratch, size_t scratch_bytes,
+                                    int32_t* status, void* stream) {
   OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && max_segments >= 0, "bad sizes");
   OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
   OMNI_REQUIRE(out_dtype == OMNI_F32 || out_dtype == OMNI_BF16, "out_dtype must be OMNI_F32 or OMNI_BF16");
   OMNI_REQUIRE(max_segments < (int64_t(1) << 31), "too many segments");
+  const int64_t P = num_tokens * k;
+  OMNI_REQUIRE(P < (int64_t(1) << 31), "too many pairs");
   if (num_tokens == 0 || max_segments == 0) return 0;
   OMNI_REQUIRE(x && dy && ds && cdown && sorted_pair_ids && expert_ids && offsets && num_segments && d_up && d_down && status,
                "NULL argument");
-  OMNI_REQUIRE(aligned16(x) && aligned16(dy) && aligned16(d_up) && aligned16(d_down), "x, dy, d_up and d_down must be 16-byte aligned");
+  OMNI_REQUIRE(aligned16(x) && aligned16(dy) && aligned16(d_up) && aligned16(d_down) && aligned16(scratch),
+               "x, dy, d_up, d_down and scratch must be 16-byte aligned");
+  OMNI_REQUIRE(scratch == nullptr || scratch_bytes >= omni_expert_bwd_rows_scratch_bytes(P, hidden),
+               "scratch too small: need %zu bytes", omni_expert_bwd_rows_scratch_bytes(P, hidden));
   const unsigned grid = static_cast<unsigned>(ceil_div64(max_segments, kWarps));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const auto* xb = static_cast<const __nv_bfloat16*>(x);
   const auto* gb = static_cast<const __nv_bfloat16*>(dy);
+  // without a scratch every segment, however long, is summed by one warp
+  const int long_threshold = scratch ? kLongBlock : 0x7fffffff;
   if (out_dtype == OMNI_F32)
     expert_bwd_rows_kernel<true><<<grid, kThreads, 0, st>>>(xb, gb, ds, cdown, sorted_pair_ids, expert_ids, offsets, num_segments,
-                                                            num_tokens, k, hidden, compact, d_up, d_down, status);
+                                                            num_tokens, k, hidden, compact, long_threshold, d_up, d_down, status);
   else
     expert_bwd_rows_kernel<false><<<grid, kThreads, 0, st>>>(xb, gb, ds, cdown, sorted_pair_ids, expert_ids, offsets, num_segments,
-                                                             num_tokens, k, hidden, compact, d_up, d_down, status);
-  return check_launch("expert_bwd_rows_kernel");
+                                                             num_tokens, k, hidden, compact, long_threshold, d_up, d_down, status);
+  if (int e = check_launch("expert_bwd_rows_kernel")) return e;
+  if (scratch && P > kLongBlock) {
+    float* sc = static_cast<float*>(scratch);
+    expert_bwd_rows_long_kernel<<<static_cast<unsigned>(ceil_div64(P, kLongBlock)), kLongThreads, 0, st>>>(
+        xb, gb, ds, cdown, sorted_pair_ids, offsets, num_segments, P, num_tokens, k, hidden, sc, status);
+    if (int e = check_launch("expert_bwd_rows_long_kernel")) return e;
+    if (out_dtype == OMNI_F32)
+      expert_bwd_rows_reduce_kernel<true><<<grid, kThreads, 0, st>>>(sc, expert_ids, offsets, num_segments, hidden, compact, d_up, d_down);
+    else
+      expert_bwd_rows_reduce_kernel<false><<<grid, kThreads, 0, st>>>(sc, expert_ids, offsets, num_segments, hidden, compact, d_up, d_down);
+    return check_launch("expert_bwd_rows_reduce_kernel");
+  }
+  return 0;
 }

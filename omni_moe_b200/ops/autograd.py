@@ -66,7 +66,7 @@ class RouterFunction(torch.autograd.Function):
 # ------------------------------------------------------------------------------------------------
 def expert_backward(dy: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
                     weights: torch.Tensor, indices: torch.Tensor, grad_dtype: torch.dtype = torch.bfloat16,
-                    compact: bool = False, need_tables: bool = True):
+                    compact: bool = False, need_tables: bool = True, long_segments: bool = True):
     """Backward of ``y[t] = sum_j g[t,j] * silu(x[t].Up[e]) * Down[e]`` for bf16 operands.
 
     Returns ``(dx [T,H] grad_dtype, d_up, d_down, dg [T,k] fp32, expert_ids)``.  With ``compact=False``
@@ -74,6 +74,8 @@ def expert_backward(dy: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, 
     None; with ``compact=True`` they hold one row per touched expert, ``expert_ids[s]`` names the
     expert of row ``s`` and rows beyond the number of touched experts are unspecified
     (``expert_ids`` is cut to the valid length, which costs one host read).
+    ``long_segments``: give the row kernel its scratch (``16 * ceil(T*k/512) * H`` bytes) so that experts with
+    more than 512 pairs are summed by many blocks in two levels instead of by one warp.
     """
     _lib.require_cuda(dy, x, up_weight, down_weight, weights, indices)
     assert x.dtype == up_weight.dtype == down_weight.dtype == dy.dtype == torch.bfloat16
@@ -112,11 +114,15 @@ def expert_backward(dy: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, 
         alloc = torch.empty if compact else torch.zeros
         d_up = alloc((rows, h), device=dev, dtype=grad_dtype)
         d_down = alloc((rows, h), device=dev, dtype=grad_dtype)
+        scratch = None
+        if long_segments:
+            scratch = torch.empty(int(lib.omni_expert_bwd_rows_scratch_bytes(t * k, h)), device=dev, dtype=torch.uint8)
         with torch.cuda.device(dev):
             _lib.check(lib.omni_expert_bwd_rows(x.data_ptr(), dy.data_ptr(), ds.data_ptr(), cdown.data_ptr(),
                                                 sch.sorted_pair_ids.data_ptr(), sch.expert_ids.data_ptr(),
                                                 sch.offsets.data_ptr(), sch.meta.data_ptr(), cap, t, k, h, int(compact),
                                                 d_up.data_ptr(), d_down.data_ptr(), _lib.dtype_code(grad_dtype),
+                                                _lib.ptr(scratch), scratch.numel() if scratch is not None else 0,
                                                 status.data_ptr(), _lib.stream_ptr()))
         if compact:
             u = int(sch.meta[0].item())
