@@ -295,10 +295,13 @@ OMNI_API int omni_router_bwd(const float *dscores, const void *indices, int idx_
  *   omni_expert.py:1097-1098; compact rows avoid 2*N*H bytes of zeros for large tables).
  *   num_segments: device pointer to U (meta[0] of omni_schedule); max_segments: host bound on U
  *   (min(T*k, N)) that sizes the launch.  out_dtype: OMNI_F32 or OMNI_BF16.
- *   scratch: omni_expert_bwd_rows_scratch_bytes(T*k, H) bytes of device memory, or NULL.  With it,
- *   experts that received more than 512 pairs are summed in two levels (partial rows per block of 512
- *   sorted positions, then one pass over the partials, both in a fixed order), so skewed routing does
- *   not serialise on one warp; without it every segment is summed by a single warp.
+ *   scratch: omni_expert_bwd_rows_scratch_bytes(T*k, H) bytes of device memory (256-byte aligned), or
+ *   NULL.  With it, experts that received more pairs than one block of sorted positions (256, or 512
+ *   when the partial rows of 256-blocks would exceed 256 MiB) are summed in two levels (partial rows
+ *   per block, then one pass over the partials, both in a fixed order), so skewed routing does not
+ *   serialise on one warp; without it every segment is summed by a single warp.
+ *   max_segment_len: device pointer to the longest segment (meta[1] of omni_schedule) or NULL; lets the
+ *   two-level kernels return at once when no expert is that busy.
  * Limits: H % 8 == 0, 16-byte aligned pointers.
  */
 OMNI_API int omni_expert_bwd_dots(const void *x, const void *up, const void *down, const void *dy,
@@ -307,7 +310,8 @@ OMNI_API int omni_expert_bwd_dots(const void *x, const void *up, const void *dow
                          int32_t *status, void *stream);
 OMNI_API int omni_expert_bwd_rows(const void *x, const void *dy, const float *ds, const float *cdown,
                          const int32_t *sorted_pair_ids, const int32_t *expert_ids,
-                         const int32_t *offsets, const int32_t *num_segments, int64_t max_segments,
+                         const int32_t *offsets, const int32_t *num_segments,
+                         const int32_t *max_segment_len, int64_t max_segments,
                          int64_t num_tokens, int k, int hidden, int compact, void *d_up, void *d_down,
                          int out_dtype, void *scratch, size_t scratch_bytes, int32_t *status, void *stream);
 OMNI_API size_t omni_expert_bwd_rows_scratch_bytes(int64_t num_pairs, int hidden);

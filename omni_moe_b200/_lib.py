@@ -47,7 +47,7 @@ SIGNATURES = {
     "omni_router_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "omni_expert_bwd_dots": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                      c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
-    "omni_expert_bwd_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    "omni_expert_bwd_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
                                      c_void_p, c_void_p]),
     "omni_expert_bwd_rows_scratch_bytes": (c_size_t, [c_int64, c_int]),

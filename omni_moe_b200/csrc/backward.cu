@@ -172,8 +172,10 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_rows_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ ds,
     const float* __restrict__ cdown, const int32_t* __restrict__ sorted_pair_ids, const int32_t* __restrict__ expert_ids,
     const int32_t* __restrict__ offsets, const int32_t* __restrict__ num_segments, int64_t T, int k, int H, int compact,
-    int long_threshold, void* __restrict__ d_up, void* __restrict__ d_down, int* __restrict__ status) {
+    int long_threshold, int* __restrict__ long_count, void* __restrict__ d_up, void* __restrict__ d_down,
+    int* __restrict__ status) {
   const int warp = threadIdx.x >> 5, lane = lane_id();
+  if (long_count && blockIdx.x == 0 && threadIdx.x == 0) *long_count = 0;  // filled by the long-segment kernel that follows
   const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
   if (s >= *num_segments) return;
   const int begin = offsets[s], end = offsets[s + 1];
@@ -233,19 +235,19 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_rows_kernel(
 
 // ---- long segments ----------------------------------------------------------------------------
 // An expert that receives thousands of pairs (skewed routing) would keep one warp busy for
-// milliseconds.  Segments longer than kLongBlock pairs are therefore summed in two levels:
-//   expert_bwd_rows_long_kernel    block b owns the sorted positions [b*kLongBlock, (b+1)*kLongBlock).
-//                                  At most two long segments meet it (the one covering its first position
-//                                  and the one covering its last); for each, the block's 8 warps sum their
-//                                  64 positions apiece, combine through shared memory in warp order and
+// milliseconds.  Segments longer than C pairs are therefore summed in two levels:
+//   expert_bwd_rows_long_kernel    block b owns the sorted positions [b*C, (b+1)*C), C = 64 ... 512 chosen by
+//                                  the scratch size.  At most two long segments (longer than C) meet it (the
+//                                  one covering its first position and the one covering its last); for each,
+//                                  the block's C/64 warps sum their 64 positions apiece, combine through shared memory in warp order and
 //                                  store one fp32 partial row pair in slot 2b (segment covers the block's
 //                                  first position) or 2b+1.
 //   expert_bwd_rows_reduce_kernel  one warp per long segment adds its partials in block order and writes
 //                                  the gradient rows.
 // Fixed assignment and fixed order: the sums are reproducible.
-constexpr int kLongBlock = 512;
-constexpr int kLongThreads = 256;
-constexpr int kLongCols = 256;  // columns per pass: one 128-bit load per lane
+constexpr int kLongBlockMax = 512;  // positions per block: 64 per warp, 1 to 8 warps (C = 64, 128, 256 or 512)
+constexpr int kLongCols = 256;      // columns per pass: one 128-bit load per lane
+constexpr size_t kLongScratchBudget = size_t(256) << 20;
 
 // index of the segment containing sorted position p: largest s with offsets[s] <= p
 __device__ __forceinline__ int segment_of(const int32_t* __restrict__ offsets, int U, int p) {
@@ -257,15 +259,18 @@ __device__ __forceinline__ int segment_of(const int32_t* __restrict__ offsets, i
   return lo;
 }
 
-__global__ void __launch_bounds__(kLongThreads) expert_bwd_rows_long_kernel(
+__global__ void __launch_bounds__(kLongBlockMax / 2) expert_bwd_rows_long_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ ds,
     const float* __restrict__ cdown, const int32_t* __restrict__ sorted_pair_ids, const int32_t* __restrict__ offsets,
-    const int32_t* __restrict__ num_segments, int64_t P, int64_t T, int k, int H, float* __restrict__ scratch,
+    const int32_t* __restrict__ num_segments, const int32_t* __restrict__ max_segment_len, int64_t P, int64_t T, int k, int H,
+    int kLongBlock, int* __restrict__ long_count, int* __restrict__ long_list, float* __restrict__ scratch,
     int* __restrict__ status) {
-  __shared__ float s_part[kLongThreads / 32][2][kLongCols];
+  __shared__ float s_part[kLongBlockMax / 64][2][kLongCols];
+  const int warps = blockDim.x >> 5;  // = kLongBlock / 64
   const int warp = threadIdx.x >> 5, lane = lane_id();
   const int U = *num_segments;
   if (U <= 0) return;
+  if (max_segment_len && *max_segment_len <= kLongBlock) return;  // the usual case: no expert is that busy
   const int64_t lo = static_cast<int64_t>(blockIdx.x) * kLongBlock;
   if (lo >= P) return;
   const int64_t hi = (lo + kLongBlock < P) ? lo + kLongBlock : P;
@@ -280,6 +285,9 @@ __global__ void __launch_bounds__(kLongThreads) expert_bwd_rows_long_kernel(
     const int a = begin > lo ? begin : static_cast<int>(lo);
     const int c = end < hi ? end : static_cast<int>(hi);
     float* slot = scratch + (2 * static_cast<int64_t>(blockIdx.x) + which) * 2 * H;
+    // the block holding the segment's first position enters it in the list the reduce kernel walks
+    // (list order varies from run to run; every entry is reduced on its own, so results do not)
+    if (threadIdx.x == 0 && begin >= lo) long_list[atomicAdd(long_count, 1)] = s;
     // this warp's positions: a + warp*64 + {lane, lane+32}
     int my_t[2];
     float my_s[2], my_c[2];
@@ -327,12 +335,10 @@ __global__ void __launch_bounds__(kLongThreads) expert_bwd_rows_long_kernel(
         s_part[warp][1][lane * 8 + 2 * q] = ad[q].x, s_part[warp][1][lane * 8 + 2 * q + 1] = ad[q].y;
       }
       __syncthreads();
-#pragma unroll
-      for (int tb = 0; tb < 2; ++tb) {
-        const int cc2 = threadIdx.x;  // kLongThreads == kLongCols: one column per thread
+      for (int idx = threadIdx.x; idx < 2 * kLongCols; idx += blockDim.x) {
+        const int tb = idx / kLongCols, cc2 = idx - tb * kLongCols;
         float sum = 0.f;
-#pragma unroll
-        for (int w = 0; w < kLongThreads / 32; ++w) sum += s_part[w][tb][cc2];
+        for (int w = 0; w < warps; ++w) sum += s_part[w][tb][cc2];
         if (c0 + cc2 < H) slot[tb * H + c0 + cc2] = sum;
       }
       __syncthreads();
@@ -344,25 +350,44 @@ __global__ void __launch_bounds__(kLongThreads) expert_bwd_rows_long_kernel(
 template <bool OUT_F32>
 __global__ void __launch_bounds__(kThreads) expert_bwd_rows_reduce_kernel(
     const float* __restrict__ scratch, const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ offsets,
-    const int32_t* __restrict__ num_segments, int H, int compact, void* __restrict__ d_up, void* __restrict__ d_down) {
+    const int* __restrict__ long_count, const int* __restrict__ long_list, int H, int compact, int kLongBlock,
+    void* __restrict__ d_up, void* __restrict__ d_down) {
   const int warp = threadIdx.x >> 5, lane = lane_id();
-  const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
-  if (s >= *num_segments) return;
-  const int begin = offsets[s], end = offsets[s + 1];
-  if (end - begin <= kLongBlock) return;
-  const int b0 = begin / kLongBlock, b1 = (end - 1) / kLongBlock;
-  const int64_t row = compact ? s : static_cast<int64_t>(expert_ids[s]);
-  for (int c0 = lane * 8; c0 < H; c0 += 256) {
+  const int count = *long_count;
+  // blockIdx.y picks a tile of 256 columns, so a segment spread over hundreds of blocks is reduced by
+  // H / 256 warps side by side; the partials are added in block order, four loads in flight
+  const int c0 = blockIdx.y * 256 + lane * 8;
+  if (c0 >= H) return;
+  for (int i = blockIdx.x * kWarps + warp; i < count; i += gridDim.x * kWarps) {
+    const int s = long_list[i];
+    const int begin = offsets[s], end = offsets[s + 1];
+    const int b0 = begin / kLongBlock, b1 = (end - 1) / kLongBlock;
+    const int64_t row = compact ? s : static_cast<int64_t>(expert_ids[s]);
     float2 au[4], ad[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) au[q] = make_float2(0.f, 0.f), ad[q] = make_float2(0.f, 0.f);
-    for (int b = b0; b <= b1; ++b) {
-      const int which = (b == b0 && begin > b0 * kLongBlock) ? 1 : 0;
-      const float* slot = scratch + (2 * static_cast<int64_t>(b) + which) * 2 * H;
-      const float4 u0 = *reinterpret_cast<const float4*>(slot + c0), u1 = *reinterpret_cast<const float4*>(slot + c0 + 4);
-      const float4 d0 = *reinterpret_cast<const float4*>(slot + H + c0), d1 = *reinterpret_cast<const float4*>(slot + H + c0 + 4);
-      au[0].x += u0.x, au[0].y += u0.y, au[1].x += u0.z, au[1].y += u0.w, au[2].x += u1.x, au[2].y += u1.y, au[3].x += u1.z, au[3].y += u1.w;
-      ad[0].x += d0.x, ad[0].y += d0.y, ad[1].x += d0.z, ad[1].y += d0.w, ad[2].x += d1.x, ad[2].y += d1.y, ad[3].x += d1.z, ad[3].y += d1.w;
+    const int first_which = begin > b0 * kLongBlock ? 1 : 0;
+    for (int b = b0; b <= b1; b += 4) {
+      float4 u0[4], u1[4], d0[4], d1[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int bb = b + u;
+        const bool on = bb <= b1;
+        const int which = (bb == b0) ? first_which : 0;
+        const float* slot = scratch + (2 * static_cast<int64_t>(on ? bb : b0) + which) * 2 * H;
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        u0[u] = on ? *reinterpret_cast<const float4*>(slot + c0) : z;
+        u1[u] = on ? *reinterpret_cast<const float4*>(slot + c0 + 4) : z;
+        d0[u] = on ? *reinterpret_cast<const float4*>(slot + H + c0) : z;
+        d1[u] = on ? *reinterpret_cast<const float4*>(slot + H + c0 + 4) : z;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        au[0].x += u0[u].x, au[0].y += u0[u].y, au[1].x += u0[u].z, au[1].y += u0[u].w;
+        au[2].x += u1[u].x, au[2].y += u1[u].y, au[3].x += u1[u].z, au[3].y += u1[u].w;
+        ad[0].x += d0[u].x, ad[0].y += d0[u].y, ad[1].x += d0[u].z, ad[1].y += d0[u].w;
+        ad[2].x += d1[u].x, ad[2].y += d1[u].y, ad[3].x += d1[u].z, ad[3].y += d1[u].w;
+      }
     }
     store8<OUT_F32>(d_up, row * H + c0, au);
     store8<OUT_F32>(d_down, row * H + c0, ad);
@@ -403,16 +428,29 @@ extern "C" int omni_expert_bwd_dots(const void* x, const void* up, const void* d
   return check_launch("expert_bwd_dots_kernel");
 }
 
+namespace {
+// scratch layout: int32 count, int32 list[blocks] (padded to 256 bytes), then 2 partial row pairs per block
+size_t long_header_bytes(int64_t num_pairs, int block) {
+  return (static_cast<size_t>(ceil_div64(num_pairs, block) + 1) * sizeof(int32_t) + 255) / 256 * 256;
+}
+size_t long_scratch_need(int64_t num_pairs, int hidden, int block) {
+  return long_header_bytes(num_pairs, block) +
+         static_cast<size_t>(2 * ceil_div64(num_pairs, block)) * 2 * static_cast<size_t>(hidden) * sizeof(float);
+}
+}  // namespace
+
+// Blocks of 256 sorted positions if their partial rows fit 256 MiB, of 512 otherwise.
 extern "C" size_t omni_expert_bwd_rows_scratch_bytes(int64_t num_pairs, int hidden) {
   if (num_pairs <= 0 || hidden <= 0) return 0;
-  return static_cast<size_t>(2 * ceil_div64(num_pairs, kLongBlock)) * 2 * static_cast<size_t>(hidden) * sizeof(float);
+  const size_t fine = long_scratch_need(num_pairs, hidden, 256);
+  return fine <= kLongScratchBudget ? fine : long_scratch_need(num_pairs, hidden, kLongBlockMax);
 }
 
 extern "C" int omni_expert_bwd_rows(const void* x, const void* dy, const float* ds, const float* cdown,
                                     const int32_t* sorted_pair_ids, const int32_t* expert_ids, const int32_t* offsets,
-                                    const int32_t* num_segments, int64_t max_segments, int64_t num_tokens, int k, int hidden,
-                                    int compact, void* d_up, void* d_down, int out_dtype, void* scratch, size_t scratch_bytes,
-                                    int32_t* status, void* stream) {
+                                    const int32_t* num_segments, const int32_t* max_segment_len, int64_t max_segments,
+                                    int64_t num_tokens, int k, int hidden, int compact, void* d_up, void* d_down, int out_dtype,
+                                    void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
   OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && max_segments >= 0, "bad sizes");
   OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
   OMNI_REQUIRE(out_dtype == OMNI_F32 || out_dtype == OMNI_BF16, "out_dtype must be OMNI_F32 or OMNI_BF16");
@@ -422,32 +460,45 @@ extern "C" int omni_expert_bwd_rows(const void* x, const void* dy, const float* 
   if (num_tokens == 0 || max_segments == 0) return 0;
   OMNI_REQUIRE(x && dy && ds && cdown && sorted_pair_ids && expert_ids && offsets && num_segments && d_up && d_down && status,
                "NULL argument");
-  OMNI_REQUIRE(aligned16(x) && aligned16(dy) && aligned16(d_up) && aligned16(d_down) && aligned16(scratch),
-               "x, dy, d_up, d_down and scratch must be 16-byte aligned");
-  OMNI_REQUIRE(scratch == nullptr || scratch_bytes >= omni_expert_bwd_rows_scratch_bytes(P, hidden),
-               "scratch too small: need %zu bytes", omni_expert_bwd_rows_scratch_bytes(P, hidden));
+  OMNI_REQUIRE(aligned16(x) && aligned16(dy) && aligned16(d_up) && aligned16(d_down), "x, dy, d_up and d_down must be 16-byte aligned");
+  OMNI_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255) == 0, "scratch must be 256-byte aligned");
+  OMNI_REQUIRE(scratch == nullptr || scratch_bytes >= long_scratch_need(P, hidden, kLongBlockMax),
+               "scratch too small: need at least %zu bytes", long_scratch_need(P, hidden, kLongBlockMax));
+  // the finest split the given scratch has room for
+  int long_block = kLongBlockMax;
+  for (int block = 64; scratch && block < kLongBlockMax; block *= 2)
+    if (long_scratch_need(P, hidden, block) <= scratch_bytes) { long_block = block; break; }
   const unsigned grid = static_cast<unsigned>(ceil_div64(max_segments, kWarps));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const auto* xb = static_cast<const __nv_bfloat16*>(x);
   const auto* gb = static_cast<const __nv_bfloat16*>(dy);
+  const bool two_level = scratch != nullptr && P > long_block;
   // without a scratch every segment, however long, is summed by one warp
-  const int long_threshold = scratch ? kLongBlock : 0x7fffffff;
+  const int long_threshold = two_level ? long_block : 0x7fffffff;
+  int* long_count = two_level ? static_cast<int*>(scratch) : nullptr;
+  int* long_list = two_level ? long_count + 1 : nullptr;
+  float* partials = two_level ? reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + long_header_bytes(P, long_block)) : nullptr;
   if (out_dtype == OMNI_F32)
     expert_bwd_rows_kernel<true><<<grid, kThreads, 0, st>>>(xb, gb, ds, cdown, sorted_pair_ids, expert_ids, offsets, num_segments,
-                                                            num_tokens, k, hidden, compact, long_threshold, d_up, d_down, status);
+                                                            num_tokens, k, hidden, compact, long_threshold, long_count, d_up, d_down,
+                                                            status);
   else
     expert_bwd_rows_kernel<false><<<grid, kThreads, 0, st>>>(xb, gb, ds, cdown, sorted_pair_ids, expert_ids, offsets, num_segments,
-                                                             num_tokens, k, hidden, compact, long_threshold, d_up, d_down, status);
+                                                             num_tokens, k, hidden, compact, long_threshold, long_count, d_up, d_down,
+                                                             status);
   if (int e = check_launch("expert_bwd_rows_kernel")) return e;
-  if (scratch && P > kLongBlock) {
-    float* sc = static_cast<float*>(scratch);
-    expert_bwd_rows_long_kernel<<<static_cast<unsigned>(ceil_div64(P, kLongBlock)), kLongThreads, 0, st>>>(
-        xb, gb, ds, cdown, sorted_pair_ids, offsets, num_segments, P, num_tokens, k, hidden, sc, status);
+  if (two_level) {
+    expert_bwd_rows_long_kernel<<<static_cast<unsigned>(ceil_div64(P, long_block)), long_block / 2, 0, st>>>(
+        xb, gb, ds, cdown, sorted_pair_ids, offsets, num_segments, max_segment_len, P, num_tokens, k, hidden, long_block, long_count,
+        long_list, partials, status);
     if (int e = check_launch("expert_bwd_rows_long_kernel")) return e;
+    const dim3 rgrid(64, ceil_div(hidden, 256));
     if (out_dtype == OMNI_F32)
-      expert_bwd_rows_reduce_kernel<true><<<grid, kThreads, 0, st>>>(sc, expert_ids, offsets, num_segments, hidden, compact, d_up, d_down);
+      expert_bwd_rows_reduce_kernel<true><<<rgrid, kThreads, 0, st>>>(partials, expert_ids, offsets, long_count, long_list, hidden,
+                                                                      compact, long_block, d_up, d_down);
     else
-      expert_bwd_rows_reduce_kernel<false><<<grid, kThreads, 0, st>>>(sc, expert_ids, offsets, num_segments, hidden, compact, d_up, d_down);
+      expert_bwd_rows_reduce_kernel<false><<<rgrid, kThreads, 0, st>>>(partials, expert_ids, offsets, long_count, long_list, hidden,
+                                                                       compact, long_block, d_up, d_down);
     return check_launch("expert_bwd_rows_reduce_kernel");
   }
   return 0;

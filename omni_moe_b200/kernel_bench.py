@@ -1,6 +1,6 @@
 """Per-kernel timings of the layer's stages against their rooflines.
 
-    python -m omni_moe_b200.kernel_bench [--config c2|c3|c4|c5|all] [--reps N]
+    python -m omni_moe_b200.kernel_bench [--config c2|c3|c4|c5|all] [--reps N] [--backward]
 
 For each stage of a configuration the script launches the kernel through the C ABI inside a CUDA
 graph (several launches per replay, so host launch cost does not count), times replays with CUDA
@@ -86,6 +86,102 @@ def time_graph(fn, launches=4, reps=10):
         ts.append(a.elapsed_time(b) * 1e3 / launches)
     ts.sort()
     return ts[len(ts) // 2]
+
+
+def run_backward(name: str, reps: int):
+    """Stages of the backward pass (router scatter, expert gradients, MLP gradient GEMMs and helpers)."""
+    from .ops.scheduler import schedule
+    c = CONFIGS[name]
+    T, H, I, n, k = c["T"], c["H"], c["I"], c["n"], c["k"]
+    N, P = n * n, T * k
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hbm, tf, src = peaks()
+    lib = _lib.load()
+    chk = _lib.check
+    i32 = dict(device=dev, dtype=torch.int32)
+    f32 = dict(device=dev, dtype=torch.float32)
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    status = torch.zeros(1, **i32)
+
+    def report(stage, us, bound, work, note=""):
+        ach = work / (us * 1e-6) / (1e9 if bound == "hbm" else 1e12)
+        line = dict(config=name, stage=stage, us=round(us, 2), bound=bound)
+        if bound == "hbm":
+            line.update(algorithmic_bytes=int(work), achieved_gbs=round(ach, 1), peak_gbs=hbm, frac=round(ach / hbm, 3))
+        else:
+            line.update(flops=int(work), achieved_tflops=round(ach, 1), peak_tflops=tf, frac=round(ach / tf, 3))
+        line["peak_source"] = src
+        if note:
+            line["note"] = note
+        print(json.dumps(line), flush=True)
+
+    x = _randn_bf16((T, H), 1.0, dev, 0)
+    dy = _randn_bf16((T, H), 0.1, dev, 9)
+    if c["zipf"]:
+        indices = _zipf_indices(T, k, N, c["zipf"], 0, dev)
+    else:
+        indices = torch.randint(0, N, (T, k), device=dev, dtype=torch.int32, generator=torch.Generator(device=dev).manual_seed(3))
+    weights = torch.rand((T, k), **f32)
+    U = int(torch.unique(indices).numel())
+    # ---- router scatter -------------------------------------------------------------------------
+    dsc = torch.randn((T, k), **f32)
+    dlx, dly = torch.empty((T, n), **f32), torch.empty((T, n), **f32)
+    us = time_graph(lambda s: chk(lib.omni_router_bwd(dsc.data_ptr(), indices.data_ptr(), 0, T, n, k, dlx.data_ptr(),
+                                                      dly.data_ptr(), status.data_ptr(), s)), reps=reps)
+    report("router_bwd_scatter", us, "hbm", 8.0 * P + 8.0 * T * n)
+    # ---- routed experts ---------------------------------------------------------------------------
+    up = _randn_bf16((N, H), 0.02, dev, 3)
+    down = _randn_bf16((N, H), 0.02, dev, 4)
+    ds, cd, dg = torch.empty((T, k), **f32), torch.empty((T, k), **f32), torch.empty((T, k), **f32)
+    us = time_graph(lambda s: chk(lib.omni_expert_bwd_dots(x.data_ptr(), up.data_ptr(), down.data_ptr(), dy.data_ptr(),
+                                                           weights.data_ptr(), indices.data_ptr(), T, k, H, N, ds.data_ptr(),
+                                                           cd.data_ptr(), dg.data_ptr(), status.data_ptr(), s)), reps=reps)
+    report("expert_bwd_dots", us, "hbm", 4.0 * T * H + 4.0 * U * H + 20.0 * P, f"U={U} distinct experts; gathers 2 rows per pair")
+    dx = torch.empty((T, H), **bf)
+    us = time_graph(lambda s: chk(lib.omni_expert_combine(up.data_ptr(), ds.data_ptr(), indices.data_ptr(), T, k, H, N, None,
+                                                          dx.data_ptr(), _lib.OMNI_BF16, status.data_ptr(), s)), reps=reps)
+    report("expert_bwd_dx (combine kernel)", us, "hbm", 2.0 * T * H + 2.0 * U * H + 8.0 * P)
+    sch = schedule(indices, N, segments=True)
+    cap = sch.expert_ids.numel()
+    d_up, d_dn = torch.empty((cap, H), **bf), torch.empty((cap, H), **bf)
+    scratch = torch.empty(int(lib.omni_expert_bwd_rows_scratch_bytes(P, H)), device=dev, dtype=torch.uint8)
+    for label, sc in (("expert_bwd_rows", scratch), ("expert_bwd_rows (one warp per segment)", None)):
+        if sc is None and c["zipf"]:
+            continue  # a 100k-pair segment on one warp takes a large fraction of a second
+        us = time_graph(lambda s: chk(lib.omni_expert_bwd_rows(
+            x.data_ptr(), dy.data_ptr(), ds.data_ptr(), cd.data_ptr(), sch.sorted_pair_ids.data_ptr(), sch.expert_ids.data_ptr(),
+            sch.offsets.data_ptr(), sch.meta.data_ptr(), sch.meta[1:].data_ptr(), cap, T, k, H, 1, d_up.data_ptr(), d_dn.data_ptr(), _lib.OMNI_BF16,
+            _lib.ptr(sc), sc.numel() if sc is not None else 0, status.data_ptr(), s)), reps=reps)
+        report(label, us, "hbm", 4.0 * T * H + 4.0 * U * H + 12.0 * P, "compact rows; gathers 2 token rows per pair")
+    # ---- shared MLP ---------------------------------------------------------------------------------
+    if I:
+        Tp = (T + 7) // 8 * 8
+        gu = _randn_bf16((T, 2 * I), 1.0, dev, 5)
+        dact = _randn_bf16((T, I), 0.1, dev, 6)
+        dgu, dgu_t, act_t = torch.empty((T, 2 * I), **bf), torch.empty((2 * I, Tp), **bf), torch.empty((I, Tp), **bf)
+        us = time_graph(lambda s: chk(lib.omni_swiglu_bwd(gu.data_ptr(), dact.data_ptr(), T, I, dgu.data_ptr(), dgu_t.data_ptr(),
+                                                          act_t.data_ptr(), Tp, s)), reps=reps)
+        report("swiglu_bwd (+ transposed outputs)", us, "hbm", 2.0 * (3 * T * I + 2 * T * I + 3 * T * I))
+        wt = torch.empty((I, H), **bf)
+        wd = _randn_bf16((H, I), I ** -0.5, dev, 7)
+        us = time_graph(lambda s: chk(lib.omni_transpose_bf16(wd.data_ptr(), H, I, I, wt.data_ptr(), H, H, s)), reps=reps)
+        report("transpose [H, I]", us, "hbm", 4.0 * H * I)
+        x_t = torch.empty((H, Tp), **bf)
+        dy_t = torch.empty((H, Tp), **bf)
+        wgu_t = _randn_bf16((H, 2 * I), H ** -0.5, dev, 8)
+        out_ti, out_th = torch.empty((T, I), **bf), torch.empty((T, H), **bf)
+        out_hi, out_2ih = torch.empty((H, I), **bf), torch.empty((2 * I, H), **bf)
+        gemms = (("gemm dact = dy Wd", dy, wt, out_ti), ("gemm dx = dgu (Wg;Wu)", dgu, wgu_t, out_th),
+                 ("gemm dWd = dy^T act", dy_t, act_t, out_hi), ("gemm dWgu = dgu^T x", dgu_t, x_t, out_2ih))
+        for label, a, b, o in gemms:
+            m_, k_ = a.shape
+            n_ = b.shape[0]
+            us = time_graph(lambda s: chk(lib.omni_gemm_bf16_nt(a.data_ptr(), b.data_ptr(), m_, n_, k_, o.data_ptr(), n_,
+                                                                status.data_ptr(), s)), reps=reps)
+            report(label, us, "tensor", 2.0 * m_ * n_ * k_, f"{m_} x {n_} x {k_}")
+    torch.cuda.synchronize()
+    if int(status.item()):
+        raise RuntimeError("a kernel reported a device-side fault: " + _lib.status_message(int(status.item())))
 
 
 def run_config(name: str, reps: int):
@@ -186,11 +282,12 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--config", default="c2", choices=[*CONFIGS, "all"])
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--backward", action="store_true", help="time the backward kernels instead of the forward ones")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("kernel_bench needs a CUDA device")
     for name in (CONFIGS if args.config == "all" else [args.config]):
-        run_config(name, args.reps)
+        (run_backward if args.backward else run_config)(name, args.reps)
         torch.cuda.empty_cache()
 
 

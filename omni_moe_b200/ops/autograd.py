@@ -66,7 +66,7 @@ class RouterFunction(torch.autograd.Function):
 # ------------------------------------------------------------------------------------------------
 def expert_backward(dy: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
                     weights: torch.Tensor, indices: torch.Tensor, grad_dtype: torch.dtype = torch.bfloat16,
-                    compact: bool = False, need_tables: bool = True, long_segments: bool = True):
+                    compact: bool = False, need_tables: bool = True, long_segments: bool | int = True):
     """Backward of ``y[t] = sum_j g[t,j] * silu(x[t].Up[e]) * Down[e]`` for bf16 operands.
 
     Returns ``(dx [T,H] grad_dtype, d_up, d_down, dg [T,k] fp32, expert_ids)``.  With ``compact=False``
@@ -74,8 +74,9 @@ def expert_backward(dy: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, 
     None; with ``compact=True`` they hold one row per touched expert, ``expert_ids[s]`` names the
     expert of row ``s`` and rows beyond the number of touched experts are unspecified
     (``expert_ids`` is cut to the valid length, which costs one host read).
-    ``long_segments``: give the row kernel its scratch (``16 * ceil(T*k/512) * H`` bytes) so that experts with
-    more than 512 pairs are summed by many blocks in two levels instead of by one warp.
+    ``long_segments``: give the row kernel its scratch so that experts with many pairs are summed by many
+    blocks in two levels instead of by one warp (True: the library's choice of split, at most 256 MiB unless
+    even the coarsest split needs more; 64 / 128 / 256 / 512: that many sorted positions per block).
     """
     _lib.require_cuda(dy, x, up_weight, down_weight, weights, indices)
     assert x.dtype == up_weight.dtype == down_weight.dtype == dy.dtype == torch.bfloat16
@@ -115,12 +116,18 @@ def expert_backward(dy: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, 
         d_up = alloc((rows, h), device=dev, dtype=grad_dtype)
         d_down = alloc((rows, h), device=dev, dtype=grad_dtype)
         scratch = None
-        if long_segments:
+        if long_segments is True:
             scratch = torch.empty(int(lib.omni_expert_bwd_rows_scratch_bytes(t * k, h)), device=dev, dtype=torch.uint8)
+        elif long_segments:
+            # an explicit split: room for partial rows of blocks of `long_segments` sorted positions
+            blocks = -(-(t * k) // int(long_segments))
+            header = ((blocks + 1) * 4 + 255) // 256 * 256
+            scratch = torch.empty(header + 2 * blocks * 2 * h * 4, device=dev, dtype=torch.uint8)
         with torch.cuda.device(dev):
             _lib.check(lib.omni_expert_bwd_rows(x.data_ptr(), dy.data_ptr(), ds.data_ptr(), cdown.data_ptr(),
                                                 sch.sorted_pair_ids.data_ptr(), sch.expert_ids.data_ptr(),
-                                                sch.offsets.data_ptr(), sch.meta.data_ptr(), cap, t, k, h, int(compact),
+                                                sch.offsets.data_ptr(), sch.meta.data_ptr(), sch.meta[1:].data_ptr(), cap, t, k, h,
+                                                int(compact),
                                                 d_up.data_ptr(), d_down.data_ptr(), _lib.dtype_code(grad_dtype),
                                                 _lib.ptr(scratch), scratch.numel() if scratch is not None else 0,
                                                 status.data_ptr(), _lib.stream_ptr()))

@@ -212,10 +212,12 @@ def test_layer_gradients_match_oracle(training):
         _scaled_close(got[name], exp, name, rtol=1e-1 if loose else 4e-2, atol_frac=6e-2 if loose else 3e-2)
 
 
+@pytest.mark.parametrize("split", [True, 64, 128, 256, 512])
 @pytest.mark.parametrize("layout", ["one_giant", "aligned_512", "mixed"])
-def test_expert_backward_long_segments(layout):
-    """Experts with more than 512 pairs take the two-level path; it must agree with the single-warp
-    path (same products, another summation order) and with the oracle, and be reproducible."""
+def test_expert_backward_long_segments(layout, split):
+    """Experts with more pairs than one block of sorted positions take the two-level path; it must agree
+    with the single-warp path (same products, another summation order) and with the oracle, and be
+    reproducible, for every block size."""
     from omni_moe_b200.ops.autograd import expert_backward
     t, h, n, k = 640, 264, 40, 4
     x, up, dn, w, idx, dy = _expert_inputs(t, h, n, k, 21)
@@ -229,14 +231,17 @@ def test_expert_backward_long_segments(layout):
         flat[: 600] = 3
         flat[600: 1300] = 5
         flat[1300: 1813] = 9                   # 513 pairs: just over the threshold
-    got = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.float32)
+    got = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.float32,
+                          long_segments=split)
     slow = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.float32,
                            long_segments=False)
     ex, eu, ed, eg = orc.expert_backward(x.float(), up.float(), dn.float(), w, idx, dy.float())
     for name, a, b, e in (("d_up", got[1], slow[1], eu), ("d_down", got[2], slow[2], ed)):
         _scaled_close(a, e, name, rtol=2e-3, atol_frac=2e-3)
         _scaled_close(a, b, name + " vs single-warp path", rtol=1e-4, atol_frac=1e-5)
-    again = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.float32)
+    again = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.float32,
+                            long_segments=split)
     assert torch.equal(again[1], got[1]) and torch.equal(again[2], got[2])
-    cu = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.bfloat16, compact=True)
+    cu = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.bfloat16, compact=True,
+                         long_segments=split)
     assert torch.equal(cu[1].float(), got[1][cu[4].long()].bfloat16().float())
