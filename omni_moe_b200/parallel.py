@@ -118,6 +118,27 @@ class ReceivedPairs:
     recv_counts: list
 
 
+class ExchangeError(RuntimeError):
+    """A step of the inter-rank exchange failed: a peer left or never joined (the backend's timeout or
+    abort surfaces here), or the ranks disagree about the shape of the exchange.  ``stage`` names the
+    step.  Raised on the host before any kernel of this library reads a buffer the failed collective
+    should have filled."""
+
+    def __init__(self, stage: str, detail: str):
+        super().__init__(f"expert exchange failed at '{stage}': {detail}")
+        self.stage = stage
+
+
+def _collective(stage: str, fn, *args, **kwargs):
+    """Runs one torch.distributed call and turns a backend failure into :class:`ExchangeError`."""
+    try:
+        return fn(*args, **kwargs)
+    except ExchangeError:
+        raise
+    except RuntimeError as e:  # DistBackendError, gloo / NCCL timeouts and aborts derive from RuntimeError
+        raise ExchangeError(stage, str(e).splitlines()[0] if str(e) else type(e).__name__) from e
+
+
 def _stable_order_by_owner(owner: torch.Tensor, world: int) -> torch.Tensor:
     """Permutation that groups the flat pairs by owning rank, ascending pair id inside a group."""
     if owner.is_cuda:
@@ -141,9 +162,20 @@ def dispatch_pairs(x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor
     owner = part.owner(flat_e).to(torch.int32)
     order = _stable_order_by_owner(owner, world)
     send_counts = torch.bincount(owner.long(), minlength=world)
-    recv_counts = torch.empty_like(send_counts)
-    dist.all_to_all_single(recv_counts, send_counts, group=group)
-    send_list, recv_list = send_counts.tolist(), recv_counts.tolist()  # one host sync: the split sizes
+    # the count exchange doubles as a handshake: every rank also states its shard shape, so a peer that
+    # left, or one configured with another token count or k, is noticed here, on the host, before any
+    # payload moves
+    hello = torch.stack([send_counts, torch.full_like(send_counts, t_local), torch.full_like(send_counts, k)], dim=1).contiguous()
+    got = torch.empty_like(hello)
+    _collective("count exchange", dist.all_to_all_single, got, hello, group=group)
+    got_host = got.tolist()  # one host sync: the split sizes
+    send_list, recv_list = send_counts.tolist(), [r[0] for r in got_host]
+    for peer, (cnt, t_peer, k_peer) in enumerate(got_host):
+        if t_peer != t_local or k_peer != k:
+            raise ExchangeError("count exchange", f"rank {peer} shards {t_peer} tokens x {k_peer} experts, this rank "
+                                                  f"{t_local} x {k}: every rank must pass the same shard shape")
+        if cnt < 0 or cnt > t_peer * k_peer:
+            raise ExchangeError("count exchange", f"rank {peer} announces {cnt} pairs, more than its {t_peer * k_peer}")
     # 12-byte records: global token id, expert row inside the owner's slice, weight bits
     tok = (torch.div(order, k, rounding_mode="floor") + rank * t_local).to(torch.int32)
     e_sorted = flat_e[order]
@@ -151,9 +183,10 @@ def dispatch_pairs(x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor
     w_bits = weights.reshape(-1).float()[order].view(torch.int32)
     send = torch.stack([tok, local_e, w_bits], dim=1).contiguous()
     recv = torch.empty((sum(recv_list), 3), device=dev, dtype=torch.int32)
-    dist.all_to_all_single(recv, send, output_split_sizes=recv_list, input_split_sizes=send_list, group=group)
+    _collective("pair dispatch", dist.all_to_all_single, recv, send, output_split_sizes=recv_list,
+                input_split_sizes=send_list, group=group)
     x_all = torch.empty((world * t_local, x.size(1)), device=dev, dtype=x.dtype)
-    dist.all_gather_into_tensor(x_all, x.contiguous(), group=group)
+    _collective("token all-gather", dist.all_gather_into_tensor, x_all, x.contiguous(), group=group)
     pair_tokens = recv[:, 0].contiguous()
     bounds = torch.arange(world * t_local + 1, device=dev, dtype=torch.int32)
     token_offsets = torch.searchsorted(pair_tokens, bounds, right=False).to(torch.int32)
@@ -197,11 +230,11 @@ def combine_partials(partial: torch.Tensor, part: ExpertPartition, group=None) -
     t_local = partial.size(0) // part.world
     if dist.get_backend(group) == "nccl":
         out = torch.empty((t_local, partial.size(1)), device=partial.device, dtype=partial.dtype)
-        dist.reduce_scatter_tensor(out, partial.contiguous(), op=dist.ReduceOp.SUM, group=group)
+        _collective("combine", dist.reduce_scatter_tensor, out, partial.contiguous(), op=dist.ReduceOp.SUM, group=group)
         return out
     # backends without reduce-scatter (gloo, used by the CPU tests): all-reduce, then keep the own rows
     full = partial.clone()
-    dist.all_reduce(full, op=dist.ReduceOp.SUM, group=group)
+    _collective("combine", dist.all_reduce, full, op=dist.ReduceOp.SUM, group=group)
     return full[part.rank * t_local:(part.rank + 1) * t_local].contiguous()
 
 

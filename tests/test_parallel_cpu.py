@@ -129,3 +129,52 @@ def test_synced_batch_statistics_without_process_group():
     mean, var, total = synced_batch_statistics(z)
     ev, em = torch.var_mean(z, dim=0, unbiased=False)
     assert torch.allclose(mean, em) and torch.allclose(var, ev) and total == 50
+
+
+def _failure_worker(rank, world, port, scenario, ret):
+    """Host-side failure injection: no device is involved, the failing rank simply behaves badly."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from omni_moe_b200.parallel import ExchangeError, ExpertPartition, dispatch_pairs, partitioned_expert_states
+    g = torch.Generator().manual_seed(rank)
+    n, k, h = 32, 4, 8
+    t_local = 6
+    if scenario == "shape_mismatch" and rank == 1:
+        t_local = 5                                   # a misconfigured rank
+    x = torch.randn(t_local, h, generator=g)
+    idx = torch.randint(0, n, (t_local, k), generator=g, dtype=torch.int32)
+    w = torch.rand(t_local, k, generator=g)
+    part = ExpertPartition(n, world, rank)
+    if scenario == "peer_leaves" and rank == 1:
+        ret[rank] = "left"
+        os._exit(0)                                   # leaves between steps, before joining the exchange
+    try:
+        dispatch_pairs(x, idx, w, part)
+        ret[rank] = "no error"
+    except ExchangeError as e:
+        ret[rank] = f"{e.stage}|{e}"
+    if scenario == "shape_mismatch":
+        dist.destroy_process_group()
+    else:
+        os._exit(0)                                   # the group is broken: do not wait for the peer in teardown
+
+
+@pytest.mark.parametrize("scenario", ["shape_mismatch", "peer_leaves"])
+def test_exchange_failures_surface_on_the_host(scenario):
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_failure_worker, args=(r, world, port, scenario, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(90)
+        assert p.exitcode == 0, p.exitcode
+    if scenario == "shape_mismatch":
+        for r in range(world):
+            assert ret[r].startswith("count exchange|") and "same shard shape" in ret[r], ret[r]
+    else:
+        assert ret[1] == "left"
+        assert "|" in ret[0] and ret[0].split("|")[0] in ("count exchange", "pair dispatch"), ret[0]
