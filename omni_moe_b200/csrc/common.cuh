@@ -46,6 +46,21 @@ inline cudaError_t launch_after_predecessor(void (*kernel)(KArgs...), dim3 grid,
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Per-device "done once" flag for settings that belong to a (kernel, device) pair, such as
+// cudaFuncSetAttribute: a process that drives several GPUs must repeat them on each.
+struct OncePerDevice {
+  bool done[64] = {};
+  // true the first time it is called with a given current device
+  bool first() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return true;
+    const bool was = done[dev];
+    done[dev] = true;
+    return !was;
+  }
+};
+
 __host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 

@@ -619,24 +619,25 @@ int make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int bo
 }
 
 int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int v = 0;
     cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 148;
-  }();
-  return n;
+    cached[dev] = v > 0 ? v : 148;
+  }
+  return cached[dev];
 }
 
 template <int BN, int EPI>
 int launch(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const GemmArgs& g, cudaStream_t st) {
   using C = Cfg<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
-      return fail(-2, "cannot raise the shared-memory limit to %d bytes", C::kSmem);
-    attr_set = true;
-  }
+  static OncePerDevice once;
+  if (once.first() &&
+      cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+    return fail(-2, "cannot raise the shared-memory limit to %d bytes", C::kSmem);
   const int tiles = g.tiles_m * g.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_kernel<BN, EPI><<<grid, kThreads, C::kSmem, st>>>(a, b0, b1, g);
@@ -647,12 +648,10 @@ template <int EPI, bool ROUTER>
 int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const CUtensorMap& r0,
                 const CUtensorMap& r1, const GemmArgs& g, cudaStream_t st) {
   using C = PairCfg;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_pair_kernel<EPI, ROUTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
-      return fail(-2, "cannot raise the shared-memory limit to %d bytes", C::kSmem);
-    attr_set = true;
-  }
+  static OncePerDevice once;
+  if (once.first() &&
+      cudaFuncSetAttribute(gemm_pair_kernel<EPI, ROUTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+    return fail(-2, "cannot raise the shared-memory limit to %d bytes", C::kSmem);
   const int tiles = g.tiles_m * (g.tiles_n + (ROUTER ? g.router_tiles : 0));
   const int max_pairs = sm_count() / 2;
   int pairs = tiles < max_pairs ? tiles : max_pairs;

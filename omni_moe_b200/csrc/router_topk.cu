@@ -45,12 +45,10 @@ int launch_cpl(const TopkArgs& a, cudaStream_t st) {
   // here lets these small blocks run next to a GEMM block instead of waiting for the SM to drain.
 #define OMNI_TOPK_LAUNCH(CPL_)                                                                                  \
   do {                                                                                                          \
-    static bool carveout_set = false;                                                                           \
-    if (!carveout_set) {                                                                                        \
+    static OncePerDevice once;                                                                                  \
+    if (once.first())                                                                                           \
       cudaFuncSetAttribute(router_topk_kernel<VPL, CPL_, PRE>, cudaFuncAttributePreferredSharedMemoryCarveout,  \
                            cudaSharedmemCarveoutMaxShared);                                                     \
-      carveout_set = true;                                                                                      \
-    }                                                                                                           \
     router_topk_kernel<VPL, CPL_, PRE><<<grid, block, 0, st>>>(a);                                              \
   } while (0)
   if (need <= 2) OMNI_TOPK_LAUNCH(2);

@@ -149,3 +149,20 @@ def test_training_batchnorm_synchronised_over_two_gpus(tmp_path):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_two_devices():
+    """Per-kernel settings (shared-memory limits) are per device: the second GPU of a process must work too."""
+    from omni_moe_b200.modules.omni_moe import OmniMoE, OmniMoEConfig
+    torch.manual_seed(0)
+    base = OmniMoE(OmniMoEConfig(256, 512, "silu", 1024, 8)).to(torch.bfloat16).eval()
+    x = torch.randn(1, 300, 256).bfloat16()
+    outs = []
+    for d in (0, 1):
+        import copy
+        m = copy.deepcopy(base).to(f"cuda:{d}")
+        y = m(x.to(f"cuda:{d}"))
+        m.check_status()
+        outs.append(y.cpu())
+    assert torch.equal(outs[0], outs[1])
