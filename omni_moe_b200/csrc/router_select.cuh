@@ -43,6 +43,22 @@ __device__ __forceinline__ float load_as_float(const void* base, int dtype, int6
   return __half2float(reinterpret_cast<const __half*>(base)[i]);
 }
 
+// Small rows (at most 64 entries, two per lane): rank every entry by counting the entries that beat
+// it.  The entries are made distinct by packing (score key, ~index) into 64 bits, so the ranks are a
+// permutation; there is no cross-lane dependency chain, only broadcast reads of shared memory.
+// Returns the rank of `mine` among the 64 packed entries in `all`.
+__device__ __forceinline__ int rank_among_64(const unsigned long long* all, unsigned long long mine) {
+  int rank = 0;
+  const ulonglong2* p = reinterpret_cast<const ulonglong2*>(all);
+#pragma unroll 8
+  for (int q = 0; q < 32; ++q) {
+    const ulonglong2 o = p[q];
+    rank += (o.x > mine) + (o.y > mine);
+  }
+  return rank;
+}
+
+
 // Sorted top-K of the E * 32 entries a warp holds in registers (entry = 32-bit key, larger wins, and a
 // 32-bit id that is unique among the entries, smaller wins on equal keys; key 0 = absent).
 //   1. radix select: a bitwise search for the K-th largest key tau (per step every lane counts its
@@ -52,11 +68,58 @@ __device__ __forceinline__ float load_as_float(const void* base, int dtype, int6
 //      search, on the ids, only when more entries tie at tau than there is room for);
 //   3. the K admitted entries are compacted into shared memory and ranked by counting.
 // out_key[r], out_id[r] receive rank r (AS_FLOAT: the key converted back to its float).
-template <int E, bool AS_FLOAT>
+template <int E, bool AS_FLOAT, bool FEW = false>
 __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], const uint32_t (&id)[E], int K,
                                                    unsigned long long* s_tmp /*[kMaxK]*/, uint32_t* out_key,
                                                    uint32_t* out_id) {
   const int lane = lane_id();
+  if (FEW && K <= 16) {
+    // Shortcut for few winners (compiled in only where the caller asks: it costs registers): the K-th largest of the 32 per-lane maxima is a lower bound of the K-th
+    // largest entry (K lanes hold an entry at least that large).  Usually only a few more than K entries
+    // reach it; if at most 64 do, they are compacted and ranked by counting like a small row, with the
+    // same (key, id) order as the general path.  Otherwise (many ties) the general path below runs.
+    uint32_t lmax = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) lmax = max(lmax, key[e]);
+    int lrank = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const uint32_t o = __shfl_sync(FULL_MASK, lmax, j);
+      lrank += (o > lmax) || (o == lmax && j < lane);
+    }
+    const unsigned who = __ballot_sync(FULL_MASK, lrank == K - 1);
+    const uint32_t bound = __shfl_sync(FULL_MASK, lmax, __ffs(who) - 1);
+    int cnt = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) cnt += (key[e] >= bound) && key[e] != 0;
+    const int total = __reduce_add_sync(FULL_MASK, cnt);
+    if (bound != 0 && total <= 64) {
+      const unsigned lt_mask = (1u << lane) - 1u;
+      s_tmp[lane] = 0ull, s_tmp[32 + lane] = 0ull;
+      __syncwarp();
+      int base = 0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const bool in = (key[e] >= bound) && key[e] != 0;
+        const unsigned m = __ballot_sync(FULL_MASK, in);
+        if (in) s_tmp[base + __popc(m & lt_mask)] = (static_cast<unsigned long long>(key[e]) << 32) | (0xffffffffu - id[e]);
+        base += __popc(m);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const unsigned long long mine = s_tmp[q * 32 + lane];
+        const int r = rank_among_64(s_tmp, mine);
+        if (mine != 0ull && r < K) {
+          const uint32_t kq = static_cast<uint32_t>(mine >> 32);
+          out_key[r] = AS_FLOAT ? __float_as_uint(key_to_float(kq)) : kq;
+          out_id[r] = 0xffffffffu - static_cast<uint32_t>(mine);
+        }
+      }
+      __syncwarp();
+      return;
+    }
+  }
   uint32_t kmax = 0, kmin = 0xffffffffu;
 #pragma unroll
   for (int e = 0; e < E; ++e) {
@@ -129,22 +192,6 @@ __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], con
   }
   __syncwarp();
 }
-
-// Small rows (at most 64 entries, two per lane): rank every entry by counting the entries that beat
-// it.  The entries are made distinct by packing (score key, ~index) into 64 bits, so the ranks are a
-// permutation; there is no cross-lane dependency chain, only broadcast reads of shared memory.
-// Returns the rank of `mine` among the 64 packed entries in `all`.
-__device__ __forceinline__ int rank_among_64(const unsigned long long* all, unsigned long long mine) {
-  int rank = 0;
-  const ulonglong2* p = reinterpret_cast<const ulonglong2*>(all);
-#pragma unroll 8
-  for (int q = 0; q < 32; ++q) {
-    const ulonglong2 o = p[q];
-    rank += (o.x > mine) + (o.y > mine);
-  }
-  return rank;
-}
-
 
 // Shared memory of one warp.
 template <int VPL, int CPL>
@@ -301,7 +348,7 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpS
       uint32_t sub[VPL];
 #pragma unroll
       for (int e = 0; e < VPL; ++e) sub[e] = e * 32 + lane;
-      warp_select_sorted<VPL, true>(key, sub, kk, w.pack, reinterpret_cast<uint32_t*>(axis == 0 ? sx : sy),
+      warp_select_sorted<VPL, true, (VPL <= 8)>(key, sub, kk, w.pack, reinterpret_cast<uint32_t*>(axis == 0 ? sx : sy),
                                     reinterpret_cast<uint32_t*>(axis == 0 ? ix : iy));
     }
   }
