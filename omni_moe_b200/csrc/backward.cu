@@ -152,6 +152,110 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_dots_kernel(
   if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
 }
 
+// The same for rows of at most 1024 columns: the token's x and dy rows stay in registers, unpacked to
+// fp32 pairs, so a pair costs two row gathers and nothing else; two pairs are in flight.
+__device__ __forceinline__ float2 dot8u(const float2 (&a)[4], const uint4& b, float2 acc) {
+  const uint32_t* pb = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc = __ffma2_rn(a[i], bf16x2_to_float2(pb[i]), acc);
+  return acc;
+}
+
+template <int HV>
+__global__ void __launch_bounds__(kThreads) expert_bwd_dots_reg_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
+    const __nv_bfloat16* __restrict__ dy, const float* __restrict__ weights, const int32_t* __restrict__ indices, int64_t T,
+    int k, int H, int64_t N, float* __restrict__ ds, float* __restrict__ cdown, float* __restrict__ dg, int* __restrict__ status) {
+  constexpr bool kUnpacked = HV <= 4;
+  constexpr int UNR = HV <= 4 ? 2 : 1;
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (t >= T) return;
+  const int c0 = lane * 8;
+  uint4 xv[HV], gv[HV];
+  float2 xf[kUnpacked ? HV : 1][4], gf[kUnpacked ? HV : 1][4];
+#pragma unroll
+  for (int v = 0; v < HV; ++v) {
+    const int col = c0 + v * 256;
+    xv[v] = col < H ? ldg128(x + t * H + col) : make_uint4(0, 0, 0, 0);
+    gv[v] = col < H ? ldg128(dy + t * H + col) : make_uint4(0, 0, 0, 0);
+    if (kUnpacked) {
+      const uint32_t* px = reinterpret_cast<const uint32_t*>(&xv[v]);
+      const uint32_t* pg = reinterpret_cast<const uint32_t*>(&gv[v]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) xf[v][q] = bf16x2_to_float2(px[q]), gf[v][q] = bf16x2_to_float2(pg[q]);
+    }
+  }
+  bool bad = false;
+  for (int j0 = 0; j0 < k; j0 += 32) {
+    const int j = j0 + lane;
+    int my_e = -1;
+    float my_g = 0.f;
+    if (j < k) {
+      my_e = indices[t * k + j];
+      my_g = weights[t * k + j];
+      if (my_e < 0 || my_e >= N) bad = true, my_e = -1;
+    }
+    const int cnt = min(32, k - j0);
+    float my_ds = 0.f, my_c = 0.f, my_dg = 0.f;
+    for (int i = 0; i < cnt; i += UNR) {
+      uint4 uv[UNR][HV], dv[UNR][HV];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int e = __shfl_sync(FULL_MASK, my_e, (i + u) & 31);
+        const bool on = i + u < cnt && e >= 0;
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          const int col = c0 + v * 256;
+          const bool ld = on && col < H;
+          uv[u][v] = ld ? ldg128(up + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+          dv[u][v] = ld ? ldg128(down + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+        }
+      }
+      float S[UNR], dA[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        float2 s2 = make_float2(0.f, 0.f), a2 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int v = 0; v < HV; ++v) {
+          if (kUnpacked) {
+            s2 = dot8u(xf[v], uv[u][v], s2);
+            a2 = dot8u(gf[v], dv[u][v], a2);
+          } else {
+            s2 = dot8f(xv[v], uv[u][v], s2);
+            a2 = dot8f(gv[v], dv[u][v], a2);
+          }
+        }
+        S[u] = s2.x + s2.y, dA[u] = a2.x + a2.y;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          S[u] += __shfl_xor_sync(FULL_MASK, S[u], o);
+          dA[u] += __shfl_xor_sync(FULL_MASK, dA[u], o);
+        }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        if (lane == i + u) {
+          const float sig = 1.0f / (1.0f + __expf(-S[u]));
+          const float h = S[u] * sig;
+          my_dg = dA[u] * h;
+          my_c = my_g * h;
+          my_ds = dA[u] * my_g * (sig * (1.0f + S[u] * (1.0f - sig)));
+        }
+      }
+    }
+    if (j < k) {
+      const bool ok = my_e >= 0;
+      ds[t * k + j] = ok ? my_ds : 0.f;
+      cdown[t * k + j] = ok ? my_c : 0.f;
+      dg[t * k + j] = ok ? my_dg : 0.f;
+    }
+  }
+  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
 template <bool OUT_F32>
 __device__ __forceinline__ void store8(void* base, int64_t off, const float2 (&a)[4]) {
   if (OUT_F32) {
@@ -422,9 +526,19 @@ extern "C" int omni_expert_bwd_dots(const void* x, const void* up, const void* d
   OMNI_REQUIRE(x && up && down && dy && weights && indices && ds && cdown && dg && status, "NULL argument");
   OMNI_REQUIRE(aligned16(x) && aligned16(up) && aligned16(down) && aligned16(dy), "x, up, down and dy must be 16-byte aligned");
   const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
-  expert_bwd_dots_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(up), static_cast<const __nv_bfloat16*>(down),
-      static_cast<const __nv_bfloat16*>(dy), weights, indices, num_tokens, k, hidden, num_experts, ds, cdown, dg, status);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const auto* xb = static_cast<const __nv_bfloat16*>(x);
+  const auto* ub = static_cast<const __nv_bfloat16*>(up);
+  const auto* db = static_cast<const __nv_bfloat16*>(down);
+  const auto* gb = static_cast<const __nv_bfloat16*>(dy);
+#define OMNI_DOTS(HV_) \
+  expert_bwd_dots_reg_kernel<HV_><<<grid, kThreads, 0, st>>>(xb, ub, db, gb, weights, indices, num_tokens, k, hidden, num_experts, ds, cdown, dg, status)
+  if (hidden <= 256) OMNI_DOTS(1);
+  else if (hidden <= 512) OMNI_DOTS(2);
+  else if (hidden <= 1024) OMNI_DOTS(4);
+  else  // wider rows: registers for two resident rows would cost more occupancy than the L1 re-reads do
+    expert_bwd_dots_kernel<<<grid, kThreads, 0, st>>>(xb, ub, db, gb, weights, indices, num_tokens, k, hidden, num_experts, ds, cdown, dg, status);
+#undef OMNI_DOTS
   return check_launch("expert_bwd_dots_kernel");
 }
 
