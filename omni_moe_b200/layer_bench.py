@@ -2,6 +2,7 @@
 row-partitioned over the GPUs of one node.
 
     python -m omni_moe_b200.layer_bench --config c5                       # one GPU, whole layer
+    python -m omni_moe_b200.layer_bench --config c2 --impl torch          # same-box bar: PyTorch eager ops, same GPU
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         -m omni_moe_b200.layer_bench --config c5 --partitioned            # tables split over N GPUs
 
@@ -63,6 +64,9 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--config", default="c5", choices=list(CONFIGS))
     ap.add_argument("--partitioned", action="store_true")
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch"],
+                    help="torch: the same layer written with PyTorch eager ops (gather / matmul experts, torch.topk "
+                         "router) on the same GPU, as a same-box bar; c2 only (it materialises [T, k, H] gathers)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -90,6 +94,10 @@ def main():
         layer.group, layer.part, layer.inner = None, part, inner
         layer._side, layer.partial_dtype = None, torch.bfloat16
         run = lambda: layer(x)
+    elif args.impl == "torch":
+        from .train_bench import torch_forward
+        inner = build_module(cfg, dev)
+        run = lambda: torch_forward(inner, x)
     else:
         inner = build_module(cfg, dev)
         run = lambda: inner(x)
@@ -121,7 +129,7 @@ def main():
     if rank == 0:
         tokens = cfg["T"] if args.partitioned else cfg["T"] * world
         print(json.dumps({
-            "config": args.config, "mode": "tables row-partitioned" if args.partitioned else "replica",
+            "config": args.config, "impl": args.impl, "mode": "tables row-partitioned" if args.partitioned else "replica",
             "n_gpus": world, "tokens_per_step": tokens, "ms_per_step": round(ms, 4),
             "tokens_per_s": round(tokens / (ms * 1e-3)), "steps": args.steps, "warmup": args.warmup,
             "scaling": "strong" if args.partitioned else "weak",

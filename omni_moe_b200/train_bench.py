@@ -41,8 +41,9 @@ def _time(fn, steps: int, warmup: int) -> float:
     return e0.elapsed_time(e1) / steps
 
 
-def torch_step(m, x, dy):
-    """The layer's training step with PyTorch ops only (the structure of the reference's PyTorch module)."""
+def torch_forward(m, x):
+    """The layer's forward with PyTorch ops only (the structure of the reference's PyTorch module,
+    omni_moe/modules/omni_moe.py:139-194): gather / matmul experts, torch.topk router."""
     t, h = x.shape[-2], x.shape[-1]
     n, k = m.num_expert_sqrt, m.top_k
     xx = x.view(t, h)
@@ -59,7 +60,12 @@ def torch_step(m, x, dy):
     s = torch.matmul(m.up_embed(ind), xx.unsqueeze(-1)).squeeze(-1)
     e = torch.matmul((F.silu(s) * g).unsqueeze(-2), m.down_embed(ind)).squeeze(-2)
     sh = m.down_proj(F.silu(m.gate_proj(xx)) * m.up_proj(xx))
-    (sh + e).backward(dy.view(t, h))
+    return sh + e
+
+
+def torch_step(m, x, dy):
+    """The layer's training step with PyTorch ops and autograd only."""
+    torch_forward(m, x).backward(dy.view(x.shape[-2], x.shape[-1]))
 
 
 def main():
