@@ -245,3 +245,33 @@ def test_expert_backward_long_segments(layout, split):
     cu = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.bfloat16, compact=True,
                          long_segments=split)
     assert torch.equal(cu[1].float(), got[1][cu[4].long()].bfloat16().float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_layer_trains_in_other_dtypes(dtype):
+    """fp32 / fp16 modules: operands are rounded to bf16 for the kernels, gradients come back in the
+    parameter dtype and match fp32 autograd on the bf16-rounded operands."""
+    from omni_moe.modules.omni_moe import OmniMoE, OmniMoEConfig
+    torch.manual_seed(1)
+    h, i, n_exp, k, t = 64, 128, 64, 4, 96
+    m = OmniMoE(OmniMoEConfig(h, i, "silu", n_exp, k))
+    with torch.no_grad():
+        m.up_embed.weight.mul_(0.3)
+        m.down_embed.weight.mul_(0.3)
+    m = m.to(dtype)
+    sd = {kk: (v.to(torch.bfloat16).float().clone() if v.is_floating_point() and "running" not in kk else v.clone())
+          for kk, v in m.state_dict().items()}
+    p = orc.params_from_state_dict({kk: (v.float() if v.is_floating_point() else v) for kk, v in sd.items()}, n_exp, k)
+    m = m.cuda().train()
+    x = torch.randn(1, t, h, generator=gen(3)).to(dtype)
+    dy = (torch.randn(1, t, h, generator=gen(4)) * 0.1).to(dtype)
+    cx = x.cuda().requires_grad_(True)
+    y = m(cx)
+    assert y.dtype == dtype
+    y.backward(dy.cuda())
+    _, eg = orc.layer_gradients(p, x.to(torch.bfloat16).float(), m.last_routing[1].cpu(), dy.float(), True)
+    for name, prm in m.named_parameters():
+        assert prm.grad is not None and prm.grad.dtype == dtype, name
+        if not name.startswith("router_gate"):   # the gates see the unrounded fp32 / fp16 x through nn.Linear
+            _scaled_close(prm.grad, eg[name], name, rtol=5e-2, atol_frac=4e-2)
+    assert cx.grad.dtype == dtype
