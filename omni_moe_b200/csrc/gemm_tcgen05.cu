@@ -92,6 +92,13 @@ struct Cfg {
   static constexpr int kSmem = kStages * kStage + kBarBytes + 1024;  // + slack to align the base to 1024
 };
 
+// 256-bit store of eight 32-bit words (a whole 32-byte sector); ptr must be 32-byte aligned.
+__device__ __forceinline__ void st256(void* ptr, const uint32_t (&p)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(p[0]), "r"(p[1]), "r"(p[2]), "r"(p[3]),
+               "r"(p[4]), "r"(p[5]), "r"(p[6]), "r"(p[7])
+               : "memory");
+}
+
 // Drains this warp's share of one accumulator tile: its 32 rows (TMEM lane quarter) and the column
 // chunks [c_begin, c_begin + 32 * NCH).  The TMEM load of chunk i+1 and the residual fetch of
 // chunk i are in flight while chunk i-1 is converted and stored.
@@ -129,7 +136,19 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile
       // training: keep the pre-activations for the backward (gate in columns [0, N), up in [N, 2N))
       __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(g.gu_out) + static_cast<int64_t>(row) * g.ldgu + col0;
       __nv_bfloat16* ou = og + g.N;
-      if (full && (g.ldgu & 7) == 0 && (g.N & 7) == 0) {
+      if (full && (g.ldgu & 15) == 0 && (g.N & 15) == 0 && (reinterpret_cast<uintptr_t>(g.gu_out) & 31) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 16) {
+          uint32_t pg[8], pu[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            pg[q] = float2_to_bf16x2(__uint_as_float(ra[i + 2 * q]), __uint_as_float(ra[i + 2 * q + 1]));
+            pu[q] = float2_to_bf16x2(__uint_as_float(rb[i + 2 * q]), __uint_as_float(rb[i + 2 * q + 1]));
+          }
+          st256(og + i, pg);
+          st256(ou + i, pu);
+        }
+      } else if (full && (g.ldgu & 7) == 0 && (g.N & 7) == 0) {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           uint4 pg, pu;
@@ -161,7 +180,15 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile
     if (!live) continue;
     if (EPI == EPI_F32) {
       float* o = reinterpret_cast<float*>(g.out) + static_cast<int64_t>(row) * g.ldo + col0;
-      if (full && (g.ldo & 3) == 0 && (col0 & 3) == 0) {
+      if (full && (g.ldo & 7) == 0 && (col0 & 7) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 31) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint32_t p[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) p[q] = __float_as_uint(v[i + q]);
+          st256(o + i, p);
+        }
+      } else if (full && (g.ldo & 3) == 0 && (col0 & 3) == 0) {
 #pragma unroll
         for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
       } else {
@@ -179,7 +206,16 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile
         }
       }
       __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + static_cast<int64_t>(row) * g.ldo + col0;
-      if (full && (g.ldo & 7) == 0) {
+      if (full && (g.ldo & 15) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 31) == 0) {
+        // 32 consecutive bf16 of this row = 64 bytes: two 256-bit stores, each a whole 32-byte sector
+#pragma unroll
+        for (int i = 0; i < 32; i += 16) {
+          uint32_t p[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) p[q] = float2_to_bf16x2(v[i + 2 * q], v[i + 2 * q + 1]);
+          st256(o + i, p);
+        }
+      } else if (full && (g.ldo & 7) == 0) {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           uint4 p;
