@@ -349,6 +349,28 @@ OMNI_API int omni_transpose_bf16(const void *in, int64_t rows, int64_t cols, int
 OMNI_API int omni_swiglu_bwd(const void *gate_up, const void *dact, int64_t num_tokens, int intermediate,
                     void *dgate_up, void *dgate_up_t, void *act_t, int64_t ld_t, void *stream);
 
+/*
+ * Training-mode BatchNorm of the router logits: batch statistics of logits [T, 2*sqrt_n] (the output
+ * of omni_router_gate) over all T tokens, folded into the bn_scale / bn_shift [2*sqrt_n] that
+ * omni_router_logits_topk and omni_route_expert_fused take, and the running statistics updated as
+ * nn.BatchNorm1d(affine=False) does in training (momentum average with the unbiased variance;
+ * num_batches_tracked incremented).  Replaces router_norm_x / router_norm_y in training mode
+ * (omni_moe/modules/omni_moe.py:53-54,70-71).  Nothing is allocated and nothing is read back, so a
+ * training-mode forward can be captured in a CUDA graph.
+ *   eps_*, momentum_*: of the two norm layers; momentum < 0 stands for momentum=None (cumulative
+ *   average, 1 / num_batches_tracked)
+ *   running_* [sqrt_n] of running_dtype (OMNI_F32 or OMNI_BF16), or NULL (track_running_stats off)
+ *   num_batches_tracked_*: int64 device scalars or NULL
+ *   scratch: omni_router_bn_train_scratch_bytes(T, sqrt_n) bytes
+ */
+OMNI_API size_t omni_router_bn_train_scratch_bytes(int64_t num_tokens, int sqrt_n);
+OMNI_API int omni_router_bn_train(const float *logits, int64_t ld_logits, int64_t num_tokens, int sqrt_n,
+                         float eps_x, float eps_y, float momentum_x, float momentum_y,
+                         void *running_mean_x, void *running_var_x, void *running_mean_y,
+                         void *running_var_y, int running_dtype, int64_t *num_batches_tracked_x,
+                         int64_t *num_batches_tracked_y, float *bn_scale, float *bn_shift,
+                         void *scratch, size_t scratch_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

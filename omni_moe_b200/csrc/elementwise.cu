@@ -148,3 +148,133 @@ extern "C" int omni_swiglu_bwd(const void* gate_up, const void* dact, int64_t nu
       static_cast<__nv_bfloat16*>(dgate_up), static_cast<uint16_t*>(dgate_up_t), static_cast<uint16_t*>(act_t), ld_t);
   return check_launch("swiglu_bwd_kernel");
 }
+
+// ------------------------------------------------------------------------------------------------
+// Training-mode BatchNorm of the router logits (nn.BatchNorm1d(affine=False), batch statistics over
+// all T tokens): column mean and biased variance of logits [T, C] (C = 2 * sqrt_n, both axes), folded
+// into the per-column scale / shift the selection kernels take, plus the update of the running
+// statistics.  Two launches, no atomics:
+//   bn_partial_kernel   block b owns rows [b * kBnRows, ...): per column its count, mean and sum of
+//                       squared deviations (two sweeps over the block's rows, so nothing cancels)
+//   bn_finalize_kernel  one thread per column merges the block partials in block order (the pairwise
+//                       update for combining means and variances), writes scale = rsqrt(var + eps),
+//                       shift = -mean * scale, and updates running_mean / running_var (momentum, unbiased
+//                       variance) and num_batches_tracked exactly as nn.BatchNorm1d does in training.
+namespace omni {
+namespace {
+constexpr int kBnRows = 128;
+
+__global__ void __launch_bounds__(256) bn_partial_kernel(const float* __restrict__ z, int64_t T, int C, int64_t ld,
+                                                         float* __restrict__ partial /*[blocks, 2, C]*/) {
+  const int64_t r0 = static_cast<int64_t>(blockIdx.x) * kBnRows;
+  const int rows = (T - r0 < kBnRows) ? static_cast<int>(T - r0) : kBnRows;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float sum = 0.f;
+    for (int r = 0; r < rows; ++r) sum += z[(r0 + r) * ld + c];
+    const float mean = sum / static_cast<float>(rows);
+    float m2 = 0.f;
+    for (int r = 0; r < rows; ++r) {
+      const float d = z[(r0 + r) * ld + c] - mean;
+      m2 = __fmaf_rn(d, d, m2);
+    }
+    partial[(static_cast<int64_t>(blockIdx.x) * 2 + 0) * C + c] = mean;
+    partial[(static_cast<int64_t>(blockIdx.x) * 2 + 1) * C + c] = m2;
+  }
+}
+
+__global__ void __launch_bounds__(256) bn_finalize_kernel(const float* __restrict__ partial, int blocks, int64_t T, int C,
+                                                          int n_axis, float eps_x, float eps_y, float momentum_x, float momentum_y,
+                                                          float* __restrict__ scale, float* __restrict__ shift,
+                                                          void* run_mean_x, void* run_var_x, void* run_mean_y, void* run_var_y,
+                                                          int run_dtype, long long* nbt_x, long long* nbt_y) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float n = 0.f, mean = 0.f, m2 = 0.f;
+  for (int b = 0; b < blocks; ++b) {
+    const int64_t left = T - static_cast<int64_t>(b) * kBnRows;
+    const float nb = static_cast<float>(left < kBnRows ? left : kBnRows);
+    const float mb = partial[(static_cast<int64_t>(b) * 2 + 0) * C + c];
+    const float qb = partial[(static_cast<int64_t>(b) * 2 + 1) * C + c];
+    const float tot = n + nb;
+    const float delta = mb - mean;
+    mean += delta * (nb / tot);
+    m2 += qb + delta * delta * (n * nb / tot);
+    n = tot;
+  }
+  const float var = m2 / n;  // biased: what normalises the batch
+  const bool is_y = c >= n_axis;
+  const float eps = is_y ? eps_y : eps_x;
+  const float sc = rsqrtf(var + eps);
+  scale[c] = sc;
+  shift[c] = -mean * sc;
+  void* rm = is_y ? run_mean_y : run_mean_x;
+  void* rv = is_y ? run_var_y : run_var_x;
+  long long* nbt = is_y ? nbt_y : nbt_x;
+  if (rm != nullptr && rv != nullptr) {
+    const int j = is_y ? c - n_axis : c;
+    float mom = is_y ? momentum_y : momentum_x;
+    // momentum < 0 stands for None: cumulative moving average over the batches seen so far
+    if (mom < 0.f) mom = 1.0f / static_cast<float>((nbt ? *nbt : 0) + 1);
+    const float unbiased = n > 1.f ? m2 / (n - 1.f) : var;
+    if (run_dtype == OMNI_F32) {
+      float* m = static_cast<float*>(rm);
+      float* v = static_cast<float*>(rv);
+      m[j] = (1.f - mom) * m[j] + mom * mean;
+      v[j] = (1.f - mom) * v[j] + mom * unbiased;
+    } else {
+      __nv_bfloat16* m = static_cast<__nv_bfloat16*>(rm);
+      __nv_bfloat16* v = static_cast<__nv_bfloat16*>(rv);
+      m[j] = __float2bfloat16_rn((1.f - mom) * __bfloat162float(m[j]) + mom * mean);
+      v[j] = __float2bfloat16_rn((1.f - mom) * __bfloat162float(v[j]) + mom * unbiased);
+    }
+  }
+}
+
+// every column of an axis reads num_batches_tracked before any thread may bump it: a kernel of its own
+__global__ void bn_count_kernel(long long* nbt_x, long long* nbt_y) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    if (nbt_x) *nbt_x += 1;
+    if (nbt_y) *nbt_y += 1;
+  }
+}
+}  // namespace
+}  // namespace omni
+
+extern "C" size_t omni_router_bn_train_scratch_bytes(int64_t num_tokens, int sqrt_n) {
+  if (num_tokens <= 0 || sqrt_n <= 0) return 0;
+  return static_cast<size_t>(ceil_div64(num_tokens, kBnRows)) * 2 * (2 * static_cast<size_t>(sqrt_n)) * sizeof(float);
+}
+
+extern "C" int omni_router_bn_train(const float* logits, int64_t ld_logits, int64_t num_tokens, int sqrt_n, float eps_x,
+                                    float eps_y, float momentum_x, float momentum_y, void* running_mean_x, void* running_var_x,
+                                    void* running_mean_y, void* running_var_y, int running_dtype, int64_t* num_batches_tracked_x,
+                                    int64_t* num_batches_tracked_y, float* bn_scale, float* bn_shift, void* scratch,
+                                    size_t scratch_bytes, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 1 && sqrt_n >= 1, "num_tokens and sqrt_n must be >= 1");
+  OMNI_REQUIRE(ld_logits >= 2 * sqrt_n, "ld_logits %lld < 2*sqrt_n", static_cast<long long>(ld_logits));
+  OMNI_REQUIRE(running_dtype == OMNI_F32 || running_dtype == OMNI_BF16, "running statistics must be float32 or bfloat16");
+  OMNI_REQUIRE(logits && bn_scale && bn_shift && scratch, "NULL argument");
+  OMNI_REQUIRE((running_mean_x == nullptr) == (running_var_x == nullptr) && (running_mean_y == nullptr) == (running_var_y == nullptr),
+               "running mean and variance must be given together");
+  OMNI_REQUIRE(scratch_bytes >= omni_router_bn_train_scratch_bytes(num_tokens, sqrt_n), "scratch too small: need %zu bytes",
+               omni_router_bn_train_scratch_bytes(num_tokens, sqrt_n));
+  const int C = 2 * sqrt_n;
+  const int64_t blocks = ceil_div64(num_tokens, kBnRows);
+  OMNI_REQUIRE(blocks < (int64_t(1) << 31), "too many tokens");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = static_cast<float*>(scratch);
+  bn_partial_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(logits, num_tokens, C, ld_logits, partial);
+  if (int e = check_launch("bn_partial_kernel")) return e;
+  bn_finalize_kernel<<<ceil_div(C, 256), 256, 0, st>>>(partial, static_cast<int>(blocks), num_tokens, C, sqrt_n, eps_x, eps_y,
+                                                      momentum_x, momentum_y, bn_scale, bn_shift, running_mean_x, running_var_x,
+                                                      running_mean_y, running_var_y, running_dtype,
+                                                      reinterpret_cast<long long*>(num_batches_tracked_x),
+                                                      reinterpret_cast<long long*>(num_batches_tracked_y));
+  if (int e = check_launch("bn_finalize_kernel")) return e;
+  if (num_batches_tracked_x || num_batches_tracked_y) {
+    bn_count_kernel<<<1, 32, 0, st>>>(reinterpret_cast<long long*>(num_batches_tracked_x),
+                                      reinterpret_cast<long long*>(num_batches_tracked_y));
+    return check_launch("bn_count_kernel");
+  }
+  return 0;
+}

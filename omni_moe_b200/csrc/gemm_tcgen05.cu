@@ -42,6 +42,7 @@ struct GemmArgs {
   int64_t ldo;
   const float* residual;  // EPI_RES
   int64_t ldr;
+  int tma_out;            // pair kernel: 1 = bf16 output tiles leave through shared memory and TMA stores
   void* gu_out;           // EPI_SWIGLU: if set, [M, 2N] bf16 that also receives the gate | up pre-activations
   int64_t ldgu;
   // router tile columns of the fused gate/up + router-gate launch (pair kernel, EPI_SWIGLU only)
@@ -227,6 +228,105 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile
         }
       } else {
         for (int i = 0; i < 32 && col0 + i < col_lim; ++i) o[i] = __float2bfloat16_rn(v[i]);
+      }
+    }
+  }
+}
+
+// The same drain with the output leaving through shared memory: every pair of 32-column chunks (64 bf16
+// = 128 bytes per row) is written into the warp's 32-row staging buffer in the 128-byte swizzle the
+// tensor map expects (16-byte piece j of row r sits at piece j ^ (r % 8): no bank conflicts although a
+// lane owns a row), and one lane hands the 32 x 64 box to the TMA engine.  The global writes are then
+// whole 128-byte lines issued by the copy engine instead of 32 scattered sectors per warp instruction,
+// rows and columns outside the matrix are clipped by the tensor map, and the warp goes on draining
+// while the box is on its way.  row0: global row of lane 0; stg: shared-memory address of the warp's
+// 4 KB staging buffer (1024-byte aligned).  bf16 outputs only (EPI_SWIGLU, EPI_RES); NCH even.
+template <int BN, int EPI, int NCH>
+__device__ __forceinline__ void store_tile_tma(uint32_t taddr, int row0, int col_tile, int col_lim, int c_begin, const GemmArgs& g,
+                                               const CUtensorMap* tm_out, uint32_t stg) {
+  static_assert(NCH % 2 == 0 && EPI != EPI_F32, "bf16 slabs of two chunks");
+  const int lane = lane_id();
+  const int row = row0 + lane;
+  uint32_t ra[32], rb[32];
+  tmem_ld32_async(taddr + c_begin, ra);
+  if (EPI == EPI_SWIGLU) tmem_ld32_async(taddr + BN / 2 + c_begin, rb);
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = c_begin + 32 * ch;
+    const int col0 = col_tile + c;
+    const bool live = row < g.M && col0 < col_lim;
+    const bool full = col0 + 32 <= col_lim;
+    float v[32];
+    tmem_ld_wait(ra);
+    if (EPI == EPI_SWIGLU) {
+      tmem_ld_wait(rb);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = silu_fast(__uint_as_float(ra[i])) * __uint_as_float(rb[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
+    }
+    if (EPI == EPI_SWIGLU && g.gu_out != nullptr && live) {
+      __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(g.gu_out) + static_cast<int64_t>(row) * g.ldgu + col0;
+      __nv_bfloat16* ou = og + g.N;
+      if (full && (g.ldgu & 15) == 0 && (g.N & 15) == 0 && (reinterpret_cast<uintptr_t>(g.gu_out) & 31) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 16) {
+          uint32_t pg[8], pu[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            pg[q] = float2_to_bf16x2(__uint_as_float(ra[i + 2 * q]), __uint_as_float(ra[i + 2 * q + 1]));
+            pu[q] = float2_to_bf16x2(__uint_as_float(rb[i + 2 * q]), __uint_as_float(rb[i + 2 * q + 1]));
+          }
+          st256(og + i, pg);
+          st256(ou + i, pu);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (col0 + i < col_lim) {
+            og[i] = __float2bfloat16_rn(__uint_as_float(ra[i]));
+            ou[i] = __float2bfloat16_rn(__uint_as_float(rb[i]));
+          }
+        }
+      }
+    }
+    if (ch + 1 < NCH) {
+      tmem_ld32_async(taddr + c + 32, ra);
+      if (EPI == EPI_SWIGLU) tmem_ld32_async(taddr + BN / 2 + c + 32, rb);
+    }
+    if (EPI == EPI_RES && g.residual && live) {
+      if (full && (g.ldr & 3) == 0) {
+        const float4* r4 = reinterpret_cast<const float4*>(g.residual + static_cast<int64_t>(row) * g.ldr + col0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 t4 = __ldg(r4 + i);
+          v[4 * i] += t4.x, v[4 * i + 1] += t4.y, v[4 * i + 2] += t4.z, v[4 * i + 3] += t4.w;
+        }
+      } else {
+        const float* r = g.residual + static_cast<int64_t>(row) * g.ldr + col0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < col_lim) v[i] += r[i];
+      }
+    }
+    if ((ch & 1) == 0) {
+      // a new slab: the box sent from this buffer before must have been read out
+      if (lane == 0) bulk_wait_read_all();
+      __syncwarp();
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int piece = ((ch & 1) * 4 + q) ^ (lane & 7);
+      st_shared_v4(stg + lane * 128 + piece * 16, float2_to_bf16x2(v[8 * q], v[8 * q + 1]), float2_to_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                   float2_to_bf16x2(v[8 * q + 4], v[8 * q + 5]), float2_to_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+    }
+    if ((ch & 1) == 1) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tm_out, stg, col0 - 32, row0);
+        bulk_commit_group();
       }
     }
   }
@@ -422,14 +522,15 @@ struct PairCfg {
   static constexpr int kStage = kStageA + kStageB;
   static constexpr int kStages = 6 / kSub;
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kSmem = kStages * kStage + 1024 + 1024;
+  static constexpr int kStaging = kEpiWarps * 4096;  // per epilogue warp: 32 rows x 128 bytes for the TMA stores
+  static constexpr int kSmem = kStages * kStage + 1024 + kStaging + 1024;
 };
 
 template <int EPI, bool ROUTER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                      const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_r0,
-                     const __grid_constant__ CUtensorMap tm_r1, const GemmArgs g) {
+                     const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_out, const GemmArgs g) {
   // ROUTER: the first g.router_tiles tile columns multiply x by the router sub-keys instead of the MLP
   // weights: rank 0 holds 128 rows of the x-axis keys, rank 1 the same rows of the y-axis keys, and the
   // epilogue stores fp32 logits.  It rides along with the gate/up GEMM because it reads the same A.
@@ -472,6 +573,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b0);
     prefetch_tmap(&tm_b1);
+    if (g.tma_out) prefetch_tmap(&tm_out);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), C::kTmemCols);
@@ -596,6 +698,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         gr.out = g.logits, gr.ldo = 2 * g.router_n;
         const int col_tile = col_half * g.router_n + tn * (BN / 2);
         store_tile<BN, EPI_F32, 4>(taddr + col_half * (BN / 2), row, col_tile, (col_half + 1) * g.router_n, 0, gr);
+      } else if (g.tma_out) {
+        const uint32_t stg = bars + 1024 + static_cast<uint32_t>(warp - 2) * 4096;
+        OMNI_TIMED(e_store, (store_tile_tma<BN, EPI, OUTC / 64>(taddr, row - lane, tn * OUTC, g.N, col_half * (OUTC / 2), g, &tm_out, stg)));
       } else {
         OMNI_TIMED(e_store, (store_tile<BN, EPI, OUTC / 64>(taddr, row, tn * OUTC, g.N, col_half * (OUTC / 2), g)));
       }
@@ -603,6 +708,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
     }
+    if (g.tma_out && lane == 0) bulk_wait_all();  // the boxes still on their way are written before the CTA leaves
     if (g.prof && warp == 2 && lane == 0)
       g.prof[blockIdx.x * 16 + 5] = e_wait, g.prof[blockIdx.x * 16 + 6] = e_store, g.prof[blockIdx.x * 16 + 7] = clock64() - e_t0;
   }
@@ -654,6 +760,33 @@ int make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int bo
   return 0;
 }
 
+// Map of a row-major bf16 output [rows, cols] with row stride ld, boxes of 32 rows x 64 columns in
+// the 128-byte swizzle: what store_tile_tma sends.
+int make_out_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeFn enc = get_encode();
+  if (!enc) return fail(-2, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {64, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-2, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
+  return 0;
+}
+
+// The bf16 outputs of the pair kernels go through TMA stores when the output qualifies (16-byte aligned
+// base and row stride).  OMNI_MOE_B200_TMA_STORE=0 keeps the direct stores.
+int g_tma_store = -1;  // -1: follow the environment; 0 / 1: set by omni_debug_gemm_tma_store
+bool tma_store_enabled() {
+  static const bool v = [] {
+    const char* e = getenv("OMNI_MOE_B200_TMA_STORE");
+    return !(e && e[0] == '0');
+  }();
+  return g_tma_store < 0 ? v : g_tma_store != 0;
+}
+
 int sm_count() {
   static int cached[64] = {};
   int dev = 0;
@@ -682,7 +815,14 @@ int launch(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, c
 
 template <int EPI, bool ROUTER>
 int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const CUtensorMap& r0,
-                const CUtensorMap& r1, const GemmArgs& g, cudaStream_t st) {
+                const CUtensorMap& r1, GemmArgs g, cudaStream_t st) {
+  // output map: only when the bf16 output qualifies for TMA stores; otherwise any valid map fills the slot
+  CUtensorMap mo = a;
+  g.tma_out = 0;
+  if (g.out != nullptr && g.N > 0 && tma_store_enabled() && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && (g.ldo & 7) == 0) {
+    if (int e = make_out_map(&mo, g.out, g.M, g.N, g.ldo)) return e;
+    g.tma_out = 1;
+  }
   using C = PairCfg;
   static OncePerDevice once;
   if (once.first() &&
@@ -692,7 +832,7 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& 
   const int max_pairs = sm_count() / 2;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
   if (g.grid_limit > 0 && g.grid_limit < pairs) pairs = g.grid_limit;
-  launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, g);
+  launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, mo, g);
   return check_launch("gemm_pair_kernel");
 }
 
@@ -888,3 +1028,5 @@ extern "C" int omni_mlp_fwd(const void* x, const void* gate_w, const void* up_w,
 // MMA total, producer wait-for-stage, producer total, epilogue wait, epilogue store, epilogue total}.
 extern "C" OMNI_API void omni_debug_gemm_profile(long long* buf) { g_prof = buf; }
 extern "C" OMNI_API void omni_debug_gemm_knobs(int knobs, int grid_limit) { g_knobs = knobs, g_grid_limit = grid_limit; }
+// Testing aid, not part of the public header: 1 / 0 forces the TMA-store / direct-store epilogue of the pair kernels, -1 restores the default.
+extern "C" OMNI_API void omni_debug_gemm_tma_store(int enable) { g_tma_store = enable; }

@@ -57,6 +57,10 @@ class _Buffers:
         self.act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
         self.workspace = torch.empty(workspace_bytes(p, n), device=dev, dtype=torch.uint8)
         self.status = torch.zeros(1, **i32)
+        self.bn_scale = torch.empty(2 * n_sqrt, **f32)      # training-mode BatchNorm fold of this forward
+        self.bn_shift = torch.empty(2 * n_sqrt, **f32)
+        self.bn_scratch = torch.empty(max(int(_lib.load().omni_router_bn_train_scratch_bytes(max(t, 1), n_sqrt)), 16),
+                                      device=dev, dtype=torch.uint8)
         self.side = torch.cuda.Stream(device=dev)
         self.ev_fork = torch.cuda.Event()
         self.ev_join = torch.cuda.Event()
@@ -128,11 +132,28 @@ class OmniMoE(nn.Module):
             return (self.router_norm_x.process_group,)
         return None
 
-    def _bn_fold_train(self, logits: torch.Tensor):
+    def _bn_fold_train(self, logits: torch.Tensor, b: "_Buffers | None" = None):
         """Training-mode BatchNorm: batch statistics over all tokens (of all ranks, when synchronised),
-        running statistics updated as nn.BatchNorm1d does (momentum average, unbiased variance)."""
+        running statistics updated as nn.BatchNorm1d does (momentum average, unbiased variance).
+        On one rank this is the library's kernel pair (no allocation, no host read: capturable); with
+        synchronised statistics the per-rank moments are merged through torch.distributed."""
         n = self.num_expert_sqrt
         grp = self._bn_group()
+        bx, by = self.router_norm_x, self.router_norm_y
+        run_dt = bx.running_mean.dtype if bx.running_mean is not None else torch.float32
+        same_layout = (bx.running_mean is None) == (by.running_mean is None) and bx.track_running_stats == by.track_running_stats
+        if (grp is None and b is not None and logits.dtype == torch.float32 and logits.is_contiguous() and same_layout
+                and run_dt in (torch.float32, torch.bfloat16)):
+            track = bx.track_running_stats and bx.running_mean is not None
+            mom = lambda bn: -1.0 if bn.momentum is None else float(bn.momentum)
+            ptr = lambda t_: t_.data_ptr() if (track and t_ is not None) else None
+            _lib.check(_lib.load().omni_router_bn_train(
+                logits.data_ptr(), logits.size(1), logits.size(0), n, float(bx.eps), float(by.eps), mom(bx), mom(by),
+                ptr(bx.running_mean), ptr(bx.running_var), ptr(by.running_mean), ptr(by.running_var), _lib.dtype_code(run_dt),
+                ptr(bx.num_batches_tracked), ptr(by.num_batches_tracked), b.bn_scale.data_ptr(), b.bn_shift.data_ptr(),
+                b.bn_scratch.data_ptr(), b.bn_scratch.numel(), _lib.stream_ptr()))
+            self._bn_cache = None  # the running statistics changed behind torch's version counters
+            return b.bn_scale, b.bn_shift
         if grp is None:
             t = logits.size(0)
             var, mean = torch.var_mean(logits, dim=0, unbiased=False)
@@ -140,14 +161,14 @@ class OmniMoE(nn.Module):
             from ..parallel import synced_batch_statistics
             mean, var, t = synced_batch_statistics(logits, grp[0])
         with torch.no_grad():
-            for bn, sl in ((self.router_norm_x, slice(0, n)), (self.router_norm_y, slice(n, 2 * n))):
-                if bn.track_running_stats:
+            for bn, sl in ((bx, slice(0, n)), (by, slice(n, 2 * n))):
+                if bn.track_running_stats and bn.running_mean is not None:
                     bn.num_batches_tracked += 1
                     mom = bn.momentum if bn.momentum is not None else 1.0 / float(bn.num_batches_tracked)
                     unbiased = var[sl] * (t / max(t - 1, 1))
                     bn.running_mean.mul_(1 - mom).add_(mean[sl].to(bn.running_mean.dtype), alpha=mom)
                     bn.running_var.mul_(1 - mom).add_(unbiased.to(bn.running_var.dtype), alpha=mom)
-        eps = torch.cat([torch.full((n,), self.router_norm_x.eps), torch.full((n,), self.router_norm_y.eps)]).to(var)
+        eps = torch.cat([torch.full((n,), bx.eps), torch.full((n,), by.eps)]).to(var)
         scale = torch.rsqrt(var + eps)
         return scale.contiguous(), (-mean * scale).contiguous()
 
@@ -186,7 +207,7 @@ class OmniMoE(nn.Module):
             b.side.wait_event(b.ev_fork)
             ss = b.side.cuda_stream
             chk(lib.omni_router_gate(x.data_ptr(), kx.data_ptr(), ky.data_ptr(), t, h, n, b.logits.data_ptr(), status, ss))
-            scale, shift = self._bn_fold_train(b.logits) if self.training else self._bn_fold_eval()
+            scale, shift = self._bn_fold_train(b.logits, b) if self.training else self._bn_fold_eval()
             if not routed:
                 chk(lib.omni_router_logits_topk(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
                                                 b.scores.data_ptr(), b.indices.data_ptr(), 0, b.weights.data_ptr(),
@@ -300,8 +321,9 @@ class GraphedOmniMoE:
     fork/join become one graph launch."""
 
     def __init__(self, module: OmniMoE, num_tokens: int, device=None):
-        if module.training:
-            raise RuntimeError("graph capture is for eval mode (training-mode BatchNorm allocates and updates buffers)")
+        if module.training and module._bn_group() is not None:
+            raise RuntimeError("graph capture of a training-mode forward needs local batch statistics "
+                               "(synchronised statistics go through torch.distributed on the host)")
         dev = torch.device(device) if device is not None else module.gate_proj.weight.device
         if module.gate_proj.weight.dtype != torch.bfloat16:
             raise RuntimeError("graph capture needs a bf16 module (module.to(torch.bfloat16)): "
@@ -312,12 +334,19 @@ class GraphedOmniMoE:
         self.buffers = _Buffers(num_tokens, module.hidden_size, module.intermediate_size, module.num_expert_sqrt,
                                 module.num_experts, module.top_k, dev)
         with torch.cuda.device(dev):
-            module._bn_fold_eval()
+            if not module.training:
+                module._bn_fold_eval()
+            # the warm-up launch of a training-mode module would count as a batch: keep the statistics as they were
+            stats = [(buf, buf.clone()) for bn in (module.router_norm_x, module.router_norm_y)
+                     for buf in (bn.running_mean, bn.running_var, bn.num_batches_tracked) if module.training and buf is not None]
             warm = torch.cuda.Stream()
             warm.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(warm):
                 module._launch(self.x, self.y, self.buffers)
             torch.cuda.current_stream().wait_stream(warm)
+            torch.cuda.synchronize()
+            for buf, saved in stats:
+                buf.copy_(saved)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):

@@ -94,3 +94,65 @@ def test_layer_training_mode_batch_statistics():
     torch.testing.assert_close(m.router_norm_x.running_mean, ref.running_mean, rtol=1e-3, atol=1e-4)
     torch.testing.assert_close(m.router_norm_x.running_var, ref.running_var, rtol=1e-3, atol=1e-4)
     assert int(m.router_norm_x.num_batches_tracked) == 1
+
+
+@pytest.mark.parametrize("momentum,dtype,tokens", [(0.1, torch.float32, 300), (None, torch.float32, 129), (0.3, torch.bfloat16, 1000),
+                                                    (0.1, torch.float32, 1)])
+def test_training_mode_batchnorm_kernel_matches_torch(momentum, dtype, tokens):
+    """Three training-mode forwards: running statistics and batch counter follow nn.BatchNorm1d, and the
+    selection uses the batch statistics (same routing as the oracle fed with the batch-normalised logits)."""
+    from omni_moe.modules.omni_moe import OmniMoE, OmniMoEConfig
+    torch.manual_seed(2)
+    n = 16
+    m = OmniMoE(OmniMoEConfig(128, 256, "silu", n * n, 4))
+    for bn in (m.router_norm_x, m.router_norm_y):
+        bn.momentum = momentum
+    m = m.to(dtype).cuda().train()
+    refs = [torch.nn.BatchNorm1d(n, affine=False, momentum=momentum).cuda() for _ in range(2)]
+    with torch.no_grad():
+        for step in range(3):
+            x = torch.randn(1, tokens, 128, generator=torch.Generator().manual_seed(step)).to(dtype).cuda()
+            m(x)
+            m.check_status()
+            xb = x.view(-1, 128).bfloat16().float()
+            for ref, gate in zip(refs, (m.router_gate_x, m.router_gate_y)):
+                z = xb @ gate.weight.bfloat16().float().t()
+                if tokens > 1:
+                    ref(z)
+    if tokens > 1:
+        tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-3, atol=1e-4)
+        for bn, ref in zip((m.router_norm_x, m.router_norm_y), refs):
+            torch.testing.assert_close(bn.running_mean.float(), ref.running_mean, **tol)
+            torch.testing.assert_close(bn.running_var.float(), ref.running_var, **tol)
+            assert int(bn.num_batches_tracked) == 3 and bn.running_mean.dtype == dtype
+    else:
+        assert int(m.router_norm_x.num_batches_tracked) == 3 and bool(torch.isfinite(m.router_norm_x.running_var).all())
+    # eval after training uses the updated running statistics (no stale fold)
+    m.eval()
+    with torch.no_grad():
+        x = torch.randn(1, 64, 128, generator=torch.Generator().manual_seed(9)).to(dtype).cuda()
+        y = m(x)
+    mean = torch.cat([m.router_norm_x.running_mean, m.router_norm_y.running_mean]).float()
+    scale, shift = m._bn_fold_eval()
+    torch.testing.assert_close(shift, -mean * scale, rtol=1e-5, atol=1e-6)
+    assert bool(torch.isfinite(y.float()).all())
+
+
+def test_training_mode_forward_in_a_cuda_graph():
+    from omni_moe.modules.omni_moe import OmniMoE, OmniMoEConfig
+    torch.manual_seed(3)
+    m = OmniMoE(OmniMoEConfig(256, 512, "silu", 1024, 8)).to(torch.bfloat16).cuda().train()
+    x = torch.randn(1, 512, 256).bfloat16().cuda()
+    g = m.graphed(512)
+    assert int(m.router_norm_x.num_batches_tracked) == 0, "building the graph must not count as a batch"
+    with torch.no_grad():
+        y_graph = g(x).clone()
+        mean_after_graph = m.router_norm_x.running_mean.clone()
+        assert int(m.router_norm_x.num_batches_tracked) == 1
+        # the same step eagerly on a fresh copy of the statistics
+        m.router_norm_x.reset_running_stats()
+        m.router_norm_y.reset_running_stats()
+        y_eager = m(x)
+    torch.cuda.synchronize()
+    assert torch.equal(y_graph.view(-1), y_eager.view(-1))
+    assert torch.equal(mean_after_graph, m.router_norm_x.running_mean)

@@ -101,3 +101,58 @@ def test_gate_up_with_router_tiles(t, h, i, n):
     assert_close(act, F.silu(xf @ wg.float().t()) * (xf @ wu.float().t()), what="activation")
     ez = torch.cat([orc.router_logits(x, kx), orc.router_logits(x, ky)], 1)
     assert_close(logits, ez, rtol=1e-4, atol=1e-4, what="router logits")
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 200, 72), (1, 8, 8), (33, 1032, 136), (4096, 1024, 1024), (513, 24, 1032)])
+def test_tma_store_epilogue_equals_direct_stores(m, n, k):
+    """The pair kernels' output leaves either through shared memory + TMA stores or through direct
+    256-bit / 128-bit / scalar stores; both must write the same bits, including clipped edge tiles and an
+    output that is a column slice of a wider matrix."""
+    from omni_moe_b200 import _lib
+    from omni_moe_b200.ops.autograd import gemm_nt
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=g) * 0.5).bfloat16().cuda()
+    b = (torch.randn(n, k, generator=g) / k ** 0.5).bfloat16().cuda()
+    outs = []
+    try:
+        for mode in (1, 0):
+            lib.omni_debug_gemm_tma_store(mode)
+            wide = torch.full((m, 2 * n + 16), 3.0, dtype=torch.bfloat16, device="cuda")
+            dense = gemm_nt(a, b)
+            gemm_nt(a, b, out=wide[:, 8:8 + n])
+            torch.cuda.synchronize()
+            assert bool((wide[:, :8] == 3).all()) and bool((wide[:, 8 + n:] == 3).all()), "wrote outside the slice"
+            assert torch.equal(wide[:, 8:8 + n], dense)
+            outs.append(dense)
+    finally:
+        lib.omni_debug_gemm_tma_store(-1)
+    assert torch.equal(outs[0], outs[1])
+    ref = a.float() @ b.float().t()
+    assert float((outs[0].float() - ref).abs().max()) <= 2e-2 * float(ref.abs().max()) + 1e-3
+
+
+def test_tma_store_swiglu_and_saved_preactivations():
+    from omni_moe_b200 import _lib
+    from omni_moe_b200.ops import mlp_forward
+    lib = _lib.load()
+    t, h, i = 777, 264, 1096
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(t, h, generator=g).bfloat16().cuda()
+    wg = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16().cuda()
+    wu = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16().cuda()
+    wd = (torch.randn(h, i, generator=g) / i ** 0.5).bfloat16().cuda()
+    res = torch.randn(t, h, generator=g).cuda()
+    got = []
+    try:
+        for mode in (1, 0):
+            lib.omni_debug_gemm_tma_store(mode)
+            gu = torch.empty(t, 2 * i, dtype=torch.bfloat16, device="cuda")
+            act = torch.empty(t, i, dtype=torch.bfloat16, device="cuda")
+            y = mlp_forward(x, wg, wu, wd, residual=res, act=act, gate_up=gu)
+            torch.cuda.synchronize()
+            got.append((y, act, gu))
+    finally:
+        lib.omni_debug_gemm_tma_store(-1)
+    for a_, b_ in zip(got[0], got[1]):
+        assert torch.equal(a_, b_)
