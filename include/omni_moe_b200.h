@@ -371,6 +371,26 @@ OMNI_API int omni_router_bn_train(const float *logits, int64_t ld_logits, int64_
                          int64_t *num_batches_tracked_y, float *bn_scale, float *bn_shift,
                          void *scratch, size_t scratch_bytes, void *stream);
 
+/*
+ * Backward of the router front as one call: from the gradient of the selected scores back to the
+ * gradient of the gate logits, through the gather, the per-axis log-softmax and the BatchNorm
+ * (torch autograd does this in the reference through F.log_softmax and nn.BatchNorm1d,
+ * omni_moe/modules/omni_moe.py:70-86, and OmniRouterFunc.backward, omni_router.py:235-305).
+ *   dscores [T, k] float32, indices [T, k] int32 (as selected in the forward)
+ *   log_probs [T, 2*sqrt_n] float32 (the forward's log_probs_out), logits [T, ld_logits] float32
+ *   bn_scale / bn_shift [2*sqrt_n]: the fold the forward used (batch statistics in training)
+ *   training != 0: the statistics were batch statistics, so the gradient also flows through them
+ *   dlogits [T, 2*sqrt_n] bf16 (the operand of the two gate-weight GEMMs that follow)
+ *   scratch: omni_router_norm_bwd_scratch_bytes(T, sqrt_n) bytes (training only)
+ * Limit: sqrt_n <= 256.  No atomics: the sums are reproducible.
+ */
+OMNI_API size_t omni_router_norm_bwd_scratch_bytes(int64_t num_tokens, int sqrt_n);
+OMNI_API int omni_router_norm_bwd(const float *dscores, const int32_t *indices, const float *log_probs,
+                         const float *logits, int64_t ld_logits, const float *bn_scale,
+                         const float *bn_shift, int64_t num_tokens, int sqrt_n, int k, int training,
+                         void *dlogits, void *scratch, size_t scratch_bytes, int32_t *status,
+                         void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -617,3 +617,186 @@ extern "C" int omni_expert_bwd_rows(const void* x, const void* dy, const float* 
   }
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Backward of the router front: logits z [T, 2n] -> BatchNorm (batch or running statistics, folded into
+// scale / shift) -> log-softmax per axis -> scores[t,j] = lp[t, ix] + lp[t, n + iy].
+//   g       = scatter of dscores into the 2n log-prob columns          (as in router_bwd_kernel)
+//   dzhat   = g - exp(lp) * sum_axis(g)                                 (log-softmax backward, per axis)
+//   eval:     dz = scale * dzhat
+//   training: dz = scale * (dzhat - mean_t(dzhat) - zhat * mean_t(dzhat * zhat)),  zhat = z * scale + shift
+// router_norm_bwd_kernel does everything per token and, in training, leaves dzhat in fp32 plus per-block
+// column sums of dzhat and dzhat * zhat; router_norm_bwd_sums_kernel adds the block sums in block order;
+// router_norm_bwd_apply_kernel forms dz.  No atomics.  Rows of at most 512 columns (n <= 256).
+// ------------------------------------------------------------------------------------------------
+namespace omni {
+namespace {
+constexpr int kNormTokensPerWarp = 8;
+constexpr int kNormMaxCols = 512;
+
+template <int VPL>
+__global__ void __launch_bounds__(kThreads) router_norm_bwd_kernel(
+    const float* __restrict__ dscores, const int32_t* __restrict__ indices, const float* __restrict__ lp,
+    const float* __restrict__ logits, int64_t ld_logits, const float* __restrict__ scale, const float* __restrict__ shift,
+    int64_t T, int n, int k, int training, float* __restrict__ dzhat, __nv_bfloat16* __restrict__ dz,
+    float* __restrict__ partial /*[blocks, 2, 2n]*/, int* __restrict__ status) {
+  __shared__ float s_g[kWarps][kNormMaxCols];
+  __shared__ float s_red[kWarps][2][kNormMaxCols];
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const int C = 2 * n;
+  float* g = s_g[warp];
+  float s1[VPL], s2[VPL], sc[VPL], sh[VPL];
+#pragma unroll
+  for (int e = 0; e < VPL; ++e) {
+    const int c = lane + 32 * e;
+    s1[e] = 0.f, s2[e] = 0.f;
+    sc[e] = c < C ? scale[c] : 0.f;
+    sh[e] = c < C ? shift[c] : 0.f;
+  }
+  bool bad = false;
+  const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kNormTokensPerWarp;
+  for (int i = 0; i < kNormTokensPerWarp; ++i) {
+    const int64_t t = t0 + i;
+    if (t >= T) break;  // warp-uniform
+    for (int c = lane; c < C; c += 32) g[c] = 0.f;
+    __syncwarp();
+    for (int j0 = 0; j0 < k; j0 += 32) {
+      const int j = j0 + lane;
+      int e_ = -1;
+      float d = 0.f;
+      if (j < k) {
+        e_ = indices[t * k + j];
+        d = dscores[t * k + j];
+        if (e_ < 0 || e_ >= n * n) bad = true, e_ = -1;
+      }
+      const int ix = e_ < 0 ? -1 : e_ / n;
+      const int iy = e_ < 0 ? -1 : n + (e_ - ix * n);
+      const int cnt = min(32, k - j0);
+      for (int q = 0; q < cnt; ++q) {
+        const int bx = __shfl_sync(FULL_MASK, ix, q), by = __shfl_sync(FULL_MASK, iy, q);
+        const float bd = __shfl_sync(FULL_MASK, d, q);
+        if (bx >= 0) {
+          if ((bx & 31) == lane) g[bx] += bd;
+          if ((by & 31) == lane) g[by] += bd;
+        }
+      }
+    }
+    __syncwarp();
+    float gv[VPL];
+    float sum_x = 0.f, sum_y = 0.f;
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) {
+      const int c = lane + 32 * e;
+      gv[e] = c < C ? g[c] : 0.f;
+      if (c < n) sum_x += gv[e];
+      else sum_y += gv[e];
+    }
+    sum_x = warp_sum(sum_x);
+    sum_y = warp_sum(sum_y);
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) {
+      const int c = lane + 32 * e;
+      if (c < C) {
+        const float p = __expf(lp[t * C + c]);
+        const float dh = gv[e] - p * (c < n ? sum_x : sum_y);
+        if (training) {
+          const float zh = __fmaf_rn(logits[t * ld_logits + c], sc[e], sh[e]);
+          dzhat[t * C + c] = dh;
+          s1[e] += dh;
+          s2[e] = __fmaf_rn(dh, zh, s2[e]);
+        } else {
+          dz[t * C + c] = __float2bfloat16_rn(sc[e] * dh);
+        }
+      }
+    }
+    __syncwarp();
+  }
+  if (training) {
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) {
+      const int c = lane + 32 * e;
+      if (c < C) s_red[warp][0][c] = s1[e], s_red[warp][1][c] = s2[e];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 2 * C; idx += blockDim.x) {
+      const int which = idx / C, c = idx - which * C;
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) sum += s_red[w][which][c];
+      partial[(static_cast<int64_t>(blockIdx.x) * 2 + which) * C + c] = sum;
+    }
+  }
+  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
+__global__ void __launch_bounds__(256) router_norm_bwd_sums_kernel(const float* __restrict__ partial, int blocks, int C, int64_t T,
+                                                                   float* __restrict__ means /*[2, C]*/) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= 2 * C) return;
+  const int which = idx / C, c = idx - which * C;
+  float sum = 0.f;
+  for (int b = 0; b < blocks; ++b) sum += partial[(static_cast<int64_t>(b) * 2 + which) * C + c];
+  means[idx] = sum / static_cast<float>(T);
+}
+
+__global__ void __launch_bounds__(256) router_norm_bwd_apply_kernel(const float* __restrict__ dzhat, const float* __restrict__ logits,
+                                                                    int64_t ld_logits, const float* __restrict__ scale,
+                                                                    const float* __restrict__ shift, const float* __restrict__ means,
+                                                                    int64_t T, int C, __nv_bfloat16* __restrict__ dz) {
+  const int64_t total = T * C;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / C;
+    const int c = static_cast<int>(i - t * C);
+    const float zh = __fmaf_rn(logits[t * ld_logits + c], scale[c], shift[c]);
+    dz[i] = __float2bfloat16_rn(scale[c] * (dzhat[i] - means[c] - zh * means[C + c]));
+  }
+}
+}  // namespace
+}  // namespace omni
+
+extern "C" size_t omni_router_norm_bwd_scratch_bytes(int64_t num_tokens, int sqrt_n) {
+  if (num_tokens <= 0 || sqrt_n <= 0) return 0;
+  const int64_t blocks = ceil_div64(num_tokens, kWarps * kNormTokensPerWarp);
+  const size_t C = 2 * static_cast<size_t>(sqrt_n);
+  // dzhat [T, C] + block sums [blocks, 2, C] + means [2, C]
+  return (static_cast<size_t>(num_tokens) * C + static_cast<size_t>(blocks) * 2 * C + 2 * C) * sizeof(float);
+}
+
+extern "C" int omni_router_norm_bwd(const float* dscores, const int32_t* indices, const float* log_probs, const float* logits,
+                                    int64_t ld_logits, const float* bn_scale, const float* bn_shift, int64_t num_tokens, int sqrt_n,
+                                    int k, int training, void* dlogits, void* scratch, size_t scratch_bytes, int32_t* status,
+                                    void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 0, "bad sizes");
+  OMNI_REQUIRE(sqrt_n >= 1 && 2 * sqrt_n <= kNormMaxCols, "omni_router_norm_bwd handles sqrt_n <= %d, got %d", kNormMaxCols / 2, sqrt_n);
+  OMNI_REQUIRE(ld_logits >= 2 * sqrt_n, "ld_logits %lld < 2*sqrt_n", static_cast<long long>(ld_logits));
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(log_probs && logits && bn_scale && bn_shift && dlogits && status && (k == 0 || (dscores && indices)), "NULL argument");
+  OMNI_REQUIRE(!training || (scratch && scratch_bytes >= omni_router_norm_bwd_scratch_bytes(num_tokens, sqrt_n)),
+               "scratch too small: need %zu bytes", omni_router_norm_bwd_scratch_bytes(num_tokens, sqrt_n));
+  const int C = 2 * sqrt_n;
+  const int64_t blocks = ceil_div64(num_tokens, kWarps * kNormTokensPerWarp);
+  OMNI_REQUIRE(blocks < (int64_t(1) << 31), "too many tokens");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* dzhat = training ? static_cast<float*>(scratch) : nullptr;
+  float* partial = training ? dzhat + num_tokens * C : nullptr;
+  float* means = training ? partial + blocks * 2 * C : nullptr;
+  __nv_bfloat16* dz = static_cast<__nv_bfloat16*>(dlogits);
+  if (C <= 128)
+    router_norm_bwd_kernel<4><<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(dscores, indices, log_probs, logits, ld_logits, bn_scale,
+                                                                              bn_shift, num_tokens, sqrt_n, k, training, dzhat, dz,
+                                                                              partial, status);
+  else
+    router_norm_bwd_kernel<16><<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(dscores, indices, log_probs, logits, ld_logits,
+                                                                               bn_scale, bn_shift, num_tokens, sqrt_n, k, training,
+                                                                               dzhat, dz, partial, status);
+  if (int e = check_launch("router_norm_bwd_kernel")) return e;
+  if (!training) return 0;
+  router_norm_bwd_sums_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(partial, static_cast<int>(blocks), C, num_tokens, means);
+  if (int e = check_launch("router_norm_bwd_sums_kernel")) return e;
+  const int64_t total = num_tokens * C;
+  const int64_t want = ceil_div64(total, 256);
+  router_norm_bwd_apply_kernel<<<static_cast<unsigned>(want < 148 * 8 ? want : 148 * 8), 256, 0, st>>>(
+      dzhat, logits, ld_logits, bn_scale, bn_shift, means, num_tokens, C, dz);
+  return check_launch("router_norm_bwd_apply_kernel");
+}

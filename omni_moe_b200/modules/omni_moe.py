@@ -264,20 +264,50 @@ class OmniMoE(nn.Module):
             return False
         return hidden_states.requires_grad or (self.training and any(p.requires_grad for p in self.parameters()))
 
+    def _fused_router_front_ok(self) -> bool:
+        """The one-op router front (ops.autograd.RouterFrontFunction) covers plain BatchNorm1d layers with
+        local statistics, sqrt(N) <= 256 and an even top-k in the reference's range."""
+        from ..ops.autograd import ROUTER_FRONT_MAX_SQRT_N
+        bx, by = self.router_norm_x, self.router_norm_y
+        plain = type(bx) is nn.BatchNorm1d and type(by) is nn.BatchNorm1d and bx.track_running_stats and by.track_running_stats
+        return (plain and self._bn_group() is None and self.num_expert_sqrt <= ROUTER_FRONT_MAX_SQRT_N
+                and 0 < self.top_k <= 128 and self.hidden_size % 8 == 0)
+
     def _forward_autograd(self, hidden_states: torch.Tensor) -> torch.Tensor:
-        """Differentiable forward, composed like the reference module (omni_moe/modules/omni_moe.py:60-106):
-        router gates, BatchNorm and log-softmax are torch modules / functions (as they are in the
-        reference), the three operators run the kernels of this library and carry their own backward."""
+        """Differentiable forward, composed like the reference module (omni_moe/modules/omni_moe.py:60-106) from
+        operators that run the kernels of this library and carry their own backward.  The router front
+        (gates, BatchNorm, log-softmax, selection) is one such operator where its limits allow, otherwise
+        torch modules / functions followed by the router op, as in the reference."""
         from ..ops import omni_expert_func, omni_mlp_func, omni_router_func
         bsz, seq_len, _ = hidden_states.shape
         x = hidden_states.reshape(-1, self.hidden_size)
-        logits_x = self.router_norm_x(self.router_gate_x(x))
-        logits_y = self.router_norm_y(self.router_gate_y(x))
-        # log-probabilities, scores and routing weights stay in fp32 (the reference keeps the module dtype):
-        # bf16 log-probs tie massively, and ties are what makes a selection irreproducible
-        log_probs_x = torch.nn.functional.log_softmax(logits_x, dim=-1, dtype=torch.float32)
-        log_probs_y = torch.nn.functional.log_softmax(logits_y, dim=-1, dtype=torch.float32)
-        scores, indices = omni_router_func(log_probs_x, log_probs_y, self.num_expert_sqrt, self.top_k)
+        if self._fused_router_front_ok():
+            # gate GEMMs (fp32 logits), BatchNorm fold, log-softmax and selection by the kernels of the fused
+            # path; the backward goes from dscores to dlogits in one call
+            import types
+            from ..ops.autograd import RouterFrontFunction
+            n = self.num_expert_sqrt
+            if self.training:
+                def fold(logits):
+                    dev = logits.device
+                    tmp = types.SimpleNamespace(
+                        bn_scale=torch.empty(2 * n, device=dev, dtype=torch.float32),
+                        bn_shift=torch.empty(2 * n, device=dev, dtype=torch.float32),
+                        bn_scratch=torch.empty(max(int(_lib.load().omni_router_bn_train_scratch_bytes(max(logits.size(0), 1), n)), 16),
+                                               device=dev, dtype=torch.uint8))
+                    return self._bn_fold_train(logits, tmp)
+            else:
+                fold = lambda logits: self._bn_fold_eval()
+            scores, indices = RouterFrontFunction.apply(x, self.router_gate_x.weight, self.router_gate_y.weight, self.top_k,
+                                                        fold, self.training)
+        else:
+            logits_x = self.router_norm_x(self.router_gate_x(x))
+            logits_y = self.router_norm_y(self.router_gate_y(x))
+            # log-probabilities, scores and routing weights stay in fp32 (the reference keeps the module dtype):
+            # bf16 log-probs tie massively, and ties are what makes a selection irreproducible
+            log_probs_x = torch.nn.functional.log_softmax(logits_x, dim=-1, dtype=torch.float32)
+            log_probs_y = torch.nn.functional.log_softmax(logits_y, dim=-1, dtype=torch.float32)
+            scores, indices = omni_router_func(log_probs_x, log_probs_y, self.num_expert_sqrt, self.top_k)
         routing_weights = torch.exp(scores)
         experts_states = omni_expert_func(x, self.up_embed.weight, self.down_embed.weight, routing_weights, indices)
         shared = omni_mlp_func(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)

@@ -282,3 +282,75 @@ class MlpFunction(torch.autograd.Function):
         dx, d_wg, d_wu, d_wd = mlp_backward(as_bf16(dy), xb, wg, wu, wd, need_weight_grads=need_w, gate_up=gu)
         cast = lambda g, j: g.to(ctx.dtypes[j]) if (g is not None and ctx.needs_input_grad[j]) else None
         return cast(dx, 0), cast(d_wg, 1), cast(d_wu, 2), cast(d_wd, 3)
+
+
+# ------------------------------------------------------------------------------------------------
+# router front: gate GEMMs -> BatchNorm -> log-softmax -> product-key top-k, as one differentiable op
+# ------------------------------------------------------------------------------------------------
+ROUTER_FRONT_MAX_SQRT_N = 256
+
+
+class RouterFrontFunction(torch.autograd.Function):
+    """``scores, indices = topk(log_softmax(BN(x Kx^T)) (+) log_softmax(BN(x Ky^T)))`` with the forward
+    kernels of the fused inference path (tcgen05 gate GEMM with fp32 logits, fused BatchNorm fold /
+    log-softmax / selection) and a backward that goes from ``dscores`` to ``dlogits`` in one call
+    (``omni_router_norm_bwd``); the two small gate-weight products that remain are torch matmuls.
+
+    ``fold`` is a callable ``logits -> (scale, shift)`` supplied by the module: the eval-mode fold of the
+    running statistics, or the training-mode kernel that also updates them.
+    """
+
+    @staticmethod
+    def forward(ctx, x, gate_x, gate_y, k, fold, training):
+        xb, kx, ky = as_bf16(x), as_bf16(gate_x), as_bf16(gate_y)
+        t, h = xb.shape
+        n = kx.size(0)
+        dev = xb.device
+        lib = _lib.load()
+        status = _status(dev)
+        f32 = dict(device=dev, dtype=torch.float32)
+        logits = torch.empty((t, 2 * n), **f32)
+        lp = torch.empty((t, 2 * n), **f32)
+        scores = torch.empty((t, k), **f32)
+        indices = torch.empty((t, k), device=dev, dtype=torch.int32)
+        with torch.cuda.device(dev):
+            st = _lib.stream_ptr()
+            if t > 0:
+                _lib.check(lib.omni_router_gate(xb.data_ptr(), kx.data_ptr(), ky.data_ptr(), t, h, n, logits.data_ptr(),
+                                                status.data_ptr(), st))
+            scale, shift = fold(logits)
+            if t > 0 and k > 0:
+                _lib.check(lib.omni_router_logits_topk(logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), t, n, k,
+                                                       scores.data_ptr(), indices.data_ptr(), 0, None, lp.data_ptr(), st))
+        ctx.save_for_backward(xb, kx, ky, logits, lp, scale.clone(), shift.clone(), indices)
+        ctx.training = bool(training)
+        ctx.dtypes = (x.dtype, gate_x.dtype, gate_y.dtype)
+        ctx.mark_non_differentiable(indices)
+        return scores, indices
+
+    @staticmethod
+    def backward(ctx, dscores, _dindices):
+        xb, kx, ky, logits, lp, scale, shift, indices = ctx.saved_tensors
+        t, k = indices.shape
+        n = kx.size(0)
+        dev = xb.device
+        lib = _lib.load()
+        status = _status(dev)
+        dz = torch.empty((t, 2 * n), device=dev, dtype=torch.bfloat16)
+        ds = dscores.detach().float().contiguous()
+        scratch = None
+        if ctx.training:
+            scratch = torch.empty(int(lib.omni_router_norm_bwd_scratch_bytes(t, n)), device=dev, dtype=torch.uint8)
+        if t > 0:
+            with torch.cuda.device(dev):
+                _lib.check(lib.omni_router_norm_bwd(ds.data_ptr(), indices.data_ptr(), lp.data_ptr(), logits.data_ptr(), 2 * n,
+                                                    scale.data_ptr(), shift.data_ptr(), t, n, k, int(ctx.training), dz.data_ptr(),
+                                                    _lib.ptr(scratch), scratch.numel() if scratch is not None else 0,
+                                                    status.data_ptr(), _lib.stream_ptr()))
+        dx = dkx = dky = None
+        if ctx.needs_input_grad[0]:
+            dx = (dz @ torch.cat([kx, ky], dim=0)).to(ctx.dtypes[0])
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            dk = dz.t() @ xb
+            dkx, dky = dk[:n].to(ctx.dtypes[1]), dk[n:].to(ctx.dtypes[2])
+        return dx, dkx, dky, None, None, None
