@@ -118,8 +118,9 @@ xs = shard_tokens(x, rank, world).cuda().view(1, 96, 256)
 with torch.no_grad():
     y = dp(xs)
 for a, b in ((dp.router_norm_x, whole.router_norm_x), (dp.router_norm_y, whole.router_norm_y)):
-    assert torch.allclose(a.running_mean, b.running_mean, atol=1e-5), (a.running_mean - b.running_mean).abs().max()
-    assert torch.allclose(a.running_var, b.running_var, rtol=1e-4, atol=1e-6), (a.running_var - b.running_var).abs().max()
+    # bf16 buffers: the two paths (merged per-rank moments / one-GPU kernel) may round the last bit differently
+    assert torch.allclose(a.running_mean.float(), b.running_mean.float(), atol=2e-4), (a.running_mean - b.running_mean).abs().max()
+    assert torch.allclose(a.running_var.float(), b.running_var.float(), rtol=1e-2, atol=1e-4), (a.running_var - b.running_var).abs().max()
 sl = slice(rank * 96, (rank + 1) * 96)
 same = (dp.last_routing[1] == whole.last_routing[1][sl]).all(dim=1)
 assert same.float().mean() > 0.97, float(same.float().mean())
