@@ -135,3 +135,34 @@ def check_status(status: torch.Tensor) -> None:
     word = int(status.item())
     if word:
         raise RuntimeError("omni_moe_b200 kernel status: " + status_message(word))
+
+
+_DEVICE_STATUS: dict = {}
+
+
+def device_status(device) -> torch.Tensor:
+    """The int32 status word of ``device`` that the operator wrappers hand to every kernel they launch when the
+    caller passes none: kernels OR fault bits into it (bad expert index, a bounded wait that ran out) and
+    never clear it, so one word per device collects everything since the last :func:`check_device_status`.
+    Allocated once per device (no fill kernel per call)."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _DEVICE_STATUS.get(key)
+    if st is None:
+        st = torch.zeros(1, device=torch.device("cuda", key), dtype=torch.int32)
+        _DEVICE_STATUS[key] = st
+    return st
+
+
+def check_device_status(device=None) -> None:
+    """Synchronises and raises if any kernel launched through the operator wrappers on ``device`` (default:
+    every device used so far) reported a fault; the word is cleared afterwards."""
+    keys = list(_DEVICE_STATUS) if device is None else [torch.device(device).index or 0]
+    for key in keys:
+        st = _DEVICE_STATUS.get(key)
+        if st is None:
+            continue
+        word = int(st.item())
+        if word:
+            st.zero_()
+            raise RuntimeError("omni_moe_b200 kernel status: " + status_message(word))

@@ -343,6 +343,7 @@ class OmniMoE(nn.Module):
         st = getattr(self, "last_status", None)
         if st is not None:
             _lib.check_status(st)
+        _lib.check_device_status()   # the operators of the differentiable forward / backward report here
 
 
 class GraphedOmniMoE:

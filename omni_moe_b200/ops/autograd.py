@@ -16,7 +16,9 @@ from .scheduler import schedule
 
 
 def _status(dev) -> torch.Tensor:
-    return torch.zeros(1, device=dev, dtype=torch.int32)
+    """The per-device status word (see _lib.device_status): faults of the backward kernels surface in
+    _lib.check_device_status() / OmniMoE.check_status()."""
+    return _lib.device_status(dev)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -91,7 +91,7 @@ def expert_forward(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.
     k = indices.size(1)
     dev = x.device
     if status is None:
-        status = torch.zeros(1, device=dev, dtype=torch.int32)
+        status = _lib.device_status(dev)  # shared per-device word: see _lib.check_device_status
     y = torch.empty((t, h), device=dev, dtype=out_dtype)
     if residual is not None:
         assert residual.shape == y.shape and residual.dtype == out_dtype and residual.is_contiguous()

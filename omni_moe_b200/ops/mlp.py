@@ -25,7 +25,7 @@ def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Ten
     assert gate_weight.shape == up_weight.shape == (i, h) and down_weight.shape == (h, i)
     dev = x.device
     if status is None:
-        status = torch.zeros(1, device=dev, dtype=torch.int32)
+        status = _lib.device_status(dev)  # shared per-device word: see _lib.check_device_status
     if act is None:
         act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
     if residual is not None:

@@ -63,7 +63,7 @@ def router_gate_topk(x: torch.Tensor, gate_x: torch.Tensor, gate_y: torch.Tensor
     n = gate_x.size(0)
     dev = x.device
     if status is None:
-        status = torch.zeros(1, device=dev, dtype=torch.int32)
+        status = _lib.device_status(dev)  # shared per-device word: see _lib.check_device_status
     if logits is None:
         logits = torch.empty((t, 2 * n), device=dev, dtype=torch.float32)
     scores = torch.empty((t, k), device=dev, dtype=torch.float32)

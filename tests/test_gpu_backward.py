@@ -275,3 +275,18 @@ def test_layer_trains_in_other_dtypes(dtype):
         if not name.startswith("router_gate"):   # the gates see the unrounded fp32 / fp16 x through nn.Linear
             _scaled_close(prm.grad, eg[name], name, rtol=5e-2, atol_frac=4e-2)
     assert cx.grad.dtype == dtype
+
+
+def test_backward_faults_surface_through_the_device_status():
+    """An out-of-range expert index in the backward is skipped by the kernels and reported (no trap):
+    the shared per-device status word collects it and check_device_status() raises once."""
+    from omni_moe_b200 import _lib
+    from omni_moe_b200.ops.autograd import expert_backward
+    _lib.check_device_status()        # start clean
+    x, up, dn, w, idx, dy = _expert_inputs(16, 64, 32, 4, 5)
+    idx[2, 1] = 999
+    dx, d_up, d_dn, dg, _ = expert_backward(dy.cuda(), x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), grad_dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="expert index"):
+        _lib.check_device_status()
+    _lib.check_device_status()        # cleared by the report
+    assert bool(torch.isfinite(dx).all()) and float(dg[2, 1]) == 0.0
