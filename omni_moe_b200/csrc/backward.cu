@@ -631,7 +631,7 @@ extern "C" int omni_expert_bwd_rows(const void* x, const void* dy, const float* 
 // ------------------------------------------------------------------------------------------------
 namespace omni {
 namespace {
-constexpr int kNormTokensPerWarp = 8;
+constexpr int kNormTokensPerWarp = 2;
 constexpr int kNormMaxCols = 512;
 
 template <int VPL>
@@ -729,14 +729,27 @@ __global__ void __launch_bounds__(kThreads) router_norm_bwd_kernel(
   if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
 }
 
+// One block per 32 of the 2C column sums: thread (slice, column) adds the block partials b = slice, slice + 8, ...
+// and the eight slice sums are added in slice order: same result every run, 8 x shorter loops.
 __global__ void __launch_bounds__(256) router_norm_bwd_sums_kernel(const float* __restrict__ partial, int blocks, int C, int64_t T,
                                                                    float* __restrict__ means /*[2, C]*/) {
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= 2 * C) return;
-  const int which = idx / C, c = idx - which * C;
+  __shared__ float s_part[8][32];
+  const int col = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int idx = blockIdx.x * 32 + col;
   float sum = 0.f;
-  for (int b = 0; b < blocks; ++b) sum += partial[(static_cast<int64_t>(b) * 2 + which) * C + c];
-  means[idx] = sum / static_cast<float>(T);
+  if (idx < 2 * C) {
+    const int which = idx / C, c = idx - which * C;
+#pragma unroll 4
+    for (int b = slice; b < blocks; b += 8) sum += partial[(static_cast<int64_t>(b) * 2 + which) * C + c];
+  }
+  s_part[slice][col] = sum;
+  __syncthreads();
+  if (slice == 0 && idx < 2 * C) {
+    float tot = 0.f;
+#pragma unroll
+    for (int s_ = 0; s_ < 8; ++s_) tot += s_part[s_][col];
+    means[idx] = tot / static_cast<float>(T);
+  }
 }
 
 __global__ void __launch_bounds__(256) router_norm_bwd_apply_kernel(const float* __restrict__ dzhat, const float* __restrict__ logits,
@@ -792,7 +805,7 @@ extern "C" int omni_router_norm_bwd(const float* dscores, const int32_t* indices
                                                                                dzhat, dz, partial, status);
   if (int e = check_launch("router_norm_bwd_kernel")) return e;
   if (!training) return 0;
-  router_norm_bwd_sums_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(partial, static_cast<int>(blocks), C, num_tokens, means);
+  router_norm_bwd_sums_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(partial, static_cast<int>(blocks), C, num_tokens, means);
   if (int e = check_launch("router_norm_bwd_sums_kernel")) return e;
   const int64_t total = num_tokens * C;
   const int64_t want = ceil_div64(total, 256);

@@ -154,18 +154,25 @@ extern "C" int omni_swiglu_bwd(const void* gate_up, const void* dact, int64_t nu
 // all T tokens): column mean and biased variance of logits [T, C] (C = 2 * sqrt_n, both axes), folded
 // into the per-column scale / shift the selection kernels take, plus the update of the running
 // statistics.  Two launches, no atomics:
-//   bn_partial_kernel   block b owns rows [b * kBnRows, ...): per column its count, mean and sum of
-//                       squared deviations (two sweeps over the block's rows, so nothing cancels)
-//   bn_finalize_kernel  one thread per column merges the block partials in block order (the pairwise
-//                       update for combining means and variances), writes scale = rsqrt(var + eps),
+//   bn_partial_kernel   block b owns rows [b * kBnRows, ...): per column its mean and sum of squared
+//                       deviations (two sweeps over the block's rows, so nothing cancels); it also
+//                       counts the batch in num_batches_tracked
+//   bn_finalize_kernel  one thread per column combines the block partials in block order (weighted mean of
+//                       the means, squared deviations re-centred on it), writes scale = rsqrt(var + eps),
 //                       shift = -mean * scale, and updates running_mean / running_var (momentum, unbiased
 //                       variance) and num_batches_tracked exactly as nn.BatchNorm1d does in training.
 namespace omni {
 namespace {
-constexpr int kBnRows = 128;
+constexpr int kBnRows = 32;
 
 __global__ void __launch_bounds__(256) bn_partial_kernel(const float* __restrict__ z, int64_t T, int C, int64_t ld,
-                                                         float* __restrict__ partial /*[blocks, 2, C]*/) {
+                                                         float* __restrict__ partial /*[blocks, 2, C]*/, long long* nbt_x,
+                                                         long long* nbt_y) {
+  // this batch counts: the finalize kernel, launched after this one, reads the incremented counters
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (nbt_x) *nbt_x += 1;
+    if (nbt_y) *nbt_y += 1;
+  }
   const int64_t r0 = static_cast<int64_t>(blockIdx.x) * kBnRows;
   const int rows = (T - r0 < kBnRows) ? static_cast<int>(T - r0) : kBnRows;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
@@ -187,20 +194,42 @@ __global__ void __launch_bounds__(256) bn_finalize_kernel(const float* __restric
                                                           float* __restrict__ scale, float* __restrict__ shift,
                                                           void* run_mean_x, void* run_var_x, void* run_mean_y, void* run_var_y,
                                                           int run_dtype, long long* nbt_x, long long* nbt_y) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float n = 0.f, mean = 0.f, m2 = 0.f;
-  for (int b = 0; b < blocks; ++b) {
-    const int64_t left = T - static_cast<int64_t>(b) * kBnRows;
-    const float nb = static_cast<float>(left < kBnRows ? left : kBnRows);
-    const float mb = partial[(static_cast<int64_t>(b) * 2 + 0) * C + c];
-    const float qb = partial[(static_cast<int64_t>(b) * 2 + 1) * C + c];
-    const float tot = n + nb;
-    const float delta = mb - mean;
-    mean += delta * (nb / tot);
-    m2 += qb + delta * delta * (n * nb / tot);
-    n = tot;
-  }
+  // 256 threads = 8 slices x 32 columns: slice s adds the block partials b = s, s + 8, ...; the eight slice sums are
+  // added in slice order.  All blocks but the last hold kBnRows rows: the batch mean is the count-weighted mean of
+  // the block means and the squared deviations add up as sum_b [M2_b + n_b (mean_b - mean)^2].
+  __shared__ float s_part[8][32];
+  const int col = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + col;
+  const bool live = c < C;
+  const float n = static_cast<float>(T);
+  float wsum = 0.f;
+  if (live)
+    for (int b = slice; b < blocks; b += 8) {
+      const int64_t left = T - static_cast<int64_t>(b) * kBnRows;
+      const float nb = static_cast<float>(left < kBnRows ? left : kBnRows);
+      wsum = __fmaf_rn(nb, partial[(static_cast<int64_t>(b) * 2 + 0) * C + c], wsum);
+    }
+  s_part[slice][col] = wsum;
+  __syncthreads();
+  float mean = 0.f;
+#pragma unroll
+  for (int s_ = 0; s_ < 8; ++s_) mean += s_part[s_][col];
+  mean /= n;
+  __syncthreads();
+  float q = 0.f;
+  if (live)
+    for (int b = slice; b < blocks; b += 8) {
+      const int64_t left = T - static_cast<int64_t>(b) * kBnRows;
+      const float nb = static_cast<float>(left < kBnRows ? left : kBnRows);
+      const float d = partial[(static_cast<int64_t>(b) * 2 + 0) * C + c] - mean;
+      q += partial[(static_cast<int64_t>(b) * 2 + 1) * C + c] + nb * d * d;
+    }
+  s_part[slice][col] = q;
+  __syncthreads();
+  if (slice != 0 || !live) return;
+  float m2 = 0.f;
+#pragma unroll
+  for (int s_ = 0; s_ < 8; ++s_) m2 += s_part[s_][col];
   const float var = m2 / n;  // biased: what normalises the batch
   const bool is_y = c >= n_axis;
   const float eps = is_y ? eps_y : eps_x;
@@ -214,7 +243,7 @@ __global__ void __launch_bounds__(256) bn_finalize_kernel(const float* __restric
     const int j = is_y ? c - n_axis : c;
     float mom = is_y ? momentum_y : momentum_x;
     // momentum < 0 stands for None: cumulative moving average over the batches seen so far
-    if (mom < 0.f) mom = 1.0f / static_cast<float>((nbt ? *nbt : 0) + 1);
+    if (mom < 0.f) mom = 1.0f / static_cast<float>(nbt ? *nbt : 1);  // already counts this batch
     const float unbiased = n > 1.f ? m2 / (n - 1.f) : var;
     if (run_dtype == OMNI_F32) {
       float* m = static_cast<float*>(rm);
@@ -230,13 +259,6 @@ __global__ void __launch_bounds__(256) bn_finalize_kernel(const float* __restric
   }
 }
 
-// every column of an axis reads num_batches_tracked before any thread may bump it: a kernel of its own
-__global__ void bn_count_kernel(long long* nbt_x, long long* nbt_y) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    if (nbt_x) *nbt_x += 1;
-    if (nbt_y) *nbt_y += 1;
-  }
-}
 }  // namespace
 }  // namespace omni
 
@@ -263,18 +285,14 @@ extern "C" int omni_router_bn_train(const float* logits, int64_t ld_logits, int6
   OMNI_REQUIRE(blocks < (int64_t(1) << 31), "too many tokens");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(scratch);
-  bn_partial_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(logits, num_tokens, C, ld_logits, partial);
+  bn_partial_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(logits, num_tokens, C, ld_logits, partial,
+                                                                   reinterpret_cast<long long*>(num_batches_tracked_x),
+                                                                   reinterpret_cast<long long*>(num_batches_tracked_y));
   if (int e = check_launch("bn_partial_kernel")) return e;
-  bn_finalize_kernel<<<ceil_div(C, 256), 256, 0, st>>>(partial, static_cast<int>(blocks), num_tokens, C, sqrt_n, eps_x, eps_y,
+  bn_finalize_kernel<<<ceil_div(C, 32), 256, 0, st>>>(partial, static_cast<int>(blocks), num_tokens, C, sqrt_n, eps_x, eps_y,
                                                       momentum_x, momentum_y, bn_scale, bn_shift, running_mean_x, running_var_x,
                                                       running_mean_y, running_var_y, running_dtype,
                                                       reinterpret_cast<long long*>(num_batches_tracked_x),
                                                       reinterpret_cast<long long*>(num_batches_tracked_y));
-  if (int e = check_launch("bn_finalize_kernel")) return e;
-  if (num_batches_tracked_x || num_batches_tracked_y) {
-    bn_count_kernel<<<1, 32, 0, st>>>(reinterpret_cast<long long*>(num_batches_tracked_x),
-                                      reinterpret_cast<long long*>(num_batches_tracked_y));
-    return check_launch("bn_count_kernel");
-  }
-  return 0;
+  return check_launch("bn_finalize_kernel");
 }
