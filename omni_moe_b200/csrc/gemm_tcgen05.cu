@@ -43,6 +43,7 @@ struct GemmArgs {
   const float* residual;  // EPI_RES
   int64_t ldr;
   int tma_out;            // pair kernel: 1 = bf16 output tiles leave through shared memory and TMA stores
+  int tma_logits;         // pair kernel: 1 = the fp32 router logits do too (tensor map tm_lg)
   void* gu_out;           // EPI_SWIGLU: if set, [M, 2N] bf16 that also receives the gate | up pre-activations
   int64_t ldgu;
   // router tile columns of the fused gate/up + router-gate launch (pair kernel, EPI_SWIGLU only)
@@ -332,6 +333,37 @@ __device__ __forceinline__ void store_tile_tma(uint32_t taddr, int row0, int col
   }
 }
 
+// fp32 variant for the router logits: a chunk of 32 columns is 128 bytes per row, one box per chunk through
+// the same staging buffer.  NCH chunks starting at TMEM column offset 0 of `taddr`; output columns
+// col_tile + 32 * ch.  The tensor map clips rows; the caller guarantees the columns are inside the axis.
+template <int NCH>
+__device__ __forceinline__ void store_logits_tma(uint32_t taddr, int row0, int col_tile, const CUtensorMap* tm_lg, uint32_t stg) {
+  const int lane = lane_id();
+  uint32_t ra[32];
+  tmem_ld32_async(taddr, ra);
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    uint32_t v[32];
+    tmem_ld_wait(ra);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = ra[i];
+    if (ch + 1 < NCH) tmem_ld32_async(taddr + 32 * (ch + 1), ra);
+    if (lane == 0) bulk_wait_read_all();
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int piece = q ^ (lane & 7);
+      st_shared_v4(stg + lane * 128 + piece * 16, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tm_lg, stg, col_tile + 32 * ch, row0);
+      bulk_commit_group();
+    }
+  }
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                                                            const __grid_constant__ CUtensorMap tm_b0,
@@ -530,7 +562,8 @@ template <int EPI, bool ROUTER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                      const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_r0,
-                     const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_out, const GemmArgs g) {
+                     const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_out,
+                     const __grid_constant__ CUtensorMap tm_lg, const GemmArgs g) {
   // ROUTER: the first g.router_tiles tile columns multiply x by the router sub-keys instead of the MLP
   // weights: rank 0 holds 128 rows of the x-axis keys, rank 1 the same rows of the y-axis keys, and the
   // epilogue stores fp32 logits.  It rides along with the gate/up GEMM because it reads the same A.
@@ -574,6 +607,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     prefetch_tmap(&tm_b0);
     prefetch_tmap(&tm_b1);
     if (g.tma_out) prefetch_tmap(&tm_out);
+    if (g.tma_logits) prefetch_tmap(&tm_lg);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), C::kTmemCols);
@@ -697,7 +731,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         GemmArgs gr = g;
         gr.out = g.logits, gr.ldo = 2 * g.router_n;
         const int col_tile = col_half * g.router_n + tn * (BN / 2);
-        store_tile<BN, EPI_F32, 4>(taddr + col_half * (BN / 2), row, col_tile, (col_half + 1) * g.router_n, 0, gr);
+        if (g.tma_logits)
+          store_logits_tma<4>(taddr + col_half * (BN / 2), row - lane, col_tile, &tm_lg,
+                              bars + 1024 + static_cast<uint32_t>(warp - 2) * 4096);
+        else
+          store_tile<BN, EPI_F32, 4>(taddr + col_half * (BN / 2), row, col_tile, (col_half + 1) * g.router_n, 0, gr);
       } else if (g.tma_out) {
         const uint32_t stg = bars + 1024 + static_cast<uint32_t>(warp - 2) * 4096;
         OMNI_TIMED(e_store, (store_tile_tma<BN, EPI, OUTC / 64>(taddr, row - lane, tn * OUTC, g.N, col_half * (OUTC / 2), g, &tm_out, stg)));
@@ -708,7 +746,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
     }
-    if (g.tma_out && lane == 0) bulk_wait_all();  // the boxes still on their way are written before the CTA leaves
+    if ((g.tma_out || g.tma_logits) && lane == 0) bulk_wait_all();  // the boxes still on their way are written before the CTA leaves
     if (g.prof && warp == 2 && lane == 0)
       g.prof[blockIdx.x * 16 + 5] = e_wait, g.prof[blockIdx.x * 16 + 6] = e_store, g.prof[blockIdx.x * 16 + 7] = clock64() - e_t0;
   }
@@ -776,6 +814,21 @@ int make_out_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, in
   return 0;
 }
 
+// Map of the fp32 router logits [rows, cols] (row stride = cols): boxes of 32 rows x 32 columns = 128-byte rows.
+int make_logits_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols) {
+  EncodeFn enc = get_encode();
+  if (!enc) return fail(-2, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 4};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-2, "cuTensorMapEncodeTiled (logits) failed with CUresult %d", static_cast<int>(r));
+  return 0;
+}
+
 // The bf16 outputs of the pair kernels go through TMA stores when the output qualifies (16-byte aligned
 // base and row stride).  OMNI_MOE_B200_TMA_STORE=0 keeps the direct stores.
 int g_tma_store = -1;  // -1: follow the environment; 0 / 1: set by omni_debug_gemm_tma_store
@@ -823,6 +876,14 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& 
     if (int e = make_out_map(&mo, g.out, g.M, g.N, g.ldo)) return e;
     g.tma_out = 1;
   }
+  // router logits: whole 128-column tiles per axis only (a narrower axis would spill into its neighbour's columns)
+  CUtensorMap ml = a;
+  g.tma_logits = 0;
+  if (ROUTER && g.logits != nullptr && g.router_tiles > 0 && g.router_n % 128 == 0 && tma_store_enabled() &&
+      (reinterpret_cast<uintptr_t>(g.logits) & 15) == 0) {
+    if (int e = make_logits_map(&ml, g.logits, g.M, 2 * static_cast<int64_t>(g.router_n))) return e;
+    g.tma_logits = 1;
+  }
   using C = PairCfg;
   static OncePerDevice once;
   if (once.first() &&
@@ -832,7 +893,7 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& 
   const int max_pairs = sm_count() / 2;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
   if (g.grid_limit > 0 && g.grid_limit < pairs) pairs = g.grid_limit;
-  launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, mo, g);
+  launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, mo, ml, g);
   return check_launch("gemm_pair_kernel");
 }
 
