@@ -1,9 +1,9 @@
 """Generate the golden fixtures in this directory from the reference project.
 
-Run where the reference checkout is available (path in ``OMNI_MOE_REFERENCE``,
-default ``/root/reference``)::
+Run where a checkout of the reference project (HKUSTDial/omni-moe) is available, with its path in
+``OMNI_MOE_REFERENCE``::
 
-    python tests/golden/make_golden.py
+    OMNI_MOE_REFERENCE=<checkout> python tests/golden/make_golden.py
 
 The reference package cannot be imported as shipped on a CPU-only host (its
 ``omni_moe.ops.triton`` package needs Triton, a GPU and an un-vendored
@@ -31,7 +31,9 @@ import types
 import numpy as np
 import torch
 
-REF = os.environ.get("OMNI_MOE_REFERENCE", "/root/reference")
+REF = os.environ.get("OMNI_MOE_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set OMNI_MOE_REFERENCE to a checkout of the reference project (HKUSTDial/omni-moe)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
