@@ -156,3 +156,31 @@ def test_tma_store_swiglu_and_saved_preactivations():
         lib.omni_debug_gemm_tma_store(-1)
     for a_, b_ in zip(got[0], got[1]):
         assert torch.equal(a_, b_)
+
+
+def test_single_cta_gemm_path_in_a_subprocess():
+    """OMNI_MOE_B200_GEMM=1cta selects the single-CTA kernels for the MLP GEMMs (read once per process)."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = r"""
+import sys, torch
+sys.path.insert(0, %r)
+from oracle import omni_oracle as orc
+from omni_moe_b200.ops import mlp_forward
+g = torch.Generator().manual_seed(0)
+t, h, i = 300, 264, 520
+x = torch.randn(t, h, generator=g).bfloat16()
+wg = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+wu = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+wd = (torch.randn(h, i, generator=g) / i ** 0.5).bfloat16()
+res = torch.randn(t, h, generator=g)
+y = mlp_forward(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), residual=res.cuda())
+e = orc.mlp_forward(x.float(), wg.float(), wu.float(), wd.float()) + res
+bad = (y.float().cpu() - e).abs() > 2e-2 + 2e-2 * e.abs()
+assert not bad.any(), int(bad.sum())
+print("single-cta ok")
+""" % root
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, OMNI_MOE_B200_GEMM="1cta"), capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0 and "single-cta ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
