@@ -286,7 +286,10 @@ OMNI_API int omni_router_bwd(const float *dscores, const void *indices, int idx_
  *   dx[t]   = sum_j ds[t,j] * Up[e]          -> omni_expert_combine(up, ds, indices, ...)
  *   dUp[e]  = sum_{p on e} ds[p] * x[t_p],   dDown[e] = sum_{p on e} cdown[p] * dy[t_p]
  *
- * omni_expert_bwd_dots: token-centric; writes ds, cdown, dg ([T, k] float32 each).
+ * omni_expert_bwd_dots: token-centric; writes ds, cdown, dg ([T, k] float32 each) and, if dx != NULL, the
+ *   input gradient dx [T, H] of dx_dtype as well (the Up rows are in registers for the dot products);
+ *   fusing dx is available when omni_expert_bwd_dots_fuses_dx(hidden) != 0 (hidden <= 1024), otherwise
+ *   pass NULL and form dx with omni_expert_combine.
  * omni_expert_bwd_rows: expert-centric over the schedule of the same indices (omni_schedule with
  *   expert_ids / offsets / meta requested): one gradient row per touched expert, pairs summed in
  *   ascending pair order in fp32, no atomics.  compact = 0: row e of d_up / d_down ([N, H], rows of
@@ -307,7 +310,8 @@ OMNI_API int omni_router_bwd(const float *dscores, const void *indices, int idx_
 OMNI_API int omni_expert_bwd_dots(const void *x, const void *up, const void *down, const void *dy,
                          const float *weights, const int32_t *indices, int64_t num_tokens, int k,
                          int hidden, int64_t num_experts, float *ds, float *cdown, float *dg,
-                         int32_t *status, void *stream);
+                         void *dx, int dx_dtype, int32_t *status, void *stream);
+OMNI_API int omni_expert_bwd_dots_fuses_dx(int hidden);
 OMNI_API int omni_expert_bwd_rows(const void *x, const void *dy, const float *ds, const float *cdown,
                          const int32_t *sorted_pair_ids, const int32_t *expert_ids,
                          const int32_t *offsets, const int32_t *num_segments,

@@ -46,7 +46,8 @@ SIGNATURES = {
                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "omni_router_bwd": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "omni_expert_bwd_dots": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
-                                     c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                     c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "omni_expert_bwd_dots_fuses_dx": (c_int, [c_int]),
     "omni_expert_bwd_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
                                      c_void_p, c_void_p]),

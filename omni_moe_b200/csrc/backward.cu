@@ -152,6 +152,20 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_dots_kernel(
   if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
 }
 
+template <bool OUT_F32>
+__device__ __forceinline__ void store8(void* base, int64_t off, const float2 (&a)[4]) {
+  if (OUT_F32) {
+    float* o = reinterpret_cast<float*>(base) + off;
+    *reinterpret_cast<float4*>(o) = make_float4(a[0].x, a[0].y, a[1].x, a[1].y);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(a[2].x, a[2].y, a[3].x, a[3].y);
+  } else {
+    uint4 p;
+    p.x = float2_to_bf16x2(a[0].x, a[0].y), p.y = float2_to_bf16x2(a[1].x, a[1].y);
+    p.z = float2_to_bf16x2(a[2].x, a[2].y), p.w = float2_to_bf16x2(a[3].x, a[3].y);
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + off) = p;
+  }
+}
+
 // The same for rows of at most 1024 columns: the token's x and dy rows stay in registers, unpacked to
 // fp32 pairs, so a pair costs two row gathers and nothing else; two pairs are in flight.
 __device__ __forceinline__ float2 dot8u(const float2 (&a)[4], const uint4& b, float2 acc) {
@@ -165,7 +179,8 @@ template <int HV>
 __global__ void __launch_bounds__(kThreads) expert_bwd_dots_reg_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
     const __nv_bfloat16* __restrict__ dy, const float* __restrict__ weights, const int32_t* __restrict__ indices, int64_t T,
-    int k, int H, int64_t N, float* __restrict__ ds, float* __restrict__ cdown, float* __restrict__ dg, int* __restrict__ status) {
+    int k, int H, int64_t N, float* __restrict__ ds, float* __restrict__ cdown, float* __restrict__ dg, void* __restrict__ dx,
+    int dx_f32, int* __restrict__ status) {
   constexpr bool kUnpacked = HV <= 4;
   constexpr int UNR = HV <= 4 ? 2 : 1;
   const int warp = threadIdx.x >> 5, lane = lane_id();
@@ -186,6 +201,13 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_dots_reg_kernel(
       for (int q = 0; q < 4; ++q) xf[v][q] = bf16x2_to_float2(px[q]), gf[v][q] = bf16x2_to_float2(pg[q]);
     }
   }
+  // dx[t] = sum_j dS[t,j] * Up[e]: the Up row of a pair is in registers for the dot product anyway, so the
+  // input gradient is accumulated here too when the caller asks for it (dx != null)
+  float2 dxa[HV][4];
+#pragma unroll
+  for (int v = 0; v < HV; ++v)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) dxa[v][q] = make_float2(0.f, 0.f);
   bool bad = false;
   for (int j0 = 0; j0 < k; j0 += 32) {
     const int j = j0 + lane;
@@ -237,12 +259,19 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_dots_reg_kernel(
         }
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
+        // S and dA are warp-uniform after the reduction: every lane forms dS (all of them need it for dx)
+        const float gq = __shfl_sync(FULL_MASK, my_g, (i + u) & 31);
+        const float sig = 1.0f / (1.0f + __expf(-S[u]));
+        const float h = S[u] * sig;
+        const float dsq = dA[u] * gq * (sig * (1.0f + S[u] * (1.0f - sig)));
         if (lane == i + u) {
-          const float sig = 1.0f / (1.0f + __expf(-S[u]));
-          const float h = S[u] * sig;
           my_dg = dA[u] * h;
           my_c = my_g * h;
-          my_ds = dA[u] * my_g * (sig * (1.0f + S[u] * (1.0f - sig)));
+          my_ds = dsq;
+        }
+        if (dx != nullptr) {
+#pragma unroll
+          for (int v = 0; v < HV; ++v) axpy8f(dsq, uv[u][v], dxa[v]);  // rows of dead pairs were loaded as zeros
         }
       }
     }
@@ -253,21 +282,17 @@ __global__ void __launch_bounds__(kThreads) expert_bwd_dots_reg_kernel(
       dg[t * k + j] = ok ? my_dg : 0.f;
     }
   }
-  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
-}
-
-template <bool OUT_F32>
-__device__ __forceinline__ void store8(void* base, int64_t off, const float2 (&a)[4]) {
-  if (OUT_F32) {
-    float* o = reinterpret_cast<float*>(base) + off;
-    *reinterpret_cast<float4*>(o) = make_float4(a[0].x, a[0].y, a[1].x, a[1].y);
-    *reinterpret_cast<float4*>(o + 4) = make_float4(a[2].x, a[2].y, a[3].x, a[3].y);
-  } else {
-    uint4 p;
-    p.x = float2_to_bf16x2(a[0].x, a[0].y), p.y = float2_to_bf16x2(a[1].x, a[1].y);
-    p.z = float2_to_bf16x2(a[2].x, a[2].y), p.w = float2_to_bf16x2(a[3].x, a[3].y);
-    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + off) = p;
+  if (dx != nullptr) {
+#pragma unroll
+    for (int v = 0; v < HV; ++v) {
+      const int col = c0 + v * 256;
+      if (col < H) {
+        if (dx_f32) store8<true>(dx, t * H + col, dxa[v]);
+        else store8<false>(dx, t * H + col, dxa[v]);
+      }
+    }
   }
+  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
 }
 
 // One warp per segment s of the schedule (expert expert_ids[s], sorted positions offsets[s] .. offsets[s+1]).
@@ -517,9 +542,15 @@ extern "C" int omni_router_bwd(const float* dscores, const void* indices, int id
   return check_launch("router_bwd_kernel");
 }
 
+extern "C" int omni_expert_bwd_dots_fuses_dx(int hidden) { return hidden <= 1024 ? 1 : 0; }
+
 extern "C" int omni_expert_bwd_dots(const void* x, const void* up, const void* down, const void* dy, const float* weights,
                                     const int32_t* indices, int64_t num_tokens, int k, int hidden, int64_t num_experts,
-                                    float* ds, float* cdown, float* dg, int32_t* status, void* stream) {
+                                    float* ds, float* cdown, float* dg, void* dx, int dx_dtype, int32_t* status, void* stream) {
+  OMNI_REQUIRE(dx == nullptr || omni_expert_bwd_dots_fuses_dx(hidden),
+               "dx can be fused for hidden <= 1024 only; pass NULL and use omni_expert_combine");
+  OMNI_REQUIRE(dx == nullptr || dx_dtype == OMNI_F32 || dx_dtype == OMNI_BF16, "dx_dtype must be OMNI_F32 or OMNI_BF16");
+  OMNI_REQUIRE(aligned16(dx), "dx must be 16-byte aligned");
   OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && num_experts >= 1, "bad sizes");
   OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
   if (num_tokens == 0) return 0;
@@ -532,7 +563,7 @@ extern "C" int omni_expert_bwd_dots(const void* x, const void* up, const void* d
   const auto* db = static_cast<const __nv_bfloat16*>(down);
   const auto* gb = static_cast<const __nv_bfloat16*>(dy);
 #define OMNI_DOTS(HV_) \
-  expert_bwd_dots_reg_kernel<HV_><<<grid, kThreads, 0, st>>>(xb, ub, db, gb, weights, indices, num_tokens, k, hidden, num_experts, ds, cdown, dg, status)
+  expert_bwd_dots_reg_kernel<HV_><<<grid, kThreads, 0, st>>>(xb, ub, db, gb, weights, indices, num_tokens, k, hidden, num_experts, ds, cdown, dg, dx, dx_dtype == OMNI_F32, status)
   if (hidden <= 256) OMNI_DOTS(1);
   else if (hidden <= 512) OMNI_DOTS(2);
   else if (hidden <= 1024) OMNI_DOTS(4);

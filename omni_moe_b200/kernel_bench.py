@@ -135,7 +135,7 @@ def run_backward(name: str, reps: int):
     ds, cd, dg = torch.empty((T, k), **f32), torch.empty((T, k), **f32), torch.empty((T, k), **f32)
     us = time_graph(lambda s: chk(lib.omni_expert_bwd_dots(x.data_ptr(), up.data_ptr(), down.data_ptr(), dy.data_ptr(),
                                                            weights.data_ptr(), indices.data_ptr(), T, k, H, N, ds.data_ptr(),
-                                                           cd.data_ptr(), dg.data_ptr(), status.data_ptr(), s)), reps=reps)
+                                                           cd.data_ptr(), dg.data_ptr(), None, _lib.OMNI_BF16, status.data_ptr(), s)), reps=reps)
     report("expert_bwd_dots", us, "hbm", 4.0 * T * H + 4.0 * U * H + 20.0 * P, f"U={U} distinct experts; gathers 2 rows per pair")
     dx = torch.empty((T, H), **bf)
     us = time_graph(lambda s: chk(lib.omni_expert_combine(up.data_ptr(), ds.data_ptr(), indices.data_ptr(), T, k, H, N, None,

@@ -102,14 +102,17 @@ def expert_backward(dy: torch.Tensor, x: torch.Tensor, up_weight: torch.Tensor, 
             d_up = torch.zeros((n, h), device=dev, dtype=grad_dtype)
             d_down = torch.zeros((n, h), device=dev, dtype=grad_dtype)
         return dx, d_up, d_down, dg, expert_ids
+    fuse_dx = bool(lib.omni_expert_bwd_dots_fuses_dx(h))
     with torch.cuda.device(dev):
         st = _lib.stream_ptr()
         _lib.check(lib.omni_expert_bwd_dots(x.data_ptr(), up_weight.data_ptr(), down_weight.data_ptr(), dy.data_ptr(),
                                             weights.data_ptr(), indices.data_ptr(), t, k, h, n, ds.data_ptr(),
-                                            cdown.data_ptr(), dg.data_ptr(), status.data_ptr(), st))
-        # dx[t] = sum_j ds[t,j] * Up[e[t,j]]: the forward's token-centric combine with the Up table
-        _lib.check(lib.omni_expert_combine(up_weight.data_ptr(), ds.data_ptr(), indices.data_ptr(), t, k, h, n, None,
-                                           dx.data_ptr(), _lib.dtype_code(grad_dtype), status.data_ptr(), st))
+                                            cdown.data_ptr(), dg.data_ptr(), dx.data_ptr() if fuse_dx else None,
+                                            _lib.dtype_code(grad_dtype), status.data_ptr(), st))
+        if not fuse_dx:
+            # dx[t] = sum_j ds[t,j] * Up[e[t,j]]: the forward's token-centric combine with the Up table
+            _lib.check(lib.omni_expert_combine(up_weight.data_ptr(), ds.data_ptr(), indices.data_ptr(), t, k, h, n, None,
+                                               dx.data_ptr(), _lib.dtype_code(grad_dtype), status.data_ptr(), st))
     if need_tables:
         sch = schedule(indices, n, segments=True)
         cap = sch.expert_ids.numel()
