@@ -9,7 +9,8 @@
 // Routed experts, per pair p = (t, j), e = indices[t, j], g = weights[t, j]:
 //   S  = x[t] . Up[e]            h = silu(S)          dA = dY[t] . Down[e]
 //   dg = dA * h                  c = g * h            dS = dA * g * silu'(S)
-//   dX[t]    += dS * Up[e]       (token-centric: the forward's combine kernel with Up and dS)
+//   dX[t]    += dS * Up[e]       (token-centric: in the dots kernel for rows up to 1024 columns, else the
+//                                forward's combine kernel with Up and dS)
 //   dUp[e]   += dS * x[t]        dDown[e] += c * dY[t]      (expert-centric, needs the schedule)
 //   expert_bwd_dots_kernel  token-centric, one warp per token: both dot products of every pair, then
 //                           dS, c and dg at the pair's place in the [T, k] tables.
