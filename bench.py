@@ -66,7 +66,7 @@ class ClockSampler:
         try:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25", "-i",
                  str(self.index)], stdout=self.file, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
