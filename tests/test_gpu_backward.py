@@ -290,3 +290,56 @@ def test_backward_faults_surface_through_the_device_status():
         _lib.check_device_status()
     _lib.check_device_status()        # cleared by the report
     assert bool(torch.isfinite(dx).all()) and float(dg[2, 1]) == 0.0
+
+
+@pytest.mark.parametrize("t,h,n,k,training", [(300, 64, 16, 4, True), (300, 64, 16, 4, False), (1000, 128, 64, 16, True),
+                                                (257, 256, 256, 32, True), (129, 256, 256, 16, False), (5, 64, 40, 6, True)])
+def test_router_front_operator_matches_fp32_autograd(t, h, n, k, training):
+    """gates -> BatchNorm -> log-softmax -> selection as one operator: forward scores / indices and the
+    gradients of x and both gate matrices against fp32 torch autograd fed with the same selection."""
+    import torch.nn.functional as F
+    from omni_moe_b200.ops.autograd import RouterFrontFunction
+    g = gen(t + n + k)
+    x = torch.randn(t, h, generator=g).bfloat16()
+    kx = (torch.randn(n, h, generator=g) / h ** 0.5).bfloat16()
+    ky = (torch.randn(n, h, generator=g) / h ** 0.5).bfloat16()
+    run_mean = torch.randn(2 * n, generator=g) * 0.1
+    run_var = torch.rand(2 * n, generator=g) + 0.5
+    ds = torch.randn(t, k, generator=g)
+    eps = 1e-5
+    state = {}
+
+    def fold(logits):
+        if training:
+            var, mean = torch.var_mean(logits, dim=0, unbiased=False)
+        else:
+            mean, var = run_mean.cuda(), run_var.cuda()
+        scale = torch.rsqrt(var + eps)
+        state["fold"] = (scale, -mean * scale)
+        return scale.contiguous(), (-mean * scale).contiguous()
+
+    cx, ckx, cky = (v.cuda().requires_grad_(True) for v in (x, kx, ky))
+    scores, indices = RouterFrontFunction.apply(cx, ckx, cky, k, fold, training)
+    (scores * ds.cuda()).sum().backward()
+    # fp32 reference with the same indices
+    rx, rkx, rky = (v.float().requires_grad_(True) for v in (x, kx, ky))
+    z = torch.cat([rx @ rkx.t(), rx @ rky.t()], dim=1)
+    if training:
+        var, mean = torch.var_mean(z, dim=0, unbiased=False)
+    else:
+        mean, var = run_mean, run_var
+    zh = (z - mean) / torch.sqrt(var + eps)
+    lp = torch.cat([F.log_softmax(zh[:, :n], -1), F.log_softmax(zh[:, n:], -1)], dim=1)
+    idx = indices.cpu().long()
+    ref_scores = lp.gather(1, idx // n) + lp.gather(1, n + idx % n)
+    (ref_scores * ds).sum().backward()
+    torch.testing.assert_close(scores.cpu(), ref_scores.detach(), rtol=2e-3, atol=2e-3)
+    assert bool((scores[:, :-1] >= scores[:, 1:]).all())
+    for got, ref, name in ((cx.grad, rx.grad, "dx"), (ckx.grad, rkx.grad, "dKx"), (cky.grad, rky.grad, "dKy")):
+        assert got.dtype == torch.bfloat16
+        _scaled_close(got, ref, name, rtol=5e-2, atol_frac=3e-2)
+    # reproducible
+    cx2, ckx2, cky2 = (v.cuda().requires_grad_(True) for v in (x, kx, ky))
+    s2, i2 = RouterFrontFunction.apply(cx2, ckx2, cky2, k, fold, training)
+    (s2 * ds.cuda()).sum().backward()
+    assert torch.equal(i2, indices) and torch.equal(cx2.grad, cx.grad) and torch.equal(ckx2.grad, ckx.grad)
