@@ -138,3 +138,39 @@ def test_fused_logits_topk_matches_oracle_on_its_own_log_probs():
     zy = orc.router_batchnorm_eval(orc.router_logits(x, ky), mean[n:], var[n:])
     np.testing.assert_allclose(lp[:, :n].numpy(), orc.router_log_probs(zx).numpy(), rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(lp[:, n:].numpy(), orc.router_log_probs(zy).numpy(), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("t,n,momentum,dt", [(1000, 64, 0.1, torch.float32), (65, 1024, None, torch.float32), (4097, 256, 0.25, torch.bfloat16),
+                                              (1, 8, 0.1, torch.float32)])
+def test_batchnorm_statistics_kernel(t, n, momentum, dt):
+    """omni_router_bn_train against torch: fold (scale, shift) from biased batch variance, running
+    statistics with the unbiased one, batch counter; a large common offset shows any cancellation."""
+    from omni_moe_b200 import _lib
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(t + n)
+    z = (torch.randn(t, 2 * n, generator=g) * 2.0 + 50.0).cuda()
+    rm = [(torch.randn(n, generator=g) * 0.1).to(dt).cuda() for _ in range(2)]
+    rv = [(torch.rand(n, generator=g) + 0.5).to(dt).cuda() for _ in range(2)]
+    nbt = [torch.full((), 4, dtype=torch.int64, device="cuda") for _ in range(2)]
+    rm0, rv0 = [v.clone() for v in rm], [v.clone() for v in rv]
+    scale = torch.empty(2 * n, device="cuda")
+    shift = torch.empty(2 * n, device="cuda")
+    scratch = torch.empty(int(lib.omni_router_bn_train_scratch_bytes(t, n)), dtype=torch.uint8, device="cuda")
+    mom = -1.0 if momentum is None else momentum
+    _lib.check(lib.omni_router_bn_train(z.data_ptr(), 2 * n, t, n, 1e-5, 1e-3, mom, mom, rm[0].data_ptr(), rv[0].data_ptr(),
+                                        rm[1].data_ptr(), rv[1].data_ptr(), _lib.dtype_code(dt), nbt[0].data_ptr(), nbt[1].data_ptr(),
+                                        scale.data_ptr(), shift.data_ptr(), scratch.data_ptr(), scratch.numel(), _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    var, mean = torch.var_mean(z.double(), dim=0, unbiased=False)
+    eps = torch.cat([torch.full((n,), 1e-5), torch.full((n,), 1e-3)]).double().cuda()
+    e_scale = torch.rsqrt(var + eps)
+    torch.testing.assert_close(scale.double(), e_scale, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(shift.double(), -mean * e_scale, rtol=1e-4, atol=1e-3)
+    assert int(nbt[0]) == 5 and int(nbt[1]) == 5
+    m_eff = 1.0 / 5 if momentum is None else momentum
+    unb = var * (t / max(t - 1, 1))
+    tol = dict(rtol=2e-2, atol=2e-2) if dt == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)
+    for a in range(2):
+        sl = slice(a * n, (a + 1) * n)
+        torch.testing.assert_close(rm[a].double(), (1 - m_eff) * rm0[a].double() + m_eff * mean[sl], **tol)
+        torch.testing.assert_close(rv[a].double(), (1 - m_eff) * rv0[a].double() + m_eff * unb[sl], **tol)
