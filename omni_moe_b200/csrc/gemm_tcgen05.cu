@@ -14,6 +14,9 @@
 //   warps 2-9   epilogue: a warp may read the 32 TMEM lanes (= tile rows) its warp id modulo 4 selects;
 //               two warps share a lane quarter and split the columns
 // Two accumulators alternate, so the epilogue of tile i overlaps the MMAs of tile i+1.
+// In the CTA-pair kernels the bf16 output (and the fp32 router logits) leave through a swizzled shared-memory
+// staging buffer per epilogue warp and TMA stores (store_tile_tma); outputs that do not qualify and the
+// single-CTA kernels store from registers with 256-bit accesses (store_tile).
 //
 // Every mbarrier wait is bounded.  A wait that runs out sets OMNI_ST_WAIT_TIMEOUT in the status
 // word and raises a CTA-wide abort flag that turns all later waits into no-ops, so the kernel still
