@@ -1,6 +1,6 @@
 """Training-step (forward + backward) throughput of the layer on one GPU.
 
-    python -m omni_moe_b200.train_bench [--config c2] [--steps 20] [--warmup 5]
+    python -m omni_moe_b200.train_bench [--config c2] [--steps 20] [--warmup 5] [--profile]
 
 One step = forward of the module in training mode (batch-statistics BatchNorm) on a fixed batch and
 the backward of a fixed output gradient into every parameter and the input; no optimizer.  Three
@@ -10,6 +10,9 @@ timings, CUDA events around K steps, one JSON line each:
   graphed    the same step captured once in a CUDA graph and replayed
   torch      the same mathematics written with PyTorch eager ops and autograd on the same GPU
              (gather / matmul experts, torch.topk router), as the same-box bar
+
+--profile instead prints the device time of every kernel of one eager step (torch.profiler, CUDA activity
+only, averaged over five steps), largest first: the shares of the training step.
 
 Synthetic data: x ~ N(0,1) and dy ~ N(0, 0.1) in bf16, parameters from the module's default
 initialisation under seed 0.
@@ -73,6 +76,7 @@ def main():
     ap.add_argument("--config", default="c2", choices=list(CONFIGS))
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--profile", action="store_true", help="per-kernel device time of one eager step instead of the timings")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("train_bench needs a CUDA device")
@@ -89,6 +93,30 @@ def main():
         print(json.dumps({"config": args.config, "impl": impl, "metric": "OmniMoE layer fwd+bwd tokens/s",
                           "value": round(c["T"] / (ms * 1e-3)), "unit": "tokens/s", "ms_per_step": round(ms, 4),
                           "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "data": "synthetic"}), flush=True)
+
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+
+        def one_step():
+            for p in m.parameters():
+                p.grad = None
+            m(x).backward(dy)
+        for _ in range(3):
+            one_step()
+        torch.cuda.synchronize()
+        reps = 5
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(reps):
+                one_step()
+            torch.cuda.synchronize()
+        rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in rows) / reps
+        print(f"device time per step: {total:.1f} us over {sum(e.count for e in rows) // reps} kernels / copies")
+        for e in rows:
+            if e.device_time_total / reps < 1.0:
+                break
+            print(f"{e.device_time_total / reps:8.1f} us {100 * e.device_time_total / reps / total:5.1f} %  x{e.count // reps:<3d} {e.key[:120]}")
+        return
 
     # graphed first: whole-step capture wants gradient accumulators that were created on the capture stream
     side = torch.cuda.Stream()
