@@ -81,11 +81,19 @@ __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], con
     uint32_t lmax = 0;
 #pragma unroll
     for (int e = 0; e < E; ++e) lmax = max(lmax, key[e]);
+    // rank of this lane's maximum among the 32 (ties: lower lane first), read back as eight 128-bit words
+    uint32_t* s_max = reinterpret_cast<uint32_t*>(s_tmp);
+    s_max[lane] = lmax;
+    __syncwarp();
     int lrank = 0;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const uint32_t o = __shfl_sync(FULL_MASK, lmax, j);
-      lrank += (o > lmax) || (o == lmax && j < lane);
+    for (int q = 0; q < 8; ++q) {
+      const uint4 o = reinterpret_cast<const uint4*>(s_max)[q];
+      const int j = 4 * q;
+      lrank += (o.x > lmax) || (o.x == lmax && j < lane);
+      lrank += (o.y > lmax) || (o.y == lmax && j + 1 < lane);
+      lrank += (o.z > lmax) || (o.z == lmax && j + 2 < lane);
+      lrank += (o.w > lmax) || (o.w == lmax && j + 3 < lane);
     }
     const unsigned who = __ballot_sync(FULL_MASK, lrank == K - 1);
     const uint32_t bound = __shfl_sync(FULL_MASK, lmax, __ffs(who) - 1);
@@ -95,8 +103,7 @@ __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], con
     const int total = __reduce_add_sync(FULL_MASK, cnt);
     if (bound != 0 && total <= 64) {
       const unsigned lt_mask = (1u << lane) - 1u;
-      s_tmp[lane] = 0ull, s_tmp[32 + lane] = 0ull;
-      __syncwarp();
+      __syncwarp();  // every lane has read s_max
       int base = 0;
 #pragma unroll
       for (int e = 0; e < E; ++e) {
@@ -105,12 +112,22 @@ __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], con
         if (in) s_tmp[base + __popc(m & lt_mask)] = (static_cast<unsigned long long>(key[e]) << 32) | (0xffffffffu - id[e]);
         base += __popc(m);
       }
+      if ((total & 1) && lane == 0) s_tmp[total] = 0ull;  // the pairwise reads below may touch one slot past the end
       __syncwarp();
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const unsigned long long mine = s_tmp[q * 32 + lane];
-        const int r = rank_among_64(s_tmp, mine);
-        if (mine != 0ull && r < K) {
+      // rank the `total` candidates among themselves (distinct packed values): slot lane and, if there are
+      // more than 32, slot 32 + lane; only the live slots are compared against
+      const int pairs = (total + 1) >> 1;
+      const int slots = total > 32 ? 2 : 1;
+      for (int q = 0; q < slots; ++q) {
+        const int slot = q * 32 + lane;
+        const unsigned long long mine = slot < total ? s_tmp[slot] : 0ull;
+        int r = 0;
+        const ulonglong2* p = reinterpret_cast<const ulonglong2*>(s_tmp);
+        for (int j = 0; j < pairs; ++j) {
+          const ulonglong2 o = p[j];
+          r += (o.x > mine) + (o.y > mine);
+        }
+        if (slot < total && r < K) {
           const uint32_t kq = static_cast<uint32_t>(mine >> 32);
           out_key[r] = AS_FLOAT ? __float_as_uint(key_to_float(kq)) : kq;
           out_id[r] = 0xffffffffu - static_cast<uint32_t>(mine);
@@ -119,6 +136,7 @@ __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], con
       __syncwarp();
       return;
     }
+    __syncwarp();  // s_max is dead before the general path reuses the scratch
   }
   uint32_t kmax = 0, kmin = 0xffffffffu;
 #pragma unroll
