@@ -59,6 +59,38 @@ __device__ __forceinline__ int rank_among_64(const unsigned long long* all, unsi
 }
 
 
+// Final stage of warp_select_sorted: the K winners sit packed (key << 32 | ~id, all distinct) in s_tmp[0, K);
+// lane l ranks the entries l, 32 + l, ... (NS of them) by counting the winners that beat them.
+template <int NS, bool AS_FLOAT>
+__device__ __forceinline__ void rank_winners(unsigned long long* s_tmp, int K, uint32_t* out_key, uint32_t* out_id) {
+  const int lane = lane_id();
+  unsigned long long mine[NS];
+  int rank[NS];
+#pragma unroll
+  for (int q = 0; q < NS; ++q) {
+    const int r = q * 32 + lane;
+    mine[q] = r < K ? s_tmp[r] : 0ull;
+    rank[q] = 0;
+  }
+  if ((K & 1) && lane == 0) s_tmp[K] = 0ull;  // K <= kMaxK - 1 when odd: the pairwise reads may touch one slot past the end
+  __syncwarp();
+  const ulonglong2* p = reinterpret_cast<const ulonglong2*>(s_tmp);
+  const int pairs = (K + 1) >> 1;
+  for (int j = 0; j < pairs; ++j) {
+    const ulonglong2 o = p[j];
+#pragma unroll
+    for (int q = 0; q < NS; ++q) rank[q] += (o.x > mine[q]) + (o.y > mine[q]);
+  }
+#pragma unroll
+  for (int q = 0; q < NS; ++q) {
+    if (q * 32 + lane < K) {
+      const uint32_t kq = static_cast<uint32_t>(mine[q] >> 32);
+      out_key[rank[q]] = AS_FLOAT ? __float_as_uint(key_to_float(kq)) : kq;
+      out_id[rank[q]] = 0xffffffffu - static_cast<uint32_t>(mine[q]);
+    }
+  }
+}
+
 // Sorted top-K of the E * 32 entries a warp holds in registers (entry = 32-bit key, larger wins, and a
 // 32-bit id that is unique among the entries, smaller wins on equal keys; key 0 = absent).
 //   1. radix select: a bitwise search for the K-th largest key tau (per step every lane counts its
@@ -187,27 +219,11 @@ __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], con
     base += __popc(m);
   }
   __syncwarp();
-  unsigned long long mine[kMaxK / 32];
-  int rank[kMaxK / 32];
-#pragma unroll
-  for (int q = 0; q < kMaxK / 32; ++q) {
-    const int r = q * 32 + lane;
-    mine[q] = r < K ? s_tmp[r] : 0ull;
-    rank[q] = 0;
-  }
-  for (int j = 0; j < K; ++j) {
-    const unsigned long long o = s_tmp[j];
-#pragma unroll
-    for (int q = 0; q < kMaxK / 32; ++q) rank[q] += o > mine[q];
-  }
-#pragma unroll
-  for (int q = 0; q < kMaxK / 32; ++q) {
-    if (q * 32 + lane < K) {
-      const uint32_t kq = static_cast<uint32_t>(mine[q] >> 32);
-      out_key[rank[q]] = AS_FLOAT ? __float_as_uint(key_to_float(kq)) : kq;
-      out_id[rank[q]] = 0xffffffffu - static_cast<uint32_t>(mine[q]);
-    }
-  }
+  // rank the K admitted entries among themselves; NS = ceil(K / 32) slots per lane, two entries per shared-memory read
+  const int nslot = (K + 31) >> 5;
+  if (nslot == 1) rank_winners<1, AS_FLOAT>(s_tmp, K, out_key, out_id);
+  else if (nslot == 2) rank_winners<2, AS_FLOAT>(s_tmp, K, out_key, out_id);
+  else rank_winners<kMaxK / 32, AS_FLOAT>(s_tmp, K, out_key, out_id);
   __syncwarp();
 }
 

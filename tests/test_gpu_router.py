@@ -25,7 +25,8 @@ def _check(lx, ly, n, k, **kw):
 
 
 @pytest.mark.parametrize("t,n,k", [(257, 32, 8), (1024, 64, 16), (333, 256, 32), (70, 512, 32), (64, 1024, 64),
-                                     (40, 128, 128), (5, 8, 64), (3, 4, 16), (9, 16, 2), (17, 100, 12), (1, 1, 1)])
+                                     (40, 128, 128), (5, 8, 64), (3, 4, 16), (9, 16, 2), (17, 100, 12), (1, 1, 1),
+                                     (90, 300, 16), (65, 400, 6), (129, 200, 10), (77, 130, 3), (50, 513, 33), (31, 72, 127)])
 def test_topk_matches_oracle_fp32(t, n, k):
     g = gen(t * 131 + n)
     lx = torch.log_softmax(torch.randn(t, n, generator=g), -1)
