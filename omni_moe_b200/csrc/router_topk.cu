@@ -62,6 +62,7 @@ int launch_cpl(const TopkArgs& a, cudaStream_t st) {
 template <bool PRE>
 int launch(const TopkArgs& a, cudaStream_t st) {
   if (a.n <= 64) return launch_cpl<2, PRE>(a, st);
+  if (a.n <= 128) return launch_cpl<4, PRE>(a, st);
   if (a.n <= 256) return launch_cpl<8, PRE>(a, st);
   if (a.n <= 512) return launch_cpl<16, PRE>(a, st);
   return launch_cpl<32, PRE>(a, st);
