@@ -41,8 +41,8 @@ WORKLOAD = "quick-start layer: hidden 1024, intermediate 4096, 4096 experts (64x
 SLOTS = 4  # independent weight + activation sets rotated between steps (working set > L2)
 
 # DRAM bytes (read + write) per launch of the gate/up GEMM kernel, from the ncu capture summarised
-# in profiles/gemm_pair_gate_up_quickstart.md (25.35 MB read + 3.26 MB written)
-GATE_UP_DRAM_BYTES_PER_LAUNCH = 28_604_416
+# in profiles/gemm_pair_gate_up_quickstart.md (25.26 MB read + 1.27 MB written)
+GATE_UP_DRAM_BYTES_PER_LAUNCH = 26_528_768
 
 
 def peaks():
