@@ -346,6 +346,20 @@ OMNI_API size_t omni_expert_bwd_rows_scratch_bytes(int64_t num_pairs, int hidden
 OMNI_API int omni_mlp_gate_up_save(const void *x, const void *gate_w, const void *up_w, int64_t num_tokens,
                           int hidden, int intermediate, void *act, void *gate_up, int32_t *status,
                           void *stream);
+/*
+ * omni_mlp_gate_up_limit / omni_swiglu_bwd_limit: the same two steps with the clamp of the reference's
+ *   activation (compute_silu_mul, omni_moe/ops/triton/omni_mlp.py:54-61; PrecisionConfig.limit, :27):
+ *   with limit > 0 gate and up are limited to [-limit, limit] before silu(gate) * up; limit == 0 is no
+ *   clamp.  gate_up may be NULL (nothing saved); when given it receives the UNCLAMPED pre-activations,
+ *   from which omni_swiglu_bwd_limit derives both the clamped values and where no gradient passes
+ *   (outside [-limit, limit]; the boundary passes, as torch.clamp's gradient does).
+ */
+OMNI_API int omni_mlp_gate_up_limit(const void *x, const void *gate_w, const void *up_w, int64_t num_tokens,
+                           int hidden, int intermediate, float limit, void *act, void *gate_up,
+                           int32_t *status, void *stream);
+OMNI_API int omni_swiglu_bwd_limit(const void *gate_up, const void *dact, int64_t num_tokens, int intermediate,
+                          float limit, void *dgate_up, void *dgate_up_t, void *act_t, int64_t ld_t,
+                          void *stream);
 OMNI_API int omni_gemm_bf16_nt(const void *a, const void *b, int64_t m, int64_t n, int64_t k, void *out,
                       int64_t ldo, int32_t *status, void *stream);
 OMNI_API int omni_transpose_bf16(const void *in, int64_t rows, int64_t cols, int64_t ld_in, void *out,

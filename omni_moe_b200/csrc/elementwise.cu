@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256) transpose_bf16_kernel(const uint16_t* __r
 // that contract over tokens, the transposed copies dgu_t [2I, ld_t] and act_t [I, ld_t] (columns
 // T..ld_t-1 zero).  A block owns a 64-token x 64-column tile; the transposes go through shared memory.
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dact,
-                                                         int64_t T, int I, __nv_bfloat16* __restrict__ dgu,
+                                                         int64_t T, int I, float limit, __nv_bfloat16* __restrict__ dgu,
                                                          uint16_t* __restrict__ dgu_t, uint16_t* __restrict__ act_t, int64_t ld_t) {
   __shared__ uint16_t s_dg[kTile][kTile + 2], s_du[kTile][kTile + 2], s_ac[kTile][kTile + 2];
   const int64_t r0 = static_cast<int64_t>(blockIdx.x) * kTile;
@@ -67,11 +67,15 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __
         const float gg[2] = {g.x, g.y}, uu[2] = {u.x, u.y}, dd[2] = {d.x, d.y};
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float sig = 1.0f / (1.0f + __expf(-gg[e]));
-          const float sl = gg[e] * sig;
-          ra[e] = sl * uu[e];
-          rg[e] = dd[e] * uu[e] * (sig * (1.0f + gg[e] * (1.0f - sig)));
-          ru[e] = dd[e] * sl;
+          // clamp of the forward (limit > 0): values are limited to [-limit, limit] and no gradient passes
+          // where the pre-activation lies outside (the boundary itself passes, as torch.clamp does)
+          const bool g_in = !(limit > 0.f) || fabsf(gg[e]) <= limit, u_in = !(limit > 0.f) || fabsf(uu[e]) <= limit;
+          const float gc = g_in ? gg[e] : copysignf(limit, gg[e]), uc = u_in ? uu[e] : copysignf(limit, uu[e]);
+          const float sig = 1.0f / (1.0f + __expf(-gc));
+          const float sl = gc * sig;
+          ra[e] = sl * uc;
+          rg[e] = g_in ? dd[e] * uc * (sig * (1.0f + gc * (1.0f - sig))) : 0.f;
+          ru[e] = u_in ? dd[e] * sl : 0.f;
         }
         og[q] = float2_to_bf16x2(rg[0], rg[1]);
         ou[q] = float2_to_bf16x2(ru[0], ru[1]);
@@ -130,8 +134,9 @@ extern "C" int omni_transpose_bf16(const void* in, int64_t rows, int64_t cols, i
   return check_launch("transpose_bf16_kernel");
 }
 
-extern "C" int omni_swiglu_bwd(const void* gate_up, const void* dact, int64_t num_tokens, int intermediate, void* dgate_up,
-                               void* dgate_up_t, void* act_t, int64_t ld_t, void* stream) {
+extern "C" int omni_swiglu_bwd_limit(const void* gate_up, const void* dact, int64_t num_tokens, int intermediate, float limit,
+                                     void* dgate_up, void* dgate_up_t, void* act_t, int64_t ld_t, void* stream) {
+  OMNI_REQUIRE(limit >= 0.f, "limit must be >= 0 (0 = no clamp)");
   OMNI_REQUIRE(num_tokens >= 0 && intermediate >= 8 && intermediate % 8 == 0, "intermediate must be a positive multiple of 8");
   OMNI_REQUIRE((dgate_up_t == nullptr) == (act_t == nullptr), "dgate_up_t and act_t must be given together");
   OMNI_REQUIRE(dgate_up_t == nullptr || (ld_t >= num_tokens && ld_t % 2 == 0), "ld_t must be even and >= num_tokens");
@@ -144,9 +149,14 @@ extern "C" int omni_swiglu_bwd(const void* gate_up, const void* dact, int64_t nu
   const int64_t gy = ceil_div64(intermediate, kTile);
   OMNI_REQUIRE(gy <= 65535, "intermediate too large for one launch");
   swiglu_bwd_kernel<<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up), static_cast<const __nv_bfloat16*>(dact), num_tokens, intermediate,
+      static_cast<const __nv_bfloat16*>(gate_up), static_cast<const __nv_bfloat16*>(dact), num_tokens, intermediate, limit,
       static_cast<__nv_bfloat16*>(dgate_up), static_cast<uint16_t*>(dgate_up_t), static_cast<uint16_t*>(act_t), ld_t);
   return check_launch("swiglu_bwd_kernel");
+}
+
+extern "C" int omni_swiglu_bwd(const void* gate_up, const void* dact, int64_t num_tokens, int intermediate, void* dgate_up,
+                               void* dgate_up_t, void* act_t, int64_t ld_t, void* stream) {
+  return omni_swiglu_bwd_limit(gate_up, dact, num_tokens, intermediate, 0.f, dgate_up, dgate_up_t, act_t, ld_t, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -34,13 +34,17 @@ using namespace tc;
 constexpr int kEpiWarps = 8;  // two per TMEM lane quarter, each draining half of the columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 
-enum { EPI_F32 = 0, EPI_SWIGLU = 1, EPI_RES = 2 };
+enum { EPI_F32 = 0, EPI_SWIGLU = 1, EPI_RES = 2, EPI_SWIGLU_CLAMP = 3 };
+// EPI_SWIGLU_CLAMP is EPI_SWIGLU with gate and up limited to [-limit, limit] before the activation; a
+// separate instantiation, so the kernels of the common no-clamp case are compiled without it.
+__host__ __device__ constexpr bool is_swiglu(int epi) { return epi == EPI_SWIGLU || epi == EPI_SWIGLU_CLAMP; }
 
 struct GemmArgs {
   int M, N, K;          // N: logical output columns (EPI_SWIGLU: activation columns; EPI_F32 dual: per-axis columns)
   int dual;             // EPI_F32: 1 = two B matrices of N rows each, outputs side by side (ldc >= 2N)
   int tiles_m, tiles_n; // tiles_n counts tiles over all axes
   int tiles_n_axis;     // tiles per axis (EPI_F32 dual), else tiles_n
+  float limit;          // EPI_SWIGLU_CLAMP: gate and up are limited to [-limit, limit] before the activation
   void* out;
   int64_t ldo;
   const float* residual;  // EPI_RES
@@ -104,6 +108,19 @@ __device__ __forceinline__ void st256(void* ptr, const uint32_t (&p)[8]) {
                : "memory");
 }
 
+// silu(gate) * up of one 32-column chunk.  CLAMP limits gate and up to [-limit, limit] first, as the
+// reference's activation does (compute_silu_mul, omni_moe/ops/triton/omni_mlp.py:54-61); the registers
+// keep the unclamped values (the training forward saves those).
+template <bool CLAMP>
+__device__ __forceinline__ void swiglu_chunk(const uint32_t (&ra)[32], const uint32_t (&rb)[32], float limit, float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float a = __uint_as_float(ra[i]), b = __uint_as_float(rb[i]);
+    if (CLAMP) a = fminf(fmaxf(a, -limit), limit), b = fminf(fmaxf(b, -limit), limit);
+    v[i] = silu_fast(a) * b;
+  }
+}
+
 // Drains this warp's share of one accumulator tile: its 32 rows (TMEM lane quarter) and the column
 // chunks [c_begin, c_begin + 32 * NCH).  The TMEM load of chunk i+1 and the residual fetch of
 // chunk i are in flight while chunk i-1 is converted and stored.
@@ -113,7 +130,7 @@ template <int BN, int EPI, int NCH>
 __device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile, int col_lim, int c_begin, const GemmArgs& g) {
   uint32_t ra[32], rb[32];
   tmem_ld32_async(taddr + c_begin, ra);
-  if (EPI == EPI_SWIGLU) tmem_ld32_async(taddr + BN / 2 + c_begin, rb);
+  if (is_swiglu(EPI)) tmem_ld32_async(taddr + BN / 2 + c_begin, rb);
 #pragma unroll
   for (int ch = 0; ch < NCH; ++ch) {
     const int c = c_begin + 32 * ch;
@@ -129,15 +146,14 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile
     }
     float v[32];
     tmem_ld_wait(ra);
-    if (EPI == EPI_SWIGLU) {
+    if (is_swiglu(EPI)) {
       tmem_ld_wait(rb);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = silu_fast(__uint_as_float(ra[i])) * __uint_as_float(rb[i]);
+      swiglu_chunk<EPI == EPI_SWIGLU_CLAMP>(ra, rb, g.limit, v);
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
     }
-    if (EPI == EPI_SWIGLU && g.gu_out != nullptr && live) {
+    if (is_swiglu(EPI) && g.gu_out != nullptr && live) {
       // training: keep the pre-activations for the backward (gate in columns [0, N), up in [N, 2N))
       __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(g.gu_out) + static_cast<int64_t>(row) * g.ldgu + col0;
       __nv_bfloat16* ou = og + g.N;
@@ -180,7 +196,7 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, int col_tile
     }
     if (ch + 1 < NCH) {
       tmem_ld32_async(taddr + c + 32, ra);
-      if (EPI == EPI_SWIGLU) tmem_ld32_async(taddr + BN / 2 + c + 32, rb);
+      if (is_swiglu(EPI)) tmem_ld32_async(taddr + BN / 2 + c + 32, rb);
     }
     if (!live) continue;
     if (EPI == EPI_F32) {
@@ -253,7 +269,7 @@ __device__ __forceinline__ void store_tile_tma(uint32_t taddr, int row0, int col
   const int row = row0 + lane;
   uint32_t ra[32], rb[32];
   tmem_ld32_async(taddr + c_begin, ra);
-  if (EPI == EPI_SWIGLU) tmem_ld32_async(taddr + BN / 2 + c_begin, rb);
+  if (is_swiglu(EPI)) tmem_ld32_async(taddr + BN / 2 + c_begin, rb);
 #pragma unroll
   for (int ch = 0; ch < NCH; ++ch) {
     const int c = c_begin + 32 * ch;
@@ -262,15 +278,14 @@ __device__ __forceinline__ void store_tile_tma(uint32_t taddr, int row0, int col
     const bool full = col0 + 32 <= col_lim;
     float v[32];
     tmem_ld_wait(ra);
-    if (EPI == EPI_SWIGLU) {
+    if (is_swiglu(EPI)) {
       tmem_ld_wait(rb);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = silu_fast(__uint_as_float(ra[i])) * __uint_as_float(rb[i]);
+      swiglu_chunk<EPI == EPI_SWIGLU_CLAMP>(ra, rb, g.limit, v);
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
     }
-    if (EPI == EPI_SWIGLU && g.gu_out != nullptr && live) {
+    if (is_swiglu(EPI) && g.gu_out != nullptr && live) {
       __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(g.gu_out) + static_cast<int64_t>(row) * g.ldgu + col0;
       __nv_bfloat16* ou = og + g.N;
       if (full && (g.ldgu & 15) == 0 && (g.N & 15) == 0 && (reinterpret_cast<uintptr_t>(g.gu_out) & 31) == 0) {
@@ -297,7 +312,7 @@ __device__ __forceinline__ void store_tile_tma(uint32_t taddr, int row0, int col
     }
     if (ch + 1 < NCH) {
       tmem_ld32_async(taddr + c + 32, ra);
-      if (EPI == EPI_SWIGLU) tmem_ld32_async(taddr + BN / 2 + c + 32, rb);
+      if (is_swiglu(EPI)) tmem_ld32_async(taddr + BN / 2 + c + 32, rb);
     }
     if (EPI == EPI_RES && g.residual && live) {
       if (full && (g.ldr & 3) == 0) {
@@ -437,7 +452,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           mbar_arrive_expect_tx(full, C::kStage);
           tma_load_2d(sA + stage * C::kStageA, &tm_a, kb * BK, tm * BM, full);
           const uint32_t dstB = sB + stage * C::kStageB;
-          if (EPI == EPI_SWIGLU) {
+          if (is_swiglu(EPI)) {
             tma_load_2d(dstB, &tm_b0, kb * BK, tj * (BN / 2), full);
             tma_load_2d(dstB + (BN / 2) * BK * 2, &tm_b1, kb * BK, tj * (BN / 2), full);
           } else {
@@ -506,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       if (!ok) break;
       const int row = tm * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      constexpr int OUTC = (EPI == EPI_SWIGLU) ? BN / 2 : BN;  // output columns of this tile
+      constexpr int OUTC = (is_swiglu(EPI)) ? BN / 2 : BN;  // output columns of this tile
       const int col_tile = (EPI == EPI_F32 && g.dual) ? axis * g.N + tj * OUTC : tj * OUTC;
       const int col_lim = (EPI == EPI_F32 && g.dual) ? (axis + 1) * g.N : g.N;  // exclusive bound of valid columns
       OMNI_TIMED(e_store, (store_tile<BN, EPI, OUTC / 64>(taddr, row, col_tile, col_lim, col_half * (OUTC / 2), g)));
@@ -640,8 +655,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         const int tn = router_tile ? tn_all : tn_all - rt;
         const int row_a = tm * (2 * BM) + static_cast<int>(rank) * BM;
         const CUtensorMap* mb = router_tile ? (rank == 1 ? &tm_r1 : &tm_r0)
-                                            : ((EPI == EPI_SWIGLU && rank == 1) ? &tm_b1 : &tm_b0);
-        const int row_b = (EPI == EPI_SWIGLU || router_tile) ? tn * (BN / 2) : tn * BN + static_cast<int>(rank) * (BN / 2);
+                                            : ((is_swiglu(EPI) && rank == 1) ? &tm_b1 : &tm_b0);
+        const int row_b = (is_swiglu(EPI) || router_tile) ? tn * (BN / 2) : tn * BN + static_cast<int>(rank) * (BN / 2);
         for (int kb = 0; kb < kblocks; ++kb) {
           bool ok;
           OMNI_TIMED(p_wait, ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, g.status));
@@ -727,7 +742,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       if (!ok) break;
       const int row = tm * (2 * BM) + static_cast<int>(rank) * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      constexpr int OUTC = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+      constexpr int OUTC = (is_swiglu(EPI)) ? BN / 2 : BN;
       if (router_tile) {
         // accumulator columns [0, 128) are x-axis sub-keys tn*128.., [128, 256) the y-axis ones;
         // the warps of column half h store axis h
@@ -983,13 +998,14 @@ extern "C" int omni_mlp_gate_up(const void* x, const void* gate_w, const void* u
   return launch<256, EPI_SWIGLU>(ma, mg, mu, g, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int omni_mlp_gate_up_save(const void* x, const void* gate_w, const void* up_w, int64_t num_tokens, int hidden,
-                                     int intermediate, void* act, void* gate_up, int32_t* status, void* stream) {
+extern "C" int omni_mlp_gate_up_limit(const void* x, const void* gate_w, const void* up_w, int64_t num_tokens, int hidden,
+                                      int intermediate, float limit, void* act, void* gate_up, int32_t* status, void* stream) {
   OMNI_REQUIRE(num_tokens >= 0 && num_tokens < (int64_t(1) << 31) - 2 * BM, "num_tokens out of range");
   OMNI_REQUIRE(hidden >= 8 && hidden % 8 == 0, "hidden must be a positive multiple of 8, got %d", hidden);
   OMNI_REQUIRE(intermediate >= 8 && intermediate % 8 == 0, "intermediate must be a positive multiple of 8, got %d", intermediate);
+  OMNI_REQUIRE(limit >= 0.f, "limit must be >= 0 (0 = no clamp), got %g", static_cast<double>(limit));  // also refuses NaN
   if (num_tokens == 0) return 0;
-  OMNI_REQUIRE(x && gate_w && up_w && act && gate_up && status, "NULL argument");
+  OMNI_REQUIRE(x && gate_w && up_w && act && status, "NULL argument");
   OMNI_REQUIRE(aligned16(x) && aligned16(gate_w) && aligned16(up_w) && aligned16(act) && aligned16(gate_up), "pointers must be 16-byte aligned");
   CUtensorMap ma, mg, mu;
   if (int e = make_map(&ma, x, num_tokens, hidden, BM)) return e;
@@ -1000,8 +1016,16 @@ extern "C" int omni_mlp_gate_up_save(const void* x, const void* gate_w, const vo
   g.tiles_m = ceil_div(g.M, 2 * BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(intermediate, 128);
   g.out = act, g.ldo = intermediate, g.gu_out = gate_up, g.ldgu = 2 * static_cast<int64_t>(intermediate);
+  g.limit = limit;
   g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  if (limit > 0.f) return launch_pair<EPI_SWIGLU_CLAMP, false>(ma, mg, mu, mg, mu, g, static_cast<cudaStream_t>(stream));
   return launch_pair<EPI_SWIGLU, false>(ma, mg, mu, mg, mu, g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int omni_mlp_gate_up_save(const void* x, const void* gate_w, const void* up_w, int64_t num_tokens, int hidden,
+                                     int intermediate, void* act, void* gate_up, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens == 0 || gate_up, "NULL argument");
+  return omni_mlp_gate_up_limit(x, gate_w, up_w, num_tokens, hidden, intermediate, 0.f, act, gate_up, status, stream);
 }
 
 extern "C" int omni_mlp_gate_up_router(const void* x, const void* gate_w, const void* up_w, const void* gate_x,

@@ -213,11 +213,13 @@ def transpose_padded(src: torch.Tensor, out: torch.Tensor | None = None) -> torc
 
 
 def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor,
-                 down_weight: torch.Tensor, need_weight_grads: bool = True, gate_up: torch.Tensor | None = None):
+                 down_weight: torch.Tensor, need_weight_grads: bool = True, gate_up: torch.Tensor | None = None,
+                 limit: float | None = None):
     """Backward of ``y = (silu(x Wg^T) * (x Wu^T)) Wd^T`` on bf16 operands.
 
     ``gate_up [T, 2I]`` bf16 are the pre-activations saved by the training forward
     (``mlp_forward(..., gate_up=...)``); without them they are recomputed here with two more GEMMs.
+    ``limit``: the clamp the forward ran with (``mlp_forward(..., limit=...)``), if any.
     GEMMs on the tensor cores: dact = dy Wd, dx = (dgate | dup) (Wg ; Wu), dWd = dy^T act,
     (dWg ; dWu) = (dgate | dup)^T x.
     Returns ``(dx, d_gate_weight, d_up_weight, d_down_weight)`` in bf16.
@@ -251,8 +253,8 @@ def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, u
     dgu_t = torch.empty((2 * i, tp), **bf) if need_weight_grads else None
     act_t = torch.empty((i, tp), **bf) if need_weight_grads else None
     with torch.cuda.device(dev):
-        _lib.check(lib.omni_swiglu_bwd(gu.data_ptr(), dact.data_ptr(), t, i, dgu.data_ptr(), _lib.ptr(dgu_t), _lib.ptr(act_t),
-                                       tp, _lib.stream_ptr()))
+        _lib.check(lib.omni_swiglu_bwd_limit(gu.data_ptr(), dact.data_ptr(), t, i, float(limit or 0.0), dgu.data_ptr(),
+                                             _lib.ptr(dgu_t), _lib.ptr(act_t), tp, _lib.stream_ptr()))
     # dx = dgate @ Wg + dup @ Wu = dgu @ (Wg ; Wu): B operand [H, 2I] = (Wg^T | Wu^T)
     wgu_t = torch.empty((h, 2 * i), **bf)
     transpose_padded(wg, wgu_t[:, :i])
@@ -271,22 +273,24 @@ class MlpFunction(torch.autograd.Function):
     """Shared SwiGLU MLP with gradients for x and the three weight matrices."""
 
     @staticmethod
-    def forward(ctx, x, gate_weight, up_weight, down_weight):
+    def forward(ctx, x, gate_weight, up_weight, down_weight, limit=None):
         from .mlp import mlp_forward
         xb, wg, wu, wd = as_bf16(x), as_bf16(gate_weight), as_bf16(up_weight), as_bf16(down_weight)
         gu = torch.empty((xb.size(0), 2 * wg.size(0)), device=xb.device, dtype=torch.bfloat16)
-        y = mlp_forward(xb, wg, wu, wd, gate_up=gu)
+        y = mlp_forward(xb, wg, wu, wd, gate_up=gu, limit=limit)
         ctx.save_for_backward(xb, wg, wu, wd, gu)
+        ctx.limit = limit
         ctx.dtypes = (x.dtype, gate_weight.dtype, up_weight.dtype, down_weight.dtype)
         return y.to(x.dtype)
 
     @staticmethod
     def backward(ctx, dy):
         xb, wg, wu, wd, gu = ctx.saved_tensors
-        need_w = any(ctx.needs_input_grad[1:])
-        dx, d_wg, d_wu, d_wd = mlp_backward(as_bf16(dy), xb, wg, wu, wd, need_weight_grads=need_w, gate_up=gu)
+        need_w = any(ctx.needs_input_grad[1:4])
+        dx, d_wg, d_wu, d_wd = mlp_backward(as_bf16(dy), xb, wg, wu, wd, need_weight_grads=need_w, gate_up=gu,
+                                            limit=ctx.limit)
         cast = lambda g, j: g.to(ctx.dtypes[j]) if (g is not None and ctx.needs_input_grad[j]) else None
-        return cast(dx, 0), cast(d_wg, 1), cast(d_wu, 2), cast(d_wd, 3)
+        return cast(dx, 0), cast(d_wg, 1), cast(d_wu, 2), cast(d_wd, 3), None
 
 
 # ------------------------------------------------------------------------------------------------

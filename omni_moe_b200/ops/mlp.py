@@ -9,14 +9,19 @@ from ._common import as_bf16
 
 def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
                 residual: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                act: torch.Tensor | None = None, gate_up: torch.Tensor | None = None) -> torch.Tensor:
+                act: torch.Tensor | None = None, gate_up: torch.Tensor | None = None,
+                limit: float | None = None) -> torch.Tensor:
     """``(silu(x Wg^T) * (x Wu^T)) Wd^T (+ residual)`` on bf16 operands with two tcgen05 GEMMs.
 
     ``residual``: optional fp32 ``[T, H]`` added before the result is rounded to bf16.
     ``act``: optional bf16 ``[T, I]`` scratch for the activation.
     ``gate_up``: optional bf16 ``[T, 2I]`` that receives the pre-activations ``(x Wg^T | x Wu^T)`` (kept
     for the backward in training).
+    ``limit``: optional clamp of the reference's fused activation (``compute_silu_mul``,
+    omni_moe/ops/triton/omni_mlp.py:54-61): gate and up are limited to ``[-limit, limit]`` before
+    ``silu(gate) * up``; ``gate_up`` still receives the unclamped values.
     """
+    assert limit is None or limit > 0, "limit must be positive"
     _lib.require_cuda(x, gate_weight, up_weight, down_weight)
     assert x.dtype == gate_weight.dtype == up_weight.dtype == down_weight.dtype == torch.bfloat16
     x, gate_weight, up_weight, down_weight = (v.contiguous() for v in (x, gate_weight, up_weight, down_weight))
@@ -37,7 +42,10 @@ def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Ten
         lib = _lib.load()
         with torch.cuda.device(dev):
             st = _lib.stream_ptr()
-            if gate_up is None:
+            if limit is not None:
+                _lib.check(lib.omni_mlp_gate_up_limit(x.data_ptr(), gate_weight.data_ptr(), up_weight.data_ptr(), t, h, i,
+                                                      float(limit), act.data_ptr(), _lib.ptr(gate_up), status.data_ptr(), st))
+            elif gate_up is None:
                 _lib.check(lib.omni_mlp_gate_up(x.data_ptr(), gate_weight.data_ptr(), up_weight.data_ptr(), t, h, i,
                                                 act.data_ptr(), status.data_ptr(), st))
             else:
@@ -49,16 +57,18 @@ def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Ten
 
 
 def omni_mlp_func(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor,
-                  down_weight: torch.Tensor) -> torch.Tensor:
+                  down_weight: torch.Tensor, limit: float | None = None) -> torch.Tensor:
     """Drop-in for ``triton_omni_mlp_func`` (omni_moe/ops/triton/interface.py:7-29).
 
     :param x: (num_tokens, hidden_size)
     :param gate_weight, up_weight: (intermediate_size, hidden_size)
     :param down_weight: (hidden_size, intermediate_size)
+    :param limit: optional clamp of gate and up before the activation (the ``limit`` of the reference's
+        ``PrecisionConfig``, omni_moe/ops/triton/omni_mlp.py:27,54-61, which its public entry leaves unset)
     :return y: (num_tokens, hidden_size), dtype of ``x``
     """
     assert x.dim() == 2
     if torch.is_grad_enabled() and any(t.requires_grad for t in (x, gate_weight, up_weight, down_weight)):
         from .autograd import MlpFunction
-        return MlpFunction.apply(x, gate_weight, up_weight, down_weight)
-    return mlp_forward(as_bf16(x), as_bf16(gate_weight), as_bf16(up_weight), as_bf16(down_weight)).to(x.dtype)
+        return MlpFunction.apply(x, gate_weight, up_weight, down_weight, limit)
+    return mlp_forward(as_bf16(x), as_bf16(gate_weight), as_bf16(up_weight), as_bf16(down_weight), limit=limit).to(x.dtype)

@@ -207,15 +207,20 @@ def expert_coefficients(x, up_w, routing_w, indices) -> torch.Tensor:
 # --------------------------------------------------------------------------- #
 # shared SwiGLU MLP
 # --------------------------------------------------------------------------- #
-def mlp_forward(x, gate_w, up_w, down_w) -> torch.Tensor:
+def mlp_forward(x, gate_w, up_w, down_w, limit=None) -> torch.Tensor:
     """``(silu(x Wg^T) * (x Wu^T)) Wd^T`` in fp32.
 
     Follows omni_moe/modules/omni_moe.py:190-192, omni_moe/ops/triton/interface.py:23-29
-    and tests/test_mlp.py:8-21.
+    and tests/test_mlp.py:8-21.  ``limit`` is the clamp of the reference's fused activation
+    (``compute_silu_mul``, omni_moe/ops/triton/omni_mlp.py:54-61, ``PrecisionConfig.limit`` :27):
+    gate and up are limited to ``[-limit, limit]`` before ``silu(gate) * up``; the reference's public
+    entry never sets it, so ``None`` is the layer's behaviour.
     """
     x = torch.as_tensor(x).float()
-    a = F.silu(x @ torch.as_tensor(gate_w).float().t()) * (x @ torch.as_tensor(up_w).float().t())
-    return a @ torch.as_tensor(down_w).float().t()
+    g, u = x @ torch.as_tensor(gate_w).float().t(), x @ torch.as_tensor(up_w).float().t()
+    if limit is not None:
+        g, u = g.clamp(-limit, limit), u.clamp(-limit, limit)
+    return (F.silu(g) * u) @ torch.as_tensor(down_w).float().t()
 
 
 # --------------------------------------------------------------------------- #
@@ -309,13 +314,16 @@ def expert_backward(x, up_w, down_w, routing_w, indices, dy):
     return x.grad, up.grad, dn.grad, g.grad
 
 
-def mlp_backward(x, gate_w, up_w, down_w, dy):
+def mlp_backward(x, gate_w, up_w, down_w, dy, limit=None):
     """``(dx, d_gate_w, d_up_w, d_down_w)`` of :func:`mlp_forward` by autograd in fp32."""
     x = torch.as_tensor(x).float().clone().requires_grad_(True)
     wg = torch.as_tensor(gate_w).float().clone().requires_grad_(True)
     wu = torch.as_tensor(up_w).float().clone().requires_grad_(True)
     wd = torch.as_tensor(down_w).float().clone().requires_grad_(True)
-    y = F.linear(F.silu(F.linear(x, wg)) * F.linear(x, wu), wd)
+    g, u = F.linear(x, wg), F.linear(x, wu)
+    if limit is not None:
+        g, u = g.clamp(-limit, limit), u.clamp(-limit, limit)
+    y = F.linear(F.silu(g) * u, wd)
     y.backward(torch.as_tensor(dy).float())
     return x.grad, wg.grad, wu.grad, wd.grad
 

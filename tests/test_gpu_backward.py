@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import omni_oracle as orc
-from _util import gen
+from _util import assert_close, gen
 
 pytestmark = pytest.mark.gpu
 
@@ -161,6 +161,58 @@ def test_mlp_backward_matches_oracle(t, h, i):
     _scaled_close(dwg, eg, "d_gate_weight", rtol=3e-2, atol_frac=2e-2)
     _scaled_close(dwu, eu, "d_up_weight", rtol=3e-2, atol_frac=2e-2)
     _scaled_close(dwd, ed, "d_down_weight", rtol=3e-2, atol_frac=2e-2)
+
+
+@pytest.mark.parametrize("t,h,i,limit", [(300, 256, 1024, 0.75), (257, 1024, 4096, 1.5), (77, 72, 200, 0.3), (64, 64, 128, 7.0)])
+def test_mlp_limit_forward_and_backward(t, h, i, limit):
+    """The clamp of the reference's fused activation (omni_moe/ops/triton/omni_mlp.py:54-61): gate and up limited
+    to [-limit, limit] in the forward, no gradient through clamped entries in the backward."""
+    from omni_moe_b200.ops import mlp_forward, omni_mlp_func
+    from omni_moe_b200.ops.autograd import mlp_backward
+    g = gen(t + i)
+    x = torch.randn(t, h, generator=g).bfloat16()
+    wg = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wu = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16()
+    wd = (torch.randn(h, i, generator=g) / i ** 0.5).bfloat16()
+    dy = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
+    gate = x.float() @ wg.float().t()
+    clamped = float((gate.abs() > limit).float().mean())
+    assert (clamped > 0.04) == (limit < 2.0), "the case must exercise the clamp (or, for the wide limit, not)"
+    cx, cg, cu, cd = x.cuda(), wg.cuda(), wu.cuda(), wd.cuda()
+    exp = orc.mlp_forward(x, wg, wu, wd, limit=limit)
+    gu = torch.empty(t, 2 * i, dtype=torch.bfloat16, device="cuda")
+    y = mlp_forward(cx, cg, cu, cd, gate_up=gu, limit=limit)
+    assert_close(y, exp, what="mlp with limit")
+    assert torch.equal(y, mlp_forward(cx, cg, cu, cd, limit=limit)), "saving must not change the output"
+    assert torch.equal(y, omni_mlp_func(cx, cg, cu, cd, limit=limit))
+    if clamped > 0.04:
+        assert not torch.allclose(y.float().cpu(), orc.mlp_forward(x, wg, wu, wd), rtol=2e-2, atol=2e-2), "the clamp must matter here"
+    # the saved pre-activations are the unclamped ones
+    _scaled_close(gu[:, :i], gate, "saved gate", rtol=1e-2, atol_frac=4e-3)
+    ex, eg, eu, ed = orc.mlp_backward(x.float(), wg.float(), wu.float(), wd.float(), dy.float(), limit=limit)
+    for gate_up in (gu, None):
+        dx, dwg, dwu, dwd = mlp_backward(dy.cuda(), cx, cg, cu, cd, gate_up=gate_up, limit=limit)
+        for got, want, name in ((dx, ex, "dx"), (dwg, eg, "d_gate_weight"), (dwu, eu, "d_up_weight"), (dwd, ed, "d_down_weight")):
+            _scaled_close(got, want, f"{name} (limit {limit})", rtol=3e-2, atol_frac=2e-2)
+    # through autograd, limit passed positionally like the other arguments
+    ax, ag, au, ad = (v.clone().requires_grad_(True) for v in (cx, cg, cu, cd))
+    omni_mlp_func(ax, ag, au, ad, limit).backward(dy.cuda())
+    for got, want, name in ((ax.grad, ex, "dx"), (ag.grad, eg, "dwg"), (au.grad, eu, "dwu"), (ad.grad, ed, "dwd")):
+        _scaled_close(got, want, f"autograd {name} (limit {limit})", rtol=3e-2, atol_frac=2e-2)
+
+
+def test_mlp_limit_arguments_are_checked():
+    from omni_moe_b200 import _lib
+    lib = _lib.load()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a = torch.zeros(8, 8, dtype=torch.bfloat16, device="cuda")
+    rc = lib.omni_mlp_gate_up_limit(a.data_ptr(), a.data_ptr(), a.data_ptr(), 8, 8, 8, -1.0, a.data_ptr(), None, st.data_ptr(), None)
+    assert rc < 0 and b"limit" in lib.omni_last_error()
+    rc = lib.omni_mlp_gate_up_limit(a.data_ptr(), a.data_ptr(), a.data_ptr(), 8, 8, 8, float("nan"), a.data_ptr(), None, st.data_ptr(), None)
+    assert rc < 0
+    with pytest.raises(AssertionError):
+        from omni_moe_b200.ops import mlp_forward
+        mlp_forward(a, a, a, a, limit=0.0)
 
 
 def test_mlp_op_autograd():

@@ -78,6 +78,23 @@ def test_mlp_mirror(golden_dir):
     np.testing.assert_allclose(y.numpy(), g["y"], rtol=1e-5, atol=1e-7)
 
 
+def test_mlp_limit_clamps_gate_and_up(golden_dir):
+    """``limit`` follows compute_silu_mul (omni_moe/ops/triton/omni_mlp.py:54-61): clamp, then silu(gate) * up.
+    Hand-computable case: identity-like weights make gate = up = x."""
+    import torch
+    x = torch.tensor([[-3.0, -0.5, 0.25, 4.0]])
+    eye = torch.eye(4)
+    y = orc.mlp_forward(x, eye, eye, eye, limit=1.0)
+    c = x.clamp(-1.0, 1.0)
+    np.testing.assert_allclose(y.numpy(), (c * torch.sigmoid(c) * c).numpy(), rtol=1e-6)
+    g = _load(golden_dir, "mlp_mirror.npz")
+    wide = orc.mlp_forward(g["x"], g["gate"], g["up"], g["down"], limit=1e30)   # a limit nothing reaches is no limit
+    np.testing.assert_allclose(wide.numpy(), g["y"], rtol=1e-5, atol=1e-7)
+    dx, dg, du, dd = orc.mlp_backward(x, eye, eye, eye, torch.ones(1, 4), limit=1.0)
+    assert float(dg[0].abs().sum()) == 0 and float(dg[3].abs().sum()) == 0   # clamped entries pass no gradient
+    assert float(dg[1].abs().sum()) > 0 and float(dg[2].abs().sum()) > 0
+
+
 def test_schedule_against_reference(golden_dir):
     g = _load(golden_dir, "schedule_ref.npz")
     for tag in "abc":
