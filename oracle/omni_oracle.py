@@ -314,13 +314,22 @@ def expert_backward(x, up_w, down_w, routing_w, indices, dy):
     return x.grad, up.grad, dn.grad, g.grad
 
 
-def mlp_backward(x, gate_w, up_w, down_w, dy, limit=None):
-    """``(dx, d_gate_w, d_up_w, d_down_w)`` of :func:`mlp_forward` by autograd in fp32."""
+def mlp_backward(x, gate_w, up_w, down_w, dy, limit=None, preact_dtype=None):
+    """``(dx, d_gate_w, d_up_w, d_down_w)`` of :func:`mlp_forward` by autograd in fp32.
+
+    ``preact_dtype`` (e.g. ``torch.bfloat16``): round the gate / up pre-activations to that dtype before
+    the clamp and the activation, with the gradient passed straight through the rounding.  The
+    reference keeps gate and up in the input dtype between its GEMMs and its activation kernels
+    (omni_moe/ops/triton/omni_mlp.py:359-375), so with ``limit`` the set of clamped entries (a
+    discontinuity of the gradient) is decided on the rounded values."""
     x = torch.as_tensor(x).float().clone().requires_grad_(True)
     wg = torch.as_tensor(gate_w).float().clone().requires_grad_(True)
     wu = torch.as_tensor(up_w).float().clone().requires_grad_(True)
     wd = torch.as_tensor(down_w).float().clone().requires_grad_(True)
     g, u = F.linear(x, wg), F.linear(x, wu)
+    if preact_dtype is not None:
+        g = g + (g.detach().to(preact_dtype).float() - g.detach())
+        u = u + (u.detach().to(preact_dtype).float() - u.detach())
     if limit is not None:
         g, u = g.clamp(-limit, limit), u.clamp(-limit, limit)
     y = F.linear(F.silu(g) * u, wd)

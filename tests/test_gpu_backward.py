@@ -189,7 +189,9 @@ def test_mlp_limit_forward_and_backward(t, h, i, limit):
         assert not torch.allclose(y.float().cpu(), orc.mlp_forward(x, wg, wu, wd), rtol=2e-2, atol=2e-2), "the clamp must matter here"
     # the saved pre-activations are the unclamped ones
     _scaled_close(gu[:, :i], gate, "saved gate", rtol=1e-2, atol_frac=4e-3)
-    ex, eg, eu, ed = orc.mlp_backward(x.float(), wg.float(), wu.float(), wd.float(), dy.float(), limit=limit)
+    # which entries are clamped (a jump of the gradient) is decided on the bf16 pre-activations, as in the reference
+    ex, eg, eu, ed = orc.mlp_backward(x.float(), wg.float(), wu.float(), wd.float(), dy.float(), limit=limit,
+                                      preact_dtype=torch.bfloat16)
     for gate_up in (gu, None):
         dx, dwg, dwu, dwd = mlp_backward(dy.cuda(), cx, cg, cu, cd, gate_up=gate_up, limit=limit)
         for got, want, name in ((dx, ex, "dx"), (dwg, eg, "d_gate_weight"), (dwu, eu, "d_up_weight"), (dwd, ed, "d_down_weight")):
