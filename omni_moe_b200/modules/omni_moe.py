@@ -316,7 +316,9 @@ class OmniMoE(nn.Module):
 
     def forward(self, hidden_states: torch.Tensor, **kwargs) -> torch.Tensor:
         _lib.require_cuda(hidden_states)
-        if self._needs_grad(hidden_states):
+        if self._needs_grad(hidden_states) or self.hidden_size % 8 or self.intermediate_size % 8:
+            # sizes that are not multiples of 8 go through the operators one by one (they pad): the fused
+            # launch sequence moves rows in 16-byte pieces
             return self._forward_autograd(hidden_states)
         bsz, seq_len, _ = hidden_states.shape
         in_dtype = hidden_states.dtype
@@ -359,6 +361,9 @@ class GraphedOmniMoE:
         if module.gate_proj.weight.dtype != torch.bfloat16:
             raise RuntimeError("graph capture needs a bf16 module (module.to(torch.bfloat16)): "
                                "other dtypes are converted per call, which a graph would freeze")
+        if module.hidden_size % 8 or module.intermediate_size % 8:
+            raise RuntimeError("graph capture needs hidden and intermediate sizes that are a multiple of 8 "
+                               "(other sizes run operator by operator with padded copies)")
         self.module = module
         self.x = torch.zeros((num_tokens, module.hidden_size), device=dev, dtype=torch.bfloat16)
         self.y = torch.zeros((num_tokens, module.hidden_size), device=dev, dtype=torch.bfloat16)

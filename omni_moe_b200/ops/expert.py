@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import as_bf16
+from ._common import as_bf16, pad_last
 from .scheduler import schedule
 
 L2_RESIDENT_TABLE_BYTES = 48 << 20  # both tables together; above this the expert-ordered path reads less HBM
@@ -138,6 +138,11 @@ def omni_expert_func(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torc
     """
     assert x.dim() == 2 and up_weight.dim() == 2 and down_weight.shape == up_weight.shape
     assert routing_weights.shape == indices.shape and indices.size(0) == x.size(0)
+    if x.size(1) % 8:
+        # rows that are not whole 16-byte pieces: zero-padded columns add nothing to the dot products and
+        # produce output columns that are cut off again
+        y = omni_expert_func(pad_last(x), pad_last(up_weight), pad_last(down_weight), routing_weights, indices)
+        return y[:, :x.size(1)].contiguous()
     if torch.is_grad_enabled() and any(t.requires_grad for t in (x, up_weight, down_weight, routing_weights)):
         from .autograd import ExpertFunction
         return ExpertFunction.apply(x, up_weight, down_weight, routing_weights, indices)

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import as_bf16
+from ._common import as_bf16, pad_both, pad_last
 
 
 def mlp_forward(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
@@ -68,6 +68,11 @@ def omni_mlp_func(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.T
     :return y: (num_tokens, hidden_size), dtype of ``x``
     """
     assert x.dim() == 2
+    if x.size(1) % 8 or gate_weight.size(0) % 8:
+        # hidden or intermediate size not a multiple of 8: zero padding leaves the result unchanged
+        # (padded gate / up rows give silu(0) * 0 = 0 against zero columns of the down projection)
+        y = omni_mlp_func(pad_last(x), pad_both(gate_weight), pad_both(up_weight), pad_both(down_weight), limit)
+        return y[:, :x.size(1)].contiguous()
     if torch.is_grad_enabled() and any(t.requires_grad for t in (x, gate_weight, up_weight, down_weight)):
         from .autograd import MlpFunction
         return MlpFunction.apply(x, gate_weight, up_weight, down_weight, limit)
