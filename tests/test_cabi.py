@@ -45,6 +45,15 @@ def test_version_and_rejections(lib):
     assert rc < 0 and b"multiple of 8" in lib.omni_last_error()
     rc = lib.omni_mlp_fwd(None, None, None, None, 4, 64, 100, None, None, None, None, None)
     assert rc < 0 and b"intermediate" in lib.omni_last_error()
+    # entries of the backward and of the clamp: argument errors come back as codes with a message
+    rc = lib.omni_mlp_gate_up_limit(None, None, None, 4, 64, 64, -0.5, None, None, None, None)
+    assert rc < 0 and b"limit" in lib.omni_last_error()
+    rc = lib.omni_swiglu_bwd_limit(None, None, 4, 64, float("nan"), None, None, None, 0, None)
+    assert rc < 0 and b"limit" in lib.omni_last_error()
+    rc = lib.omni_swiglu_bwd(None, None, 4, 12, None, None, None, 0, None)
+    assert rc < 0 and b"multiple of 8" in lib.omni_last_error()
+    rc = lib.omni_mlp_gate_up_save(None, None, None, 4, 64, 64, None, None, None, None)
+    assert rc < 0 and b"NULL" in lib.omni_last_error()
     assert lib.omni_schedule_workspace_bytes(65536, 4096) > 4 * 65536 * 4
     assert lib.omni_schedule_workspace_bytes(-1, 4096) == 0
 
