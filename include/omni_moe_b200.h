@@ -353,15 +353,32 @@ OMNI_API int omni_mlp_gate_up_save(const void *x, const void *gate_w, const void
  *   clamp.  gate_up may be NULL (nothing saved); when given it receives the UNCLAMPED pre-activations,
  *   from which omni_swiglu_bwd_limit derives both the clamped values and where no gradient passes
  *   (outside [-limit, limit]; the boundary passes, as torch.clamp's gradient does).
+ *   omni_swiglu_bwd_limit also takes act (may be NULL): [T, I] bf16 that receives the recomputed
+ *   activation silu(gate) * up untransposed, for callers whose weight-gradient GEMMs read their
+ *   operands transposed in place (omni_gemm_bf16) and so need no transposed copies.
  */
 OMNI_API int omni_mlp_gate_up_limit(const void *x, const void *gate_w, const void *up_w, int64_t num_tokens,
                            int hidden, int intermediate, float limit, void *act, void *gate_up,
                            int32_t *status, void *stream);
 OMNI_API int omni_swiglu_bwd_limit(const void *gate_up, const void *dact, int64_t num_tokens, int intermediate,
                           float limit, void *dgate_up, void *dgate_up_t, void *act_t, int64_t ld_t,
-                          void *stream);
+                          void *act, void *stream);
 OMNI_API int omni_gemm_bf16_nt(const void *a, const void *b, int64_t m, int64_t n, int64_t k, void *out,
                       int64_t ldo, int32_t *status, void *stream);
+/*
+ * omni_gemm_bf16: out[m, n] = sum_k A[m, k] * B[n, k] with either operand optionally given transposed,
+ *   so that the gradient GEMMs of the backward (dy Wd, dy^T act, (dgate|dup)^T x, ...) read their
+ *   operands where they lie:
+ *     a_transposed == 0: a is [m, k] row-major with row stride lda;  == 1: a is [k, m] with row stride lda
+ *     b_transposed == 0: b is [n, k] row-major with row stride ldb;  == 1: b is [k, n] with row stride ldb
+ *   (a_transposed = 0, b_transposed = 0 is omni_gemm_bf16_nt).  bf16 operands, fp32 accumulation on the
+ *   tcgen05 tensor cores (a transposed operand is fed as an MN-major shared-memory tile), out bf16
+ *   with row stride ldo >= n.  lda, ldb multiples of 8; k % 8 == 0 unless both operands are
+ *   transposed (then any k: rows past k are zero-filled by the loads); pointers 16-byte aligned.
+ */
+OMNI_API int omni_gemm_bf16(const void *a, int a_transposed, int64_t lda, const void *b, int b_transposed,
+                   int64_t ldb, int64_t m, int64_t n, int64_t k, void *out, int64_t ldo, int32_t *status,
+                   void *stream);
 OMNI_API int omni_transpose_bf16(const void *in, int64_t rows, int64_t cols, int64_t ld_in, void *out,
                         int64_t out_cols, int64_t ldo, void *stream);
 OMNI_API int omni_swiglu_bwd(const void *gate_up, const void *dact, int64_t num_tokens, int intermediate,

@@ -56,9 +56,12 @@ SIGNATURES = {
     "omni_transpose_bf16": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "omni_swiglu_bwd": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "omni_mlp_gate_up_save": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "omni_gemm_bf16": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                               c_void_p, c_void_p]),
     "omni_mlp_gate_up_limit": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
                                        c_void_p]),
-    "omni_swiglu_bwd_limit": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "omni_swiglu_bwd_limit": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                      c_void_p]),
     "omni_router_bn_train_scratch_bytes": (c_size_t, [c_int64, c_int]),
     "omni_router_bn_train": (c_int, [c_void_p, c_int64, c_int64, c_int, c_float, c_float, c_float, c_float, c_void_p, c_void_p,
                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,

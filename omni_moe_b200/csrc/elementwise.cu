@@ -44,7 +44,8 @@ __global__ void __launch_bounds__(256) transpose_bf16_kernel(const uint16_t* __r
 // T..ld_t-1 zero).  A block owns a 64-token x 64-column tile; the transposes go through shared memory.
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dact,
                                                          int64_t T, int I, float limit, __nv_bfloat16* __restrict__ dgu,
-                                                         uint16_t* __restrict__ dgu_t, uint16_t* __restrict__ act_t, int64_t ld_t) {
+                                                         uint16_t* __restrict__ dgu_t, uint16_t* __restrict__ act_t, int64_t ld_t,
+                                                         __nv_bfloat16* __restrict__ act) {
   __shared__ uint16_t s_dg[kTile][kTile + 2], s_du[kTile][kTile + 2], s_ac[kTile][kTile + 2];
   const int64_t r0 = static_cast<int64_t>(blockIdx.x) * kTile;
   const int c0 = blockIdx.y * kTile;
@@ -83,6 +84,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __
       }
       *reinterpret_cast<uint4*>(dgu + t * 2 * I + c) = make_uint4(og[0], og[1], og[2], og[3]);
       *reinterpret_cast<uint4*>(dgu + t * 2 * I + I + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+      if (act) *reinterpret_cast<uint4*>(act + t * I + c) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
     }
     if (dgu_t) {
 #pragma unroll
@@ -135,14 +137,14 @@ extern "C" int omni_transpose_bf16(const void* in, int64_t rows, int64_t cols, i
 }
 
 extern "C" int omni_swiglu_bwd_limit(const void* gate_up, const void* dact, int64_t num_tokens, int intermediate, float limit,
-                                     void* dgate_up, void* dgate_up_t, void* act_t, int64_t ld_t, void* stream) {
+                                     void* dgate_up, void* dgate_up_t, void* act_t, int64_t ld_t, void* act, void* stream) {
   OMNI_REQUIRE(limit >= 0.f, "limit must be >= 0 (0 = no clamp)");
   OMNI_REQUIRE(num_tokens >= 0 && intermediate >= 8 && intermediate % 8 == 0, "intermediate must be a positive multiple of 8");
   OMNI_REQUIRE((dgate_up_t == nullptr) == (act_t == nullptr), "dgate_up_t and act_t must be given together");
   OMNI_REQUIRE(dgate_up_t == nullptr || (ld_t >= num_tokens && ld_t % 2 == 0), "ld_t must be even and >= num_tokens");
   if (num_tokens == 0) return 0;
   OMNI_REQUIRE(gate_up && dact && dgate_up, "NULL argument");
-  OMNI_REQUIRE(aligned16(gate_up) && aligned16(dact) && aligned16(dgate_up) && aligned16(dgate_up_t) && aligned16(act_t),
+  OMNI_REQUIRE(aligned16(gate_up) && aligned16(dact) && aligned16(dgate_up) && aligned16(dgate_up_t) && aligned16(act_t) && aligned16(act),
                "pointers must be 16-byte aligned");
   // with transposed outputs the token tiles also cover the padding columns num_tokens..ld_t-1 (zeros)
   const int64_t gx = ceil_div64(dgate_up_t ? ld_t : num_tokens, kTile);
@@ -150,13 +152,14 @@ extern "C" int omni_swiglu_bwd_limit(const void* gate_up, const void* dact, int6
   OMNI_REQUIRE(gy <= 65535, "intermediate too large for one launch");
   swiglu_bwd_kernel<<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gate_up), static_cast<const __nv_bfloat16*>(dact), num_tokens, intermediate, limit,
-      static_cast<__nv_bfloat16*>(dgate_up), static_cast<uint16_t*>(dgate_up_t), static_cast<uint16_t*>(act_t), ld_t);
+      static_cast<__nv_bfloat16*>(dgate_up), static_cast<uint16_t*>(dgate_up_t), static_cast<uint16_t*>(act_t), ld_t,
+      static_cast<__nv_bfloat16*>(act));
   return check_launch("swiglu_bwd_kernel");
 }
 
 extern "C" int omni_swiglu_bwd(const void* gate_up, const void* dact, int64_t num_tokens, int intermediate, void* dgate_up,
                                void* dgate_up_t, void* act_t, int64_t ld_t, void* stream) {
-  return omni_swiglu_bwd_limit(gate_up, dact, num_tokens, intermediate, 0.f, dgate_up, dgate_up_t, act_t, ld_t, stream);
+  return omni_swiglu_bwd_limit(gate_up, dact, num_tokens, intermediate, 0.f, dgate_up, dgate_up_t, act_t, ld_t, nullptr, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -576,7 +576,12 @@ struct PairCfg {
   static constexpr int kSmem = kStages * kStage + 1024 + kStaging + 1024;
 };
 
-template <int EPI, bool ROUTER>
+// MAJOR: bit 0 = the B operand is given transposed ([K, N], N contiguous), bit 1 = the A operand is
+// ([K, M], M contiguous).  Such an operand is loaded as boxes of 64 K rows x 64 M/N elements and fed to
+// the tensor cores as an MN-major tile, so the gradient GEMMs of the backward (dy Wd, dy^T act, ...)
+// read their operands where they lie instead of transposed copies.  Per slice the two 64-element
+// groups of this CTA's 128 rows / columns lie 8 KB apart.
+template <int EPI, bool ROUTER, int MAJOR = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                      const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_r0,
@@ -669,8 +674,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int sub = 0; sub < C::kSub; ++sub) {
               const int kcol = (kb * C::kSub + sub) * BK;  // past K the box is zero-filled
-              tma_load_2d_pair(sA + stage * C::kStageA + sub * C::kSliceA, &tm_a, kcol, row_a, full_leader);
-              tma_load_2d_pair(sB + stage * C::kStageB + sub * C::kSliceB, mb, kcol, row_b, full_leader);
+              const uint32_t dst_a = sA + stage * C::kStageA + sub * C::kSliceA;
+              const uint32_t dst_b = sB + stage * C::kStageB + sub * C::kSliceB;
+              if (MAJOR & 2) {
+                tma_load_2d_pair(dst_a, &tm_a, row_a, kcol, full_leader);
+                tma_load_2d_pair(dst_a + C::kSliceA / 2, &tm_a, row_a + 64, kcol, full_leader);
+              } else {
+                tma_load_2d_pair(dst_a, &tm_a, kcol, row_a, full_leader);
+              }
+              if (MAJOR & 1) {
+                tma_load_2d_pair(dst_b, mb, row_b, kcol, full_leader);
+                tma_load_2d_pair(dst_b + C::kSliceB / 2, mb, row_b + 64, kcol, full_leader);
+              } else {
+                tma_load_2d_pair(dst_b, mb, kcol, row_b, full_leader);
+              }
             }
           }
           if (++stage == C::kStages) stage = 0, phase ^= 1;
@@ -682,13 +699,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) ---------------------------
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc(2 * BM, BN);
+      constexpr uint32_t idesc = make_idesc(2 * BM, BN, (MAJOR >> 1) & 1, MAJOR & 1);
+      // start-address step of one 16-wide K step, in 16-byte units: 32 bytes along a K-major row, 16 rows of an MN-major tile
+      constexpr uint64_t kStepA = (MAJOR & 2) ? (16 * 128) >> 4 : 2, kStepB = (MAJOR & 1) ? (16 * 128) >> 4 : 2;
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       long long m_full = 0, m_tempty = 0;
       bool dead = false;
-      const uint64_t adesc0 = make_smem_desc(sA), bdesc0 = make_smem_desc(sB);
+      const uint64_t adesc0 = (MAJOR & 2) ? make_smem_desc_mn(sA, C::kSliceA / 2) : make_smem_desc(sA);
+      const uint64_t bdesc0 = (MAJOR & 1) ? make_smem_desc_mn(sB, C::kSliceB / 2) : make_smem_desc(sB);
       const long long m_t0 = clock64();
       for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
         const int acc = it & 1;
@@ -711,7 +731,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
               const uint64_t bd = bdesc + static_cast<uint64_t>(sub * (C::kSliceB >> 4));
 #pragma unroll
               for (int ks = 0; ks < BK / UMMA_K; ++ks)
-                umma_bf16_pair(d_tmem, ad + 2 * ks, bd + 2 * ks, idesc, (kb | sub | ks) != 0);
+                umma_bf16_pair(d_tmem, ad + kStepA * ks, bd + kStepB * ks, idesc, (kb | sub | ks) != 0);
             }
           }
           umma_commit_pair(bar_empty + 8 * stage, 3);  // both CTAs may refill this stage
@@ -802,11 +822,11 @@ EncodeFn get_encode() {
 }
 
 // Map of a row-major bf16 matrix [rows, cols] with boxes of box_rows x 64 columns, 128-byte swizzle.
-int make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+int make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int box_rows, int64_t ld = 0) {
   EncodeFn enc = get_encode();
   if (!enc) return fail(-2, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld > 0 ? ld : cols) * 2};
   const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -884,7 +904,7 @@ int launch(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, c
   return check_launch("gemm_kernel");
 }
 
-template <int EPI, bool ROUTER>
+template <int EPI, bool ROUTER, int MAJOR = 0>
 int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const CUtensorMap& r0,
                 const CUtensorMap& r1, GemmArgs g, cudaStream_t st) {
   // output map: only when the bf16 output qualifies for TMA stores; otherwise any valid map fills the slot
@@ -905,13 +925,13 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& 
   using C = PairCfg;
   static OncePerDevice once;
   if (once.first() &&
-      cudaFuncSetAttribute(gemm_pair_kernel<EPI, ROUTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+      cudaFuncSetAttribute(gemm_pair_kernel<EPI, ROUTER, MAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
     return fail(-2, "cannot raise the shared-memory limit to %d bytes", C::kSmem);
   const int tiles = g.tiles_m * (g.tiles_n + (ROUTER ? g.router_tiles : 0));
   const int max_pairs = sm_count() / 2;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
   if (g.grid_limit > 0 && g.grid_limit < pairs) pairs = g.grid_limit;
-  launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, mo, ml, g);
+  launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER, MAJOR>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, mo, ml, g);
   return check_launch("gemm_pair_kernel");
 }
 
@@ -1102,6 +1122,39 @@ extern "C" int omni_gemm_bf16_nt(const void* a, const void* b, int64_t m, int64_
   g.tiles_m = ceil_div(g.M, BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(g.N, 128);
   return launch<128, EPI_RES>(ma, mb, mb, g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int omni_gemm_bf16(const void* a, int a_transposed, int64_t lda, const void* b, int b_transposed, int64_t ldb, int64_t m,
+                              int64_t n, int64_t k, void* out, int64_t ldo, int32_t* status, void* stream) {
+  OMNI_REQUIRE(m >= 0 && m < (int64_t(1) << 31) - 2 * BM, "m out of range");
+  OMNI_REQUIRE(n >= 0 && n < (int64_t(1) << 31) - 256, "n out of range");
+  OMNI_REQUIRE(k >= 1 && k < (int64_t(1) << 31) - 256, "k out of range");
+  OMNI_REQUIRE(ldo >= n, "ldo %lld < n", static_cast<long long>(ldo));
+  // rows of either operand must be whole 16-byte pieces: the row stride, and the row length where it is the K extent
+  OMNI_REQUIRE(lda >= (a_transposed ? m : k) && lda % 8 == 0, "lda must be a multiple of 8 and cover a row, got %lld", static_cast<long long>(lda));
+  OMNI_REQUIRE(ldb >= (b_transposed ? n : k) && ldb % 8 == 0, "ldb must be a multiple of 8 and cover a row, got %lld", static_cast<long long>(ldb));
+  OMNI_REQUIRE((a_transposed && b_transposed) || k % 8 == 0, "k must be a multiple of 8 unless both operands are transposed, got %lld",
+               static_cast<long long>(k));
+  if (m == 0 || n == 0) return 0;
+  OMNI_REQUIRE(a && b && out && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(a) && aligned16(b) && aligned16(out), "pointers must be 16-byte aligned");
+  OMNI_REQUIRE(use_pairs(), "omni_gemm_bf16 runs on the CTA-pair kernels only (OMNI_MOE_B200_GEMM=1cta is set)");
+  CUtensorMap ma, mb;
+  // transposed operand: the matrix in memory is [k, m] (or [k, n]); boxes of 64 K rows x 64 elements
+  if (int e = a_transposed ? make_map(&ma, a, k, m, 64, lda) : make_map(&ma, a, m, k, BM, lda)) return e;
+  if (int e = b_transposed ? make_map(&mb, b, k, n, 64, ldb) : make_map(&mb, b, n, k, 128, ldb)) return e;
+  GemmArgs g{};
+  g.M = static_cast<int>(m), g.N = static_cast<int>(n), g.K = static_cast<int>(k), g.dual = 0;
+  g.out = out, g.ldo = ldo, g.residual = nullptr, g.ldr = 0, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  g.tiles_m = ceil_div(g.M, 2 * BM);
+  g.tiles_n = g.tiles_n_axis = ceil_div(g.N, 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch ((a_transposed ? 2 : 0) | (b_transposed ? 1 : 0)) {
+    case 0: return launch_pair<EPI_RES, false, 0>(ma, mb, mb, mb, mb, g, st);
+    case 1: return launch_pair<EPI_RES, false, 1>(ma, mb, mb, mb, mb, g, st);
+    case 2: return launch_pair<EPI_RES, false, 2>(ma, mb, mb, mb, mb, g, st);
+    default: return launch_pair<EPI_RES, false, 3>(ma, mb, mb, mb, mb, g, st);
+  }
 }
 
 extern "C" int omni_mlp_fwd(const void* x, const void* gate_w, const void* up_w, const void* down_w, int64_t num_tokens,

@@ -147,9 +147,26 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, both K-major, M x N tile.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+// Shared-memory matrix descriptor of an MN-major tile (the operand is stored transposed: rows are K
+// indices, the M or N index is contiguous): 128-byte rows of 64 consecutive M/N elements in the
+// 128-byte swizzle, one row per K index, 8 K rows = one 1024-byte swizzle atom (stride byte offset
+// between 8-row groups: 1024), and the next 64 M/N elements start `group_bytes` further on (leading
+// byte offset).  A 16-wide K step of the MMA advances the start address by 16 rows = 2048 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t group_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>(group_bytes >> 4) << 16;       // leading byte offset: next 64-element M/N group
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset: next 8 K rows
+  d |= static_cast<uint64_t>(1) << 46;                      // version
+  d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, M x N tile; a_mn / b_mn = 1 when
+// that operand's shared-memory tile is MN-major (bits 15 and 16), 0 for K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn = 0, int b_mn = 0) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 

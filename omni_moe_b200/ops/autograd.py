@@ -197,6 +197,29 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, s
     return out
 
 
+def gemm(a: torch.Tensor, b: torch.Tensor, a_transposed: bool = False, b_transposed: bool = False,
+         out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``out [m, n] = A @ B^T`` with ``A = a`` (``[m, k]``) or ``a^T`` (``a`` is ``[k, m]``, ``a_transposed``) and
+    ``B = b`` (``[n, k]``) or ``b^T`` (``b`` is ``[k, n]``, ``b_transposed``): bf16 operands read where they lie
+    (row strides honoured, so column slices of wider matrices work), fp32 accumulation, bf16 result."""
+    _lib.require_cuda(a, b)
+    assert a.dtype == b.dtype == torch.bfloat16 and a.dim() == b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    k, m = a.shape if a_transposed else a.shape[::-1]
+    kb, n = b.shape if b_transposed else b.shape[::-1]
+    assert k == kb, f"contraction sizes differ: {k} vs {kb}"
+    if out is None:
+        out = torch.empty((m, n), device=a.device, dtype=torch.bfloat16)
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16 and out.stride(1) == 1
+    if status is None:
+        status = _status(a.device)
+    if m and n:
+        with torch.cuda.device(a.device):
+            _lib.check(_lib.load().omni_gemm_bf16(a.data_ptr(), int(a_transposed), a.stride(0), b.data_ptr(), int(b_transposed),
+                                                  b.stride(0), m, n, k, out.data_ptr(), out.stride(0), status.data_ptr(),
+                                                  _lib.stream_ptr()))
+    return out
+
+
 def transpose_padded(src: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """``src [r, c]`` bf16 (row stride honoured) -> ``[c, pad8(r)]`` with zero padding columns, or into
     ``out``, a ``[c, >= r]`` column slice of a wider row-major matrix."""
@@ -210,6 +233,14 @@ def transpose_padded(src: torch.Tensor, out: torch.Tensor | None = None) -> torc
             _lib.check(_lib.load().omni_transpose_bf16(src.data_ptr(), r, c, src.stride(0), out.data_ptr(), out.size(1),
                                                        out.stride(0), _lib.stream_ptr()))
     return out
+
+
+def _operands_in_place() -> bool:
+    """The gradient GEMMs read transposed operands in place on the CTA-pair kernels; with the single-CTA
+    kernels forced (``OMNI_MOE_B200_GEMM=1cta``) or ``OMNI_MOE_B200_MLP_BWD=copies`` they go through
+    transposed copies and the K-contiguous GEMM."""
+    import os
+    return os.environ.get("OMNI_MOE_B200_GEMM", "")[:1] != "1" and os.environ.get("OMNI_MOE_B200_MLP_BWD", "") != "copies"
 
 
 def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tensor,
@@ -246,6 +277,23 @@ def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, u
         gu = torch.empty((t, 2 * i), **bf)
         gemm_nt(x, wg, gu[:, :i], status)
         gemm_nt(x, wu, gu[:, i:], status)
+    if _operands_in_place():
+        # every GEMM reads its operands where they lie: a matrix whose contraction index is not the
+        # contiguous one is fed to the tensor cores as an MN-major tile (omni_gemm_bf16)
+        dact = gemm(dy, wd, False, True, status=status)                       # dy [T,H] @ Wd [H,I]
+        dgu = torch.empty((t, 2 * i), **bf)
+        act = torch.empty((t, i), **bf) if need_weight_grads else None
+        with torch.cuda.device(dev):
+            _lib.check(lib.omni_swiglu_bwd_limit(gu.data_ptr(), dact.data_ptr(), t, i, float(limit or 0.0), dgu.data_ptr(),
+                                                 None, None, 0, _lib.ptr(act), _lib.stream_ptr()))
+        # dx = dgate @ Wg + dup @ Wu = (dgate | dup) @ (Wg ; Wu)
+        dx = gemm(dgu, torch.cat((wg, wu), 0), False, True, status=status)
+        d_wg = d_wu = d_wd = None
+        if need_weight_grads:
+            d_wd = gemm(dy, act, True, True, status=status)                   # dy^T [H,T] @ act [T,I]
+            d_wgu = gemm(dgu, x, True, True, status=status)                   # (dgate | dup)^T [2I,T] @ x [T,H]
+            d_wg, d_wu = d_wgu[:i], d_wgu[i:]
+        return dx, d_wg, d_wu, d_wd
     # dact = dy @ Wd   (Wd is [H, I]: its transpose has the contraction dimension contiguous)
     dact = gemm_nt(dy, transpose_padded(wd), None, status)
     dgu = torch.empty((t, 2 * i), **bf)
@@ -254,7 +302,7 @@ def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, u
     act_t = torch.empty((i, tp), **bf) if need_weight_grads else None
     with torch.cuda.device(dev):
         _lib.check(lib.omni_swiglu_bwd_limit(gu.data_ptr(), dact.data_ptr(), t, i, float(limit or 0.0), dgu.data_ptr(),
-                                             _lib.ptr(dgu_t), _lib.ptr(act_t), tp, _lib.stream_ptr()))
+                                             _lib.ptr(dgu_t), _lib.ptr(act_t), tp, None, _lib.stream_ptr()))
     # dx = dgate @ Wg + dup @ Wu = dgu @ (Wg ; Wu): B operand [H, 2I] = (Wg^T | Wu^T)
     wgu_t = torch.empty((h, 2 * i), **bf)
     transpose_padded(wg, wgu_t[:, :i])

@@ -48,7 +48,7 @@ def test_version_and_rejections(lib):
     # entries of the backward and of the clamp: argument errors come back as codes with a message
     rc = lib.omni_mlp_gate_up_limit(None, None, None, 4, 64, 64, -0.5, None, None, None, None)
     assert rc < 0 and b"limit" in lib.omni_last_error()
-    rc = lib.omni_swiglu_bwd_limit(None, None, 4, 64, float("nan"), None, None, None, 0, None)
+    rc = lib.omni_swiglu_bwd_limit(None, None, 4, 64, float("nan"), None, None, None, 0, None, None)
     assert rc < 0 and b"limit" in lib.omni_last_error()
     rc = lib.omni_swiglu_bwd(None, None, 4, 12, None, None, None, 0, None)
     assert rc < 0 and b"multiple of 8" in lib.omni_last_error()

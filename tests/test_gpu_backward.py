@@ -217,6 +217,47 @@ def test_mlp_limit_arguments_are_checked():
         mlp_forward(a, a, a, a, limit=0.0)
 
 
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (300, 200, 72), (8, 8, 8), (1000, 1032, 264), (4096, 1024, 4096), (129, 520, 1000)])
+def test_gemm_with_transposed_operands(m, n, k, a_t, b_t):
+    """Operands given as [k, m] / [k, n] are fed to the tensor cores as MN-major tiles: same product."""
+    from omni_moe_b200.ops.autograd import gemm
+    if (a_t and m % 8) or (b_t and n % 8):
+        pytest.skip("a transposed operand's rows (m or n elements) must be whole 16-byte pieces")
+    g = gen(m + n + k)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    b = torch.randn(n, k, generator=g).bfloat16()
+    want = a.float() @ b.float().t()
+    ca = (a.t().contiguous() if a_t else a).cuda()
+    cb = (b.t().contiguous() if b_t else b).cuda()
+    out = gemm(ca, cb, a_t, b_t)
+    _lib_status_ok()
+    _scaled_close(out, want, f"gemm a_t={a_t} b_t={b_t}", rtol=1e-2, atol_frac=4e-3)
+    # operands that are column slices of wider matrices (row stride > row length), output likewise
+    wide_a = torch.zeros(ca.size(0), ca.size(1) + 16, dtype=torch.bfloat16, device="cuda")
+    wide_a[:, 8:8 + ca.size(1)] = ca
+    wide_b = torch.zeros(cb.size(0), cb.size(1) + 24, dtype=torch.bfloat16, device="cuda")   # row strides stay multiples of 8
+    wide_b[:, 16:16 + cb.size(1)] = cb
+    wide_o = torch.full((m, n + 8), 7.0, dtype=torch.bfloat16, device="cuda")
+    gemm(wide_a[:, 8:8 + ca.size(1)], wide_b[:, 16:16 + cb.size(1)], a_t, b_t, out=wide_o[:, :n])
+    assert torch.equal(wide_o[:, :n], out) and bool((wide_o[:, n:] == 7.0).all())
+
+
+def _lib_status_ok():
+    from omni_moe_b200 import _lib
+    _lib.check_device_status()
+
+
+def test_gemm_transposed_any_k():
+    from omni_moe_b200.ops.autograd import gemm
+    g = gen(77)
+    for k in (1, 5, 63, 65, 1001):
+        a = torch.randn(k, 136, generator=g).bfloat16()
+        b = torch.randn(k, 72, generator=g).bfloat16()
+        out = gemm(a.cuda(), b.cuda(), True, True)
+        _scaled_close(out, a.float().t() @ b.float(), f"k={k}", rtol=1e-2, atol_frac=4e-3)
+
+
 def test_mlp_op_autograd():
     from omni_moe.ops.triton import triton_omni_mlp_func
     t, h, i = 200, 128, 512
