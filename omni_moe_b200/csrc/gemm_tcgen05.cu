@@ -821,6 +821,22 @@ EncodeFn get_encode() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled is a driver call and wants a context current on the calling thread.  A thread that
+// has made no runtime call on this device yet (the autograd engine's backward thread, when a GEMM is the
+// first thing it runs) has none: a runtime query of one of this file's kernels binds the device's primary
+// context, after which the encode is retried once.
+void bind_primary_context();
+
+template <typename... Args>
+CUresult encode_tiled(EncodeFn enc, Args... args) {
+  CUresult r = enc(args...);
+  if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+    bind_primary_context();
+    r = enc(args...);
+  }
+  return r;
+}
+
 // Map of a row-major bf16 matrix [rows, cols] with boxes of box_rows x 64 columns, 128-byte swizzle.
 int make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int box_rows, int64_t ld = 0) {
   EncodeFn enc = get_encode();
@@ -829,7 +845,7 @@ int make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int bo
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld > 0 ? ld : cols) * 2};
   const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  const CUresult r = encode_tiled(enc, m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-2, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
@@ -845,7 +861,7 @@ int make_out_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, in
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
   const cuuint32_t box[2] = {64, 32};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  const CUresult r = encode_tiled(enc, m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-2, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
@@ -860,7 +876,7 @@ int make_logits_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols)
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 4};
   const cuuint32_t box[2] = {32, 32};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  const CUresult r = encode_tiled(enc, m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-2, "cuTensorMapEncodeTiled (logits) failed with CUresult %d", static_cast<int>(r));
@@ -933,6 +949,12 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& 
   if (g.grid_limit > 0 && g.grid_limit < pairs) pairs = g.grid_limit;
   launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER, MAJOR>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, mo, ml, g);
   return check_launch("gemm_pair_kernel");
+}
+
+void bind_primary_context() {
+  cudaFuncAttributes attr;
+  (void)cudaFuncGetAttributes(&attr, gemm_kernel<64, EPI_F32>);
+  (void)cudaGetLastError();
 }
 
 // OMNI_MOE_B200_GEMM=1cta selects the single-CTA kernels for the MLP GEMMs (default: CTA pairs).

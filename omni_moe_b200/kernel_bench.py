@@ -179,6 +179,22 @@ def run_backward(name: str, reps: int):
             us = time_graph(lambda s: chk(lib.omni_gemm_bf16_nt(a.data_ptr(), b.data_ptr(), m_, n_, k_, o.data_ptr(), n_,
                                                                 status.data_ptr(), s)), reps=reps)
             report(label, us, "tensor", 2.0 * m_ * n_ * k_, f"{m_} x {n_} x {k_}")
+        # the same four products with the operands read in place (transposed ones as MN-major tiles): what the
+        # MLP backward runs by default
+        act = torch.empty((T, I), **bf)
+        us = time_graph(lambda s: chk(lib.omni_swiglu_bwd_limit(gu.data_ptr(), dact.data_ptr(), T, I, 0.0, dgu.data_ptr(), None, None,
+                                                                0, act.data_ptr(), s)), reps=reps)
+        report("swiglu_bwd (dgate | dup and act, no transposed copies)", us, "hbm", 2.0 * (3 * T * I + 2 * T * I + T * I))
+        wgu = _randn_bf16((2 * I, H), H ** -0.5, dev, 9)
+        xb = _randn_bf16((T, H), 1.0, dev, 10)
+        in_place = (("gemm dact = dy Wd, Wd in place", dy, 0, wd, 1, T, I, H, out_ti),
+                    ("gemm dx = dgu (Wg;Wu), weights in place", dgu, 0, wgu, 1, T, H, 2 * I, out_th),
+                    ("gemm dWd = dy^T act, both in place", dy, 1, act, 1, H, I, T, out_hi),
+                    ("gemm dWgu = dgu^T x, both in place", dgu, 1, xb, 1, 2 * I, H, T, out_2ih))
+        for label, a, at, b, bt, m_, n_, k_, o in in_place:
+            us = time_graph(lambda s: chk(lib.omni_gemm_bf16(a.data_ptr(), at, a.stride(0), b.data_ptr(), bt, b.stride(0), m_, n_, k_,
+                                                             o.data_ptr(), n_, status.data_ptr(), s)), reps=reps)
+            report(label, us, "tensor", 2.0 * m_ * n_ * k_, f"{m_} x {n_} x {k_}")
     torch.cuda.synchronize()
     if int(status.item()):
         raise RuntimeError("a kernel reported a device-side fault: " + _lib.status_message(int(status.item())))

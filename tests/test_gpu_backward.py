@@ -258,6 +258,30 @@ def test_gemm_transposed_any_k():
         _scaled_close(out, a.float().t() @ b.float(), f"k={k}", rtol=1e-2, atol_frac=4e-3)
 
 
+def test_gemm_first_call_on_a_fresh_thread():
+    """The tensor-map encode is a driver call: it must also work on a thread that has not touched CUDA yet
+    (the autograd engine runs the backward on such a thread)."""
+    import threading
+    from omni_moe_b200.ops.autograd import gemm
+    g = gen(3)
+    a = torch.randn(64, 136, generator=g).bfloat16().cuda()
+    b = torch.randn(64, 72, generator=g).bfloat16().cuda()
+    torch.cuda.synchronize()
+    box = {}
+
+    def work():
+        try:
+            box["out"] = gemm(a, b, True, True)
+            torch.cuda.synchronize()
+        except Exception as e:  # noqa: BLE001
+            box["err"] = e
+    th = threading.Thread(target=work)
+    th.start()
+    th.join()
+    assert "err" not in box, box.get("err")
+    _scaled_close(box["out"], a.float().t() @ b.float(), "gemm on a fresh thread", rtol=1e-2, atol_frac=4e-3)
+
+
 def test_mlp_op_autograd():
     from omni_moe.ops.triton import triton_omni_mlp_func
     t, h, i = 200, 128, 512
