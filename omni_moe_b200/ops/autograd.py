@@ -286,11 +286,14 @@ def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, u
         with torch.cuda.device(dev):
             _lib.check(lib.omni_swiglu_bwd_limit(gu.data_ptr(), dact.data_ptr(), t, i, float(limit or 0.0), dgu.data_ptr(),
                                                  None, None, 0, _lib.ptr(act), _lib.stream_ptr()))
-        # dx = dgate @ Wg + dup @ Wu = (dgate | dup) @ (Wg ; Wu)
-        dx = gemm(dgu, torch.cat((wg, wu), 0), False, True, status=status)
+        # order: the product that reads act runs right after the kernel that wrote it, and the two that read
+        # (dgate | dup) run back to back, so the second finds it in L2
         d_wg = d_wu = d_wd = None
         if need_weight_grads:
             d_wd = gemm(dy, act, True, True, status=status)                   # dy^T [H,T] @ act [T,I]
+        # dx = dgate @ Wg + dup @ Wu = (dgate | dup) @ (Wg ; Wu)
+        dx = gemm(dgu, torch.cat((wg, wu), 0), False, True, status=status)
+        if need_weight_grads:
             d_wgu = gemm(dgu, x, True, True, status=status)                   # (dgate | dup)^T [2I,T] @ x [T,H]
             d_wg, d_wu = d_wgu[:i], d_wgu[i:]
         return dx, d_wg, d_wu, d_wd
