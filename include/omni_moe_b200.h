@@ -379,6 +379,15 @@ OMNI_API int omni_gemm_bf16_nt(const void *a, const void *b, int64_t m, int64_t 
 OMNI_API int omni_gemm_bf16(const void *a, int a_transposed, int64_t lda, const void *b, int b_transposed,
                    int64_t ldb, int64_t m, int64_t n, int64_t k, void *out, int64_t ldo, int32_t *status,
                    void *stream);
+/*
+ * omni_gemm_bf16_stacked_b: omni_gemm_bf16 with a transposed B given as two matrices stacked along K:
+ *   B^T = (b0 ; b1), b0 [k_split, n] and b1 [k - k_split, n], both with row stride ldb; k_split a
+ *   multiple of 64.  out = A (b0 ; b1): the input gradient of two linear layers that share their
+ *   input, dx = (dgate | dup) (Wg ; Wu), without concatenating the weights.
+ */
+OMNI_API int omni_gemm_bf16_stacked_b(const void *a, int a_transposed, int64_t lda, const void *b0, const void *b1,
+                             int64_t k_split, int64_t ldb, int64_t m, int64_t n, int64_t k, void *out,
+                             int64_t ldo, int32_t *status, void *stream);
 OMNI_API int omni_transpose_bf16(const void *in, int64_t rows, int64_t cols, int64_t ld_in, void *out,
                         int64_t out_cols, int64_t ldo, void *stream);
 OMNI_API int omni_swiglu_bwd(const void *gate_up, const void *dact, int64_t num_tokens, int intermediate,

@@ -58,6 +58,8 @@ SIGNATURES = {
     "omni_mlp_gate_up_save": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "omni_gemm_bf16": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                c_void_p, c_void_p]),
+    "omni_gemm_bf16_stacked_b": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                         c_void_p, c_int64, c_void_p, c_void_p]),
     "omni_mlp_gate_up_limit": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
                                        c_void_p]),
     "omni_swiglu_bwd_limit": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,

@@ -55,7 +55,7 @@ struct GemmArgs {
   int64_t ldgu;
   // router tile columns of the fused gate/up + router-gate launch (pair kernel, EPI_SWIGLU only)
   int router_tiles;       // tile columns holding router sub-keys (0 = none); they come first in tile order
-  int router_n;           // sqrt_n
+  int router_n;           // sqrt_n; kernels without router tiles and with a transposed B: k_split (0 = one B matrix)
   float* logits;          // [M, 2 * sqrt_n]
   int* status;
   long long* prof;  // debug: per-CTA cycle counters (8 words per CTA), normally null
@@ -683,8 +683,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 tma_load_2d_pair(dst_a, &tm_a, kcol, row_a, full_leader);
               }
               if (MAJOR & 1) {
-                tma_load_2d_pair(dst_b, mb, row_b, kcol, full_leader);
-                tma_load_2d_pair(dst_b + C::kSliceB / 2, mb, row_b + 64, kcol, full_leader);
+                // a transposed B may be two matrices stacked along K ((Wg ; Wu) of the MLP backward): rows
+                // [0, k_split) come from the first map, the rest from the second (k_split is a multiple of 64)
+                const bool second = !ROUTER && g.router_n > 0 && kcol >= g.router_n;
+                const CUtensorMap* mbk = second ? &tm_b1 : mb;
+                const int kb_row = second ? kcol - g.router_n : kcol;
+                tma_load_2d_pair(dst_b, mbk, row_b, kb_row, full_leader);
+                tma_load_2d_pair(dst_b + C::kSliceB / 2, mbk, row_b + 64, kb_row, full_leader);
               } else {
                 tma_load_2d_pair(dst_b, mb, kcol, row_b, full_leader);
               }
@@ -1146,8 +1151,9 @@ extern "C" int omni_gemm_bf16_nt(const void* a, const void* b, int64_t m, int64_
   return launch<128, EPI_RES>(ma, mb, mb, g, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int omni_gemm_bf16(const void* a, int a_transposed, int64_t lda, const void* b, int b_transposed, int64_t ldb, int64_t m,
-                              int64_t n, int64_t k, void* out, int64_t ldo, int32_t* status, void* stream) {
+namespace {
+int gemm_bf16_impl(const void* a, int a_transposed, int64_t lda, const void* b, const void* b1, int64_t k_split, int b_transposed,
+                   int64_t ldb, int64_t m, int64_t n, int64_t k, void* out, int64_t ldo, int32_t* status, void* stream) {
   OMNI_REQUIRE(m >= 0 && m < (int64_t(1) << 31) - 2 * BM, "m out of range");
   OMNI_REQUIRE(n >= 0 && n < (int64_t(1) << 31) - 256, "n out of range");
   OMNI_REQUIRE(k >= 1 && k < (int64_t(1) << 31) - 256, "k out of range");
@@ -1164,19 +1170,44 @@ extern "C" int omni_gemm_bf16(const void* a, int a_transposed, int64_t lda, cons
   CUtensorMap ma, mb;
   // transposed operand: the matrix in memory is [k, m] (or [k, n]); boxes of 64 K rows x 64 elements
   if (int e = a_transposed ? make_map(&ma, a, k, m, 64, lda) : make_map(&ma, a, m, k, BM, lda)) return e;
-  if (int e = b_transposed ? make_map(&mb, b, k, n, 64, ldb) : make_map(&mb, b, n, k, 128, ldb)) return e;
+  CUtensorMap mb1;
+  if (b1 != nullptr) {
+    // first matrix: K rows [0, k_split); second: the remaining k - k_split rows
+    if (int e = make_map(&mb, b, k_split, n, 64, ldb)) return e;
+    if (int e = make_map(&mb1, b1, k - k_split, n, 64, ldb)) return e;
+  } else {
+    if (int e = b_transposed ? make_map(&mb, b, k, n, 64, ldb) : make_map(&mb, b, n, k, 128, ldb)) return e;
+    mb1 = mb;
+  }
   GemmArgs g{};
+  g.router_n = b1 != nullptr ? static_cast<int>(k_split) : 0;
   g.M = static_cast<int>(m), g.N = static_cast<int>(n), g.K = static_cast<int>(k), g.dual = 0;
   g.out = out, g.ldo = ldo, g.residual = nullptr, g.ldr = 0, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
   g.tiles_m = ceil_div(g.M, 2 * BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(g.N, 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch ((a_transposed ? 2 : 0) | (b_transposed ? 1 : 0)) {
-    case 0: return launch_pair<EPI_RES, false, 0>(ma, mb, mb, mb, mb, g, st);
-    case 1: return launch_pair<EPI_RES, false, 1>(ma, mb, mb, mb, mb, g, st);
-    case 2: return launch_pair<EPI_RES, false, 2>(ma, mb, mb, mb, mb, g, st);
-    default: return launch_pair<EPI_RES, false, 3>(ma, mb, mb, mb, mb, g, st);
+    case 0: return launch_pair<EPI_RES, false, 0>(ma, mb, mb1, mb, mb, g, st);
+    case 1: return launch_pair<EPI_RES, false, 1>(ma, mb, mb1, mb, mb, g, st);
+    case 2: return launch_pair<EPI_RES, false, 2>(ma, mb, mb1, mb, mb, g, st);
+    default: return launch_pair<EPI_RES, false, 3>(ma, mb, mb1, mb, mb, g, st);
   }
+}
+}  // namespace
+
+extern "C" int omni_gemm_bf16(const void* a, int a_transposed, int64_t lda, const void* b, int b_transposed, int64_t ldb, int64_t m,
+                              int64_t n, int64_t k, void* out, int64_t ldo, int32_t* status, void* stream) {
+  return gemm_bf16_impl(a, a_transposed, lda, b, nullptr, 0, b_transposed, ldb, m, n, k, out, ldo, status, stream);
+}
+
+extern "C" int omni_gemm_bf16_stacked_b(const void* a, int a_transposed, int64_t lda, const void* b0, const void* b1, int64_t k_split,
+                                        int64_t ldb, int64_t m, int64_t n, int64_t k, void* out, int64_t ldo, int32_t* status,
+                                        void* stream) {
+  OMNI_REQUIRE(b0 && b1, "NULL argument");
+  OMNI_REQUIRE(k_split > 0 && k_split < k && k_split % 64 == 0, "k_split must be a multiple of 64 inside (0, k), got %lld",
+               static_cast<long long>(k_split));
+  OMNI_REQUIRE(aligned16(b1), "pointers must be 16-byte aligned");
+  return gemm_bf16_impl(a, a_transposed, lda, b0, b1, k_split, 1, ldb, m, n, k, out, ldo, status, stream);
 }
 
 extern "C" int omni_mlp_fwd(const void* x, const void* gate_w, const void* up_w, const void* down_w, int64_t num_tokens,

@@ -292,7 +292,14 @@ def mlp_backward(dy: torch.Tensor, x: torch.Tensor, gate_weight: torch.Tensor, u
         if need_weight_grads:
             d_wd = gemm(dy, act, True, True, status=status)                   # dy^T [H,T] @ act [T,I]
         # dx = dgate @ Wg + dup @ Wu = (dgate | dup) @ (Wg ; Wu)
-        dx = gemm(dgu, torch.cat((wg, wu), 0), False, True, status=status)
+        if i % 64 == 0:
+            # the two weight matrices are read in place as one B operand stacked along K
+            dx = torch.empty((t, h), **bf)
+            with torch.cuda.device(dev):
+                _lib.check(lib.omni_gemm_bf16_stacked_b(dgu.data_ptr(), 0, 2 * i, wg.data_ptr(), wu.data_ptr(), i, h, t, h, 2 * i,
+                                                        dx.data_ptr(), h, status.data_ptr(), _lib.stream_ptr()))
+        else:
+            dx = gemm(dgu, torch.cat((wg, wu), 0), False, True, status=status)
         if need_weight_grads:
             d_wgu = gemm(dgu, x, True, True, status=status)                   # (dgate | dup)^T [2I,T] @ x [T,H]
             d_wg, d_wu = d_wgu[:i], d_wgu[i:]

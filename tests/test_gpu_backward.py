@@ -258,6 +258,25 @@ def test_gemm_transposed_any_k():
         _scaled_close(out, a.float().t() @ b.float(), f"k={k}", rtol=1e-2, atol_frac=4e-3)
 
 
+@pytest.mark.parametrize("m,n,k0,k1", [(256, 256, 64, 64), (300, 1024, 4096, 4096), (129, 72, 128, 40), (64, 520, 192, 1000)])
+def test_gemm_with_b_stacked_along_k(m, n, k0, k1):
+    """out = A (b0 ; b1) with the two transposed B matrices read in place."""
+    from omni_moe_b200 import _lib
+    g = gen(m + n + k0 + k1)
+    k = k0 + k1
+    a = torch.randn(m, k, generator=g).bfloat16()
+    b0 = torch.randn(k0, n, generator=g).bfloat16()
+    b1 = torch.randn(k1, n, generator=g).bfloat16()
+    want = a.float() @ torch.cat((b0, b1), 0).float()
+    ca, c0, c1 = a.cuda(), b0.cuda(), b1.cuda()
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    st = _lib.device_status(out.device)
+    _lib.check(_lib.load().omni_gemm_bf16_stacked_b(ca.data_ptr(), 0, k, c0.data_ptr(), c1.data_ptr(), k0, n, m, n, k, out.data_ptr(), n,
+                                                    st.data_ptr(), _lib.stream_ptr()))
+    _lib.check_device_status()
+    _scaled_close(out, want, "stacked B", rtol=1e-2, atol_frac=4e-3)
+
+
 def test_gemm_first_call_on_a_fresh_thread():
     """The tensor-map encode is a driver call: it must also work on a thread that has not touched CUDA yet
     (the autograd engine runs the backward on such a thread)."""
