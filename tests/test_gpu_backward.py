@@ -277,6 +277,25 @@ def test_gemm_with_b_stacked_along_k(m, n, k0, k1):
     _scaled_close(out, want, "stacked B", rtol=1e-2, atol_frac=4e-3)
 
 
+@pytest.mark.parametrize("t,h,i", [(300, 256, 1024), (77, 72, 264)])
+def test_mlp_backward_routes_agree(t, h, i, monkeypatch):
+    """Operands read in place (default) and the route through transposed copies give the same gradients up to
+    the bf16 rounding of the intermediates."""
+    from omni_moe_b200.ops.autograd import mlp_backward
+    g = gen(t * 3 + i)
+    x = torch.randn(t, h, generator=g).bfloat16().cuda()
+    wg = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16().cuda()
+    wu = (torch.randn(i, h, generator=g) / h ** 0.5).bfloat16().cuda()
+    wd = (torch.randn(h, i, generator=g) / i ** 0.5).bfloat16().cuda()
+    dy = (torch.randn(t, h, generator=g) * 0.5).bfloat16().cuda()
+    monkeypatch.delenv("OMNI_MOE_B200_MLP_BWD", raising=False)
+    in_place = mlp_backward(dy, x, wg, wu, wd)
+    monkeypatch.setenv("OMNI_MOE_B200_MLP_BWD", "copies")
+    copies = mlp_backward(dy, x, wg, wu, wd)
+    for a, b, name in zip(in_place, copies, ("dx", "d_gate", "d_up", "d_down")):
+        _scaled_close(a, b, name, rtol=1e-2, atol_frac=4e-3)
+
+
 def test_gemm_first_call_on_a_fresh_thread():
     """The tensor-map encode is a driver call: it must also work on a thread that has not touched CUDA yet
     (the autograd engine runs the backward on such a thread)."""
