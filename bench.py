@@ -16,13 +16,27 @@ Printed JSON keys (one line, rank 0):
              its tokens from pinned host memory, runs the forward and copies the result back;
              steps are pipelined over independent slots
   roofline   of the dominant kernel (gate/up GEMM with the SwiGLU epilogue), timed live here
-  cpu_baseline  the CPU oracle (a restatement of the reference's PyTorch path) on the host cores
-Synthetic data: x ~ N(0,1), weights from the module's default initialisation under seed 0.
+  cpu_baseline  the reference's own PyTorch layer (OmniMoE_Torch) on the host cores, N = 1 only
+  config     static description of the workload, identical in both arms
+  detail     measured extras: the same step one at a time, the sustained figure (the K-step block repeated for
+             a second or more, median block, with the SM clock sampled meanwhile), layer_frac (algorithmic
+             FLOP of the whole layer / step time / measured peak)
+  partitioned_c5  the largest configuration (65536 tokens, hidden 4096, intermediate 11008, 1024 x 1024
+             experts, top-k 64; strong scaling): on one GPU the whole layer, on N > 1 GPUs with the expert
+             tables row-partitioned and dispatched / combined over NCCL; with the device time of its
+             phases and a parity check of sampled tokens against the CPU oracle
+Synthetic data: x ~ N(0,1), weights from the module's default initialisation under seed 0 (quick-start
+shape) or N(0, 0.02) (largest configuration).
+
+--impl reference times the reference project's own CPU implementation of the same workload (its
+PyTorch module, staged unmodified under oracle/_ref by `python -m oracle.make_ref`; the restatement in
+oracle/omni_oracle.py only if that folder is empty) on all host cores; rank 0 only.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -39,10 +53,19 @@ if ROOT not in sys.path:
 CFG = dict(hidden=1024, intermediate=4096, experts=4096, top_k=16, tokens=4096)
 WORKLOAD = "quick-start layer: hidden 1024, intermediate 4096, 4096 experts (64x64), top-k 16, x bf16 [1,4096,1024]"
 SLOTS = 4  # independent weight + activation sets rotated between steps (working set > L2)
+RESIDENT_STREAMS = 2  # steps in flight: the tail of one step's kernels overlaps the head of the next one's
+C5 = dict(T=65536, H=4096, I=11008, N=1 << 20, k=64)
 
-# DRAM bytes (read + write) per launch of the gate/up GEMM kernel, from the ncu capture summarised
-# in profiles/gemm_pair_gate_up_quickstart.md (25.26 MB read + 1.27 MB written)
+# DRAM bytes (read + write) per launch of the gate/up GEMM kernel: ncu, one launch of this workload
+# (25.26 MB read + 1.27 MB written)
 GATE_UP_DRAM_BYTES_PER_LAUNCH = 26_528_768
+
+
+def static_config(world: int) -> dict:
+    """Description of the workload; the same dictionary in both arms."""
+    return {"workload": WORKLOAD, "tokens_per_gpu_per_step": CFG["tokens"], "parallelism": f"token-dp{world}",
+            "l2": f"GPU arm: {SLOTS} independent weight+activation sets rotated between steps (about 130 MB each, > 126 MB L2 in total)",
+            "launch": f"GPU arm: one CUDA graph per step, {RESIDENT_STREAMS} independent steps in flight (round-robin over {RESIDENT_STREAMS} streams)"}
 
 
 def peaks():
@@ -128,30 +151,44 @@ def max_over_ranks(ms: float, dist_on: bool, dev) -> float:
     return float(t.item())
 
 
-RESIDENT_STREAMS = 2  # steps in flight: the tail of one step's kernels overlaps the head of the next one's
-
-
-def time_resident(slots, steps, warmup, dist_on, dev, n_streams=RESIDENT_STREAMS):
+def time_resident(slots, steps, warmup, dist_on, dev, n_streams=RESIDENT_STREAMS, sustain_s: float = 0.0):
     """K graph replays, rotating the slots, issued round-robin on n_streams streams (independent
     steps, as a server with several batches in flight runs them); CUDA events on the main stream, which
-    forks to and joins the replay streams, around the lot."""
+    forks to and joins the replay streams, around the lot.  Returns (ms of the first K-step block, list of
+    the ms of the further identical blocks issued back to back until `sustain_s` seconds have passed)."""
     streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
     for i in range(warmup):
         slots[i % SLOTS]["graph"].replay()
     barrier(dist_on)
     main = torch.cuda.current_stream()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(main)
-    for s in streams:
-        s.wait_event(e0)
-    for i in range(steps):
-        with torch.cuda.stream(streams[i % n_streams]):
-            slots[i % SLOTS]["graph"].replay()
-    for s in streams:
-        main.wait_stream(s)
-    e1.record(main)
+
+    def block():
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(main)
+        for s in streams:
+            s.wait_event(e0)
+        for i in range(steps):
+            with torch.cuda.stream(streams[i % n_streams]):
+                slots[i % SLOTS]["graph"].replay()
+        for s in streams:
+            main.wait_stream(s)
+        e1.record(main)
+        return e0, e1
+
+    first = block()
     barrier(dist_on)
-    return max_over_ranks(e0.elapsed_time(e1), dist_on, dev)
+    first_ms = max_over_ranks(first[0].elapsed_time(first[1]), dist_on, dev)
+    later = []
+    if sustain_s > 0:
+        t0 = time.perf_counter()
+        pending = []
+        while time.perf_counter() - t0 < sustain_s or len(pending) < 3:
+            pending.append(block())
+            if len(pending) % 8 == 0:
+                pending[-8][1].synchronize()   # keep the host at most a few blocks ahead of the device
+        barrier(dist_on)
+        later = [a.elapsed_time(b) for a, b in pending]
+    return first_ms, later
 
 
 def time_e2e(slots, steps, warmup, dist_on, dev):
@@ -215,70 +252,212 @@ def time_gate_up(slots, reps):
     return statistics.mean(times)
 
 
-def _oracle_setup(sample_tokens: int):
-    from oracle import omni_oracle as orc
-    from omni_moe_b200.modules.omni_moe import OmniMoE, OmniMoEConfig
+def _workload_inputs():
+    """x of slot 0 of the workload, as the GPU arm draws it."""
+    return torch.randn(1, CFG["tokens"], CFG["hidden"], generator=torch.Generator().manual_seed(100)).to(torch.bfloat16)
+
+
+def _cpu_forward_fn():
+    """A callable running one forward of the whole workload on the CPU, and what it is.
+
+    First choice: the reference project's own PyTorch module (OmniMoE_Torch, omni_moe/modules/omni_moe.py:109-194),
+    loaded unmodified from oracle/_ref, built as the quick-start snippet builds it (default initialisation under
+    seed 0, then .to(bfloat16)) and fed the bf16 tokens.  Fallback when oracle/_ref is empty: the fp32
+    restatement in oracle/omni_oracle.py on bf16-rounded parameters."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
+    x = _workload_inputs()
+    from oracle import ref_loader
+    ref = ref_loader.load_layer()
+    if ref is not None:
+        ref_layer, ref_config = ref
+        torch.manual_seed(0)
+        m = ref_layer(ref_config(CFG["hidden"], CFG["intermediate"], "silu", CFG["experts"], CFG["top_k"]))
+        m = m.to(torch.bfloat16).eval()
+        return (lambda: m(x)), "reference", "bf16", cores, "OmniMoE_Torch of the reference project (unmodified file), module and tokens in bf16"
+    from oracle import omni_oracle as orc
+    from omni_moe_b200.modules.omni_moe import OmniMoE, OmniMoEConfig
     torch.manual_seed(0)
     m = OmniMoE(OmniMoEConfig(CFG["hidden"], CFG["intermediate"], "silu", CFG["experts"], CFG["top_k"]))
     sd = {k: v.detach().to(torch.bfloat16).float() if v.is_floating_point() else v for k, v in m.state_dict().items()}
-    p = orc.params_from_state_dict(sd, CFG["experts"], CFG["top_k"])
-    x = torch.randn(1, sample_tokens, CFG["hidden"], generator=torch.Generator().manual_seed(100)).bfloat16().float()
-    return orc, p, x, cores
+    prm = orc.params_from_state_dict(sd, CFG["experts"], CFG["top_k"])
+    xf = x.float()
+    return (lambda: orc.layer_forward(prm, xf)), "port", "f32", cores, "restatement of OmniMoE_Torch (oracle/omni_oracle.py), fp32 math on bf16-rounded parameters"
 
 
-def cpu_oracle_rate(seconds_budget: float = 15.0, sample_tokens: int = 1024):
-    """tokens/s of the CPU oracle on a bounded sample of the workload, all host threads."""
-    orc, p, x, cores = _oracle_setup(sample_tokens)
+def cpu_baseline_rate(seconds_budget: float = 12.0):
+    """tokens/s of the CPU path over whole-workload forwards for about `seconds_budget` seconds, all host threads."""
+    fwd, kind, dtype, cores, what = _cpu_forward_fn()
     with torch.no_grad():
-        orc.layer_forward(p, x)  # warm-up
+        fwd()  # warm-up
         n, t0 = 0, time.perf_counter()
         while True:
-            orc.layer_forward(p, x)
+            fwd()
             n += 1
             el = time.perf_counter() - t0
-            if el > seconds_budget or n >= 50:
+            if el > seconds_budget or n >= 100:
                 break
-    return sample_tokens * n / el, cores, (f"{n} forwards of the first {sample_tokens} tokens of the workload, "
-                                           "fp32 math on bf16-rounded parameters")
+    return {"value": CFG["tokens"] * n / el, "unit": "tokens/s", "cores": cores, "kind": kind, "dtype": dtype,
+            "sample": f"{n} forwards of the whole workload ({CFG['tokens']} tokens each) in {el:.1f} s; {what}"}
 
 
 def run_reference(args, rank):
-    """The reference's CPU implementation of the path: its PyTorch layer, restated in oracle/ (the
-    reference package itself cannot be imported without Triton and a GPU).  Rank 0 only.  A step is
-    one forward over a bounded sample of the workload's tokens, sized so the run ends in ~2 minutes."""
+    """The reference's CPU implementation of the path on the host cores; rank 0 only.  Every step is one
+    forward over the whole workload (4096 tokens).  If the requested number of steps would take more than
+    about two and a half minutes on this host, fewer steps are run and the line says so."""
     if rank != 0:
         return
-    sample = 512
-    orc, p, x, cores = _oracle_setup(sample)
+    fwd, kind, dtype, cores, what = _cpu_forward_fn()
+    steps, warmup, note = args.steps, args.warmup, ""
     with torch.no_grad():
-        orc.layer_forward(p, x)
+        fwd()
         t0 = time.perf_counter()
-        orc.layer_forward(p, x)
+        fwd()
         d = time.perf_counter() - t0
-        total = args.steps + args.warmup
-        if total * d > 120.0:
-            sample = int(max(32, min(512, sample * 120.0 / (total * d))))
-            x = x[:, :sample].contiguous()
-        for _ in range(args.warmup):
-            orc.layer_forward(p, x)
+        if (steps + warmup) * d > 150.0:
+            warmup = min(warmup, 3)
+            steps = max(3, int(150.0 / d) - warmup)
+            note = f"; {steps} steps instead of {args.steps} to stay within the time budget ({d:.2f} s per step on this host)"
+        for _ in range(warmup):
+            fwd()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
-            orc.layer_forward(p, x)
+        for _ in range(steps):
+            fwd()
         el = time.perf_counter() - t0
-    v = sample * args.steps / el
-    note = f"each step = one forward over the first {sample} tokens of the workload, fp32 math on bf16-rounded parameters"
+    v = CFG["tokens"] * steps / el
     line = {
         "impl": "reference", "metric": "OmniMoE layer fwd tokens/s", "value": v, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * el / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample_tokens_per_step": sample},
-        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": note},
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": 1e3 * el / steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": static_config(args.gpus),
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": kind, "dtype": dtype,
+                         "sample": f"each step = one forward over the whole workload ({CFG['tokens']} tokens); {what}{note}"},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# largest configuration: one GPU, or expert tables row-partitioned over the ranks
+# ------------------------------------------------------------------------------------------------
+def _c5_parity(inner, tables, part, x_local, y_local, indices, rank, world, dist_on, dev, samples_total=256):
+    """Sampled tokens of the step against the CPU oracle.  Every rank contributes `samples_total / world`
+    of its tokens (rows of x, y and the selected expert ids); rank 0 reruns the router on the CPU, asks
+    every rank for the table rows the sampled tokens touch (a rank fills in the rows it owns, the rest stay
+    zero, a sum-reduce assembles them), and recomputes the outputs in fp32."""
+    import numpy as np
+    import torch.distributed as dist
+    from oracle import omni_oracle as orc
+    t_local, h = x_local.shape
+    k, n = inner.top_k, inner.num_expert_sqrt
+    per = max(1, -(-samples_total // world))
+    pick = torch.linspace(0, t_local - 1, per, device=dev).long()
+    xs, ys, gi = x_local[pick].contiguous(), y_local.reshape(-1, h)[pick].contiguous(), indices[pick].contiguous()
+    if dist_on:
+        def gather(t):
+            out = torch.empty((world * t.size(0),) + tuple(t.shape[1:]), device=dev, dtype=t.dtype)
+            dist.all_gather_into_tensor(out, t)
+            return out
+        xs, ys, gi = gather(xs), gather(ys), gather(gi)
+    s_total = xs.size(0)
+    lpx = lpy = es = ei = None
+    if rank == 0:
+        xf = xs.float().cpu()
+        sd = {kk: v.detach().float().cpu() for kk, v in inner.state_dict().items() if "embed" not in kk}
+        lpx = orc.router_log_probs(orc.router_batchnorm_eval(orc.router_logits(xf, sd["router_gate_x.weight"]),
+                                                             sd["router_norm_x.running_mean"], sd["router_norm_x.running_var"]))
+        lpy = orc.router_log_probs(orc.router_batchnorm_eval(orc.router_logits(xf, sd["router_gate_y.weight"]),
+                                                             sd["router_norm_y.running_mean"], sd["router_norm_y.running_var"]))
+        es, ei = orc.router_topk(lpx, lpy, n, k)
+        need = torch.unique(torch.cat([torch.from_numpy(ei).reshape(-1), gi.reshape(-1).long().cpu()]))
+        need = need[(need >= 0) & (need < inner.num_experts)].to(dev)
+        count = torch.tensor([need.numel()], device=dev)
+    else:
+        count = torch.zeros(1, dtype=torch.long, device=dev)
+    if dist_on:
+        dist.broadcast(count, 0)
+        if rank != 0:
+            need = torch.empty(int(count.item()), dtype=torch.long, device=dev)
+        dist.broadcast(need, 0)
+    up_l, down_l = tables
+    lo, hi = (part.lo, part.hi) if part is not None else (0, inner.num_experts)
+    mine = (need >= lo) & (need < hi)
+    rows = []
+    for tab in (up_l, down_l):
+        r = torch.zeros((need.numel(), h), device=dev, dtype=torch.float32)
+        r[mine] = tab[need[mine] - lo].float()
+        if dist_on:
+            dist.reduce(r, 0, op=dist.ReduceOp.SUM)
+        rows.append(r)
+    if rank != 0:
+        return None
+    up_rows, down_rows = (r.cpu() for r in rows)
+    need_c = need.cpu()
+    compact = torch.searchsorted(need_c, torch.from_numpy(ei).reshape(-1)).view(s_total, k)
+    ey = orc.expert_forward(xf, up_rows, down_rows, orc.routing_weights(es), compact)
+    ey += orc.mlp_forward(xf, sd["gate_proj.weight"], sd["up_proj.weight"], sd["down_proj.weight"])
+    gi_c = gi.cpu()
+    ndiff, gaps = orc.routing_flip_gaps(lpx, lpy, es, ei, gi_c, n)
+    same = (gi_c.long().numpy() == ei).all(axis=1)
+    a, e = ys.float().cpu()[same], ey[same]
+    err = (a - e).abs()
+    within = bool((err <= 2e-2 + 2e-2 * e.abs()).all()) if same.any() else False
+    return {"tokens_checked": int(s_total), "tokens_compared": int(same.sum()),
+            "routing_mismatch_frac": float(ndiff) / float(s_total * k),
+            "max_flip_gap": float(gaps.max()) if ndiff else 0.0,
+            "max_abs_err": float(err.max()) if same.any() else None,
+            "within_rtol2e-2_atol2e-2": within,
+            "oracle": "oracle/omni_oracle.py, fp32 on the bf16 operands; rows fetched from the ranks that own them"}
+
+
+def run_c5(world, rank, dev, dist_on, steps=5, warmup=2):
+    """One GPU: the whole layer.  N > 1: tokens sharded (65536 / N per rank), tables row-partitioned."""
+    from omni_moe_b200.layer_bench import build_module, _fill_normal_
+    cfg = C5
+    t_local = cfg["T"] // world
+    x = torch.empty(1, t_local, cfg["H"], device=dev, dtype=torch.bfloat16)
+    _fill_normal_(x, 1.0, 7 + rank)
+    part = None
+    if dist_on:
+        from omni_moe_b200.parallel import ExpertPartition, PartitionedOmniMoE
+        part = ExpertPartition(cfg["N"], world, rank)
+        inner = build_module(cfg, dev, table_rows=part.hi - part.lo, row_offset=part.lo)
+        layer = PartitionedOmniMoE(inner, None, table_slices=(inner.up_embed.weight.data, inner.down_embed.weight.data))
+        tables = (layer.up_local.data, layer.down_local.data)
+        run = lambda: layer(x)
+    else:
+        inner = build_module(cfg, dev)
+        layer = None
+        tables = (inner.up_embed.weight.data, inner.down_embed.weight.data)
+        run = lambda: inner(x)
+    with torch.no_grad():
+        for _ in range(warmup):
+            y = run()
+        inner.check_status()
+        barrier(dist_on)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            y = run()
+        e1.record()
+        barrier(dist_on)
+        ms = max_over_ranks(e0.elapsed_time(e1) / steps, dist_on, dev)
+        phases = None
+        if layer is not None:
+            layer.record_phases = True
+            y = run()
+            phases = layer.phases_ms()
+            layer.record_phases = False
+        inner.check_status()
+        parity = _c5_parity(inner, tables, part, x.view(t_local, cfg["H"]), y, inner.last_routing[1], rank, world, dist_on, dev)
+    out = {"workload": "largest configuration: 65536 tokens, hidden 4096, intermediate 11008, 1048576 experts (1024x1024), top-k 64, bf16",
+           "mode": f"expert tables row-partitioned over {world} GPUs, NCCL dispatch / combine" if dist_on else "whole layer on one GPU",
+           "scaling": "strong", "ms_per_step": ms, "tokens_s": cfg["T"] / (ms * 1e-3), "steps": steps, "warmup": warmup,
+           "tables_gib_per_gpu": 2 * tables[0].numel() * 2 / 2 ** 30, "phases_ms": phases, "parity": parity}
+    del layer, inner, tables, x, y
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -288,6 +467,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-c5", action="store_true", help="skip the largest-configuration leg")
+    ap.add_argument("--sustain", type=float, default=1.0, help="seconds of back-to-back blocks for the sustained figure")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -311,36 +492,56 @@ def main():
     cpu_line = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         # first, while the process may still run on every host core (the placement below narrows that)
-        rate, cores, sample = cpu_oracle_rate()
-        cpu_line = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        cpu_line = cpu_baseline_rate()
     from omni_moe_b200.host import bind_near_gpu
     placement = bind_near_gpu(local_rank)   # before the pinned host buffers are allocated
     slots = build_slots(dev)
     from omni_moe_b200.modules.omni_moe import OmniMoE
+    ms, _ = time_resident(slots, args.steps, args.warmup, dist_on, dev)
+    ms_serial, _ = time_resident(slots, args.steps, args.warmup, dist_on, dev, n_streams=1)   # one step at a time, for the record
+    ms_e2e = time_e2e(slots, args.steps, args.warmup, dist_on, dev)
+    # sustained: the same K-step block back to back for a second or more, clocks sampled meanwhile
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = time_resident(slots, args.steps, args.warmup, dist_on, dev)
-    ms_serial = time_resident(slots, args.steps, args.warmup, dist_on, dev, n_streams=1)   # one step at a time, for the record
-    ms_e2e = time_e2e(slots, args.steps, args.warmup, dist_on, dev)
+    _, later = time_resident(slots, args.steps, 3, dist_on, dev, sustain_s=args.sustain)
     clocks = sampler.stop() if rank == 0 else None
+    sustained_ms = max_over_ranks(statistics.median(later), dist_on, dev)
     for s in slots:
         s["module"].check_status()
     gemm_ms = time_gate_up(slots, 40)
+    del slots
+    torch.cuda.empty_cache()
+    c5 = None
+    if not args.no_c5:
+        c5 = run_c5(world, rank, dev, dist_on)
 
     if rank == 0:
         pk = peaks()
         tokens_total = CFG["tokens"] * args.steps * world
         flops = 4.0 * CFG["tokens"] * CFG["hidden"] * CFG["intermediate"]
         achieved = flops / (gemm_ms * 1e-3) / 1e12
+        t_, h_, i_, k_ = CFG["tokens"], CFG["hidden"], CFG["intermediate"], CFG["top_k"]
+        n_ = int(math.isqrt(CFG["experts"]))
+        layer_flops = 6.0 * t_ * h_ * i_ + 4.0 * t_ * h_ * n_ + 4.0 * t_ * k_ * h_   # MLP + router gates + routed experts
+        step_ms = ms / args.steps
         line = {
             "metric": "OmniMoE layer fwd tokens/s", "value": tokens_total / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "tokens_per_gpu_per_step": CFG["tokens"], "parallelism": f"token-dp{world}",
-                       "l2": f"{SLOTS} independent weight+activation sets rotated between steps (about 130 MB each, > 126 MB L2 in total)",
-                       "one_step_at_a_time_ms_per_step": ms_serial / args.steps,
-                       "launch": f"one CUDA graph per step, {RESIDENT_STREAMS} independent steps in flight (round-robin over {RESIDENT_STREAMS} streams)"},
+            "config": static_config(world),
+            "detail": {
+                "one_step_at_a_time_ms_per_step": ms_serial / args.steps,
+                "sustained_ms_per_step": sustained_ms / args.steps,
+                "sustained_tokens_s": CFG["tokens"] * world / (sustained_ms / args.steps * 1e-3),
+                "sustained_blocks": len(later), "sustained_seconds": sum(later) * 1e-3,
+                "sustained_sm_mhz_median": clocks["sm_mhz"] if clocks else None,
+                "layer_flops_per_step": layer_flops,
+                "layer_frac": layer_flops / (step_ms * 1e-3) / 1e12 / pk["tf"],
+                "layer_frac_sustained": (layer_flops / (sustained_ms / args.steps * 1e-3) / 1e12 / pk["tf_sustained"]) if pk["tf_sustained"] else None,
+                "layer_frac_note": "algorithmic FLOP of one step (6THI + 4TH sqrtN + 4TkH) / step time / measured bf16 peak "
+                                   "(burst peak for the first block, sustained peak for the sustained blocks)",
+            },
             "e2e": {"value": tokens_total / (ms_e2e * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": CFG["tokens"] * CFG["hidden"] * 2, "d2h_bytes_per_step": CFG["tokens"] * CFG["hidden"] * 2,
                     "ms_per_step": ms_e2e / args.steps, "pipeline": f"{SLOTS} slots, one stream each",
@@ -351,6 +552,7 @@ def main():
                          "achieved": achieved, "peak": pk["tf"], "unit": "TFLOP/s", "frac": achieved / pk["tf"],
                          "traffic": GATE_UP_DRAM_BYTES_PER_LAUNCH, "peak_source": pk["src"] + " (burst: kernel timed alone)",
                          "ms_per_launch": gemm_ms, "flops_per_launch": flops},
+            "partitioned_c5": c5,
         }
         if cpu_line is not None:
             line["cpu_baseline"] = cpu_line

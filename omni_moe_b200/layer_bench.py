@@ -67,6 +67,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "torch"],
                     help="torch: the same layer written with PyTorch eager ops (gather / matmul experts, torch.topk "
                          "router) on the same GPU, as a same-box bar; c2 only (it materialises [T, k, H] gathers)")
+    ap.add_argument("--chunks", type=int, default=2, help="token ranges pipelined through the exchange (--partitioned)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -89,10 +90,9 @@ def main():
         from .parallel import ExpertPartition, PartitionedOmniMoE
         part = ExpertPartition(cfg["N"], world, rank)
         inner = build_module(cfg, dev, table_rows=part.hi - part.lo, row_offset=part.lo)
-        layer = PartitionedOmniMoE.__new__(PartitionedOmniMoE)   # the tables are already slices: skip the cutting
-        torch.nn.Module.__init__(layer)
-        layer.group, layer.part, layer.inner = None, part, inner
-        layer._side, layer.partial_dtype = None, torch.bfloat16
+        # the tables were built as slices in the first place: 16 GiB of rows never exist on one GPU
+        layer = PartitionedOmniMoE(inner, None, chunks=args.chunks,
+                                   table_slices=(inner.up_embed.weight.data, inner.down_embed.weight.data))
         run = lambda: layer(x)
     elif args.impl == "torch":
         from .train_bench import torch_forward

@@ -184,6 +184,9 @@ class OmniMoE(nn.Module):
     # ------------------------------------------------------------------------------------------
     def _operands(self):
         """bf16 views (or per-call bf16 copies, for fp32 / fp16 modules) of all weights."""
+        if getattr(self, "_tables_partitioned", False):
+            raise RuntimeError("this module's expert tables were handed to a PartitionedOmniMoE: call that wrapper, "
+                               "the module alone no longer holds the rows its router selects")
         return tuple(self._bf16_weight(p.weight) for p in (
             self.gate_proj, self.up_proj, self.down_proj, self.router_gate_x, self.router_gate_y,
             self.up_embed, self.down_embed))
@@ -316,6 +319,8 @@ class OmniMoE(nn.Module):
 
     def forward(self, hidden_states: torch.Tensor, **kwargs) -> torch.Tensor:
         _lib.require_cuda(hidden_states)
+        if getattr(self, "_tables_partitioned", False):
+            self._operands()  # raises: the tables live in the PartitionedOmniMoE wrapper
         if self._needs_grad(hidden_states) or self.hidden_size % 8 or self.intermediate_size % 8:
             # sizes that are not multiples of 8 go through the operators one by one (they pad): the fused
             # launch sequence moves rows in 16-byte pieces

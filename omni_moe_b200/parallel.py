@@ -139,59 +139,130 @@ def _collective(stage: str, fn, *args, **kwargs):
         raise ExchangeError(stage, str(e).splitlines()[0] if str(e) else type(e).__name__) from e
 
 
-def _stable_order_by_owner(owner: torch.Tensor, world: int) -> torch.Tensor:
-    """Permutation that groups the flat pairs by owning rank, ascending pair id inside a group."""
-    if owner.is_cuda:
+def _stable_order_by_key(key: torch.Tensor, bins: int) -> torch.Tensor:
+    """Permutation that groups the flat pairs by ``key`` (in ``[0, bins)``), ascending pair id inside a group."""
+    if key.is_cuda:
         from .ops.scheduler import schedule
-        raw = schedule(owner.view(-1, 1), world)  # the radix scheduler, one pass over `world` bins
+        raw = schedule(key.view(-1, 1), bins, segments=False)  # the radix scheduler, one pass over `bins` bins
         return raw.sorted_pair_ids.long()
-    return torch.sort(owner.view(-1).long(), stable=True).indices
+    return torch.sort(key.view(-1).long(), stable=True).indices
+
+
+@dataclass
+class ExchangePlan:
+    """Everything the dispatch of one step needs, after the count exchange (the one host synchronisation).
+
+    The local tokens are cut into ``chunks`` equal ranges; a chunk is exchanged, computed and combined on
+    its own, so that one chunk's transfers overlap another chunk's kernels.  ``send[c]`` holds the records of
+    chunk ``c`` grouped by destination rank (ascending pair id inside a destination)."""
+    chunks: int
+    tokens_per_chunk: int
+    send: list              # per chunk: int32 [n_c, 3] records (token id inside the chunk's all-gathered rows, local expert row, weight bits)
+    send_counts: list       # per chunk: list of `world` ints
+    recv_counts: list       # per chunk: list of `world` ints
+
+
+def plan_exchange(indices: torch.Tensor, weights: torch.Tensor, part: ExpertPartition, group=None,
+                  chunks: int = 1, comm_stream=None) -> ExchangePlan:
+    """Sorts this rank's pairs by (chunk, owning rank) and exchanges the counts.
+
+    ``indices [T_local, k]`` global expert ids, ``weights [T_local, k]``.  The count exchange doubles as a
+    handshake: every rank also states its shard shape, so a peer that left, or one configured with another
+    token count, k or chunk count, is noticed here, on the host, before any payload moves.  On CUDA with a
+    ``comm_stream`` the collective is issued on that stream (after the sort, which runs on the current one)."""
+    world, rank = part.world, part.rank
+    t_local, k = indices.shape
+    if chunks < 1 or t_local % chunks:
+        chunks = 1
+    tc = t_local // chunks
+    flat_e = indices.reshape(-1).to(torch.int32)
+    owner = part.owner(flat_e).to(torch.int32)
+    pair = torch.arange(flat_e.numel(), device=flat_e.device, dtype=torch.int32)
+    token = torch.div(pair, max(k, 1), rounding_mode="floor")
+    chunk_of = torch.div(token, max(tc, 1), rounding_mode="floor") if chunks > 1 else torch.zeros_like(token)
+    key = chunk_of * world + owner
+    order = _stable_order_by_key(key, chunks * world)
+    counts = torch.bincount(key.long(), minlength=chunks * world).view(chunks, world)
+    shape_cols = [torch.full((world, 1), v, dtype=counts.dtype, device=counts.device) for v in (t_local, k, chunks)]
+    hello = torch.cat([counts.t()] + shape_cols, dim=1).contiguous()
+    got = torch.empty_like(hello)
+    if comm_stream is not None and hello.is_cuda:
+        main = torch.cuda.current_stream()
+        ready, done = torch.cuda.Event(), torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(comm_stream):
+            comm_stream.wait_event(ready)
+            _collective("count exchange", dist.all_to_all_single, got, hello, group=group)
+            done.record(comm_stream)
+        main.wait_event(done)
+        hello.record_stream(comm_stream)
+        got.record_stream(comm_stream)
+    else:
+        _collective("count exchange", dist.all_to_all_single, got, hello, group=group)
+    got_host = got.tolist()  # the one host synchronisation of a step: the split sizes
+    send_host = counts.tolist()
+    for peer, row in enumerate(got_host):
+        t_peer, k_peer, c_peer = row[-3:]
+        if t_peer != t_local or k_peer != k or c_peer != chunks or len(row) != chunks + 3:
+            raise ExchangeError("count exchange", f"rank {peer} shards {t_peer} tokens x {k_peer} experts in {c_peer} chunks, this "
+                                                  f"rank {t_local} x {k} in {chunks}: every rank must pass the same shard shape")
+        for cnt in row[:chunks]:
+            if cnt < 0 or cnt > tc * k:
+                raise ExchangeError("count exchange", f"rank {peer} announces {cnt} pairs, more than its {tc * k} per chunk")
+    # 12-byte records: token id among the chunk's all-gathered rows, expert row inside the owner's slice, weight bits
+    tok_rec = (token[order] - chunk_of[order] * tc + rank * tc).to(torch.int32)
+    local_e = flat_e[order] - owner[order] * part.rows_per_rank
+    w_bits = weights.reshape(-1).float()[order].view(torch.int32)
+    records = torch.stack([tok_rec, local_e, w_bits], dim=1).contiguous()
+    starts = [0]
+    for c in range(chunks):
+        starts.append(starts[-1] + sum(send_host[c]))
+    send = [records[starts[c]:starts[c + 1]] for c in range(chunks)]
+    recv_counts = [[got_host[p][c] for p in range(world)] for c in range(chunks)]
+    return ExchangePlan(chunks, tc, send, send_host, recv_counts)
+
+
+def send_pairs(plan: ExchangePlan, c: int, recv: torch.Tensor, group=None) -> None:
+    """The payload collective of chunk ``c``: its 12-byte records into ``recv [sum(recv_counts[c]), 3]`` int32."""
+    _collective("pair dispatch", dist.all_to_all_single, recv, plan.send[c], output_split_sizes=plan.recv_counts[c],
+                input_split_sizes=plan.send_counts[c], group=group)
+
+
+def received_pairs(plan: ExchangePlan, c: int, recv: torch.Tensor, x_all: torch.Tensor) -> ReceivedPairs:
+    """Splits the received records of chunk ``c`` and builds the CSR of pairs by token.  What a rank receives is
+    grouped by source rank and, inside a source, in ascending pair order, i.e. already ordered by token id."""
+    pair_tokens = recv[:, 0].contiguous()
+    bounds = torch.arange(x_all.size(0) + 1, device=recv.device, dtype=torch.int32)
+    token_offsets = torch.searchsorted(pair_tokens, bounds, right=False).to(torch.int32)
+    return ReceivedPairs(x_all, pair_tokens, recv[:, 1].contiguous(), recv[:, 2].contiguous().view(torch.float32),
+                         token_offsets, plan.send_counts[c], plan.recv_counts[c])
+
+
+def gather_token_rows(x_chunk: torch.Tensor, part: ExpertPartition, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """All-gather of a token range: ``[T, H]`` per rank -> ``[world * T, H]`` ordered by rank."""
+    if out is None:
+        out = torch.empty((part.world * x_chunk.size(0), x_chunk.size(1)), device=x_chunk.device, dtype=x_chunk.dtype)
+    _collective("token all-gather", dist.all_gather_into_tensor, out, x_chunk.contiguous(), group=group)
+    return out
+
+
+def exchange_chunk(plan: ExchangePlan, c: int, x_chunk: torch.Tensor, part: ExpertPartition, group=None) -> ReceivedPairs:
+    """Moves chunk ``c`` on the current stream: its pair records to the owners of the expert rows and its token
+    rows ``x_chunk [T_local / chunks, H]`` to every rank."""
+    recv = torch.empty((sum(plan.recv_counts[c]), 3), device=x_chunk.device, dtype=torch.int32)
+    send_pairs(plan, c, recv, group)
+    return received_pairs(plan, c, recv, gather_token_rows(x_chunk, part, group))
 
 
 def dispatch_pairs(x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, part: ExpertPartition,
                    group=None) -> ReceivedPairs:
-    """Step 2: send every routed pair of this rank's tokens to the rank that owns the expert row.
+    """Step 2 in one piece: send every routed pair of this rank's tokens to the rank that owns the expert row.
 
     ``x [T_local, H]``, ``indices [T_local, k]`` global expert ids, ``weights [T_local, k]`` float32.
     Every rank must pass the same ``T_local``.
     """
-    world, rank = part.world, part.rank
-    t_local, k = indices.shape
-    dev = x.device
-    flat_e = indices.reshape(-1).to(torch.int32)
-    owner = part.owner(flat_e).to(torch.int32)
-    order = _stable_order_by_owner(owner, world)
-    send_counts = torch.bincount(owner.long(), minlength=world)
-    # the count exchange doubles as a handshake: every rank also states its shard shape, so a peer that
-    # left, or one configured with another token count or k, is noticed here, on the host, before any
-    # payload moves
-    hello = torch.stack([send_counts, torch.full_like(send_counts, t_local), torch.full_like(send_counts, k)], dim=1).contiguous()
-    got = torch.empty_like(hello)
-    _collective("count exchange", dist.all_to_all_single, got, hello, group=group)
-    got_host = got.tolist()  # one host sync: the split sizes
-    send_list, recv_list = send_counts.tolist(), [r[0] for r in got_host]
-    for peer, (cnt, t_peer, k_peer) in enumerate(got_host):
-        if t_peer != t_local or k_peer != k:
-            raise ExchangeError("count exchange", f"rank {peer} shards {t_peer} tokens x {k_peer} experts, this rank "
-                                                  f"{t_local} x {k}: every rank must pass the same shard shape")
-        if cnt < 0 or cnt > t_peer * k_peer:
-            raise ExchangeError("count exchange", f"rank {peer} announces {cnt} pairs, more than its {t_peer * k_peer}")
-    # 12-byte records: global token id, expert row inside the owner's slice, weight bits
-    tok = (torch.div(order, k, rounding_mode="floor") + rank * t_local).to(torch.int32)
-    e_sorted = flat_e[order]
-    local_e = e_sorted - owner[order] * part.rows_per_rank
-    w_bits = weights.reshape(-1).float()[order].view(torch.int32)
-    send = torch.stack([tok, local_e, w_bits], dim=1).contiguous()
-    recv = torch.empty((sum(recv_list), 3), device=dev, dtype=torch.int32)
-    _collective("pair dispatch", dist.all_to_all_single, recv, send, output_split_sizes=recv_list,
-                input_split_sizes=send_list, group=group)
-    x_all = torch.empty((world * t_local, x.size(1)), device=dev, dtype=x.dtype)
-    _collective("token all-gather", dist.all_gather_into_tensor, x_all, x.contiguous(), group=group)
-    pair_tokens = recv[:, 0].contiguous()
-    bounds = torch.arange(world * t_local + 1, device=dev, dtype=torch.int32)
-    token_offsets = torch.searchsorted(pair_tokens, bounds, right=False).to(torch.int32)
-    return ReceivedPairs(x_all, pair_tokens, recv[:, 1].contiguous(), recv[:, 2].contiguous().view(torch.float32),
-                         token_offsets, send_list, recv_list)
+    plan = plan_exchange(indices, weights, part, group, chunks=1)
+    return exchange_chunk(plan, 0, x, part, group)
 
 
 def local_partial_states(recv: ReceivedPairs, up_local: torch.Tensor, down_local: torch.Tensor,
@@ -214,7 +285,7 @@ def local_partial_states(recv: ReceivedPairs, up_local: torch.Tensor, down_local
     with torch.cuda.device(dev):
         st = _lib.stream_ptr()
         if p:
-            sch = schedule(recv.pair_experts.view(-1, 1), n_local)  # expert order over the received pairs
+            sch = schedule(recv.pair_experts.view(-1, 1), n_local, segments=False)  # expert order over the received pairs
             _lib.check(lib.omni_expert_coef_pairs(x_all.data_ptr(), up_local.data_ptr(), recv.pair_tokens.data_ptr(),
                                                   recv.pair_weights.data_ptr(), sch.sorted_pair_ids.data_ptr(),
                                                   sch.sorted_experts.data_ptr(), p, t_total, h, n_local, coef.data_ptr(),
@@ -225,11 +296,12 @@ def local_partial_states(recv: ReceivedPairs, up_local: torch.Tensor, down_local
     return partial
 
 
-def combine_partials(partial: torch.Tensor, part: ExpertPartition, group=None) -> torch.Tensor:
+def combine_partials(partial: torch.Tensor, part: ExpertPartition, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
     """Step 4: sum the per-rank partial ``[T_total, H]`` states and return this rank's token rows."""
     t_local = partial.size(0) // part.world
     if dist.get_backend(group) == "nccl":
-        out = torch.empty((t_local, partial.size(1)), device=partial.device, dtype=partial.dtype)
+        if out is None:
+            out = torch.empty((t_local, partial.size(1)), device=partial.device, dtype=partial.dtype)
         _collective("combine", dist.reduce_scatter_tensor, out, partial.contiguous(), op=dist.ReduceOp.SUM, group=group)
         return out
     # backends without reduce-scatter (gloo, used by the CPU tests): all-reduce, then keep the own rows
@@ -238,49 +310,198 @@ def combine_partials(partial: torch.Tensor, part: ExpertPartition, group=None) -
     return full[part.rank * t_local:(part.rank + 1) * t_local].contiguous()
 
 
+class _PhaseClock:
+    """CUDA-event stopwatch for the phases of a partitioned step.  A phase may run in several pieces and on
+    several streams; its time is the sum of its pieces, each measured on the stream it runs on."""
+
+    def __init__(self, enabled: bool):
+        self.enabled = enabled
+        self.pieces = []
+
+    def start(self, name: str):
+        if not self.enabled:
+            return None
+        a = torch.cuda.Event(enable_timing=True)
+        a.record()
+        return (name, a)
+
+    def stop(self, tok):
+        if tok is None:
+            return
+        b = torch.cuda.Event(enable_timing=True)
+        b.record()
+        self.pieces.append((tok[0], tok[1], b))
+
+    def totals(self) -> dict:
+        """Milliseconds per phase; call after a synchronisation."""
+        out = {}
+        for name, a, b in self.pieces:
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
+
+
 def partitioned_expert_states(x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, up_local: torch.Tensor,
                               down_local: torch.Tensor, part: ExpertPartition, group=None,
-                              local_fn: Callable[[ReceivedPairs, torch.Tensor, torch.Tensor], torch.Tensor] | None = None
-                              ) -> torch.Tensor:
-    """Steps 2-4: routed-expert states ``[T_local, H]`` (fp32) of this rank's tokens with the tables
-    partitioned by rows.  ``local_fn`` replaces step 3 (the CPU tests pass the oracle's arithmetic there);
-    by default it is :func:`local_partial_states`, the CUDA kernels."""
-    recv = dispatch_pairs(x, indices, weights, part, group)
-    partial = (local_fn or local_partial_states)(recv, up_local, down_local)
-    return combine_partials(partial, part, group)
+                              local_fn: Callable[[ReceivedPairs, torch.Tensor, torch.Tensor], torch.Tensor] | None = None,
+                              chunks: int = 1, comm_stream=None, x_ready=None, clock: "_PhaseClock | None" = None,
+                              between_chunks: Callable[[int], None] | None = None,
+                              local_partial_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Steps 2-4: routed-expert states ``[T_local, H]`` of this rank's tokens with the tables partitioned by
+    rows.  ``local_fn`` replaces step 3 (the CPU tests pass the oracle's arithmetic there); by default it is
+    :func:`local_partial_states`, the CUDA kernels.
+
+    With ``chunks > 1`` the local tokens are cut into that many equal ranges which go through dispatch,
+    local kernels and combine one after another; on CUDA with a ``comm_stream`` every collective is issued
+    on that stream, so the transfers of one chunk run beside the kernels of another.  ``x_ready`` is an event
+    after which ``x`` may be read (default: now, on the current stream); ``between_chunks(c)`` is called on
+    the compute stream after chunk ``c``'s kernels were enqueued (the caller's own work, e.g. a GEMM that
+    needs no exchange); ``local_partial_dtype`` is the dtype ``local_fn`` returns (default float32) - the
+    pipelined form allocates the reduce-scatter outputs before the kernels run.  Returns float32 in the
+    pipelined form, the dtype of ``local_fn``'s result otherwise."""
+    local_fn = local_fn or local_partial_states
+    clock = clock or _PhaseClock(False)
+    t_local = x.size(0)
+    if chunks < 1 or t_local % chunks:
+        chunks = 1
+    tc = t_local // chunks
+    piped = x.is_cuda and comm_stream is not None
+    if not piped:
+        plan = plan_exchange(indices, weights, part, group, chunks)
+        outs = []
+        for c in range(chunks):
+            recv = exchange_chunk(plan, c, x[c * tc:(c + 1) * tc], part, group)
+            outs.append(combine_partials(local_fn(recv, up_local, down_local), part, group))
+            if between_chunks is not None:
+                between_chunks(c)
+        return outs[0] if chunks == 1 else torch.cat(outs, dim=0)
+
+    main = torch.cuda.current_stream()
+    dev, h, world = x.device, x.size(1), part.world
+    if x_ready is None:
+        x_ready = torch.cuda.Event()
+        x_ready.record(main)
+    # Every buffer is allocated here, while the compute stream is current, and handed to the communication
+    # stream by events; record_stream() at the end tells the caching allocator about the second user.
+    x_alls = [torch.empty((world * tc, h), device=dev, dtype=x.dtype) for _ in range(chunks)]
+    # token rows first: they need no routing, so their all-gathers start while the router still runs
+    with torch.cuda.stream(comm_stream):
+        comm_stream.wait_event(x_ready)
+        tk = clock.start("dispatch")
+        for c in range(chunks):
+            gather_token_rows(x[c * tc:(c + 1) * tc], part, group, out=x_alls[c])
+        clock.stop(tk)
+    tk = clock.start("plan")
+    plan = plan_exchange(indices, weights, part, group, chunks, comm_stream=comm_stream)
+    clock.stop(tk)
+    raw = [torch.empty((sum(plan.recv_counts[c]), 3), device=dev, dtype=torch.int32) for c in range(chunks)]
+    probe = local_partial_dtype if local_partial_dtype is not None else torch.float32
+    reduced = [torch.empty((tc, h), device=dev, dtype=probe) for _ in range(chunks)]
+    states = torch.empty((t_local, h), device=dev, dtype=torch.float32)
+    ev_send = torch.cuda.Event()
+    ev_send.record(main)   # the records were built on the compute stream
+    ev_disp = [torch.cuda.Event() for _ in range(chunks)]
+    ev_local = [torch.cuda.Event() for _ in range(chunks)]
+    ev_comb = [torch.cuda.Event() for _ in range(chunks)]
+    partials = [None] * chunks
+
+    def issue_dispatch(c):
+        with torch.cuda.stream(comm_stream):
+            if c == 0:
+                comm_stream.wait_event(ev_send)
+            tk_ = clock.start("dispatch")
+            send_pairs(plan, c, raw[c], group)
+            clock.stop(tk_)
+            ev_disp[c].record(comm_stream)
+
+    issue_dispatch(0)
+    for c in range(chunks):
+        if c + 1 < chunks:
+            issue_dispatch(c + 1)
+        main.wait_event(ev_disp[c])
+        tk = clock.start("local")
+        partials[c] = local_fn(received_pairs(plan, c, raw[c], x_alls[c]), up_local, down_local)
+        clock.stop(tk)
+        assert partials[c].dtype == probe, "local_fn must return local_partial_dtype"
+        ev_local[c].record(main)
+        with torch.cuda.stream(comm_stream):
+            comm_stream.wait_event(ev_local[c])
+            tk_ = clock.start("combine")
+            combine_partials(partials[c], part, group, out=reduced[c])
+            clock.stop(tk_)
+            ev_comb[c].record(comm_stream)
+        if between_chunks is not None:
+            between_chunks(c)
+    for c in range(chunks):
+        main.wait_event(ev_comb[c])
+        states[c * tc:(c + 1) * tc].copy_(reduced[c])
+    for tns in x_alls + raw + partials + reduced + plan.send + [x]:
+        tns.record_stream(comm_stream)
+    return states
 
 
 class PartitionedOmniMoE(torch.nn.Module):
     """``OmniMoE`` with the expert tables row-partitioned over the ranks of a process group.
 
-    Build it from a full module on every rank (``PartitionedOmniMoE(full_module, group)``): the
-    router and the shared MLP are kept whole, ``up_embed`` / ``down_embed`` are cut down to this
-    rank's rows.  ``forward(hidden_states)`` takes this rank's tokens ``[B, S, H]`` (the same count on
-    every rank) and returns their outputs.  Eval mode, bf16."""
+    Build it from a full module on every rank (``PartitionedOmniMoE(full_module, group)``): the router and
+    the shared MLP are kept whole, and this wrapper keeps rows ``[lo, hi)`` of ``up_embed`` / ``down_embed``
+    as ``up_local`` / ``down_local``.  The wrapped module is left without tables and refuses to run on its
+    own (its kernels would index a slice with global expert ids).  ``forward(hidden_states)`` takes this
+    rank's tokens ``[B, S, H]`` (the same count on every rank) and returns their outputs.  Eval mode, bf16.
 
-    def __init__(self, module, group=None):
+    ``chunks`` token ranges go through the exchange one after another with the collectives on a second
+    stream (see :func:`partitioned_expert_states`); ``record_phases = True`` makes every forward leave the
+    device time of its phases in ``last_phases_ms`` (after a synchronisation, via :meth:`phases_ms`)."""
+
+    def __init__(self, module, group=None, chunks: int = 2, table_slices=None):
         super().__init__()
         from .modules.omni_moe import OmniMoE
         assert isinstance(module, OmniMoE)
         self.group = group
         self.part = ExpertPartition(module.num_experts, dist.get_world_size(group), dist.get_rank(group))
+        if self.part.hi - self.part.lo < 1:
+            raise ValueError(f"{module.num_experts} expert rows over {self.part.world} ranks leave rank {self.part.rank} "
+                             "without rows: use fewer ranks")
         self.inner = module
-        with torch.no_grad():
-            up = self.part.slice_rows(module.up_embed.weight.detach())
-            down = self.part.slice_rows(module.down_embed.weight.detach())
-        # the full tables are dropped: this rank keeps only its rows
-        module.up_embed.weight = torch.nn.Parameter(up, requires_grad=False)
-        module.down_embed.weight = torch.nn.Parameter(down, requires_grad=False)
-        self._side = None
+        if table_slices is None:
+            with torch.no_grad():
+                up = self.part.slice_rows(module.up_embed.weight.detach())
+                down = self.part.slice_rows(module.down_embed.weight.detach())
+        else:
+            up, down = table_slices  # built as slices in the first place (tables too large to exist whole)
+        assert up.shape == down.shape == (self.part.hi - self.part.lo, module.hidden_size)
+        self.up_local = torch.nn.Parameter(up.to(torch.bfloat16).contiguous(), requires_grad=False)
+        self.down_local = torch.nn.Parameter(down.to(torch.bfloat16).contiguous(), requires_grad=False)
+        # the full tables are dropped; the wrapped module can no longer run by itself
+        empty = lambda: torch.nn.Parameter(torch.empty(0, module.hidden_size, dtype=up.dtype, device=up.device), requires_grad=False)
+        module.up_embed.weight, module.down_embed.weight = empty(), empty()
+        module._tables_partitioned = True
+        self.chunks = chunks
+        #: the gate/up GEMM of the shared MLP is enqueued after this chunk's expert kernels (default: the last one,
+        #: so that it runs while the last reduce-scatter is on the wire)
+        self.mlp_after_chunk = None
+        self._comm = None
+        self.record_phases = False
+        self._clock = None
         #: dtype of the per-rank partial sums that are reduce-scattered: bfloat16 halves the bytes on
         #: NVLink at the cost of one rounding per rank; float32 keeps the single-GPU accuracy
         self.partial_dtype = torch.bfloat16
 
+    def phases_ms(self) -> dict:
+        """Device time of the phases of the latest forward (``record_phases`` must be on): route, dispatch
+        (count exchange, pair records, token rows), local (schedule + expert kernels), combine
+        (reduce-scatter), mlp.  Phases on different streams overlap, so they can add up to more than the step."""
+        if self._clock is None:
+            return {}
+        torch.cuda.synchronize()
+        t = self._clock.totals()
+        t["dispatch"] = t.get("dispatch", 0.0) + t.pop("plan", 0.0)
+        return {k: round(v, 4) for k, v in t.items()}
+
     @torch.no_grad()
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
-        """Streams: the gate/up GEMM of the shared MLP (which needs only x) runs on a side stream while
-        the main stream routes, exchanges pairs and token rows, computes this rank's partial expert
-        states and reduce-scatters them; the down projection then adds the reduced states."""
+        """Compute stream: router, then per chunk the local expert kernels, the gate/up GEMM after the first
+        chunk, the down projection (which adds the reduced expert states) at the end.  Communication stream:
+        token all-gathers (from the start), count exchange, pair records, reduce-scatters."""
         from .ops.router import router_gate_topk
         m = self.inner
         if m.training:
@@ -290,30 +511,42 @@ class PartitionedOmniMoE(torch.nn.Module):
         x = hidden_states.detach().reshape(-1, m.hidden_size).to(torch.bfloat16).contiguous()
         t, h, i = x.size(0), m.hidden_size, m.intermediate_size
         dev = x.device
-        wg, wu, wd, kx, ky, up_l, down_l = m._operands()
+        wg, wu, wd, kx, ky = (m._bf16_weight(q.weight) for q in (m.gate_proj, m.up_proj, m.down_proj, m.router_gate_x, m.router_gate_y))
         scale, shift = m._bn_fold_eval()
         status = torch.zeros(1, device=dev, dtype=torch.int32)
         lib = _lib.load()
-        if self._side is None:
-            self._side = torch.cuda.Stream(device=dev)
+        clock = self._clock = _PhaseClock(self.record_phases)
         act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
         y = torch.empty((t, h), device=dev, dtype=torch.bfloat16)
         with torch.cuda.device(dev):
+            if self._comm is None:
+                self._comm = torch.cuda.Stream(device=dev)
             main = torch.cuda.current_stream()
-            self._side.wait_stream(main)
-            with torch.cuda.stream(self._side):
-                _lib.check(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, act.data_ptr(),
-                                                status.data_ptr(), self._side.cuda_stream))
-                for tns in (x, wg, wu, act):
-                    tns.record_stream(self._side)
+            x_ready = torch.cuda.Event()
+            x_ready.record(main)
+            tk = clock.start("route")
             scores, indices, weights = router_gate_topk(x, kx, ky, m.top_k, scale, shift, status=status)
+            clock.stop(tk)
+
+            n_chunks = self.chunks if (self.chunks >= 1 and t % max(self.chunks, 1) == 0) else 1
+            mlp_at = n_chunks - 1 if self.mlp_after_chunk is None else min(self.mlp_after_chunk, n_chunks - 1)
+
+            def gate_up(c):
+                if c == mlp_at:
+                    tk_ = clock.start("mlp")
+                    _lib.check(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, act.data_ptr(),
+                                                    status.data_ptr(), main.cuda_stream))
+                    clock.stop(tk_)
+
             states = partitioned_expert_states(
-                x, indices, weights, up_l, down_l, self.part, self.group,
-                local_fn=lambda r, u, d: local_partial_states(r, u, d, out_dtype=self.partial_dtype, status=status))
-            states = states.float()  # [T_local, H]: the down-projection epilogue adds fp32
-            main.wait_stream(self._side)
+                x, indices, weights, self.up_local, self.down_local, self.part, self.group,
+                local_fn=lambda r, u, d: local_partial_states(r, u, d, out_dtype=self.partial_dtype, status=status),
+                chunks=self.chunks, comm_stream=self._comm, x_ready=x_ready, clock=clock, between_chunks=gate_up,
+                local_partial_dtype=self.partial_dtype)
+            tk = clock.start("mlp")
             _lib.check(lib.omni_mlp_down(act.data_ptr(), wd.data_ptr(), t, h, i, states.data_ptr(), y.data_ptr(),
                                          status.data_ptr(), main.cuda_stream))
+            clock.stop(tk)
         m.last_routing = (scores, indices, weights)
         m.last_status = status
         return y.view(shape).to(hidden_states.dtype)

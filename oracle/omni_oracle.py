@@ -123,6 +123,35 @@ def routing_weights(scores) -> np.ndarray:
     return np.exp(np.asarray(scores, dtype=np.float32)).astype(np.float32)
 
 
+def routing_flip_gaps(log_probs_x, log_probs_y, oracle_scores, oracle_indices, got_indices, num_expert_sqrt: int):
+    """How far from a tie the routing slots are in which another implementation disagrees with :func:`router_topk`.
+
+    An implementation that forms the router logits with a different summation order sees log-probs that
+    differ in the last bits, so two candidates whose fp32 scores are closer than that may swap ranks or swap
+    in and out of the top k.  For every slot ``[t, j]`` with ``got_indices != oracle_indices`` this returns
+    ``|oracle_scores[t, j] - (lpx[t, ix] + lpy[t, iy])|`` where ``(ix, iy)`` is the expert the other
+    implementation put there: the distance, in the oracle's own fp32 scores, between the candidate the oracle
+    ranks ``j``-th and the one found in its place.  A legitimate flip has a gap of the order of the log-prob
+    rounding (1e-5 .. 1e-4); a selection bug shows as a large gap.
+
+    Returns ``(number of differing slots, gaps float32 [that many])``.
+    """
+    lpx = torch.as_tensor(log_probs_x).float().numpy()
+    lpy = torch.as_tensor(log_probs_y).float().numpy()
+    es = np.asarray(oracle_scores, dtype=np.float32)
+    ei = np.asarray(oracle_indices).astype(np.int64)
+    gi = np.asarray(torch.as_tensor(got_indices).cpu().numpy()).astype(np.int64)
+    n = int(num_expert_sqrt)
+    tt, jj = np.nonzero(gi != ei)
+    if tt.size == 0:
+        return 0, np.zeros(0, np.float32)
+    e = gi[tt, jj]
+    ok = (e >= 0) & (e < n * n)
+    sc = np.full(tt.shape, -np.inf, np.float32)
+    sc[ok] = (lpx[tt[ok], e[ok] // n] + lpy[tt[ok], e[ok] % n]).astype(np.float32)
+    return int(tt.size), np.abs(es[tt, jj] - sc).astype(np.float32)
+
+
 # --------------------------------------------------------------------------- #
 # expert-centric scheduling
 # --------------------------------------------------------------------------- #
@@ -249,14 +278,32 @@ class LayerParams:
         return math.floor(math.sqrt(self.num_experts))  # omni_moe/modules/omni_moe.py:38
 
 
-def layer_forward(p: LayerParams, hidden_states, return_routing: bool = False, chunk: int = 1024):
-    """Eval-mode ``OmniMoE_Torch.forward`` in fp32 (omni_moe/modules/omni_moe.py:139-194)."""
+def router_batchnorm_train(z: torch.Tensor, eps: float = BN_EPS):
+    """``BatchNorm1d(affine=False)`` in training mode: every column is normalised with the mean and the
+    biased variance of the batch (all tokens of the call), omni_moe/modules/omni_moe.py:53-54,70-71.
+    Returns ``(normalised, batch mean, unbiased batch variance)``; the last two are what the running
+    statistics are updated with (momentum 0.1 by default)."""
+    z = z.float()
+    var_b, mean_b = torch.var_mean(z, dim=0, unbiased=False)
+    t = z.size(0)
+    return (z - mean_b) / torch.sqrt(var_b + eps), mean_b, var_b * (t / max(t - 1, 1))
+
+
+def layer_forward(p: LayerParams, hidden_states, return_routing: bool = False, chunk: int = 1024,
+                  training: bool = False):
+    """``OmniMoE_Torch.forward`` in fp32 (omni_moe/modules/omni_moe.py:139-194): eval mode (running
+    statistics) by default, batch statistics with ``training=True`` (the module as constructed)."""
     hs = torch.as_tensor(hidden_states)
     shape = hs.shape
     x = hs.reshape(-1, shape[-1]).float()
     n = p.sqrt_n
-    lpx = router_log_probs(router_batchnorm_eval(router_logits(x, p.router_gate_x), p.norm_x_mean, p.norm_x_var))
-    lpy = router_log_probs(router_batchnorm_eval(router_logits(x, p.router_gate_y), p.norm_y_mean, p.norm_y_var))
+    zx, zy = router_logits(x, p.router_gate_x), router_logits(x, p.router_gate_y)
+    if training:
+        zx, zy = router_batchnorm_train(zx)[0], router_batchnorm_train(zy)[0]
+    else:
+        zx = router_batchnorm_eval(zx, p.norm_x_mean, p.norm_x_var)
+        zy = router_batchnorm_eval(zy, p.norm_y_mean, p.norm_y_var)
+    lpx, lpy = router_log_probs(zx), router_log_probs(zy)
     scores, idx = router_topk(lpx, lpy, n, p.top_k)
     w = routing_weights(scores)
     y = expert_forward(x, p.up_embed, p.down_embed, w, idx, chunk=chunk)

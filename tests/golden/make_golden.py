@@ -115,6 +115,53 @@ def main():
         y_every8=y.view(512, 256)[::8].numpy(), y_checksum=checksum(y),
         scores=sc.numpy(), indices=idx.numpy().astype(np.int16))
 
+    # ---- training mode (the module as constructed, omni_moe/modules/omni_moe.py:53-54): batch statistics -----
+    torch.manual_seed(4321)
+    m = OmniMoE_Torch(OmniMoEConfig(**cfg)).train()
+    x = torch.randn(2, 16, 64)
+    sd_before = state_arrays(m)
+    with torch.no_grad():
+        y = m(x)
+    np.savez_compressed(os.path.join(HERE, "layer_tiny_train.npz"), x=x.numpy(), y=y.numpy(), num_experts=256, top_k=4,
+                        run_mean_x=m.router_norm_x.running_mean.numpy(), run_var_x=m.router_norm_x.running_var.numpy(),
+                        run_mean_y=m.router_norm_y.running_mean.numpy(), run_var_y=m.router_norm_y.running_var.numpy(),
+                        **sd_before)
+    torch.manual_seed(0)
+    m = OmniMoE_Torch(OmniMoEConfig(256, 1024, "silu", 1024, 8)).train()
+    x = torch.randn(2, 256, 256)
+    with torch.no_grad():
+        y = m(x)
+    np.savez_compressed(
+        os.path.join(HERE, "layer_c1_train.npz"), seed=0, x_checksum=checksum(x), gate_proj_checksum=checksum(m.gate_proj.weight),
+        y_every8=y.view(512, 256)[::8].numpy(), y_checksum=checksum(y),
+        run_mean_x=m.router_norm_x.running_mean.numpy(), run_var_x=m.router_norm_x.running_var.numpy(),
+        run_mean_y=m.router_norm_y.running_mean.numpy(), run_var_y=m.router_norm_y.running_var.numpy())
+
+    # ---- configuration 2 (quick-start shape): fp32 run on bf16-rounded parameters and tokens -----------------
+    # what the bf16 kernels are compared with: the reference module computing in fp32 on exactly the bf16 operands
+    torch.set_num_threads(max(1, (os.cpu_count() or 2) // 2))
+    torch.manual_seed(0)
+    m = OmniMoE_Torch(OmniMoEConfig(1024, 4096, "silu", 4096, 16)).eval()
+    with torch.no_grad():
+        for prm in m.parameters():
+            prm.copy_(prm.to(torch.bfloat16).float())
+        x = torch.randn(1, 4096, 1024).to(torch.bfloat16).float()
+        y = m(x)
+        h = x.view(-1, 1024)
+        lpx = torch.log_softmax(m.router_norm_x(m.router_gate_x(h)), -1)
+        lpy = torch.log_softmax(m.router_norm_y(m.router_gate_y(h)), -1)
+        sx, ix = lpx.topk(16, -1)
+        sy, iy = lpy.topk(16, -1)
+        alls = (sx.unsqueeze(-1) + sy.unsqueeze(-2)).view(4096, -1)
+        alli = (ix.unsqueeze(-1) * 64 + iy.unsqueeze(-2)).view(4096, -1)
+        sc, pos = alls.topk(16, -1)
+        idx = alli.gather(-1, pos)
+    np.savez_compressed(
+        os.path.join(HERE, "layer_c2.npz"), seed=0, x_checksum=checksum(x), gate_proj_checksum=checksum(m.gate_proj.weight),
+        up_embed_checksum=checksum(m.up_embed.weight), y_every64=y.view(4096, 1024)[::64].numpy(), y_checksum=checksum(y),
+        scores_every64=sc[::64].numpy(), indices=idx.numpy().astype(np.int16))
+    torch.set_num_threads(1)
+
     # ---- router mirror (tests/test_router.py:8-22) --------------------------------------
     g = torch.Generator().manual_seed(0)
     lx = torch.log_softmax(torch.randn(64, 32, generator=g), -1)

@@ -174,3 +174,79 @@ def test_routed_kernel_equals_separate_router_and_expert_kernels(t, h, n, k):
                                            up.data_ptr(), dn.data_ptr(), t, n, k, h, N, y_in.data_ptr(), y_in.data_ptr(),
                                            None, None, None, _lib.stream_ptr()))
     assert torch.equal(y_in, y_ref)
+
+
+def _sampled_oracle(x, up, dn, w, idx, sel):
+    """fp32 oracle output for the tokens `sel` of device-resident inputs: only the table rows those tokens
+    touch are copied to the host (the oracle indexes a compact table through remapped ids)."""
+    isel = idx[sel].long()
+    need = torch.unique(isel)
+    compact = torch.searchsorted(need, isel.reshape(-1)).view(isel.shape)
+    return orc.expert_forward(x[sel].float().cpu(), up[need].float().cpu(), dn[need].float().cpu(), w[sel].float().cpu(),
+                              compact.cpu())
+
+
+def _normal_on_device(shape, std, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    out = torch.empty(shape, device="cuda", dtype=torch.bfloat16)
+    flat = out.view(-1)
+    for s in range(0, flat.numel(), 1 << 27):
+        e = min(flat.numel(), s + (1 << 27))
+        flat[s:e] = (torch.randn(e - s, device="cuda", generator=g) * std).to(torch.bfloat16)
+    return out
+
+
+def test_expert_stress_shape_full_size_against_sampled_oracle():
+    """The whole skewed stress configuration (32768 tokens, hidden 2048, 512 x 512 experts, k = 32, Zipf(1.1) with
+    replacement, Dirichlet(1) weights, tables ~ N(0, 0.02)) through the scheduled path; every 128th token is
+    recomputed by the oracle.  Also: the schedule puts the head expert's ~136 k pairs in one segment."""
+    from omni_moe_b200.ops import expert_forward
+    t, h, n, k = 32768, 2048, 262144, 32
+    x = _normal_on_device((t, h), 1.0, 1)
+    up = _normal_on_device((n, h), 0.02, 2)
+    dn = _normal_on_device((n, h), 0.02, 3)
+    idx = zipf_indices(t, k, n, 1.1, 0).cuda()
+    w = torch.distributions.Dirichlet(torch.ones(k)).sample((t,)).to(torch.bfloat16).float().cuda()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y, coef = expert_forward(x, up, dn, w, idx, out_dtype=torch.float32, status=st, return_coef=True, mode="scheduled")
+    yb = expert_forward(x, up, dn, w, idx, out_dtype=torch.bfloat16, status=st, mode="scheduled")
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert int((idx == 0).sum()) > t, "the head expert owns more pairs than there are tokens (duplicates inside a token)"
+    sel = torch.arange(0, t, 128, device="cuda")
+    ey = _sampled_oracle(x, up, dn, w, idx, sel)
+    assert_close(y[sel], ey, rtol=1e-3, atol=1e-4, what="stress shape, fp32 output")
+    assert_close(yb[sel], ey, what="stress shape, bf16 output")
+    ec = orc.expert_coefficients(x[sel].float().cpu(), up[torch.unique(idx[sel].long())].float().cpu(), w[sel].cpu(),
+                                 torch.searchsorted(torch.unique(idx[sel].long()), idx[sel].long().reshape(-1)).view(-1, k).cpu())
+    assert_close(coef[sel], ec, rtol=1e-3, atol=1e-4, what="stress shape, coefficients")
+
+
+def test_expert_largest_configuration_dimensions_against_sampled_oracle():
+    """Expert path at the dimensions of the largest configuration (hidden 4096, k = 64, 2^20 experts: 8 GiB per
+    table) on 4096 tokens: the 16-vector coefficient kernel and the two-slab combine at their real size; 64
+    tokens are recomputed by the oracle from the rows they touch."""
+    from omni_moe_b200.ops import expert_forward
+    t, h, n, k = 4096, 4096, 1 << 20, 64
+    free, _ = torch.cuda.mem_get_info()
+    if free < 24 << 30:
+        pytest.skip("needs 24 GiB of free device memory")
+    x = _normal_on_device((t, h), 1.0, 4)
+    up = _normal_on_device((n, h), 0.02, 5)
+    dn = _normal_on_device((n, h), 0.02, 6)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    idx = torch.randint(0, n, (t, k), device="cuda", dtype=torch.int32, generator=g)
+    idx[:, 1] = idx[:, 0]                      # a duplicate inside every token
+    idx[5, :] = n - 1                          # one token entirely on the last row
+    w = torch.rand(t, k, device="cuda", generator=g) * 0.1
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = expert_forward(x, up, dn, w, idx, out_dtype=torch.float32, status=st, mode="scheduled")
+    yb = expert_forward(x, up, dn, w, idx, out_dtype=torch.bfloat16, status=st, mode="scheduled")
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    sel = torch.cat([torch.arange(0, t, 65, device="cuda"), torch.tensor([5], device="cuda")])
+    ey = _sampled_oracle(x, up, dn, w, idx, sel)
+    assert_close(y[sel], ey, rtol=1e-3, atol=1e-4, what="largest configuration, fp32 output")
+    assert_close(yb[sel], ey, what="largest configuration, bf16 output")
+    del up, dn
+    torch.cuda.empty_cache()

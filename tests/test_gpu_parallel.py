@@ -67,7 +67,7 @@ x = torch.randn(1, 64 * world, 256).bfloat16()
 p = orc.params_from_state_dict(sd, 1024, 8)
 ey, _, _, _, ei = orc.layer_forward(p, x.float(), return_routing=True)
 m = PartitionedOmniMoE(full.cuda(), None)
-assert m.inner.up_embed.weight.shape[0] == 1024 // world
+assert m.up_local.shape[0] == 1024 // world and m.inner.up_embed.weight.shape[0] == 0
 xs = shard_tokens(x, rank, world).cuda().view(1, 64, 256)
 y = m(xs)
 m.inner.check_status()

@@ -40,7 +40,7 @@ def _oracle_local(recv, up_local, down_local):
     return out
 
 
-def _worker(rank, world, port, t_local, h, n, k, seed, ret):
+def _worker(rank, world, port, t_local, h, n, k, seed, ret, chunks=1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -59,25 +59,69 @@ def _worker(rank, world, port, t_local, h, n, k, seed, ret):
         sl = slice(rank * t_local, (rank + 1) * t_local)
         assert torch.equal(shard_tokens(x, rank, world), x[sl])
         got = partitioned_expert_states(x[sl], idx[sl], w[sl], part.slice_rows(up), part.slice_rows(down), part,
-                                        local_fn=_oracle_local)
+                                        local_fn=_oracle_local, chunks=chunks)
         expect = orc.expert_forward(x, up, down, w, idx)[sl]
         ret[rank] = float((got - expect).abs().max())
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,t_local,n", [(2, 12, 64), (3, 5, 50), (2, 8, 3)])
-def test_partitioned_dispatch_and_combine_gloo(world, t_local, n):
+@pytest.mark.parametrize("world,t_local,n,chunks", [(2, 12, 64, 1), (3, 5, 50, 1), (2, 8, 3, 1), (2, 12, 64, 3), (3, 8, 50, 2),
+                                                     (2, 7, 20, 2)])
+def test_partitioned_dispatch_and_combine_gloo(world, t_local, n, chunks):
+    """chunks > 1: the token ranges go through the exchange one after another (7 tokens in 2 chunks falls back to one)."""
     port = _free_port()
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, t_local, 16, n, 6, 3, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, t_local, 16, n, 6, 3, ret, chunks)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
     assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)
+
+
+def _wrapper_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from omni_moe_b200.modules.omni_moe import OmniMoE, OmniMoEConfig
+        from omni_moe_b200.parallel import PartitionedOmniMoE
+        torch.manual_seed(0)
+        full = OmniMoE(OmniMoEConfig(32, 64, "silu", 16, 2))
+        rows = full.up_embed.weight.detach().clone()
+        m = PartitionedOmniMoE(full, None)
+        out = [m.up_local.shape == (8, 32), torch.equal(m.up_local.float(), rows[rank * 8:(rank + 1) * 8].bfloat16().float()),
+               full.up_embed.weight.shape[0] == 0]
+        try:
+            full._operands()
+            out.append(False)
+        except RuntimeError as e:
+            out.append("PartitionedOmniMoE" in str(e))
+        # one expert row over two ranks: the second rank would hold nothing
+        try:
+            PartitionedOmniMoE(OmniMoE(OmniMoEConfig(32, 64, "silu", 1, 1)), None)
+            out.append(rank == 0)
+        except ValueError:
+            out.append(rank == 1)
+        ret[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+def test_partitioned_wrapper_keeps_the_slices_and_disarms_the_inner_module():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_wrapper_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert all(all(ret[r]) for r in range(world)), dict(ret)
 
 
 def test_expert_partition_arithmetic():
