@@ -210,22 +210,33 @@ OMNI_API int omni_expert_fused(const void *x, const void *up, const void *down, 
 
 /*
  * Router selection and routed experts in one kernel, for the same regime as omni_expert_fused
- * (tables resident in L2): the warp that owns a token applies the BatchNorm fold, the log-softmax
- * and the product-key top-k to the token's router logits (as omni_router_logits_topk does, same
- * results) and then gathers the k Up / Down rows.  Replaces, in OmniMoE.forward, router_norm_x/y,
+ * (tables resident in L2): the BatchNorm fold, the log-softmax and the product-key top-k are applied
+ * to the token's router logits (as omni_router_logits_topk does, same results) and the k Up / Down
+ * rows are gathered.  Replaces, in OmniMoE.forward, router_norm_x/y,
  * F.log_softmax, triton_omni_router_func, torch.exp and triton_omni_expert_func
  * (omni_moe/modules/omni_moe.py:70-95).
  *   logits [T, 2*sqrt_n] fp32 (row stride ld_logits); x, up, down bf16; y [T, H] bf16;
  *   residual [T, H] bf16 or NULL, may be y itself
  *   scores, indices (int32), weights [T, k]: the routing that was used, each may be NULL
- * Limits: hidden % 8 == 0, hidden <= 2048, sqrt_n <= 256, k <= 32.
+ *   status: device word that receives OMNI_ST_WAIT_TIMEOUT if the bounded wait of the first kernel below gives
+ *           up (a defect: the warps it waits for never block); may be NULL
+ * Two kernels.  For hidden = 256, 512 or 1024: one block per SM owns a range of tokens and its 16 warps take
+ * "select a token" and "gather a selected token" tasks from counters in shared memory, so that the selection
+ * arithmetic of some warps overlaps the row gathers of others; the k dot products x . Up[e] run on the tensor
+ * cores (mma.sync.m16n8k16: the 16 selected Up rows are the A operand, loaded straight from the table in
+ * fragment order; x, kept in shared memory, is the B operand).  The routing is bit-identical to
+ * omni_router_logits_topk; the output differs from omni_expert_fused in the last bits (another summation order)
+ * and is identical run to run.  Otherwise (hidden % 8 == 0, hidden <= 2048): one warp per token on the CUDA
+ * cores, bit-identical to omni_router_logits_topk + omni_expert_fused; OMNI_MOE_B200_ROUTED=legacy selects that
+ * kernel for every shape.  Limits of both: sqrt_n <= 256, k <= 32.
  */
 OMNI_API int omni_route_expert_fused(const float *logits, int64_t ld_logits,
                             const float *bn_scale, const float *bn_shift,
                             const void *x, const void *up, const void *down,
                             int64_t num_tokens, int sqrt_n, int k, int hidden, int64_t num_experts,
                             const void *residual, void *y,
-                            float *scores, int32_t *indices, float *weights, void *stream);
+                            float *scores, int32_t *indices, float *weights, int32_t *status,
+                            void *stream);
 
 /*
  * Shared SwiGLU MLP, y = (silu(x Wg^T) * (x Wu^T)) Wd^T (+ residual), as two tcgen05 GEMMs: the

@@ -73,7 +73,7 @@ SIGNATURES = {
                                      c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "omni_route_expert_fused": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                         c_int, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                        c_void_p]),
+                                        c_void_p, c_void_p]),
     "omni_mlp_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p]),
     "omni_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),

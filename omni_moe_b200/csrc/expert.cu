@@ -10,6 +10,8 @@
 //                       k pairs and accumulates c * Down[e] in fp32 registers, then writes the
 //                       row once.  No atomics, no zero fill, fixed summation order.
 // All row traffic is 128-bit loads, a warp reading 512 contiguous bytes per instruction.
+#include <cstdlib>
+
 #include "router_select.cuh"
 
 namespace omni {
@@ -519,6 +521,257 @@ __global__ void __launch_bounds__(kThreads, HV <= 4 ? 2 : 1) expert_routed_kerne
   store_row<HV, false>(acc, t, c0, H, residual, y);
 }
 
+// mma.sync m16n8k16, bf16 operands, fp32 accumulate: D (16 x 8) += A (16 x 16, row major) * B (16 x 8, column major).
+// Fragments (g = lane / 4, t = lane % 4): a0 = A[g][2t, 2t+1], a1 = A[g+8][2t, 2t+1], a2 = A[g][2t+8, 2t+9],
+// a3 = A[g+8][2t+8, 2t+9]; b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g]; d0, d1 = D[g][2t, 2t+1], d2, d3 = D[g+8][2t, 2t+1].
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// L2 prefetch of a contiguous range: nothing reaches the SM.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+// Router selection + routed experts, for rows of exactly HV * 256 columns (256, 512 or 1024) and k <= 32: the k dot
+// products of a token on the tensor cores, and the two stages of a token handed out dynamically.
+//
+// Dots.  The 16 x H block "Up rows of 16 selected experts" is the A operand of mma.sync.m16n8k16 and the token's x
+// row, repeated in every column, the B operand, so D[e][.] = x . Up[e].  No shared-memory staging of the rows is
+// needed: the contraction index may be permuted freely as long as both operands agree, so lane (g, t) simply loads 32
+// contiguous bytes (16 columns) of row g and of row g + 8 - four lanes cover a whole 128-byte line - and uses the
+// eight 32-bit words, two at a time, as (a0, a2) / (a1, a3) of four MMAs; the matching B words are the same 32 bytes
+// of the x row, which the warp keeps in shared memory (every lane group reads them: a broadcast).  Per 16 bytes of
+// an Up row this is half a load and half an MMA instead of eight unpack operations and four packed FMAs.
+// The k-term sum of Down rows stays on the CUDA cores (its contraction index is the row index, which mma.sync
+// could only take through a transposing copy in shared memory); every lane owns 8 contiguous columns per 256.
+// Experts that are not valid (index >= N, ranks beyond k) are replaced by a valid row with weight 0, so no load in
+// the loops is predicated.
+//
+// Scheduling.  The selection of a token is arithmetic with long dependency chains (~5 us for a warp) and the gather
+// is bound by the latency and the bandwidth of L2 (~8 us for a warp).  With one token per warp, both in a row, the
+// warps of an SM run in step - everybody selects, then everybody gathers - and a token count that is not a multiple
+// of the resident warps leaves most of them idle for a whole second round.  Here one block per SM owns a
+// contiguous range of tokens and its 16 warps take tasks from two counters in shared memory: "gather the next
+// token whose selection is finished" if there is one, otherwise "select the next unselected token".  The memory
+// system stays busy while other warps select, and the work is spread over the warps in units of half a token.
+#ifdef OMNI_TUNING
+}  // namespace
+__device__ long long g_dyn_prof[160 * 16 * 8];  // tuning builds only: per-warp clocks by part
+namespace {
+#define OMNI_TIC(v) const long long v = clock64()
+#define OMNI_TOC(acc, v) acc += clock64() - v
+#else
+#define OMNI_TIC(v)
+#define OMNI_TOC(acc, v)
+#endif
+constexpr int kDynWarps = 16;
+constexpr int kDynTokens = 32;  // tokens per block at most
+constexpr uint32_t kDynSpinLimit = 1u << 20;
+
+struct RoutedRecord {
+  int e[32];    // expert row by rank (a valid row wherever the weight is 0)
+  float w[32];  // routing weight by rank
+};
+
+template <int HV>
+__device__ __forceinline__ void gather_token_tc(const RoutedRecord& rec, int k, int64_t t, const __nv_bfloat16* __restrict__ x,
+                                                const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
+                                                uint4* xrow, const void* residual, void* y, long long* pr) {
+  constexpr int H = HV * 256;
+  const int lane = lane_id();
+  const int gq = lane >> 2, tq = lane & 3;
+  OMNI_TIC(cx);
+  uint4 xv[HV];
+#pragma unroll
+  for (int v = 0; v < HV; ++v) xv[v] = ldg128(x + t * H + v * 256 + lane * 8);
+  const int my_e = rec.e[lane];
+  const float my_w = rec.w[lane];
+  __syncwarp();  // the previous user of xrow (this warp) is done with it
+#pragma unroll
+  for (int v = 0; v < HV; ++v) xrow[v * 32 + lane] = xv[v];
+  __syncwarp();
+  float2 acc[HV][4];
+#pragma unroll
+  for (int v = 0; v < HV; ++v)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[v][q] = make_float2(0.f, 0.f);
+  const uint4* xs = xrow + 2 * tq;
+  OMNI_TOC(pr[0], cx);
+  for (int base = 0; base < k; base += 16) {
+    OMNI_TIC(cd);
+    // ---- dots of the 16 experts base .. base + 15: rows gq and gq + 8 of the tile belong to this lane group
+    const int e_a = __shfl_sync(FULL_MASK, my_e, (base + gq) & 31), e_b = __shfl_sync(FULL_MASK, my_e, (base + gq + 8) & 31);
+    const float w_a = __shfl_sync(FULL_MASK, my_w, (base + gq) & 31), w_b = __shfl_sync(FULL_MASK, my_w, (base + gq + 8) & 31);
+    const uint4* ra = reinterpret_cast<const uint4*>(up + static_cast<int64_t>(e_a) * H) + 2 * tq;
+    const uint4* rb = reinterpret_cast<const uint4*>(up + static_cast<int64_t>(e_b) * H) + 2 * tq;
+    float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 4
+    for (int s = 0; s < H / 64; ++s) {  // 64 columns per step: 16 per lane of a group
+      const uint4 a0 = __ldg(ra + 8 * s), a1 = __ldg(ra + 8 * s + 1);
+      const uint4 b0 = __ldg(rb + 8 * s), b1 = __ldg(rb + 8 * s + 1);
+      const uint4 x0 = xs[8 * s], x1 = xs[8 * s + 1];
+      mma_bf16_16816(d[0], a0.x, b0.x, a0.y, b0.y, x0.x, x0.y);
+      mma_bf16_16816(d[1], a0.z, b0.z, a0.w, b0.w, x0.z, x0.w);
+      mma_bf16_16816(d[0], a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
+      mma_bf16_16816(d[1], a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
+    }
+    // every column of D holds the same dot: d[.][0] is expert base + gq, d[.][2] expert base + gq + 8
+    const float c_a = w_a * silu(d[0][0] + d[1][0]);
+    const float c_b = w_b * silu(d[0][2] + d[1][2]);
+    OMNI_TOC(pr[1], cd);
+    OMNI_TIC(ca_);
+    // ---- y += c[j] * Down[e[j]], UNR rows in flight
+    constexpr int UNR = HV >= 4 ? 4 : 8;  // 16 x 16-byte loads per lane in flight
+    const int cnt = min(16, k - base);
+    for (int j = 0; j < cnt; j += UNR) {
+      uint4 dv[UNR][HV];
+      float c[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int jj = j + u;  // may run past cnt (but stays below 16): those ranks carry weight 0 and a valid row
+        const int e = __shfl_sync(FULL_MASK, my_e, (base + jj) & 31);
+        const float ca = __shfl_sync(FULL_MASK, c_a, (jj & 7) * 4), cb = __shfl_sync(FULL_MASK, c_b, (jj & 7) * 4);
+        c[u] = (jj & 8) ? cb : ca;
+        if (jj >= cnt) c[u] = 0.f;  // ranks of the next tile, if any, are not part of this one
+        const uint4* row = reinterpret_cast<const uint4*>(down + static_cast<int64_t>(e) * H) + lane;
+#pragma unroll
+        for (int v = 0; v < HV; ++v) dv[u][v] = __ldg(row + v * 32);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int v = 0; v < HV; ++v) axpy8p(c[u], dv[u][v], acc[v]);
+    }
+    OMNI_TOC(pr[2], ca_);
+  }
+  OMNI_TIC(cs);
+  store_row<HV, false>(acc, t, lane * 8, H, residual, y);
+  OMNI_TOC(pr[3], cs);
+}
+
+template <int HV, int VPL, int CPL>
+__global__ void __launch_bounds__(kDynWarps * 32, 1) expert_routed_dyn_kernel(
+    const sel::TopkArgs a, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up,
+    const __nv_bfloat16* __restrict__ down, int64_t N, int tok_per_block, const void* residual, void* y, int* status) {
+  constexpr int H = HV * 256;
+  using Scratch = sel::WarpScratch<VPL, CPL, 32>;  // k <= 32: at most 32 sub-keys kept per axis
+  __shared__ Scratch s_warp[kDynWarps];
+  __shared__ sel::RegionTable s_region;
+  __shared__ int s_sel_next, s_gat_next, s_abort;
+  __shared__ int s_ready[kDynTokens];
+  extern __shared__ __align__(16) unsigned char s_dyn[];
+  uint4* s_x = reinterpret_cast<uint4*>(s_dyn);  // [kDynWarps][HV * 32]
+  RoutedRecord* s_rec = reinterpret_cast<RoutedRecord*>(s_dyn + kDynWarps * HV * 32 * sizeof(uint4));  // [kDynTokens]
+  if (threadIdx.x < kDynTokens) s_ready[threadIdx.x] = 0;
+  if (threadIdx.x == 0) s_sel_next = 0, s_gat_next = 0, s_abort = 0;
+  sel::build_region_table(s_region, a.kk, a.k, kDynWarps);  // ends with a block barrier
+  // The tables are weights, not the output of an earlier kernel: every block asks for its share of both to be streamed
+  // into L2 now, so that the row gathers below, which arrive in routing order, find them there.
+  if (threadIdx.x < 2) {
+    const int64_t total = N * H * 2;  // bytes of one table
+    const int64_t share = ((total + gridDim.x - 1) / gridDim.x + 255) & ~int64_t(255);
+    const int64_t lo = share * blockIdx.x, hi = min(total, lo + share);
+    const unsigned char* tab = reinterpret_cast<const unsigned char*>(threadIdx.x == 0 ? up : down);
+    for (int64_t o = lo; o < hi; o += 16384) l2_prefetch_bulk(tab + o, static_cast<uint32_t>(min(int64_t(16384), hi - o)));
+  }
+  pdl_wait();  // the logits and y come from earlier kernels
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * tok_per_block;
+  const int ntok = static_cast<int>(min(static_cast<int64_t>(tok_per_block), a.T - t0));
+  const int k = a.k;
+  uint32_t idle = 0;
+  long long pr[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // x row, dots, output, store, select, idle, tasks, total (tuning builds)
+#ifdef OMNI_TUNING
+  const long long pr_t0 = clock64();
+#endif
+  while (true) {
+    // lane 0 picks the task: 1 = gather token idx, 2 = select token idx, 0 = nothing to do right now, -1 = finished
+    int task = 0, idx = 0;
+    if (lane == 0) {
+      const int g = *reinterpret_cast<volatile int*>(&s_gat_next);
+      if (g >= ntok || *reinterpret_cast<volatile int*>(&s_abort)) {
+        task = -1;
+      } else {
+        const bool can_gather = *reinterpret_cast<volatile int*>(&s_ready[g]) != 0;
+        const bool can_select = *reinterpret_cast<volatile int*>(&s_sel_next) < ntok;
+        // half of the warps prefer to gather, the other half to select, so that the two kinds of work overlap
+        const bool want_select = can_select && (!can_gather || warp >= kDynWarps / 2);
+        if (want_select) {
+          const int s = atomicAdd(&s_sel_next, 1);
+          if (s < ntok) task = 2, idx = s;
+          else task = 3;
+        } else if (can_gather) {
+          if (atomicCAS(&s_gat_next, g, g + 1) == g) task = 1, idx = g;
+          else task = 3;  // another warp took it: look again
+        }
+      }
+    }
+    task = __shfl_sync(FULL_MASK, task, 0);
+    idx = __shfl_sync(FULL_MASK, idx, 0);
+    if (task < 0) break;
+    if (task == 1) {
+      __threadfence_block();  // the record was written before the flag
+      gather_token_tc<HV>(s_rec[idx], k, t0 + idx, x, up, down, s_x + warp * (HV * 32), residual, y, pr);
+      pr[6] += 1;
+      idle = 0;
+    } else if (task == 2) {
+      OMNI_TIC(cq);
+      const int64_t t = t0 + idx;
+      uint32_t rkey[sel::kMaxK / 32], rflat[sel::kMaxK / 32];
+      sel::select_token<VPL, CPL, true, Scratch>(a, t, s_warp[warp], s_region.cell, rkey, rflat);
+      // k <= 32 (checked by the host), so rank r lives in lane r
+      int my_e = 0;
+      float my_w = 0.f;
+      bool valid = false;
+      if (lane < k) {
+        const float sc = key_to_float(rkey[0]);
+        my_w = expf(sc);
+        my_e = static_cast<int>(rflat[0]);  // < sqrt_n^2 <= N by construction
+        const int64_t o = t * k + lane;
+        if (a.scores) a.scores[o] = sc;
+        if (a.indices) reinterpret_cast<int32_t*>(a.indices)[o] = my_e;
+        if (a.weights) a.weights[o] = my_w;
+        valid = my_e >= 0 && my_e < N;
+      }
+      const unsigned ok_mask = __ballot_sync(FULL_MASK, valid);
+      const int safe = ok_mask ? __shfl_sync(FULL_MASK, my_e, __ffs(ok_mask) - 1) : 0;  // a row that exists
+      s_rec[idx].e[lane] = valid ? my_e : safe;
+      s_rec[idx].w[lane] = valid ? my_w : 0.f;
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&s_ready[idx]) = 1;
+      }
+      idle = 0;
+      OMNI_TOC(pr[4], cq);
+      pr[6] += 1000;
+    } else if (task == 0) {
+      OMNI_TIC(ci);
+      // every token is being selected by some other warp and none is ready yet: those warps never wait, so this ends;
+      // the limit only guards against a defect
+      __nanosleep(200);
+      if (++idle > kDynSpinLimit) {
+        if (lane == 0) {
+          s_abort = 1;
+          if (status) atomicOr(status, OMNI_ST_WAIT_TIMEOUT);
+        }
+        break;
+      }
+      OMNI_TOC(pr[5], ci);
+    }
+  }
+#ifdef OMNI_TUNING
+  if (lane == 0 && blockIdx.x < 160) {
+    pr[7] = clock64() - pr_t0;
+    for (int i = 0; i < 8; ++i) g_dyn_prof[(blockIdx.x * 16 + warp) * 8 + i] = pr[i];
+  }
+#endif
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -621,7 +874,7 @@ extern "C" int omni_route_expert_fused(const float* logits, int64_t ld_logits, c
                                        const float* bn_shift, const void* x, const void* up, const void* down,
                                        int64_t num_tokens, int sqrt_n, int k, int hidden, int64_t num_experts,
                                        const void* residual, void* y, float* scores, int32_t* indices,
-                                       float* weights, void* stream) {
+                                       float* weights, int32_t* status, void* stream) {
   OMNI_REQUIRE(num_tokens >= 0 && hidden >= 8 && hidden % 8 == 0 && hidden <= 2048,
                "hidden must be a multiple of 8 in [8, 2048], got %d", hidden);
   OMNI_REQUIRE(sqrt_n >= 1 && sqrt_n <= 256, "omni_route_expert_fused: sqrt_n must be in [1, 256], got %d", sqrt_n);
@@ -645,6 +898,47 @@ extern "C" int omni_route_expert_fused(const float* logits, int64_t ld_logits, c
   const auto* db = static_cast<const __nv_bfloat16*>(down);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
+  static const bool legacy = [] {
+    const char* e = getenv("OMNI_MOE_B200_ROUTED");
+    return e && e[0] == 'l';  // "legacy": one token per warp, dot products on the CUDA cores, for every shape
+  }();
+  if (!legacy && (hidden == 256 || hidden == 512 || hidden == 1024)) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    int tpb = static_cast<int>(ceil_div64(num_tokens, sms));
+    tpb = tpb < 1 ? 1 : (tpb > kDynTokens ? kDynTokens : tpb);
+    const unsigned dgrid = static_cast<unsigned>(ceil_div64(num_tokens, tpb));
+    const size_t dyn = static_cast<size_t>(kDynWarps) * (hidden / 8) * sizeof(uint4) + kDynTokens * sizeof(RoutedRecord);
+#define OMNI_ROUTED_DYN(HV, VPL, CPL)                                                                                      \
+  do {                                                                                                                     \
+    static OncePerDevice once;                                                                                             \
+    if (once.first() && cudaFuncSetAttribute(expert_routed_dyn_kernel<HV, VPL, CPL>,                                       \
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,                                   \
+                                             kDynWarps * HV * 32 * 16 + kDynTokens * sizeof(RoutedRecord)) != cudaSuccess) \
+      return fail(-3, "expert_routed_dyn_kernel: cannot reserve its shared memory");                                       \
+    launch_after_predecessor(expert_routed_dyn_kernel<HV, VPL, CPL>, dim3(dgrid), dim3(kDynWarps * 32), dyn, st, a, xb, ub, \
+                             db, num_experts, tpb, residual, y, status);                                                    \
+  } while (0)
+#define OMNI_ROUTED_DYN_HV(VPL, CPL)                        \
+  do {                                                      \
+    if (hidden == 256) OMNI_ROUTED_DYN(1, VPL, CPL);        \
+    else if (hidden == 512) OMNI_ROUTED_DYN(2, VPL, CPL);   \
+    else OMNI_ROUTED_DYN(4, VPL, CPL);                      \
+  } while (0)
+    const bool small = a.cells <= 64;
+    if (sqrt_n <= 64) {
+      if (small) OMNI_ROUTED_DYN_HV(2, 2);
+      else OMNI_ROUTED_DYN_HV(2, 4);
+    } else {
+      if (small) OMNI_ROUTED_DYN_HV(8, 2);
+      else OMNI_ROUTED_DYN_HV(8, 4);
+    }
+#undef OMNI_ROUTED_DYN_HV
+#undef OMNI_ROUTED_DYN
+    return check_launch("expert_routed_dyn_kernel");
+  }
 #define OMNI_ROUTED(HV, VPL, CPL) \
   launch_after_predecessor(expert_routed_kernel<HV, VPL, CPL>, dim3(grid), dim3(kThreads), 0, st, a, xb, ub, db, hidden, \
                            num_experts, residual, y)
@@ -727,3 +1021,10 @@ extern "C" int omni_expert_combine_segments(const void* down, const float* coef,
 #undef OMNI_COMBS
   return check_launch("expert_combine_segments_kernel");
 }
+
+#ifdef OMNI_TUNING
+// tuning builds only: the per-warp cycle counters of the latest expert_routed_dyn_kernel launch (160 x 16 x 8 words)
+extern "C" OMNI_API int omni_debug_routed_profile(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, omni::g_dyn_prof, sizeof(long long) * 160 * 16 * 8) == cudaSuccess ? 0 : -3;
+}
+#endif

@@ -227,14 +227,15 @@ __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], con
   __syncwarp();
 }
 
-// Shared memory of one warp.
-template <int VPL, int CPL>
+// Shared memory of one warp.  KCAP bounds kk = min(sqrt_n, k), the sub-keys kept per axis; a kernel that
+// only serves small k can shrink it.
+template <int VPL, int CPL, int KCAP = kMaxK>
 struct WarpScratch {
   static constexpr bool kAllSmall = (VPL == 2) && (CPL == 2);
   __align__(16) unsigned long long pack[kAllSmall ? 64 : kMaxK];  // ranking scratch
   uint32_t rk[CPL == 2 ? 64 : kMaxK], rf[CPL == 2 ? 64 : kMaxK];  // selected (score key, flat index) by rank
-  float sx[kMaxK], sy[kMaxK];
-  int ix[kMaxK], iy[kMaxK];
+  float sx[KCAP], sy[KCAP];
+  int ix[KCAP], iy[KCAP];
 };
 
 // Shared memory of the block: the cells of the pruned region, i | j << 8 each.
@@ -287,8 +288,8 @@ __device__ __forceinline__ bool ranks_distinct(int r0, int r1, int want) {
   return cnt == want && __popc(mask) == want;
 }
 
-template <int VPL, int CPL, bool PRE>
-__device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, WarpScratch<VPL, CPL>& w,
+template <int VPL, int CPL, bool PRE, class Scratch = WarpScratch<VPL, CPL>>
+__device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scratch& w,
                                              const uint16_t* cell_table, uint32_t (&rkey)[kMaxK / 32],
                                              uint32_t (&rflat)[kMaxK / 32]) {
   constexpr bool kSmallAxis = VPL == 2;   // n <= 64: rank by counting instead of selection rounds

@@ -88,6 +88,23 @@ def time_graph(fn, launches=4, reps=10):
     return ts[len(ts) // 2]
 
 
+def time_graph_cold(fn, reps=10):
+    """Microseconds of one launch of `fn(stream_ptr)` that finds nothing of its data in L2: a 512 MB fill runs before
+    every launch, and the fill's own time (measured the same way) is taken off."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    junk = torch.empty(512 << 20, device=dev, dtype=torch.uint8)
+
+    def flush_then(run_fn):
+        def go(stream_ptr):
+            junk.fill_(1)
+            if run_fn:
+                fn(stream_ptr)
+        return go
+    both = time_graph(flush_then(True), launches=1, reps=reps)
+    alone = time_graph(flush_then(False), launches=1, reps=reps)
+    return both - alone
+
+
 def run_backward(name: str, reps: int):
     """Stages of the backward pass (router scatter, expert gradients, MLP gradient GEMMs and helpers)."""
     from .ops.scheduler import schedule
@@ -276,6 +293,20 @@ def run_config(name: str, reps: int):
                                                             indices.data_ptr(), T, k, H, N, None, y.data_ptr(),
                                                             _lib.OMNI_BF16, None, status.data_ptr(), s)), reps=reps)
         report("expert_fused", us, "hbm", alg - 12.0 * P + 8.0 * P)
+    from .ops.expert import use_routed_kernel
+    if H <= 2048 and n <= 256 and use_routed_kernel(N, H, n, k):
+        # selection + routed experts in one kernel, from the router logits (what the layer launches for tables in L2)
+        logits_r = torch.randn((T, 2 * n), **f32)
+        sc_r, w_r = torch.empty((T, k), **f32), torch.empty((T, k), **f32)
+        idx_r = torch.empty((T, k), **i32)
+        run_routed = lambda s: chk(lib.omni_route_expert_fused(
+            logits_r.data_ptr(), 2 * n, None, None, x.data_ptr(), up.data_ptr(), down.data_ptr(), T, n, k, H, N, y.data_ptr(),
+            y.data_ptr(), sc_r.data_ptr(), idx_r.data_ptr(), w_r.data_ptr(), status.data_ptr(), s))
+        us = time_graph(run_routed, reps=reps)
+        u_r = int(torch.unique(idx_r).numel())
+        alg_r = 6.0 * T * H + 4.0 * u_r * H + 8.0 * T * n + 12.0 * P   # x in, y in and out, touched rows once, logits in, routing out
+        report("route_expert_fused_warm", us, "hbm", alg_r, f"tables in L2; {u_r} distinct experts")
+        report("route_expert_fused_cold", time_graph_cold(run_routed, reps=reps), "hbm", alg_r, "L2 flushed before every launch")
     # ---- shared MLP (tensor) --------------------------------------------------------------------
     if I:
         wg = _randn_bf16((I, H), H ** -0.5, dev, 5)

@@ -229,7 +229,7 @@ class OmniMoE(nn.Module):
             chk(lib.omni_route_expert_fused(b.logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), x.data_ptr(),
                                             up_t.data_ptr(), down_t.data_ptr(), t, n, k, h, self.num_experts,
                                             y.data_ptr(), y.data_ptr(), b.scores.data_ptr(), b.indices.data_ptr(),
-                                            b.weights.data_ptr(), st))
+                                            b.weights.data_ptr(), status, st))
         elif use_fused_path(self.num_experts, h):
             chk(lib.omni_expert_fused(x.data_ptr(), up_t.data_ptr(), down_t.data_ptr(), b.weights.data_ptr(),
                                       b.indices.data_ptr(), t, k, h, self.num_experts, y.data_ptr(), y.data_ptr(),

@@ -63,7 +63,8 @@ def route_expert_fused(logits: torch.Tensor, x: torch.Tensor, up_weight: torch.T
         _lib.check(_lib.load().omni_route_expert_fused(
             logits.data_ptr(), logits.size(1), _lib.ptr(bn_scale), _lib.ptr(bn_shift), x.data_ptr(),
             up_weight.data_ptr(), down_weight.data_ptr(), t, n, k, h, up_weight.size(0), _lib.ptr(residual),
-            y.data_ptr(), _lib.ptr(scores), _lib.ptr(indices), _lib.ptr(weights), _lib.stream_ptr()))
+            y.data_ptr(), _lib.ptr(scores), _lib.ptr(indices), _lib.ptr(weights), _lib.device_status(dev).data_ptr(),
+            _lib.stream_ptr()))
     return (y, scores, indices, weights) if return_routing else y
 
 

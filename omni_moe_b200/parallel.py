@@ -345,7 +345,8 @@ def partitioned_expert_states(x: torch.Tensor, indices: torch.Tensor, weights: t
                               local_fn: Callable[[ReceivedPairs, torch.Tensor, torch.Tensor], torch.Tensor] | None = None,
                               chunks: int = 1, comm_stream=None, x_ready=None, clock: "_PhaseClock | None" = None,
                               between_chunks: Callable[[int], None] | None = None,
-                              local_partial_dtype: torch.dtype | None = None) -> torch.Tensor:
+                              local_partial_dtype: torch.dtype | None = None,
+                              x_all_buffers: list | None = None) -> torch.Tensor:
     """Steps 2-4: routed-expert states ``[T_local, H]`` of this rank's tokens with the tables partitioned by
     rows.  ``local_fn`` replaces step 3 (the CPU tests pass the oracle's arithmetic there); by default it is
     :func:`local_partial_states`, the CUDA kernels.
@@ -353,7 +354,9 @@ def partitioned_expert_states(x: torch.Tensor, indices: torch.Tensor, weights: t
     With ``chunks > 1`` the local tokens are cut into that many equal ranges which go through dispatch,
     local kernels and combine one after another; on CUDA with a ``comm_stream`` every collective is issued
     on that stream, so the transfers of one chunk run beside the kernels of another.  ``x_ready`` is an event
-    after which ``x`` may be read (default: now, on the current stream); ``between_chunks(c)`` is called on
+    after which ``x`` may be read and ``x_all_buffers`` (one ``[world * T_local / chunks, H]`` buffer per chunk,
+    allocated by the caller BEFORE that event was recorded) may be written; without them the all-gathers start
+    now, on the current stream's position.  ``between_chunks(c)`` is called on
     the compute stream after chunk ``c``'s kernels were enqueued (the caller's own work, e.g. a GEMM that
     needs no exchange); ``local_partial_dtype`` is the dtype ``local_fn`` returns (default float32) - the
     pipelined form allocates the reduce-scatter outputs before the kernels run.  Returns float32 in the
@@ -377,12 +380,18 @@ def partitioned_expert_states(x: torch.Tensor, indices: torch.Tensor, weights: t
 
     main = torch.cuda.current_stream()
     dev, h, world = x.device, x.size(1), part.world
-    if x_ready is None:
+    if x_ready is None or x_all_buffers is None:
+        x_ready, x_all_buffers = None, None
+    # Every buffer is allocated while the compute stream is current and reaches the communication stream through
+    # an event recorded AFTER its allocation (the caching allocator may hand out a block that earlier work of the
+    # compute stream still reads: the other stream has to be behind that work before it writes the block);
+    # record_stream() at the end tells the allocator about the second user.
+    if x_all_buffers is None:
+        x_all_buffers = [torch.empty((world * tc, h), device=dev, dtype=x.dtype) for _ in range(chunks)]
         x_ready = torch.cuda.Event()
         x_ready.record(main)
-    # Every buffer is allocated here, while the compute stream is current, and handed to the communication
-    # stream by events; record_stream() at the end tells the caching allocator about the second user.
-    x_alls = [torch.empty((world * tc, h), device=dev, dtype=x.dtype) for _ in range(chunks)]
+    x_alls = x_all_buffers
+    assert len(x_alls) == chunks and all(b.shape == (world * tc, h) for b in x_alls)
     # token rows first: they need no routing, so their all-gathers start while the router still runs
     with torch.cuda.stream(comm_stream):
         comm_stream.wait_event(x_ready)
@@ -522,13 +531,15 @@ class PartitionedOmniMoE(torch.nn.Module):
             if self._comm is None:
                 self._comm = torch.cuda.Stream(device=dev)
             main = torch.cuda.current_stream()
+            n_chunks = self.chunks if (self.chunks >= 1 and t % max(self.chunks, 1) == 0) else 1
+            # the all-gathered token rows: allocated before the event the communication stream waits for
+            x_alls = [torch.empty((self.part.world * (t // n_chunks), h), device=dev, dtype=torch.bfloat16) for _ in range(n_chunks)]
             x_ready = torch.cuda.Event()
             x_ready.record(main)
             tk = clock.start("route")
             scores, indices, weights = router_gate_topk(x, kx, ky, m.top_k, scale, shift, status=status)
             clock.stop(tk)
 
-            n_chunks = self.chunks if (self.chunks >= 1 and t % max(self.chunks, 1) == 0) else 1
             mlp_at = n_chunks - 1 if self.mlp_after_chunk is None else min(self.mlp_after_chunk, n_chunks - 1)
 
             def gate_up(c):
@@ -541,8 +552,8 @@ class PartitionedOmniMoE(torch.nn.Module):
             states = partitioned_expert_states(
                 x, indices, weights, self.up_local, self.down_local, self.part, self.group,
                 local_fn=lambda r, u, d: local_partial_states(r, u, d, out_dtype=self.partial_dtype, status=status),
-                chunks=self.chunks, comm_stream=self._comm, x_ready=x_ready, clock=clock, between_chunks=gate_up,
-                local_partial_dtype=self.partial_dtype)
+                chunks=n_chunks, comm_stream=self._comm, x_ready=x_ready, clock=clock, between_chunks=gate_up,
+                local_partial_dtype=self.partial_dtype, x_all_buffers=x_alls)
             tk = clock.start("mlp")
             _lib.check(lib.omni_mlp_down(act.data_ptr(), wd.data_ptr(), t, h, i, states.data_ptr(), y.data_ptr(),
                                          status.data_ptr(), main.cuda_stream))

@@ -119,7 +119,7 @@ def main():
     torch.manual_seed(4321)
     m = OmniMoE_Torch(OmniMoEConfig(**cfg)).train()
     x = torch.randn(2, 16, 64)
-    sd_before = state_arrays(m)
+    sd_before = {k: v.copy() for k, v in state_arrays(m).items()}   # copies: the forward updates the running statistics in place
     with torch.no_grad():
         y = m(x)
     np.savez_compressed(os.path.join(HERE, "layer_tiny_train.npz"), x=x.numpy(), y=y.numpy(), num_experts=256, top_k=4,

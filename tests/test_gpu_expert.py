@@ -137,10 +137,19 @@ def test_expert_stress_shape_properties():
     assert_close(y1[sel.cuda()], ey, rtol=1e-3, atol=1e-4)
 
 
+def _mma_shape(h, n, k):
+    """Shapes whose dot products the routed kernel runs on the tensor cores (the others stay on the CUDA cores)."""
+    return h in (256, 512, 1024) and os.environ.get("OMNI_MOE_B200_ROUTED", "")[:1] != "l"
+
+
 @pytest.mark.parametrize("t,h,n,k", [(300, 256, 32, 8), (257, 1024, 64, 16), (100, 512, 100, 24), (64, 2048, 16, 32),
-                                       (130, 72, 200, 2), (50, 128, 8, 30)])
+                                       (130, 72, 200, 2), (50, 128, 8, 30), (4103, 1024, 64, 16), (1, 128, 8, 2), (33, 640, 16, 5),
+                                       (1000, 384, 64, 12), (5000, 512, 32, 16), (2, 1024, 4, 16), (95, 896, 64, 1), (77, 1024, 128, 32),
+                                       (64, 256, 200, 30), (40, 512, 16, 17)])
 def test_routed_kernel_equals_separate_router_and_expert_kernels(t, h, n, k):
-    """omni_route_expert_fused = omni_router_logits_topk followed by omni_expert_fused, bit for bit."""
+    """omni_route_expert_fused = omni_router_logits_topk followed by omni_expert_fused: the routing bit for bit;
+    the output bit for bit from the one-warp-per-token kernel, and within bf16 rounding of it (and within the
+    bf16 bar of the fp32 oracle) from the tensor-core kernel, whose sums run in another order."""
     from omni_moe_b200 import _lib
     from omni_moe_b200.ops import expert_forward, route_expert_fused
     g = gen(t + n + k)
@@ -163,8 +172,22 @@ def test_routed_kernel_equals_separate_router_and_expert_kernels(t, h, n, k):
     y_ref = expert_forward(x, up, dn, w, idx, out_dtype=torch.bfloat16, residual=res, mode="fused")
     y, sc2, idx2, w2 = route_expert_fused(logits, x, up, dn, k, scale, shift, residual=res)
     torch.cuda.synchronize()
+    _lib.check_device_status()
     assert torch.equal(idx2, idx) and torch.equal(sc2, sc) and torch.equal(w2, w)
-    assert torch.equal(y, y_ref)
+    mma = _mma_shape(h, n, k)
+
+    def same_output(got):
+        if not mma:
+            assert torch.equal(got, y_ref)
+            return
+        # both round the same fp32 sum (up to its last bits) to bf16: at most one bf16 step apart
+        assert_close(got, y_ref, rtol=2 ** -7, atol=1e-3, what="tensor-core routed kernel vs one-warp-per-token kernel")
+        ey = orc.expert_forward(x.cpu(), up.cpu(), dn.cpu(), w.cpu(), idx.cpu()) + res.float().cpu()
+        assert_close(got, ey, what="tensor-core routed kernel vs oracle")
+        y_again, _, _, _ = route_expert_fused(logits, x, up, dn, k, scale, shift, residual=res)
+        assert torch.equal(y_again, got), "the output must be identical run to run"
+
+    same_output(y)
     # and the selection is the oracle's, given the log-probs the kernel computed
     es, ei = orc.router_topk(lp[:, :n].cpu().contiguous(), lp[:, n:].cpu().contiguous(), n, k)
     np.testing.assert_array_equal(idx2.cpu().numpy(), ei)
@@ -172,8 +195,30 @@ def test_routed_kernel_equals_separate_router_and_expert_kernels(t, h, n, k):
     y_in = res.clone()
     _lib.check(lib.omni_route_expert_fused(logits.data_ptr(), 2 * n, scale.data_ptr(), shift.data_ptr(), x.data_ptr(),
                                            up.data_ptr(), dn.data_ptr(), t, n, k, h, N, y_in.data_ptr(), y_in.data_ptr(),
-                                           None, None, None, _lib.stream_ptr()))
-    assert torch.equal(y_in, y_ref)
+                                           None, None, None, None, _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    same_output(y_in)
+
+
+def test_routed_tensor_core_kernel_keeps_fp32_coefficients():
+    """Only the operands of the dot products pass through the tensor cores; the coefficient w * silu(dot) stays in
+    fp32.  With one expert per token, no residual and Down rows that are all 0.75 the output is
+    bf16(coefficient x 0.75): a coefficient cut to bf16 would round differently on a large share of the tokens."""
+    from omni_moe_b200.ops import route_expert_fused
+    t, h, n, k = 256, 256, 16, 1
+    g = gen(5)
+    x = (torch.randn(t, h, generator=g) * 0.5).bfloat16().cuda()
+    up = (torch.randn(n * n, h, generator=g) * 0.1).bfloat16().cuda()
+    dn = torch.full((n * n, h), 0.75).bfloat16().cuda()
+    logits = torch.randn(t, 2 * n, generator=g).cuda()
+    y, sc, idx, w = route_expert_fused(logits, x, up, dn, k)
+    torch.cuda.synchronize()
+    coef = orc.expert_coefficients(x.cpu(), up.cpu(), w.cpu(), idx.cpu())[:, 0]
+    expect = (coef * 0.75).bfloat16().float()       # one rounding: of the exact product
+    got = y.float().cpu()[:, 0]
+    cut = (coef.bfloat16().float() * 0.75).bfloat16().float()
+    assert (cut != expect).float().mean() > 0.1, "the inputs do not tell a truncated coefficient from a full one"
+    assert (got == expect).float().mean() > 0.97, float((got == expect).float().mean())
 
 
 def _sampled_oracle(x, up, dn, w, idx, sel):
