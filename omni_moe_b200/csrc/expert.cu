@@ -577,8 +577,9 @@ struct RoutedRecord {
   float w[32];  // routing weight by rank
 };
 
+// Lane r brings the expert row and the routing weight of rank r (a valid row with weight 0 where there is none).
 template <int HV>
-__device__ __forceinline__ void gather_token_tc(const RoutedRecord& rec, int k, int64_t t, const __nv_bfloat16* __restrict__ x,
+__device__ __forceinline__ void gather_token_tc(int my_e, float my_w, int k, int64_t t, const __nv_bfloat16* __restrict__ x,
                                                 const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
                                                 uint4* xrow, const void* residual, void* y, long long* pr) {
   constexpr int H = HV * 256;
@@ -588,8 +589,6 @@ __device__ __forceinline__ void gather_token_tc(const RoutedRecord& rec, int k, 
   uint4 xv[HV];
 #pragma unroll
   for (int v = 0; v < HV; ++v) xv[v] = ldg128(x + t * H + v * 256 + lane * 8);
-  const int my_e = rec.e[lane];
-  const float my_w = rec.w[lane];
   __syncwarp();  // the previous user of xrow (this warp) is done with it
 #pragma unroll
   for (int v = 0; v < HV; ++v) xrow[v * 32 + lane] = xv[v];
@@ -651,6 +650,43 @@ __device__ __forceinline__ void gather_token_tc(const RoutedRecord& rec, int k, 
   OMNI_TIC(cs);
   store_row<HV, false>(acc, t, lane * 8, H, residual, y);
   OMNI_TOC(pr[3], cs);
+}
+
+// The routed experts of tokens whose routing is already known (indices / weights in memory), one warp per token, dots
+// on the tensor cores as above.  bf16 output; the caller's residual is added.
+template <int HV>
+__global__ void __launch_bounds__(kThreads, 2) expert_fused_tc_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
+    const float* __restrict__ weights, const int* __restrict__ indices, int64_t T, int k, int64_t N, const void* residual,
+    void* y, int* status) {
+  constexpr int H = HV * 256;
+  __shared__ __align__(16) uint4 s_x[kWarps][HV * 32];
+  if (threadIdx.x < 2) {  // this block's share of both tables into L2, as a stream (they are weights: no dependency)
+    const int64_t total = N * H * 2;
+    const int64_t share = ((total + gridDim.x - 1) / gridDim.x + 255) & ~int64_t(255);
+    const int64_t lo = share * blockIdx.x, hi = min(total, lo + share);
+    const unsigned char* tab = reinterpret_cast<const unsigned char*>(threadIdx.x == 0 ? up : down);
+    for (int64_t o = lo; o < hi; o += 16384) l2_prefetch_bulk(tab + o, static_cast<uint32_t>(min(int64_t(16384), hi - o)));
+  }
+  pdl_wait();  // the routing and y come from earlier kernels
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (t >= T) return;
+  int my_e = 0;
+  float my_w = 0.f;
+  bool valid = false, bad = false;
+  if (lane < k) {
+    my_e = indices[t * k + lane];
+    my_w = weights[t * k + lane];
+    valid = my_e >= 0 && my_e < N;
+    bad = !valid;
+  }
+  const unsigned ok_mask = __ballot_sync(FULL_MASK, valid);
+  const int safe = ok_mask ? __shfl_sync(FULL_MASK, my_e, __ffs(ok_mask) - 1) : 0;  // a row that exists
+  if (!valid) my_e = safe, my_w = 0.f;
+  long long pr[8];
+  gather_token_tc<HV>(my_e, my_w, k, t, x, up, down, s_x[warp], residual, y, pr);
+  if (__any_sync(FULL_MASK, bad) && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
 }
 
 template <int HV, int VPL, int CPL>
@@ -715,7 +751,7 @@ __global__ void __launch_bounds__(kDynWarps * 32, 1) expert_routed_dyn_kernel(
     if (task < 0) break;
     if (task == 1) {
       __threadfence_block();  // the record was written before the flag
-      gather_token_tc<HV>(s_rec[idx], k, t0 + idx, x, up, down, s_x + warp * (HV * 32), residual, y, pr);
+      gather_token_tc<HV>(s_rec[idx].e[lane], s_rec[idx].w[lane], k, t0 + idx, x, up, down, s_x + warp * (HV * 32), residual, y, pr);
       pr[6] += 1;
       idle = 0;
     } else if (task == 2) {
@@ -773,6 +809,15 @@ __global__ void __launch_bounds__(kDynWarps * 32, 1) expert_routed_dyn_kernel(
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// OMNI_MOE_B200_ROUTED=legacy: dot products on the CUDA cores, one token per warp, for every shape
+bool routed_legacy() {
+  static const bool v = [] {
+    const char* e = getenv("OMNI_MOE_B200_ROUTED");
+    return e && e[0] == 'l';
+  }();
+  return v;
+}
 
 }  // namespace
 }  // namespace omni
@@ -853,6 +898,20 @@ extern "C" int omni_expert_fused(const void* x, const void* up, const void* down
   const auto* db = static_cast<const __nv_bfloat16*>(down);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
+  if (!routed_legacy() && out_dtype == OMNI_BF16 && coef == nullptr && k <= 32 &&
+      (hidden == 256 || hidden == 512 || hidden == 1024)) {
+    // dots on the tensor cores; output bits differ from the CUDA-core kernel below (another summation order)
+    if (hidden == 256)
+      launch_after_predecessor(expert_fused_tc_kernel<1>, dim3(grid), dim3(kThreads), 0, st, xb, ub, db, weights, indices,
+                               num_tokens, k, num_experts, residual, y, status);
+    else if (hidden == 512)
+      launch_after_predecessor(expert_fused_tc_kernel<2>, dim3(grid), dim3(kThreads), 0, st, xb, ub, db, weights, indices,
+                               num_tokens, k, num_experts, residual, y, status);
+    else
+      launch_after_predecessor(expert_fused_tc_kernel<4>, dim3(grid), dim3(kThreads), 0, st, xb, ub, db, weights, indices,
+                               num_tokens, k, num_experts, residual, y, status);
+    return check_launch("expert_fused_tc_kernel");
+  }
 #define OMNI_FUSED(HV)                                                                                                 \
   do {                                                                                                                 \
     if (out_dtype == OMNI_F32)                                                                                         \
@@ -898,11 +957,7 @@ extern "C" int omni_route_expert_fused(const float* logits, int64_t ld_logits, c
   const auto* db = static_cast<const __nv_bfloat16*>(down);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
-  static const bool legacy = [] {
-    const char* e = getenv("OMNI_MOE_B200_ROUTED");
-    return e && e[0] == 'l';  // "legacy": one token per warp, dot products on the CUDA cores, for every shape
-  }();
-  if (!legacy && (hidden == 256 || hidden == 512 || hidden == 1024)) {
+  if (!routed_legacy() && (hidden == 256 || hidden == 512 || hidden == 1024)) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

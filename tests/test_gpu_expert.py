@@ -295,3 +295,35 @@ def test_expert_largest_configuration_dimensions_against_sampled_oracle():
     assert_close(yb[sel], ey, what="largest configuration, bf16 output")
     del up, dn
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("t,h,n,k", [(300, 256, 1024, 8), (257, 1024, 4096, 16), (65, 512, 100, 32), (9, 1024, 40, 17), (1, 256, 1, 1)])
+def test_fused_tensor_core_gather_matches_oracle(t, h, n, k):
+    """omni_expert_fused with a bf16 output and no coefficient output, hidden 256 / 512 / 1024: the kernel whose dot
+    products run on the tensor cores.  Against the oracle, with a residual, run to run identical, bad indices
+    reported and skipped."""
+    from omni_moe_b200.ops import expert_forward
+    x, up, dn, w, idx = _inputs(t, h, n, k, t + h + 1)
+    res = torch.randn(t, h, generator=gen(t)).bfloat16()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = (x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda())
+    y = expert_forward(*args, out_dtype=torch.bfloat16, residual=res.cuda(), status=st, mode="fused")
+    y2 = expert_forward(*args, out_dtype=torch.bfloat16, residual=res.cuda(), status=st, mode="fused")
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and torch.equal(y, y2)
+    assert_close(y, orc.expert_forward(x, up, dn, w, idx) + res.float(), what="tensor-core gather, bf16 output")
+    # the fp32 / coefficient-returning form is the CUDA-core kernel: the two agree to bf16 rounding
+    y32 = expert_forward(*args, out_dtype=torch.float32, status=st, mode="fused")
+    y16 = expert_forward(*args, out_dtype=torch.bfloat16, status=st, mode="fused")
+    assert_close(y16, y32, rtol=2 ** -7, atol=1e-3, what="tensor-core vs CUDA-core gather")
+    if t >= 9 and k >= 2:
+        bad = idx.clone()
+        bad[3, 1] = n + 5
+        bad[5, 0] = -2
+        yb = expert_forward(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), bad.cuda(), out_dtype=torch.bfloat16, status=st, mode="fused")
+        torch.cuda.synchronize()
+        assert int(st.item()) & 1
+        wz = w.clone()
+        wz[3, 1] = 0.0
+        wz[5, 0] = 0.0
+        assert_close(yb, orc.expert_forward(x, up, dn, wz, bad.clamp(0, n - 1)), what="bad indices are skipped")
