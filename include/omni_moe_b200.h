@@ -209,6 +209,18 @@ OMNI_API int omni_expert_fused(const void *x, const void *up, const void *down, 
                       int32_t *status, void *stream);
 
 /*
+ * Self-test of the bounded device-side wait (no counterpart in the reference, whose Triton kernels have no
+ * device-side waits).  Every mbarrier poll of the GEMM kernels is limited: a wait that is never satisfied gives up
+ * after a number of probes, raises its block's abort flag, ORs OMNI_ST_WAIT_TIMEOUT into the status word and
+ * returns, so a defect shows as a status bit instead of a hung GPU.  This entry runs that code on a barrier of
+ * its own that nobody arrives on, with `probe_limit` probes (1 .. 2^20), on `stream`:
+ *   out4[0] |= OMNI_ST_WAIT_TIMEOUT      out4[1] = 0 (the wait returned false)
+ *   out4[2] = 0 (a second wait of the block returned false at once)      out4[3] = 1 (the abort flag)
+ * out4: 4 int32 of device memory, cleared by the call.  The context stays usable afterwards.
+ */
+OMNI_API int omni_selftest_wait_timeout(int32_t *out4, int probe_limit, void *stream);
+
+/*
  * Router selection and routed experts in one kernel, for the same regime as omni_expert_fused
  * (tables resident in L2): the BatchNorm fold, the log-softmax and the product-key top-k are applied
  * to the token's router logits (as omni_router_logits_topk does, same results) and the k Up / Down

@@ -58,12 +58,27 @@ struct GemmArgs {
   int router_n;           // sqrt_n; kernels without router tiles and with a transposed B: k_split (0 = one B matrix)
   float* logits;          // [M, 2 * sqrt_n]
   int* status;
-  long long* prof;  // debug: per-CTA cycle counters (8 words per CTA), normally null
-  int knobs;        // debug: 1 = no TMA loads (MMAs run on stale tiles), 2 = no MMAs; normally 0
-  int grid_limit;   // debug: cap on CTAs (pairs for the pair kernel); 0 = none
+#ifdef OMNI_TUNING
+  long long* prof;  // tuning builds: per-CTA cycle counters (8 words per CTA), normally null
+  int knobs;        // tuning builds: 1 = no TMA loads (MMAs run on stale tiles), 2 = no MMAs; normally 0
+  int grid_limit;   // tuning builds: cap on CTAs (pairs for the pair kernel); 0 = none
+#endif
 };
 
-// Cycle accounting for tuning: adds the cycles spent in `stmt` to `acc` when profiling is on.
+// The cycle counters and switches used while tuning exist only in builds with -DOMNI_TUNING; in the default build
+// they are compile-time constants and every branch on them disappears.
+#ifdef OMNI_TUNING
+#define G_PROF (g.prof)
+#define G_KNOBS (g.knobs)
+#define G_GRID_LIMIT (g.grid_limit)
+#else
+#define G_PROF (static_cast<long long*>(nullptr))
+#define G_KNOBS 0
+#define G_GRID_LIMIT 0
+#endif
+
+// Cycle accounting for tuning builds: adds the cycles spent in `stmt` to `acc` when profiling is on.
+#ifdef OMNI_TUNING
 #define OMNI_TIMED(acc, stmt)                 \
   do {                                        \
     if (g.prof) {                             \
@@ -74,6 +89,12 @@ struct GemmArgs {
       stmt;                                   \
     }                                         \
   } while (0)
+#else
+#define OMNI_TIMED(acc, stmt) \
+  do {                        \
+    stmt;                     \
+  } while (0)
+#endif
 
 // Tile order.  Tiles are handed out in groups of kGroupM tile rows: inside a group the column index
 // advances slowest within a row block, so the CTAs running at any moment share a few A tiles and a few
@@ -462,7 +483,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         }
         if (dead) break;
       }
-      if (g.prof) g.prof[blockIdx.x * 16 + 3] = p_wait, g.prof[blockIdx.x * 16 + 4] = clock64() - p_t0;
+      if (G_PROF) G_PROF[blockIdx.x * 16 + 3] = p_wait, G_PROF[blockIdx.x * 16 + 4] = clock64() - p_t0;
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------------------
@@ -500,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (dead) break;
         umma_commit(bar_tfull + 8 * acc);  // accumulator complete
       }
-      if (g.prof) g.prof[blockIdx.x * 16 + 0] = m_full, g.prof[blockIdx.x * 16 + 1] = m_tempty, g.prof[blockIdx.x * 16 + 2] = clock64() - m_t0;
+      if (G_PROF) G_PROF[blockIdx.x * 16 + 0] = m_full, G_PROF[blockIdx.x * 16 + 1] = m_tempty, G_PROF[blockIdx.x * 16 + 2] = clock64() - m_t0;
     }
   } else {
     // ------------------------------- epilogue -----------------------------------------------
@@ -529,8 +550,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
     }
-    if (g.prof && warp == 2 && lane == 0)
-      g.prof[blockIdx.x * 16 + 5] = e_wait, g.prof[blockIdx.x * 16 + 6] = e_store, g.prof[blockIdx.x * 16 + 7] = clock64() - e_t0;
+    if (G_PROF && warp == 2 && lane == 0)
+      G_PROF[blockIdx.x * 16 + 5] = e_wait, G_PROF[blockIdx.x * 16 + 6] = e_store, G_PROF[blockIdx.x * 16 + 7] = clock64() - e_t0;
   }
 
   // ------------------------------- teardown -------------------------------------------------
@@ -666,7 +687,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           bool ok;
           OMNI_TIMED(p_wait, ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, g.status));
           if (!ok) { dead = true; break; }
-          if (g.knobs & 1) {
+          if (G_KNOBS & 1) {
             if (leader) mbar_arrive(bar_full + 8 * stage);
           } else {
             if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::kStage);
@@ -699,7 +720,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         if (dead) break;
       }
-      if (g.prof) g.prof[blockIdx.x * 16 + 3] = p_wait, g.prof[blockIdx.x * 16 + 4] = clock64() - p_t0;
+      if (G_PROF) G_PROF[blockIdx.x * 16 + 3] = p_wait, G_PROF[blockIdx.x * 16 + 4] = clock64() - p_t0;
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) ---------------------------
@@ -729,7 +750,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           // descriptors of consecutive stages differ only in the start-address field (16-byte units)
           const uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * (C::kStageA >> 4));
           const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * (C::kStageB >> 4));
-          if (!(g.knobs & 2)) {
+          if (!(G_KNOBS & 2)) {
 #pragma unroll
             for (int sub = 0; sub < C::kSub; ++sub) {
               const uint64_t ad = adesc + static_cast<uint64_t>(sub * (C::kSliceA >> 4));
@@ -745,7 +766,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         if (dead) break;
         umma_commit_pair(bar_tfull + 8 * acc, 3);  // both CTAs may drain their accumulator
       }
-      if (g.prof) g.prof[blockIdx.x * 16 + 0] = m_full, g.prof[blockIdx.x * 16 + 1] = m_tempty, g.prof[blockIdx.x * 16 + 2] = clock64() - m_t0;
+      if (G_PROF) G_PROF[blockIdx.x * 16 + 0] = m_full, G_PROF[blockIdx.x * 16 + 1] = m_tempty, G_PROF[blockIdx.x * 16 + 2] = clock64() - m_t0;
     }
   } else {
     // ------------------------------- epilogue (both CTAs) -----------------------------------
@@ -790,8 +811,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
     }
     if ((g.tma_out || g.tma_logits) && lane == 0) bulk_wait_all();  // the boxes still on their way are written before the CTA leaves
-    if (g.prof && warp == 2 && lane == 0)
-      g.prof[blockIdx.x * 16 + 5] = e_wait, g.prof[blockIdx.x * 16 + 6] = e_store, g.prof[blockIdx.x * 16 + 7] = clock64() - e_t0;
+    if (G_PROF && warp == 2 && lane == 0)
+      G_PROF[blockIdx.x * 16 + 5] = e_wait, G_PROF[blockIdx.x * 16 + 6] = e_store, G_PROF[blockIdx.x * 16 + 7] = clock64() - e_t0;
   }
 
   // ------------------------------- teardown -------------------------------------------------
@@ -889,14 +910,10 @@ int make_logits_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols)
 }
 
 // The bf16 outputs of the pair kernels go through TMA stores when the output qualifies (16-byte aligned
-// base and row stride).  OMNI_MOE_B200_TMA_STORE=0 keeps the direct stores.
-int g_tma_store = -1;  // -1: follow the environment; 0 / 1: set by omni_debug_gemm_tma_store
+// base and row stride).  OMNI_MOE_B200_TMA_STORE=0 keeps the direct stores; the variable is read at every call.
 bool tma_store_enabled() {
-  static const bool v = [] {
-    const char* e = getenv("OMNI_MOE_B200_TMA_STORE");
-    return !(e && e[0] == '0');
-  }();
-  return g_tma_store < 0 ? v : g_tma_store != 0;
+  const char* e = getenv("OMNI_MOE_B200_TMA_STORE");
+  return !(e && e[0] == '0');
 }
 
 int sm_count() {
@@ -951,7 +968,7 @@ int launch_pair(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& 
   const int tiles = g.tiles_m * (g.tiles_n + (ROUTER ? g.router_tiles : 0));
   const int max_pairs = sm_count() / 2;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
-  if (g.grid_limit > 0 && g.grid_limit < pairs) pairs = g.grid_limit;
+  if (G_GRID_LIMIT > 0 && G_GRID_LIMIT < pairs) pairs = G_GRID_LIMIT;
   launch_after_predecessor(gemm_pair_kernel<EPI, ROUTER, MAJOR>, dim3(2 * pairs), dim3(kThreads), C::kSmem, st, a, b0, b1, r0, r1, mo, ml, g);
   return check_launch("gemm_pair_kernel");
 }
@@ -971,8 +988,13 @@ bool use_pairs() {
   return v;
 }
 
+#ifdef OMNI_TUNING
 long long* g_prof = nullptr;  // set by omni_debug_gemm_profile
 int g_knobs = 0, g_grid_limit = 0;
+#define OMNI_SET_TUNING(g) ((g).prof = g_prof, (g).knobs = g_knobs, (g).grid_limit = g_grid_limit)
+#else
+#define OMNI_SET_TUNING(g) ((void)0)
+#endif
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -1002,7 +1024,8 @@ extern "C" int omni_router_gate(const void* x, const void* gate_x, const void* g
     g.tiles_m = ceil_div(g.M, 2 * BM);
     g.tiles_n = g.tiles_n_axis = 0;
     g.router_tiles = ceil_div(sqrt_n, 128), g.router_n = sqrt_n, g.logits = logits;
-    g.out = nullptr, g.ldo = 0, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+    g.out = nullptr, g.ldo = 0, g.status = status;
+  OMNI_SET_TUNING(g);
     return launch_pair<EPI_SWIGLU, true>(ma, mx, my, mx, my, g, st);
   }
   const int bn = sqrt_n <= 64 ? 64 : (sqrt_n <= 128 ? 128 : 256);
@@ -1015,7 +1038,8 @@ extern "C" int omni_router_gate(const void* x, const void* gate_x, const void* g
   g.tiles_m = ceil_div(g.M, BM);
   g.tiles_n_axis = ceil_div(sqrt_n, bn);
   g.tiles_n = 2 * g.tiles_n_axis;
-  g.out = logits, g.ldo = 2 * static_cast<int64_t>(sqrt_n), g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  g.out = logits, g.ldo = 2 * static_cast<int64_t>(sqrt_n), g.status = status;
+  OMNI_SET_TUNING(g);
   if (bn == 64) return launch<64, EPI_F32>(ma, mx, my, g, st);
   if (bn == 128) return launch<128, EPI_F32>(ma, mx, my, g, st);
   return launch<256, EPI_F32>(ma, mx, my, g, st);
@@ -1037,7 +1061,8 @@ extern "C" int omni_mlp_gate_up(const void* x, const void* gate_w, const void* u
   g.M = static_cast<int>(num_tokens), g.N = intermediate, g.K = hidden, g.dual = 0;
   g.tiles_m = ceil_div(g.M, BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(intermediate, 128);
-  g.out = act, g.ldo = intermediate, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  g.out = act, g.ldo = intermediate, g.status = status;
+  OMNI_SET_TUNING(g);
   if (use_pairs()) {
     g.tiles_m = ceil_div(g.M, 2 * BM);
     return launch_pair<EPI_SWIGLU, false>(ma, mg, mu, mg, mu, g, static_cast<cudaStream_t>(stream));
@@ -1064,7 +1089,8 @@ extern "C" int omni_mlp_gate_up_limit(const void* x, const void* gate_w, const v
   g.tiles_n = g.tiles_n_axis = ceil_div(intermediate, 128);
   g.out = act, g.ldo = intermediate, g.gu_out = gate_up, g.ldgu = 2 * static_cast<int64_t>(intermediate);
   g.limit = limit;
-  g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  g.status = status;
+  OMNI_SET_TUNING(g);
   if (limit > 0.f) return launch_pair<EPI_SWIGLU_CLAMP, false>(ma, mg, mu, mg, mu, g, static_cast<cudaStream_t>(stream));
   return launch_pair<EPI_SWIGLU, false>(ma, mg, mu, mg, mu, g, static_cast<cudaStream_t>(stream));
 }
@@ -1097,7 +1123,8 @@ extern "C" int omni_mlp_gate_up_router(const void* x, const void* gate_w, const 
   g.tiles_m = ceil_div(g.M, 2 * BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(intermediate, 128);
   g.router_tiles = ceil_div(sqrt_n, 128), g.router_n = sqrt_n, g.logits = logits;
-  g.out = act, g.ldo = intermediate, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  g.out = act, g.ldo = intermediate, g.status = status;
+  OMNI_SET_TUNING(g);
   return launch_pair<EPI_SWIGLU, true>(ma, mg, mu, mx, my, g, static_cast<cudaStream_t>(stream));
 }
 
@@ -1117,7 +1144,8 @@ extern "C" int omni_mlp_down(const void* act, const void* down_w, int64_t num_to
   g.M = static_cast<int>(num_tokens), g.N = hidden, g.K = intermediate, g.dual = 0;
   g.tiles_m = ceil_div(g.M, BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(hidden, bn);
-  g.out = y, g.ldo = hidden, g.residual = residual, g.ldr = hidden, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  g.out = y, g.ldo = hidden, g.residual = residual, g.ldr = hidden, g.status = status;
+  OMNI_SET_TUNING(g);
   if (use_pairs()) {
     g.tiles_m = ceil_div(g.M, 2 * BM);
     g.tiles_n = g.tiles_n_axis = ceil_div(hidden, 256);
@@ -1140,7 +1168,8 @@ extern "C" int omni_gemm_bf16_nt(const void* a, const void* b, int64_t m, int64_
   if (int e = make_map(&mb, b, n, k, 128)) return e;
   GemmArgs g{};
   g.M = static_cast<int>(m), g.N = static_cast<int>(n), g.K = static_cast<int>(k), g.dual = 0;
-  g.out = out, g.ldo = ldo, g.residual = nullptr, g.ldr = 0, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  g.out = out, g.ldo = ldo, g.residual = nullptr, g.ldr = 0, g.status = status;
+  OMNI_SET_TUNING(g);
   if (use_pairs()) {
     g.tiles_m = ceil_div(g.M, 2 * BM);
     g.tiles_n = g.tiles_n_axis = ceil_div(g.N, 256);
@@ -1182,7 +1211,8 @@ int gemm_bf16_impl(const void* a, int a_transposed, int64_t lda, const void* b, 
   GemmArgs g{};
   g.router_n = b1 != nullptr ? static_cast<int>(k_split) : 0;
   g.M = static_cast<int>(m), g.N = static_cast<int>(n), g.K = static_cast<int>(k), g.dual = 0;
-  g.out = out, g.ldo = ldo, g.residual = nullptr, g.ldr = 0, g.status = status, g.prof = g_prof, g.knobs = g_knobs, g.grid_limit = g_grid_limit;
+  g.out = out, g.ldo = ldo, g.residual = nullptr, g.ldr = 0, g.status = status;
+  OMNI_SET_TUNING(g);
   g.tiles_m = ceil_div(g.M, 2 * BM);
   g.tiles_n = g.tiles_n_axis = ceil_div(g.N, 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -1217,10 +1247,10 @@ extern "C" int omni_mlp_fwd(const void* x, const void* gate_w, const void* up_w,
   return omni_mlp_down(act, down_w, num_tokens, hidden, intermediate, residual, y, status, stream);
 }
 
-// Tuning aid, not part of the public header: while `buf` (device memory, 8 int64 per CTA) is set,
+#ifdef OMNI_TUNING
+// Tuning builds only, not part of the public header: while `buf` (device memory, 8 int64 per CTA) is set,
 // the GEMM kernels record cycle counters there: {MMA wait-for-operands, MMA wait-for-accumulator,
 // MMA total, producer wait-for-stage, producer total, epilogue wait, epilogue store, epilogue total}.
 extern "C" OMNI_API void omni_debug_gemm_profile(long long* buf) { g_prof = buf; }
 extern "C" OMNI_API void omni_debug_gemm_knobs(int knobs, int grid_limit) { g_knobs = knobs, g_grid_limit = grid_limit; }
-// Testing aid, not part of the public header: 1 / 0 forces the TMA-store / direct-store epilogue of the pair kernels, -1 restores the default.
-extern "C" OMNI_API void omni_debug_gemm_tma_store(int enable) { g_tma_store = enable; }
+#endif

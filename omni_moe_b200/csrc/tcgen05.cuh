@@ -38,8 +38,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises the abort flag) when it gives up or when another wait
 // of this CTA already gave up.  The first probe is the fast path: no other memory is touched.
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                   uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) {
       __nanosleep(64);

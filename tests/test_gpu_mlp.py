@@ -117,7 +117,7 @@ def test_tma_store_epilogue_equals_direct_stores(m, n, k):
     outs = []
     try:
         for mode in (1, 0):
-            lib.omni_debug_gemm_tma_store(mode)
+            os.environ["OMNI_MOE_B200_TMA_STORE"] = str(mode)   # read by the library at every call
             wide = torch.full((m, 2 * n + 16), 3.0, dtype=torch.bfloat16, device="cuda")
             dense = gemm_nt(a, b)
             gemm_nt(a, b, out=wide[:, 8:8 + n])
@@ -126,7 +126,7 @@ def test_tma_store_epilogue_equals_direct_stores(m, n, k):
             assert torch.equal(wide[:, 8:8 + n], dense)
             outs.append(dense)
     finally:
-        lib.omni_debug_gemm_tma_store(-1)
+        os.environ.pop("OMNI_MOE_B200_TMA_STORE", None)
     assert torch.equal(outs[0], outs[1])
     ref = a.float() @ b.float().t()
     assert float((outs[0].float() - ref).abs().max()) <= 2e-2 * float(ref.abs().max()) + 1e-3
@@ -146,14 +146,14 @@ def test_tma_store_swiglu_and_saved_preactivations():
     got = []
     try:
         for mode in (1, 0):
-            lib.omni_debug_gemm_tma_store(mode)
+            os.environ["OMNI_MOE_B200_TMA_STORE"] = str(mode)   # read by the library at every call
             gu = torch.empty(t, 2 * i, dtype=torch.bfloat16, device="cuda")
             act = torch.empty(t, i, dtype=torch.bfloat16, device="cuda")
             y = mlp_forward(x, wg, wu, wd, residual=res, act=act, gate_up=gu)
             torch.cuda.synchronize()
             got.append((y, act, gu))
     finally:
-        lib.omni_debug_gemm_tma_store(-1)
+        os.environ.pop("OMNI_MOE_B200_TMA_STORE", None)
     for a_, b_ in zip(got[0], got[1]):
         assert torch.equal(a_, b_)
 
@@ -184,3 +184,24 @@ print("single-cta ok")
     r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, OMNI_MOE_B200_GEMM="1cta"), capture_output=True,
                        text=True, timeout=300)
     assert r.returncode == 0 and "single-cta ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_bounded_wait_gives_up_and_leaves_the_context_usable():
+    """The wait primitive of the GEMM kernels on a barrier nobody arrives on: it returns after its probe limit with
+    the time-out bit in the status word and the abort flag up, and the next ordinary call is bit-correct."""
+    from omni_moe_b200 import _lib
+    from omni_moe_b200.ops.autograd import gemm_nt
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(1)
+    a = (torch.randn(200, 256, generator=g) * 0.5).bfloat16().cuda()
+    b = (torch.randn(136, 256, generator=g) / 16).bfloat16().cuda()
+    before = gemm_nt(a, b)
+    out = torch.full((4,), 7, dtype=torch.int32, device="cuda")
+    _lib.check(lib.omni_selftest_wait_timeout(out.data_ptr(), 2000, _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    assert out.tolist() == [_lib.OMNI_ST_WAIT_TIMEOUT if hasattr(_lib, "OMNI_ST_WAIT_TIMEOUT") else 2, 0, 0, 1], out.tolist()
+    after = gemm_nt(a, b)
+    torch.cuda.synchronize()
+    assert torch.equal(before, after)
+    with pytest.raises(RuntimeError):
+        _lib.check(lib.omni_selftest_wait_timeout(out.data_ptr(), 0, _lib.stream_ptr()))
