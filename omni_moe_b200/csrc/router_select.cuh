@@ -18,6 +18,18 @@
 namespace omni {
 namespace sel {
 
+#ifdef OMNI_TUNING
+// tuning builds only: clocks spent by all warps in the parts of select_token (rows, axis selection, candidates,
+// final ranking, tie check), and the number of tokens
+__device__ unsigned long long g_sel_prof[4096 * 8];  // spread over 4096 slots so that the adds do not queue up
+#define SEL_SLOT ((blockIdx.x * 4 + (threadIdx.x >> 5)) & 4095)
+#define SEL_TIC(v) const long long v = clock64()
+#define SEL_TOC(i, v) if (lane_id() == 0) atomicAdd(&g_sel_prof[SEL_SLOT * 8 + i], static_cast<unsigned long long>(clock64() - v))
+#else
+#define SEL_TIC(v)
+#define SEL_TOC(i, v)
+#endif
+
 constexpr int kMaxK = 128;
 constexpr int kMaxCells = 704;  // cells with (i+1)(j+1) <= 128 in a 128 x 128 grid: 642
 
@@ -305,6 +317,7 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
 #pragma unroll 1
   for (int axis = 0; axis < 2; ++axis) {
     uint32_t key[VPL];
+    SEL_TIC(c_rows);
     if (PRE) {
       const float* row = reinterpret_cast<const float*>(a.in_x) + t * a.ld_in + axis * n;
       float v[VPL];
@@ -347,6 +360,8 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
         key[e] = c < n ? float_to_key(load_as_float(base, a.in_dtype, t * a.ld_in + c)) : 0u;
       }
     }
+    SEL_TOC(0, c_rows);
+    SEL_TIC(c_axis);
     if constexpr (kSmallAxis) {
       float* so = axis == 0 ? sx : sy;
       int* io = axis == 0 ? ix : iy;
@@ -386,8 +401,10 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
       warp_select_sorted<VPL, true, (VPL <= 8)>(key, sub, kk, w.pack, reinterpret_cast<uint32_t*>(axis == 0 ? sx : sy),
                                     reinterpret_cast<uint32_t*>(axis == 0 ? ix : iy));
     }
+    SEL_TOC(1, c_axis);
   }
   __syncwarp();
+  SEL_TIC(c_cand);
 
   // ---- pruned candidate search ----------------------------------------------------------
   uint32_t ckey[CPL], cflat[CPL];
@@ -407,6 +424,8 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
 #pragma unroll
   for (int s = 0; s < kMaxK / 32; ++s) rkey[s] = 0, rflat[s] = 0;
   uint32_t last_key = 0;
+  SEL_TOC(2, c_cand);
+  SEL_TIC(c_rank);
   if constexpr (kSmallCells) {
     bool done = false;
     if (k <= 32) {  // fast path on the score keys alone (see the axis selection above)
@@ -453,6 +472,8 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
     last_key = w.rk[k - 1];
   }
 
+  SEL_TOC(3, c_rank);
+  SEL_TIC(c_tie);
   // ---- did a cell outside the region tie with the k-th score? -----------------------------
   bool tie = false;
   for (int i = lane; i < kk; i += 32) {
@@ -483,7 +504,10 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
       pk = m, pf = w, first = false;
     }
   }
-
+  SEL_TOC(4, c_tie);
+#ifdef OMNI_TUNING
+  if (lane_id() == 0) atomicAdd(&g_sel_prof[SEL_SLOT * 8 + 5], 1ull);
+#endif
 }
 
 inline int region_cells(int kk, int k) {

@@ -114,3 +114,16 @@ extern "C" int omni_router_logits_topk(const float* logits, int64_t ld_logits, c
   a.scores = scores, a.indices = indices, a.idx_is_i64 = idx_is_i64, a.weights = weights;
   return launch<true>(a, static_cast<cudaStream_t>(stream));
 }
+
+#ifdef OMNI_TUNING
+// tuning builds only: reads (summed over the slots) and clears the section clocks of select_token
+extern "C" OMNI_API int omni_debug_select_profile(unsigned long long* host_out8) {
+  static unsigned long long buf[4096 * 8];
+  if (cudaMemcpyFromSymbol(buf, omni::sel::g_sel_prof, sizeof(buf)) != cudaSuccess) return -3;
+  for (int i = 0; i < 8; ++i) host_out8[i] = 0;
+  for (int s = 0; s < 4096; ++s)
+    for (int i = 0; i < 8; ++i) host_out8[i] += buf[s * 8 + i];
+  for (auto& v : buf) v = 0;
+  return cudaMemcpyToSymbol(omni::sel::g_sel_prof, buf, sizeof(buf)) == cudaSuccess ? 0 : -3;
+}
+#endif

@@ -170,15 +170,26 @@ class OmniMoE(nn.Module):
                     bn.running_var.mul_(1 - mom).add_(unbiased.to(bn.running_var.dtype), alpha=mom)
         eps = torch.cat([torch.full((n,), bx.eps), torch.full((n,), by.eps)]).to(var)
         scale = torch.rsqrt(var + eps)
+        if b is not None:
+            # into the forward's own buffers: they outlive the side stream this runs on, a temporary would belong to
+            # that stream's allocator pool while the main stream still reads it
+            b.bn_scale.copy_(scale)
+            b.bn_shift.copy_(-mean * scale)
+            return b.bn_scale, b.bn_shift
         return scale.contiguous(), (-mean * scale).contiguous()
 
     def _get_buffers(self, t: int, dev: torch.device) -> _Buffers:
-        key = (t, dev.index)
+        """Scratch of an eager forward, one set per (token count, device, stream): forwards of one module issued
+        on different streams may overlap on the GPU, so they must not share logits / activation / status buffers
+        (two forwards on the same stream are ordered by the stream).  The few most recent sets are kept."""
+        key = (t, dev.index, torch.cuda.current_stream(dev).cuda_stream)
         b = self._buffers_cache.get(key)
         if b is None:
             b = _Buffers(t, self.hidden_size, self.intermediate_size, self.num_expert_sqrt, self.num_experts,
                          self.top_k, dev)
-            self._buffers_cache = {key: b}  # keep one set: shapes rarely alternate
+            while len(self._buffers_cache) >= 4:  # shapes and streams rarely alternate: keep a handful
+                self._buffers_cache.pop(next(iter(self._buffers_cache)))
+            self._buffers_cache[key] = b
         return b
 
     # ------------------------------------------------------------------------------------------
