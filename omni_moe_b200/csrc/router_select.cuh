@@ -322,25 +322,36 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
       const float* row = reinterpret_cast<const float*>(a.in_x) + t * a.ld_in + axis * n;
       float v[VPL];
       float mx = -INFINITY;
+      // Every load of the row is issued before any value is used (predicated loads, no branch in between): with a
+      // load and its use in the same conditional block the compiler keeps them in program order and the row costs
+      // VPL memory round trips instead of one.
 #pragma unroll
       for (int e = 0; e < VPL; ++e) {
         const int c = e * 32 + lane;
-        if (c < n) {
-          float z = __ldg(row + c);
-          if (a.bn_scale) z = __fmaf_rn(z, __ldg(a.bn_scale + axis * n + c), __ldg(a.bn_shift + axis * n + c));
-          v[e] = z;
-          mx = fmaxf(mx, z);
-        } else {
-          v[e] = -INFINITY;
-        }
+        v[e] = c < n ? __ldg(row + c) : -INFINITY;
       }
+      if (a.bn_scale) {
+        float sc[VPL], sh[VPL];
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) {
+          const int c = e * 32 + lane;
+          sc[e] = c < n ? __ldg(a.bn_scale + axis * n + c) : 1.f;
+          sh[e] = c < n ? __ldg(a.bn_shift + axis * n + c) : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) v[e] = __fmaf_rn(v[e], sc[e], sh[e]);  // columns past n stay -inf
+      }
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) mx = fmaxf(mx, v[e]);
       mx = warp_max(mx);
+      SEL_TOC(6, c_rows);  // tuning: loads + max only
       float sum = 0.f;
 #pragma unroll
       for (int e = 0; e < VPL; ++e)
         if (e * 32 + lane < n) sum += __expf(v[e] - mx);  // ex2-based: 2 ulp, the sum only shifts all log-probs
       sum = warp_sum(sum);
       const float lse = logf(sum);
+      SEL_TOC(7, c_rows);  // tuning: ... + exp / sum / log
 #pragma unroll
       for (int e = 0; e < VPL; ++e) {
         const int c = e * 32 + lane;
@@ -354,11 +365,29 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
       }
     } else {
       const void* base = axis == 0 ? a.in_x : a.in_y;
+      // one loop per element type, loads first (see above): a type test per element would put every load behind a branch
+      float f[VPL];
+      if (a.in_dtype == OMNI_F32) {
+        const float* p = reinterpret_cast<const float*>(base) + t * a.ld_in;
 #pragma unroll
-      for (int e = 0; e < VPL; ++e) {
-        const int c = e * 32 + lane;
-        key[e] = c < n ? float_to_key(load_as_float(base, a.in_dtype, t * a.ld_in + c)) : 0u;
+        for (int e = 0; e < VPL; ++e) f[e] = (e * 32 + lane) < n ? __ldg(p + e * 32 + lane) : 0.f;
+      } else if (a.in_dtype == OMNI_BF16) {
+        const unsigned short* p = reinterpret_cast<const unsigned short*>(base) + t * a.ld_in;
+        unsigned short h[VPL];
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) h[e] = (e * 32 + lane) < n ? __ldg(p + e * 32 + lane) : static_cast<unsigned short>(0);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) f[e] = __uint_as_float(static_cast<uint32_t>(h[e]) << 16);
+      } else {
+        const __half* p = reinterpret_cast<const __half*>(base) + t * a.ld_in;
+        __half h[VPL];
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) h[e] = (e * 32 + lane) < n ? __ldg(p + e * 32 + lane) : __half(0.f);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) f[e] = __half2float(h[e]);
       }
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) key[e] = (e * 32 + lane) < n ? float_to_key(f[e]) : 0u;
     }
     SEL_TOC(0, c_rows);
     SEL_TIC(c_axis);
