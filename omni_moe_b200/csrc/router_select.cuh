@@ -300,6 +300,94 @@ __device__ __forceinline__ bool ranks_distinct(int r0, int r1, int want) {
   return cnt == want && __popc(mask) == want;
 }
 
+// Both axes of a token at once, for rows of at most 64 logits (two per lane) and kk <= 32: loads, BatchNorm fold,
+// log-softmax and the rank-by-counting of the two axes are written side by side, so that their dependency chains
+// (two warp reductions, a logarithm, the ranking) overlap instead of following one another.  Same arithmetic, in the
+// same order per axis, as the one-axis-at-a-time code in select_token.  Returns a mask of the axes whose best kk
+// sub-keys are strictly ordered by key alone and were written to (sx, ix) / (sy, iy); an axis with a tie among its
+// best kk is left to the caller's exact path.
+template <class Scratch>
+__device__ __forceinline__ unsigned select_axes_small(const TopkArgs& a, int64_t t, Scratch& w) {
+  const int lane = lane_id();
+  const int n = a.n, kk = a.kk;
+  const float* row = reinterpret_cast<const float*>(a.in_x) + t * a.ld_in;
+  float v[2][2];
+#pragma unroll
+  for (int ax = 0; ax < 2; ++ax)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) v[ax][e] = (e * 32 + lane) < n ? __ldg(row + ax * n + e * 32 + lane) : -INFINITY;
+  if (a.bn_scale) {
+    float sc[2][2], sh[2][2];
+#pragma unroll
+    for (int ax = 0; ax < 2; ++ax)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int c = e * 32 + lane;
+        sc[ax][e] = c < n ? __ldg(a.bn_scale + ax * n + c) : 1.f;
+        sh[ax][e] = c < n ? __ldg(a.bn_shift + ax * n + c) : 0.f;
+      }
+#pragma unroll
+    for (int ax = 0; ax < 2; ++ax)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) v[ax][e] = __fmaf_rn(v[ax][e], sc[ax][e], sh[ax][e]);
+  }
+  float mx[2], sum[2], lse[2];
+#pragma unroll
+  for (int ax = 0; ax < 2; ++ax) mx[ax] = fmaxf(fmaxf(-INFINITY, v[ax][0]), v[ax][1]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int ax = 0; ax < 2; ++ax) mx[ax] = fmaxf(mx[ax], __shfl_xor_sync(FULL_MASK, mx[ax], o));
+#pragma unroll
+  for (int ax = 0; ax < 2; ++ax) {
+    sum[ax] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+      if (e * 32 + lane < n) sum[ax] += __expf(v[ax][e] - mx[ax]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int ax = 0; ax < 2; ++ax) sum[ax] += __shfl_xor_sync(FULL_MASK, sum[ax], o);
+#pragma unroll
+  for (int ax = 0; ax < 2; ++ax) lse[ax] = logf(sum[ax]);
+  uint32_t key[2][2];
+  uint32_t* k32 = reinterpret_cast<uint32_t*>(w.pack);  // 64 keys of the x axis, then 64 of the y axis
+#pragma unroll
+  for (int ax = 0; ax < 2; ++ax)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int c = e * 32 + lane;
+      if (c < n) {
+        const float lp = (v[ax][e] - mx[ax]) - lse[ax];
+        if (a.lp_out) a.lp_out[t * (2 * n) + ax * n + c] = lp;
+        key[ax][e] = float_to_key(lp);
+      } else {
+        key[ax][e] = 0;
+      }
+      k32[ax * 64 + c] = key[ax][e];
+    }
+  __syncwarp();
+  int r[2][2];
+#pragma unroll
+  for (int ax = 0; ax < 2; ++ax)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) r[ax][e] = rank32_among_64(k32 + ax * 64, key[ax][e]);
+  unsigned done = 0;
+#pragma unroll
+  for (int ax = 0; ax < 2; ++ax) {
+    if (ranks_distinct(r[ax][0], r[ax][1], kk)) {
+      float* so = ax == 0 ? w.sx : w.sy;
+      int* io = ax == 0 ? w.ix : w.iy;
+      if (r[ax][0] < kk) so[r[ax][0]] = key_to_float(key[ax][0]), io[r[ax][0]] = lane;
+      if (r[ax][1] < kk) so[r[ax][1]] = key_to_float(key[ax][1]), io[r[ax][1]] = 32 + lane;
+      done |= 1u << ax;
+    }
+  }
+  __syncwarp();
+  return done;
+}
+
 template <int VPL, int CPL, bool PRE, class Scratch = WarpScratch<VPL, CPL>>
 __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scratch& w,
                                              const uint16_t* cell_table, uint32_t (&rkey)[kMaxK / 32],
@@ -314,8 +402,13 @@ __device__ __forceinline__ void select_token(const TopkArgs& a, int64_t t, Scrat
   int* iy = w.iy;
 
   // ---- per-axis rows -> sorted best kk --------------------------------------------------
+  unsigned axes_done = 0;
+  if constexpr (kSmallAxis && PRE) {
+    if (kk <= 32) axes_done = select_axes_small(a, t, w);  // both axes side by side; ties are left to the loop below
+  }
 #pragma unroll 1
   for (int axis = 0; axis < 2; ++axis) {
+    if ((axes_done >> axis) & 1) continue;
     uint32_t key[VPL];
     SEL_TIC(c_rows);
     if (PRE) {
