@@ -209,6 +209,17 @@ OMNI_API int omni_expert_fused(const void *x, const void *up, const void *down, 
                       int32_t *status, void *stream);
 
 /*
+ * omni_expert_fused with float32 operands and a float32 result: for callers whose tensors are float32 and who expect
+ * float32 arithmetic, as triton_omni_expert_func gives them (omni_moe/ops/triton/interface.py:54-72 computes in the
+ * dtype of its inputs; docs/omni_expert.md:24-43 lists float32).  x [T, H], up / down [N, H], weights [T, k],
+ * residual / y [T, H] all float32 (residual may be NULL or y itself), indices int32.  hidden % 4 == 0, k <= 128.
+ * CUDA cores only (one warp per token); bad indices are skipped and reported in *status.
+ */
+OMNI_API int omni_expert_fused_f32(const float *x, const float *up, const float *down, const float *weights,
+                          const int32_t *indices, int64_t num_tokens, int k, int hidden, int64_t num_experts,
+                          const float *residual, float *y, int32_t *status, void *stream);
+
+/*
  * Self-test of the bounded device-side wait (no counterpart in the reference, whose Triton kernels have no
  * device-side waits).  Every mbarrier poll of the GEMM kernels is limited: a wait that is never satisfied gives up
  * after a number of probes, raises its block's abort flag, ORs OMNI_ST_WAIT_TIMEOUT into the status word and

@@ -72,6 +72,8 @@ SIGNATURES = {
     "omni_router_norm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int,
                                      c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "omni_selftest_wait_timeout": (c_int, [c_void_p, c_int, c_void_p]),
+    "omni_expert_fused_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64,
+                                      c_void_p, c_void_p, c_void_p, c_void_p]),
     "omni_route_expert_fused": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                         c_int, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_void_p]),

@@ -808,6 +808,76 @@ __global__ void __launch_bounds__(kDynWarps * 32, 1) expert_routed_dyn_kernel(
 #endif
 }
 
+// fp32 operands end to end (x, both tables, output): the accuracy path for callers that hold float32 tensors and
+// expect float32 arithmetic (the reference computes in the dtype of its inputs, omni_moe/ops/triton/omni_expert.py:13-168).
+// One warp per token, two passes: the k coefficients w * silu(x . Up[e]) first (kept in shared memory), then the sum of
+// Down rows one slab of 1024 columns at a time (8 float4 accumulators per lane).  CUDA cores only: there is no fp32
+// tensor-core path, and this is a compatibility kernel, not a tuned one.
+__global__ void __launch_bounds__(kThreads) expert_fused_f32_kernel(
+    const float* __restrict__ x, const float* __restrict__ up, const float* __restrict__ down, const float* __restrict__ weights,
+    const int* __restrict__ indices, int64_t T, int k, int H, int64_t N, const float* residual, float* y, int* status) {
+  __shared__ float s_c[kWarps][sel::kMaxK];
+  __shared__ int s_e[kWarps][sel::kMaxK];
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (t >= T) return;
+  const float4* xr = reinterpret_cast<const float4*>(x + t * H);
+  const int h4 = H >> 2;
+  bool bad = false;
+  for (int j = 0; j < k; ++j) {
+    const int e = indices[t * k + j];
+    float c = 0.f;
+    if (e < 0 || e >= N) {
+      bad = true;
+    } else {
+      const float4* ur = reinterpret_cast<const float4*>(up + static_cast<int64_t>(e) * H);
+      float a0 = 0.f, a1 = 0.f;
+      for (int i = lane; i < h4; i += 64) {
+        const float4 p = __ldg(xr + i), q = __ldg(ur + i);
+        a0 = __fmaf_rn(p.x, q.x, a0), a0 = __fmaf_rn(p.y, q.y, a0), a0 = __fmaf_rn(p.z, q.z, a0), a0 = __fmaf_rn(p.w, q.w, a0);
+        if (i + 32 < h4) {
+          const float4 p2 = __ldg(xr + i + 32), q2 = __ldg(ur + i + 32);
+          a1 = __fmaf_rn(p2.x, q2.x, a1), a1 = __fmaf_rn(p2.y, q2.y, a1), a1 = __fmaf_rn(p2.z, q2.z, a1), a1 = __fmaf_rn(p2.w, q2.w, a1);
+        }
+      }
+      const float dot = warp_sum(a0 + a1);
+      c = weights[t * k + j] * (dot / (1.0f + expf(-dot)));
+    }
+    if (lane == 0) s_c[warp][j] = c, s_e[warp][j] = (e < 0 || e >= N) ? 0 : e;
+  }
+  __syncwarp();
+  for (int c0 = 0; c0 < h4; c0 += 256) {  // 256 float4 = 1024 columns per slab, 8 float4 per lane
+    float4 acc[8];
+#pragma unroll
+    for (int v = 0; v < 8; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+      const float c = s_c[warp][j];
+      const float4* dr = reinterpret_cast<const float4*>(down + static_cast<int64_t>(s_e[warp][j]) * H) + c0 + lane;
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        if (c0 + lane + v * 32 < h4) {
+          const float4 d = __ldg(dr + v * 32);
+          acc[v].x = __fmaf_rn(c, d.x, acc[v].x), acc[v].y = __fmaf_rn(c, d.y, acc[v].y);
+          acc[v].z = __fmaf_rn(c, d.z, acc[v].z), acc[v].w = __fmaf_rn(c, d.w, acc[v].w);
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      const int i = c0 + lane + v * 32;
+      if (i < h4) {
+        float4 o = acc[v];
+        if (residual) {
+          const float4 r = *(reinterpret_cast<const float4*>(residual + t * H) + i);  // plain load: may be y itself
+          o.x += r.x, o.y += r.y, o.z += r.z, o.w += r.w;
+        }
+        *(reinterpret_cast<float4*>(y + t * H) + i) = o;
+      }
+    }
+  }
+  if (bad && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // OMNI_MOE_B200_ROUTED=legacy: dot products on the CUDA cores, one token per warp, for every shape
@@ -1075,6 +1145,21 @@ extern "C" int omni_expert_combine_segments(const void* down, const float* coef,
   else OMNI_COMBS(8);
 #undef OMNI_COMBS
   return check_launch("expert_combine_segments_kernel");
+}
+
+extern "C" int omni_expert_fused_f32(const float* x, const float* up, const float* down, const float* weights,
+                                     const int32_t* indices, int64_t num_tokens, int k, int hidden, int64_t num_experts,
+                                     const float* residual, float* y, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && k <= sel::kMaxK && hidden >= 4 && num_experts >= 1, "bad sizes (k <= %d)", sel::kMaxK);
+  OMNI_REQUIRE(hidden % 4 == 0, "hidden must be a multiple of 4, got %d", hidden);
+  if (num_tokens == 0) return 0;
+  OMNI_REQUIRE(x && up && down && weights && indices && y && status, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(up) && aligned16(down) && aligned16(y) && aligned16(residual),
+               "x, up, down, y and residual must be 16-byte aligned");
+  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens, kWarps));
+  expert_fused_f32_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, up, down, weights, indices, num_tokens, k,
+                                                                                   hidden, num_experts, residual, y, status);
+  return check_launch("expert_fused_f32_kernel");
 }
 
 #ifdef OMNI_TUNING

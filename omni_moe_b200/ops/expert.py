@@ -124,6 +124,31 @@ def expert_forward(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.
     return (y, coef) if return_coef else y
 
 
+def expert_forward_f32(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor, weights: torch.Tensor,
+                       indices: torch.Tensor, residual: torch.Tensor | None = None, status: torch.Tensor | None = None):
+    """The routed-expert sum with float32 operands and float32 arithmetic throughout (CUDA cores, one warp per token)."""
+    _lib.require_cuda(x, up_weight, down_weight, weights, indices)
+    assert x.dtype == up_weight.dtype == down_weight.dtype == weights.dtype == torch.float32 and indices.dtype == torch.int32
+    x, up_weight, down_weight = x.contiguous(), up_weight.contiguous(), down_weight.contiguous()
+    weights, indices = weights.contiguous(), indices.contiguous()
+    t, h = x.shape
+    k = indices.size(1)
+    y = torch.empty((t, h), device=x.device, dtype=torch.float32)
+    if residual is not None:
+        assert residual.shape == y.shape and residual.dtype == torch.float32 and residual.is_contiguous()
+    if t == 0:
+        return y
+    if k == 0:
+        return y.zero_() if residual is None else y.copy_(residual)
+    if status is None:
+        status = _lib.device_status(x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().omni_expert_fused_f32(x.data_ptr(), up_weight.data_ptr(), down_weight.data_ptr(), weights.data_ptr(),
+                                                     indices.data_ptr(), t, k, h, up_weight.size(0), _lib.ptr(residual),
+                                                     y.data_ptr(), status.data_ptr(), _lib.stream_ptr()))
+    return y
+
+
 def omni_expert_func(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor,
                      routing_weights: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
     """Drop-in for ``triton_omni_expert_func`` (omni_moe/ops/triton/interface.py:54-72).
@@ -134,8 +159,9 @@ def omni_expert_func(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torc
     :param indices: (num_tokens, num_experts_per_token) integer expert ids (duplicates allowed)
     :return y: (num_tokens, hidden_size), dtype of ``x``
 
-    Operands are taken as bf16 (other float dtypes are rounded to bf16 first); the dot products,
-    the activation and the accumulation run in fp32.
+    bf16 (and fp16, rounded to bf16) operands go to the bf16 kernels: dot products, activation and accumulation in
+    fp32.  float32 ``x`` with float32 tables is computed in float32 throughout (``omni_expert_fused_f32``) when no
+    gradient is asked for; with gradients the operands are rounded to bf16 (the backward kernels are bf16).
     """
     assert x.dim() == 2 and up_weight.dim() == 2 and down_weight.shape == up_weight.shape
     assert routing_weights.shape == indices.shape and indices.size(0) == x.size(0)
@@ -147,6 +173,9 @@ def omni_expert_func(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torc
     if torch.is_grad_enabled() and any(t.requires_grad for t in (x, up_weight, down_weight, routing_weights)):
         from .autograd import ExpertFunction
         return ExpertFunction.apply(x, up_weight, down_weight, routing_weights, indices)
+    if x.dtype == up_weight.dtype == down_weight.dtype == torch.float32 and x.size(1) % 4 == 0 and indices.size(1) <= 128:
+        return expert_forward_f32(x.detach(), up_weight.detach(), down_weight.detach(), routing_weights.detach().float(),
+                                  indices.to(torch.int32))
     y = expert_forward(as_bf16(x), as_bf16(up_weight), as_bf16(down_weight), routing_weights.detach().float(),
                        indices.to(torch.int32), out_dtype=torch.float32 if x.dtype == torch.float32 else torch.bfloat16)
     return y.to(x.dtype)

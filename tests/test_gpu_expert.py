@@ -327,3 +327,38 @@ def test_fused_tensor_core_gather_matches_oracle(t, h, n, k):
         wz[3, 1] = 0.0
         wz[5, 0] = 0.0
         assert_close(yb, orc.expert_forward(x, up, dn, wz, bad.clamp(0, n - 1)), what="bad indices are skipped")
+
+
+@pytest.mark.parametrize("t,h,n,k", [(100, 256, 500, 8), (33, 1024, 4096, 32), (7, 4100, 64, 5), (64, 2048, 300, 128), (1, 4, 1, 1)])
+def test_expert_float32_operands_are_computed_in_float32(t, h, n, k):
+    """float32 tensors through the drop-in operator: float32 arithmetic end to end (omni_expert_fused_f32), checked
+    against the fp32 oracle on the unrounded operands at rtol 1e-4 / atol 1e-5 - two orders below what bf16 operands
+    give - with duplicates, a residual through the C ABI, and bad indices reported and skipped."""
+    from omni_moe.ops.triton import triton_omni_expert_func
+    from omni_moe_b200.ops.expert import expert_forward_f32
+    g = gen(t + h + n)
+    x = torch.randn(t, h, generator=g) * 0.5
+    up = torch.randn(n, h, generator=g) * 0.1
+    dn = torch.randn(n, h, generator=g) * 0.1
+    w = torch.randn(t, k, generator=g) * 0.1
+    idx = torch.randint(0, n, (t, k), generator=g, dtype=torch.int32)
+    if k > 1:
+        idx[:, 1] = idx[:, 0]
+    y = triton_omni_expert_func(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda())
+    assert y.dtype == torch.float32
+    ey = orc.expert_forward(x, up, dn, w, idx)
+    assert_close(y, ey, rtol=1e-4, atol=1e-5, what="float32 expert operator")
+    res = torch.randn(t, h, generator=g)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y2 = expert_forward_f32(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), idx.cuda(), residual=res.cuda(), status=st)
+    assert_close(y2, ey + res, rtol=1e-4, atol=1e-5, what="float32 expert kernel with residual")
+    assert int(st.item()) == 0
+    if t > 3:
+        bad = idx.clone()
+        bad[2, 0] = n
+        yb = expert_forward_f32(x.cuda(), up.cuda(), dn.cuda(), w.cuda(), bad.cuda(), status=st)
+        torch.cuda.synchronize()
+        assert int(st.item()) & 1
+        wz = w.clone()
+        wz[2, 0] = 0.0
+        assert_close(yb, orc.expert_forward(x, up, dn, wz, bad.clamp(0, n - 1)), rtol=1e-4, atol=1e-5)
