@@ -363,6 +363,8 @@ def _c5_parity(inner, tables, part, x_local, y_local, indices, rank, world, dist
     s_total = xs.size(0)
     lpx = lpy = es = ei = None
     if rank == 0:
+        # the launcher pins every rank to one OpenMP thread; the check below is a few dozen GFLOP on the host
+        torch.set_num_threads(max(1, min(16, (os.cpu_count() or 1) // max(world, 1))))
         xf = xs.float().cpu()
         sd = {kk: v.detach().float().cpu() for kk, v in inner.state_dict().items() if "embed" not in kk}
         lpx = orc.router_log_probs(orc.router_batchnorm_eval(orc.router_logits(xf, sd["router_gate_x.weight"]),
