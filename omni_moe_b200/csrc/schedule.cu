@@ -64,8 +64,24 @@ Plan make_plan(int64_t P, int64_t N) {
   return p;
 }
 
-__device__ __forceinline__ int load_key(const void* keys, int is_i64, int64_t i) {
-  return is_i64 ? static_cast<int>(reinterpret_cast<const int64_t*>(keys)[i]) : reinterpret_cast<const int32_t*>(keys)[i];
+// IPT keys of one thread at positions first + i * stride, all requested before any is used: one loop per key width
+// (a width test per element would put every load behind a branch, and loads behind branches are issued one memory
+// round trip after the other).  Positions at or past P yield `fill`.
+template <int IPT>
+__device__ __forceinline__ void load_keys(const void* keys, int is_i64, int64_t first, int64_t stride, int64_t P, int fill,
+                                          int (&out)[IPT]) {
+  if (is_i64) {
+    const int64_t* k = reinterpret_cast<const int64_t*>(keys);
+    int64_t v[IPT];
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) v[i] = (first + i * stride) < P ? k[first + i * stride] : static_cast<int64_t>(fill);
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) out[i] = static_cast<int>(v[i]);
+  } else {
+    const int32_t* k = reinterpret_cast<const int32_t*>(keys);
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) out[i] = (first + i * stride) < P ? k[first + i * stride] : fill;
+  }
 }
 
 // Block-wide exclusive scan of one int per thread; returns the exclusive prefix, total via reference.
@@ -102,13 +118,14 @@ __global__ void __launch_bounds__(kThreads) radix_count_kernel(
   __syncthreads();
   const int64_t base = static_cast<int64_t>(tile) * (kThreads * IPT);
   bool bad = false;
+  int e[IPT];
+  load_keys<IPT>(keys, key_is_i64, base + threadIdx.x, kThreads, P, 0, e);
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int64_t p = base + i * kThreads + threadIdx.x;
     if (p < P) {
-      const int e = load_key(keys, key_is_i64, p);
-      if (check_range && (e < 0 || e >= num_experts)) bad = true;
-      atomicAdd(&s_hist[(static_cast<unsigned>(e) >> shift) & (bins - 1)], 1);
+      if (check_range && (e[i] < 0 || e[i] >= num_experts)) bad = true;
+      atomicAdd(&s_hist[(static_cast<unsigned>(e[i]) >> shift) & (bins - 1)], 1);
     }
   }
   if (bad) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
@@ -216,12 +233,19 @@ __global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
   int key[IPT], val[IPT];
   uint16_t rank[IPT];
   const unsigned lt_mask = (1u << lane) - 1u;
+  // all loads of the tile first (see load_keys), then the order-preserving ranking, which is sequential by nature
+  load_keys<IPT>(keys, key_is_i64, wbase + lane, 32, P, 0, key);
+  if (vals) {
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) val[i] = (wbase + i * 32 + lane) < P ? vals[wbase + i * 32 + lane] : 0;
+  } else {
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) val[i] = static_cast<int>(wbase + i * 32 + lane);
+  }
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int64_t p = wbase + i * 32 + lane;
     const bool ok = p < P;
-    key[i] = ok ? load_key(keys, key_is_i64, p) : 0;
-    val[i] = ok ? (vals ? vals[p] : static_cast<int>(p)) : 0;
     const int d = ok ? ((static_cast<unsigned>(key[i]) >> shift) & (bins - 1)) : bins;  // bins = "none"
     const unsigned peers = __match_any_sync(FULL_MASK, d);
     const int before = ok ? cnt[d] : 0;
@@ -242,14 +266,18 @@ __global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
     }
   }
   __syncthreads();
+  int dst[IPT];
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {  // the offsets of all items first: two dependent-free gathers per item
+    const int d = (static_cast<unsigned>(key[i]) >> shift) & (bins - 1);
+    dst[i] = bin_base[d] + hist[static_cast<size_t>(d) * tiles + tile] + cnt[d] + rank[i];
+  }
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int64_t p = wbase + i * 32 + lane;
     if (p < P) {
-      const int d = (static_cast<unsigned>(key[i]) >> shift) & (bins - 1);
-      const int dst = bin_base[d] + hist[static_cast<size_t>(d) * tiles + tile] + cnt[d] + rank[i];
-      out_keys[dst] = key[i];
-      out_vals[dst] = val[i];
+      out_keys[dst[i]] = key[i];
+      out_vals[dst[i]] = val[i];
     }
   }
 }
@@ -263,10 +291,16 @@ __global__ void __launch_bounds__(kThreads) segment_count_kernel(const int* sort
   const int tiles = gridDim.x, tile = blockIdx.x;
   const int64_t base = static_cast<int64_t>(tile) * (kThreads * IPT) + static_cast<int64_t>(threadIdx.x) * IPT;
   int heads = 0;
+  int kv[IPT + 1];  // kv[i] = key at base + i - 1: every load before the first comparison
+#pragma unroll
+  for (int i = 0; i <= IPT; ++i) {
+    const int64_t q = base + i - 1;
+    kv[i] = (q >= 0 && q < P) ? sorted_keys[q] : -1;
+  }
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int64_t p = base + i;
-    if (p < P && (p == 0 || sorted_keys[p] != sorted_keys[p - 1])) ++heads;
+    if (p < P && (p == 0 || kv[i + 1] != kv[i])) ++heads;
   }
   int total;
   block_exclusive_scan(heads, s_scan, total);
@@ -309,20 +343,40 @@ __global__ void __launch_bounds__(kThreads) segment_write_kernel(
   int keyv[IPT];
   bool head[IPT];
   int heads = 0;
+  int kv[IPT + 1], pr[IPT];  // keys at base - 1 .. base + IPT - 1 and the permutation: every load before its first use
+#pragma unroll
+  for (int i = 0; i <= IPT; ++i) {
+    const int64_t q = base + i - 1;
+    kv[i] = (q >= 0 && q < P) ? sorted_keys[q] : -1;
+  }
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) pr[i] = (base + i) < P ? perm[base + i] : 0;
+  if (sorted_weights) {  // the permuted weights: gathers that depend on pr only
+    if (wbytes == 4) {
+      uint32_t wv[IPT];
+#pragma unroll
+      for (int i = 0; i < IPT; ++i) wv[i] = (base + i) < P ? reinterpret_cast<const uint32_t*>(weights)[pr[i]] : 0u;
+#pragma unroll
+      for (int i = 0; i < IPT; ++i)
+        if (base + i < P) reinterpret_cast<uint32_t*>(sorted_weights)[base + i] = wv[i];
+    } else {
+      uint16_t wv[IPT];
+#pragma unroll
+      for (int i = 0; i < IPT; ++i) wv[i] = (base + i) < P ? reinterpret_cast<const uint16_t*>(weights)[pr[i]] : uint16_t(0);
+#pragma unroll
+      for (int i = 0; i < IPT; ++i)
+        if (base + i < P) reinterpret_cast<uint16_t*>(sorted_weights)[base + i] = wv[i];
+    }
+  }
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int64_t p = base + i;
     head[i] = false;
     if (p < P) {
-      keyv[i] = sorted_keys[p];
-      head[i] = (p == 0) || (keyv[i] != sorted_keys[p - 1]);
+      keyv[i] = kv[i + 1];
+      head[i] = (p == 0) || (kv[i + 1] != kv[i]);
       heads += head[i];
-      const int pr = perm[p];
-      if (token_ids) token_ids[p] = pr / k;
-      if (sorted_weights) {
-        if (wbytes == 4) reinterpret_cast<uint32_t*>(sorted_weights)[p] = reinterpret_cast<const uint32_t*>(weights)[pr];
-        else reinterpret_cast<uint16_t*>(sorted_weights)[p] = reinterpret_cast<const uint16_t*>(weights)[pr];
-      }
+      if (token_ids) token_ids[p] = pr[i] / k;
     }
   }
   int total;
