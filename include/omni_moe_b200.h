@@ -168,6 +168,24 @@ OMNI_API int omni_expert_coef(const void *x, const void *up, const float *weight
                      const int32_t *sorted_pair_ids, const int32_t *sorted_experts,
                      int64_t num_tokens, int k, int hidden, int64_t num_experts,
                      float *coef, int32_t *status, void *stream);
+/*
+ * omni_expert_coef for skewed routing.  Experts that own long runs of the sorted pair list ("hot" experts: at least
+ * min_run pairs, up to 64 of them, taken in sorted order) are handled as a dense product: their Up rows are copied
+ * side by side and one tcgen05 GEMM gives x . Up[e] for every token, so their pairs read 4 bytes instead of
+ * gathering a token row each.  All other pairs go the way of omni_expert_coef.  The reference treats every pair
+ * alike (omni_moe/ops/triton/omni_expert.py:13-168); results agree with omni_expert_coef to fp32 summation order.
+ * The set of hot experts depends on the sorted list only, so the result is reproducible.
+ *
+ *   min_run    pairs an expert must own to be treated densely; <= 0 picks max(512, T / 32)
+ *   workspace  device scratch of omni_expert_coef_hot_workspace(T, H) bytes, 16-byte aligned
+ * Other arguments and limits as omni_expert_coef.
+ */
+OMNI_API int64_t omni_expert_coef_hot_workspace(int64_t num_tokens, int hidden);
+OMNI_API int omni_expert_coef_hot(const void *x, const void *up, const float *weights,
+                         const int32_t *sorted_pair_ids, const int32_t *sorted_experts,
+                         int64_t num_tokens, int k, int hidden, int64_t num_experts, int64_t min_run,
+                         float *coef, void *workspace, int64_t workspace_bytes,
+                         int32_t *status, void *stream);
 OMNI_API int omni_expert_combine(const void *down, const float *coef, const int32_t *indices,
                         int64_t num_tokens, int k, int hidden, int64_t num_experts,
                         const void *residual, void *y, int out_dtype,

@@ -36,6 +36,9 @@ SIGNATURES = {
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "omni_expert_coef": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64,
                                  c_void_p, c_void_p, c_void_p]),
+    "omni_expert_coef_hot_workspace": (c_int64, [c_int64, c_int]),
+    "omni_expert_coef_hot": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64,
+                                     c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "omni_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p, c_void_p,
                                     c_int, c_void_p, c_void_p]),
     "omni_expert_coef_pairs": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,

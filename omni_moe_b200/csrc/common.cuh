@@ -21,6 +21,11 @@ int fail(int code, const char* fmt, ...);
 // Checks the launch itself (configuration errors show up here; kernels report through status words).
 int check_launch(const char* what);
 
+// omni_router_gate whose launch does nothing when `enable` is given and *enable == 0 on the device at the time it
+// runs (a value written by an earlier kernel on the stream); sqrt_n < 128.
+int router_gate_if(const void* x, const void* gate_x, const void* gate_y, int64_t num_tokens, int hidden, int sqrt_n,
+                   float* logits, const int* enable, int32_t* status, void* stream);
+
 constexpr unsigned FULL_MASK = 0xffffffffu;
 
 // Programmatic dependent launch.  A kernel launched with launch_after_predecessor() may start while the

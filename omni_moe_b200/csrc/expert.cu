@@ -20,6 +20,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kRun = 16;  // sorted positions per warp in expert_coef_kernel
+constexpr int kHot = 64;  // experts whose products with every token come from a dense GEMM (omni_expert_coef_hot)
 
 __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc) {
   const uint32_t* pa = reinterpret_cast<const uint32_t*>(&a);
@@ -65,9 +66,13 @@ template <int HV>
 __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up, const float* __restrict__ weights,
     const int* __restrict__ perm, const int* __restrict__ sorted_experts, const int* __restrict__ pair_tokens,
-    int64_t P, int64_t T, int k, int H, int64_t N, float* __restrict__ coef, int* status) {
+    int64_t P, int64_t T, int k, int H, int64_t N, float* __restrict__ coef, int* status,
+    const int* __restrict__ hot_ids, const float* __restrict__ hot_dots) {
   // pair_tokens == nullptr: pairs come from a [T, k] routing table, pair p belongs to token p / k.
   // Otherwise pair p belongs to token pair_tokens[p] (pairs received from other GPUs).
+  // hot_ids != nullptr: kHot ascending expert ids (padded with INT_MAX) followed by their count; the dot
+  // products of those experts' Up rows with every token are already in hot_dots [T, kHot] (a dense GEMM),
+  // so pairs on them gather nothing.
   const int lane = lane_id();
   const int64_t w0 = (static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5)) * kRun;
   if (w0 >= P) return;
@@ -83,6 +88,20 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     }
   }
   const int count = (P - w0 < kRun) ? static_cast<int>(P - w0) : kRun;
+  unsigned hot_mask = 0;
+  if (hot_ids != nullptr && __ldg(hot_ids + kHot) > 0) {
+    int col = -1;
+    if (my_t >= 0 && my_t < T && my_e >= 0 && my_e < N) {
+      int lo = 0;  // lower bound among kHot ascending ids
+#pragma unroll
+      for (int step = kHot / 2; step > 0; step >>= 1)
+        if (__ldg(hot_ids + lo + step - 1) < my_e) lo += step;
+      if (__ldg(hot_ids + lo) == my_e) col = lo;
+    }
+    if (col >= 0) coef[my_pair] = my_g * silu(__ldg(hot_dots + static_cast<int64_t>(my_t) * kHot + col));
+    hot_mask = __ballot_sync(FULL_MASK, col >= 0);
+    if (hot_mask == (count >= 32 ? FULL_MASK : ((1u << count) - 1u))) return;
+  }
   const int slabs = ceil_div(H, HV * 256);
   // Up rows stream through once; the token rows are gathered k times and should keep their place in L2
   const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
@@ -95,7 +114,7 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     const int c0 = lane * 8;
     auto fetch_x = [&](int i, uint4 (&dst)[HV]) {
       const int64_t t = __shfl_sync(FULL_MASK, my_t, i);
-      const bool ok = t >= 0 && t < T;
+      const bool ok = t >= 0 && t < T && !((hot_mask >> i) & 1u);
 #pragma unroll
       for (int v = 0; v < HV; ++v) {
         const int c = c0 + v * 256;
@@ -111,7 +130,9 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
       const float g = __shfl_sync(FULL_MASK, my_g, i);
       const int64_t t = __shfl_sync(FULL_MASK, my_t, i);
       const bool e_ok = e >= 0 && e < N, t_ok = pair >= 0 && t >= 0 && t < T;
-      if (!e_ok) {
+      if ((hot_mask >> i) & 1u) {
+        // done above from the dense products
+      } else if (!e_ok) {
         bad_e = true;
         if (lane == 0 && pair >= 0 && pair < P) coef[pair] = 0.f;
       } else if (!t_ok) {
@@ -140,6 +161,7 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     const int e = __shfl_sync(FULL_MASK, my_e, i);
     const float g = __shfl_sync(FULL_MASK, my_g, i);
     const int64_t t = __shfl_sync(FULL_MASK, my_t, i);
+    if ((hot_mask >> i) & 1u) continue;
     if (e < 0 || e >= N) { bad_e = true; if (lane == 0 && pair >= 0 && pair < P) coef[pair] = 0.f; continue; }
     if (pair < 0 || t < 0 || t >= T) { bad_t = true; continue; }
     float acc = 0.f;
@@ -167,6 +189,59 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
   }
   if (bad_e && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
   if (bad_t && lane == 0) atomicOr(status, OMNI_ST_BAD_TOKEN_INDEX);
+}
+
+// Picks the experts that own long runs of the sorted pair list and copies their Up rows side by side, so that
+// one dense GEMM gives their products with every token.  An expert qualifies when it fills a whole aligned window
+// of `tau` sorted positions (any run of 2 * tau - 1 pairs does, none shorter than tau does); the first kHot such
+// experts in sorted order are taken.  Every block repeats the scan (a few thousand loads) and block b then copies
+// row b, so the list needs no second launch; unused slots get the id INT_MAX and a zero row.  The choice depends
+// on the sorted list only, never on timing.  A list that is not sorted yields fewer or repeated ids, which costs
+// speed only: the coefficient kernel takes a dense product only where the id matches exactly.
+__global__ void __launch_bounds__(kThreads) hot_rows_kernel(const int* __restrict__ sorted_experts, int64_t P, int tau,
+                                                            int64_t N, const __nv_bfloat16* __restrict__ up, int H,
+                                                            int* __restrict__ hot_ids, __nv_bfloat16* __restrict__ hot_rows) {
+  __shared__ int s_ids[kHot];
+  __shared__ int s_warp[kWarps];
+  __shared__ int s_count;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < kHot) s_ids[tid] = 0x7fffffff;
+  if (tid == 0) s_count = 0;
+  __syncthreads();
+  const int64_t windows = P / tau;
+  for (int64_t base = 0; base < windows; base += kThreads) {
+    const int64_t j = base + tid;
+    int e = -1;
+    bool first_full = false;
+    if (j < windows) {
+      e = sorted_experts[j * tau];
+      const int last = sorted_experts[(j + 1) * tau - 1];
+      const int before = j > 0 ? sorted_experts[(j - 1) * tau] : -1;
+      first_full = e == last && e >= 0 && e < N && !(j > 0 && before == e);
+    }
+    const unsigned m = __ballot_sync(FULL_MASK, first_full);
+    if (lane == 0) s_warp[warp] = __popc(m);
+    __syncthreads();
+    int pos = s_count + __popc(m & ((1u << lane) - 1u));
+    int total = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      if (w < warp) pos += s_warp[w];
+      total += s_warp[w];
+    }
+    if (first_full && pos < kHot) s_ids[pos] = e;
+    __syncthreads();
+    if (tid == 0) s_count += total;
+    __syncthreads();
+    if (s_count >= kHot) break;
+  }
+  const int b = blockIdx.x;
+  const int id = s_ids[b];
+  if (b == 0 && tid < kHot) hot_ids[tid] = s_ids[tid];
+  if (b == 0 && tid == kHot) hot_ids[kHot] = min(s_count, kHot);
+  uint4* dst = reinterpret_cast<uint4*>(hot_rows + static_cast<int64_t>(b) * H);
+  const uint4* src = reinterpret_cast<const uint4*>(up + static_cast<int64_t>(id == 0x7fffffff ? 0 : id) * H);
+  for (int c = tid; c < H / 8; c += kThreads) dst[c] = id == 0x7fffffff ? make_uint4(0, 0, 0, 0) : __ldg(src + c);
 }
 
 template <int HV, bool OUT_F32>
@@ -894,9 +969,10 @@ bool routed_legacy() {
 
 using namespace omni;
 
-extern "C" int omni_expert_coef(const void* x, const void* up, const float* weights, const int32_t* sorted_pair_ids,
-                                const int32_t* sorted_experts, int64_t num_tokens, int k, int hidden,
-                                int64_t num_experts, float* coef, int32_t* status, void* stream) {
+static int launch_expert_coef(const void* x, const void* up, const float* weights, const int32_t* sorted_pair_ids,
+                              const int32_t* sorted_experts, int64_t num_tokens, int k, int hidden,
+                              int64_t num_experts, float* coef, int32_t* status, void* stream, const int* hot_ids,
+                              const float* hot_dots) {
   OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && num_experts >= 1, "bad sizes");
   OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
   const int64_t P = num_tokens * k;
@@ -909,7 +985,7 @@ extern "C" int omni_expert_coef(const void* x, const void* up, const float* weig
   const unsigned grid = static_cast<unsigned>(ceil_div64(ceil_div64(P, kRun), kWarps));
 #define OMNI_COEF(HV)                                                                                         \
   expert_coef_kernel<HV><<<grid, kThreads, 0, st>>>(xb, ub, weights, sorted_pair_ids, sorted_experts, nullptr, P,     \
-                                                   num_tokens, k, hidden, num_experts, coef, status)
+                                                   num_tokens, k, hidden, num_experts, coef, status, hot_ids, hot_dots)
   if (hidden <= 256) OMNI_COEF(1);
   else if (hidden <= 512) OMNI_COEF(2);
   else if (hidden <= 1024) OMNI_COEF(4);
@@ -917,6 +993,55 @@ extern "C" int omni_expert_coef(const void* x, const void* up, const float* weig
   else OMNI_COEF(16);
 #undef OMNI_COEF
   return check_launch("expert_coef_kernel");
+}
+
+extern "C" int omni_expert_coef(const void* x, const void* up, const float* weights, const int32_t* sorted_pair_ids,
+                                const int32_t* sorted_experts, int64_t num_tokens, int k, int hidden,
+                                int64_t num_experts, float* coef, int32_t* status, void* stream) {
+  return launch_expert_coef(x, up, weights, sorted_pair_ids, sorted_experts, num_tokens, k, hidden, num_experts, coef,
+                            status, stream, nullptr, nullptr);
+}
+
+namespace {
+constexpr int64_t kHotIdsBytes = 1024;  // kHot ids + the count, padded so that the rows behind them stay aligned
+int64_t hot_rows_bytes(int hidden) { return static_cast<int64_t>(kHot) * hidden * 2; }
+}  // namespace
+
+extern "C" int64_t omni_expert_coef_hot_workspace(int64_t num_tokens, int hidden) {
+  if (num_tokens < 0 || hidden < 8) return 0;
+  return kHotIdsBytes + hot_rows_bytes(hidden) + num_tokens * kHot * static_cast<int64_t>(sizeof(float));
+}
+
+extern "C" int omni_expert_coef_hot(const void* x, const void* up, const float* weights, const int32_t* sorted_pair_ids,
+                                    const int32_t* sorted_experts, int64_t num_tokens, int k, int hidden,
+                                    int64_t num_experts, int64_t min_run, float* coef, void* workspace,
+                                    int64_t workspace_bytes, int32_t* status, void* stream) {
+  OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && hidden % 8 == 0 && num_experts >= 1, "bad sizes");
+  const int64_t P = num_tokens * k;
+  if (P == 0) return 0;
+  OMNI_REQUIRE(x && up && weights && sorted_pair_ids && sorted_experts && coef && status && workspace, "NULL argument");
+  OMNI_REQUIRE(aligned16(x) && aligned16(up) && aligned16(workspace), "x, up and workspace must be 16-byte aligned");
+  OMNI_REQUIRE(workspace_bytes >= omni_expert_coef_hot_workspace(num_tokens, hidden),
+               "workspace holds %lld bytes, omni_expert_coef_hot_workspace asks for %lld",
+               static_cast<long long>(workspace_bytes),
+               static_cast<long long>(omni_expert_coef_hot_workspace(num_tokens, hidden)));
+  if (min_run <= 0) min_run = num_tokens / 32 > 512 ? num_tokens / 32 : 512;
+  OMNI_REQUIRE(min_run < (int64_t(1) << 30), "min_run out of range");
+  char* ws = static_cast<char*>(workspace);
+  int* hot_ids = reinterpret_cast<int*>(ws);
+  auto* hot_rows = reinterpret_cast<__nv_bfloat16*>(ws + kHotIdsBytes);
+  float* hot_dots = reinterpret_cast<float*>(ws + kHotIdsBytes + hot_rows_bytes(hidden));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  hot_rows_kernel<<<kHot, kThreads, 0, st>>>(sorted_experts, P, static_cast<int>(min_run), num_experts,
+                                             static_cast<const __nv_bfloat16*>(up), hidden, hot_ids, hot_rows);
+  if (int e = check_launch("hot_rows_kernel")) return e;
+  // products of every token with the kHot rows: [T, kHot] fp32, two halves of kHot / 2 columns side by side
+  // (skipped on the device when no expert qualified)
+  if (int e = router_gate_if(x, hot_rows, hot_rows + static_cast<int64_t>(kHot / 2) * hidden, num_tokens, hidden, kHot / 2,
+                             hot_dots, hot_ids + kHot, status, stream))
+    return e;
+  return launch_expert_coef(x, up, weights, sorted_pair_ids, sorted_experts, num_tokens, k, hidden, num_experts, coef,
+                            status, stream, hot_ids, hot_dots);
 }
 
 extern "C" int omni_expert_combine(const void* down, const float* coef, const int32_t* indices, int64_t num_tokens,
@@ -1103,7 +1228,7 @@ extern "C" int omni_expert_coef_pairs(const void* x, const void* up, const int32
   const unsigned grid = static_cast<unsigned>(ceil_div64(ceil_div64(num_pairs, kRun), kWarps));
 #define OMNI_COEFP(HV)                                                                                               \
   expert_coef_kernel<HV><<<grid, kThreads, 0, st>>>(xb, ub, pair_weights, sorted_pair_ids, sorted_experts, pair_tokens, \
-                                                   num_pairs, num_tokens, 1, hidden, num_experts, coef, status)
+                                                   num_pairs, num_tokens, 1, hidden, num_experts, coef, status, nullptr, nullptr)
   if (hidden <= 256) OMNI_COEFP(1);
   else if (hidden <= 512) OMNI_COEFP(2);
   else if (hidden <= 1024) OMNI_COEFP(4);

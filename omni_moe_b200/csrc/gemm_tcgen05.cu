@@ -57,6 +57,7 @@ struct GemmArgs {
   int router_tiles;       // tile columns holding router sub-keys (0 = none); they come first in tile order
   int router_n;           // sqrt_n; kernels without router tiles and with a transposed B: k_split (0 = one B matrix)
   float* logits;          // [M, 2 * sqrt_n]
+  const int* enable;      // gemm_kernel: if set and *enable == 0 the launch does nothing (decided by an earlier kernel)
   int* status;
 #ifdef OMNI_TUNING
   long long* prof;  // tuning builds: per-CTA cycle counters (8 words per CTA), normally null
@@ -409,6 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                                                            const __grid_constant__ CUtensorMap tm_b1,
                                                            const GemmArgs g) {
   using C = Cfg<BN>;
+  if (g.enable != nullptr && *g.enable == 0) return;  // every thread of every CTA, before anything is allocated
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
@@ -1005,6 +1007,12 @@ using namespace omni;
 
 extern "C" int omni_router_gate(const void* x, const void* gate_x, const void* gate_y, int64_t num_tokens, int hidden,
                                 int sqrt_n, float* logits, int32_t* status, void* stream) {
+  return omni::router_gate_if(x, gate_x, gate_y, num_tokens, hidden, sqrt_n, logits, nullptr, status, stream);
+}
+
+int omni::router_gate_if(const void* x, const void* gate_x, const void* gate_y, int64_t num_tokens, int hidden, int sqrt_n,
+                         float* logits, const int* enable, int32_t* status, void* stream) {
+  OMNI_REQUIRE(enable == nullptr || sqrt_n < 128, "a conditional launch covers sqrt_n < 128 only");
   OMNI_REQUIRE(num_tokens >= 0 && num_tokens < (int64_t(1) << 31) - BM, "num_tokens out of range");
   OMNI_REQUIRE(hidden >= 8 && hidden % 8 == 0, "hidden must be a positive multiple of 8, got %d", hidden);
   OMNI_REQUIRE(sqrt_n >= 1, "sqrt_n must be >= 1");
@@ -1038,7 +1046,7 @@ extern "C" int omni_router_gate(const void* x, const void* gate_x, const void* g
   g.tiles_m = ceil_div(g.M, BM);
   g.tiles_n_axis = ceil_div(sqrt_n, bn);
   g.tiles_n = 2 * g.tiles_n_axis;
-  g.out = logits, g.ldo = 2 * static_cast<int64_t>(sqrt_n), g.status = status;
+  g.out = logits, g.ldo = 2 * static_cast<int64_t>(sqrt_n), g.status = status, g.enable = enable;
   OMNI_SET_TUNING(g);
   if (bn == 64) return launch<64, EPI_F32>(ma, mx, my, g, st);
   if (bn == 128) return launch<128, EPI_F32>(ma, mx, my, g, st);

@@ -286,6 +286,14 @@ def run_config(name: str, reps: int):
                                                             None, y.data_ptr(), _lib.OMNI_BF16, status.data_ptr(), s)),
                       reps=reps)
     report("expert_coef", us_c, "hbm", 2.0 * T * H + 2.0 * U * H + 12.0 * P, f"U={U} distinct experts")
+    # the same with the hot experts' products from one dense GEMM (what the scheduled path launches from 4096 tokens)
+    hot_ws = torch.empty(int(lib.omni_expert_coef_hot_workspace(T, H)), device=dev, dtype=torch.uint8)
+    us_h = time_graph(lambda s: chk(lib.omni_expert_coef_hot(x.data_ptr(), up.data_ptr(), weights.data_ptr(), perm.data_ptr(),
+                                                             sorted_e.data_ptr(), T, k, H, N, 0, coef.data_ptr(),
+                                                             hot_ws.data_ptr(), hot_ws.numel(), status.data_ptr(), s)),
+                      reps=reps)
+    n_hot = int(hot_ws[256:260].view(torch.int32).item())
+    report("expert_coef_hot", us_h, "hbm", 2.0 * T * H + 2.0 * U * H + 12.0 * P, f"{n_hot} experts treated densely")
     report("expert_combine", us_b, "hbm", 2.0 * T * H + 2.0 * U * H + 8.0 * P)
     report("expert_coef+combine", us_c + us_b, "hbm", alg, f"gather traffic through L2: {2.0 * P * H * 2 / 2**30:.2f} GiB")
     if H <= 2048:

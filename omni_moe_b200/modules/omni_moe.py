@@ -23,7 +23,7 @@ import torch
 import torch.nn as nn
 
 from .. import _lib
-from ..ops.expert import use_fused_path, use_routed_kernel
+from ..ops.expert import hot_workspace, use_fused_path, use_hot_experts, use_routed_kernel
 from ..ops.scheduler import workspace_bytes
 
 
@@ -56,6 +56,8 @@ class _Buffers:
         self.coef = torch.empty((t, k), **f32)
         self.act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
         self.workspace = torch.empty(workspace_bytes(p, n), device=dev, dtype=torch.uint8)
+        # dense products of the hot experts (large-table path only)
+        self.hot = hot_workspace(t, h, dev) if (use_hot_experts(t) and not use_fused_path(n, h)) else None
         self.status = torch.zeros(1, **i32)
         self.bn_scale = torch.empty(2 * n_sqrt, **f32)      # training-mode BatchNorm fold of this forward
         self.bn_shift = torch.empty(2 * n_sqrt, **f32)
@@ -250,16 +252,21 @@ class OmniMoE(nn.Module):
             chk(lib.omni_schedule(b.indices.data_ptr(), 0, None, 0, t, k, self.num_experts, b.perm.data_ptr(),
                                   b.sorted_experts.data_ptr(), None, None, None, None, b.meta.data_ptr(),
                                   b.workspace.data_ptr(), b.workspace.numel(), st))
-            chk(lib.omni_expert_coef(x.data_ptr(), up_t.data_ptr(), b.weights.data_ptr(), b.perm.data_ptr(),
-                                     b.sorted_experts.data_ptr(), t, k, h, self.num_experts, b.coef.data_ptr(),
-                                     status, st))
+            if b.hot is not None:
+                chk(lib.omni_expert_coef_hot(x.data_ptr(), up_t.data_ptr(), b.weights.data_ptr(), b.perm.data_ptr(),
+                                             b.sorted_experts.data_ptr(), t, k, h, self.num_experts, 0,
+                                             b.coef.data_ptr(), b.hot.data_ptr(), b.hot.numel(), status, st))
+            else:
+                chk(lib.omni_expert_coef(x.data_ptr(), up_t.data_ptr(), b.weights.data_ptr(), b.perm.data_ptr(),
+                                         b.sorted_experts.data_ptr(), t, k, h, self.num_experts, b.coef.data_ptr(),
+                                         status, st))
             chk(lib.omni_expert_combine(down_t.data_ptr(), b.coef.data_ptr(), b.indices.data_ptr(), t, k, h,
                                         self.num_experts, y.data_ptr(), y.data_ptr(), _lib.OMNI_BF16, status, st))
         self.last_routing = (b.scores, b.indices, b.weights)
         self.last_status = b.status
 
     @staticmethod
-    def kernels_per_forward(num_experts: int, hidden: int, sqrt_n: int = 0, k: int = 0) -> int:
+    def kernels_per_forward(num_experts: int, hidden: int, sqrt_n: int = 0, k: int = 0, num_tokens: int = 0) -> int:
         """Kernels of this library launched by one eval forward."""
         if sqrt_n and use_routed_kernel(num_experts, hidden, sqrt_n, k):
             return 4  # gate/up, router gates, down projection, router selection + experts
@@ -267,8 +274,9 @@ class OmniMoE(nn.Module):
             return 5  # gate/up, router gates, top-k, down projection, fused experts
         bits = max(1, (num_experts - 1).bit_length())
         passes = -(-bits // 11)
-        # gate/up, router gates, top-k, down projection, 2 per radix pass, coefficients, combine
-        return 4 + 2 * passes + 2
+        # gate/up, router gates, top-k, down projection, 2 per radix pass, coefficients, combine;
+        # from 4096 tokens also the hot-expert search and its dense GEMM
+        return 4 + 2 * passes + 2 + (2 if use_hot_experts(num_tokens) else 0)
 
     def _needs_grad(self, hidden_states: torch.Tensor) -> bool:
         """The differentiable composition is used when gradients can be asked for: the input carries a

@@ -1,6 +1,8 @@
 """Routed-expert op (reference: omni_moe/ops/triton/omni_expert.py:920-992, interface.py:54-72)."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _lib
@@ -68,16 +70,29 @@ def route_expert_fused(logits: torch.Tensor, x: torch.Tensor, up_weight: torch.T
     return (y, scores, indices, weights) if return_routing else y
 
 
+def use_hot_experts(num_tokens: int) -> bool:
+    """Whether the scheduled path looks for hot experts (``omni_expert_coef_hot``): on by default from 4096 tokens,
+    where the one extra 64-column GEMM is noise beside the gathers; ``OMNI_MOE_B200_HOT=0`` turns it off."""
+    return num_tokens >= 4096 and os.environ.get("OMNI_MOE_B200_HOT", "1") != "0"
+
+
+def hot_workspace(num_tokens: int, hidden: int, dev: torch.device) -> torch.Tensor:
+    return torch.empty(int(_lib.load().omni_expert_coef_hot_workspace(num_tokens, hidden)), device=dev, dtype=torch.uint8)
+
+
 def expert_forward(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.Tensor, weights: torch.Tensor,
                    indices: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                    residual: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                   workspace: torch.Tensor | None = None, return_coef: bool = False, mode: str = "auto"):
+                   workspace: torch.Tensor | None = None, return_coef: bool = False, mode: str = "auto",
+                   hot: bool | None = None, hot_min_run: int = 0):
     """``y[t] = sum_j w[t,j] * silu(x[t] . Up[e[t,j]]) * Down[e[t,j]]`` (+ residual).
 
     ``x [T, H]``, ``up/down [N, H]`` bf16; ``weights [T, k]`` fp32; ``indices [T, k]`` int32.
     ``mode="scheduled"``: schedules the pairs by expert, computes the per-pair coefficients in expert
     order, then combines per token.  ``mode="fused"``: one token-centric kernel (tables resident in
     L2, hidden <= 2048).  ``mode="auto"`` picks by table size (:func:`use_fused_path`).
+    ``hot`` (scheduled path): experts that own at least ``hot_min_run`` pairs (0 = max(512, T / 32)) get their
+    dot products from one dense GEMM instead of a gather per pair; None = :func:`use_hot_experts`.
     ``out_dtype`` float32 or bfloat16; ``residual`` (same dtype as the output) is added in.
     """
     assert mode in ("auto", "fused", "scheduled")
@@ -115,9 +130,16 @@ def expert_forward(x: torch.Tensor, up_weight: torch.Tensor, down_weight: torch.
     sch = schedule(indices, n, segments=False, workspace=workspace)
     with torch.cuda.device(dev):
         st = _lib.stream_ptr()
-        _lib.check(lib.omni_expert_coef(x.data_ptr(), up_weight.data_ptr(), weights.data_ptr(),
-                                        sch.sorted_pair_ids.data_ptr(), sch.sorted_experts.data_ptr(), t, k, h, n,
-                                        coef.data_ptr(), status.data_ptr(), st))
+        if use_hot_experts(t) if hot is None else hot:
+            ws = hot_workspace(t, h, dev)
+            _lib.check(lib.omni_expert_coef_hot(x.data_ptr(), up_weight.data_ptr(), weights.data_ptr(),
+                                                sch.sorted_pair_ids.data_ptr(), sch.sorted_experts.data_ptr(), t, k, h, n,
+                                                hot_min_run, coef.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                status.data_ptr(), st))
+        else:
+            _lib.check(lib.omni_expert_coef(x.data_ptr(), up_weight.data_ptr(), weights.data_ptr(),
+                                            sch.sorted_pair_ids.data_ptr(), sch.sorted_experts.data_ptr(), t, k, h, n,
+                                            coef.data_ptr(), status.data_ptr(), st))
         _lib.check(lib.omni_expert_combine(down_weight.data_ptr(), coef.data_ptr(), indices.data_ptr(), t, k, h, n,
                                            _lib.ptr(residual), y.data_ptr(), _lib.dtype_code(out_dtype),
                                            status.data_ptr(), st))

@@ -364,3 +364,103 @@ def test_expert_float32_operands_are_computed_in_float32(t, h, n, k):
         wz = w.clone()
         wz[2, 0] = 0.0
         assert_close(yb, orc.expert_forward(x, up, dn, wz, bad.clamp(0, n - 1)), rtol=1e-4, atol=1e-5)
+
+
+def _hot_run(x, up, w, idx, n, min_run):
+    """omni_expert_coef_hot through the C ABI; returns the coefficients and the ids it treated densely."""
+    from omni_moe_b200 import _lib
+    from omni_moe_b200.ops.scheduler import schedule
+    lib = _lib.load()
+    t, h = x.shape
+    k = idx.size(1)
+    sch = schedule(idx, n, segments=False)
+    ws = torch.zeros(int(lib.omni_expert_coef_hot_workspace(t, h)), dtype=torch.uint8, device="cuda")
+    coef = torch.full((t, k), float("nan"), device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(lib.omni_expert_coef_hot(x.data_ptr(), up.data_ptr(), w.data_ptr(), sch.sorted_pair_ids.data_ptr(),
+                                        sch.sorted_experts.data_ptr(), t, k, h, n, min_run, coef.data_ptr(),
+                                        ws.data_ptr(), ws.numel(), st.data_ptr(), _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    ids = ws[:65 * 4].view(torch.int32).cpu()
+    count = int(ids[64])
+    assert (ids[count:64] == 0x7fffffff).all()
+    return coef, ids[:count].tolist()
+
+
+def _plain_coef(x, up, w, idx, n):
+    from omni_moe_b200 import _lib
+    from omni_moe_b200.ops.scheduler import schedule
+    lib = _lib.load()
+    t, h = x.shape
+    k = idx.size(1)
+    sch = schedule(idx, n, segments=False)
+    coef = torch.full((t, k), float("nan"), device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(lib.omni_expert_coef(x.data_ptr(), up.data_ptr(), w.data_ptr(), sch.sorted_pair_ids.data_ptr(),
+                                    sch.sorted_experts.data_ptr(), t, k, h, n, coef.data_ptr(), st.data_ptr(),
+                                    _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    return coef
+
+
+@pytest.mark.parametrize("t,h,n,k,min_run", [(4096, 512, 4096, 8, 512), (1000, 264, 300, 6, 64), (2048, 4096, 512, 4, 128),
+                                             (4099, 1024, 70000, 16, 0)])
+def test_hot_experts_take_the_dense_products_and_agree_with_the_gathered_ones(t, h, n, k, min_run):
+    """Skewed routing: the experts that fill a whole window of min_run sorted positions are found (every expert with
+    2 * min_run - 1 pairs must be among them unless 64 others come first, none with fewer than min_run pairs may be),
+    their pairs read the GEMM's products, and all coefficients agree with the gather-only kernel and the oracle."""
+    x = (torch.randn((t, h), generator=gen(1)) * 1.0).cuda().to(torch.bfloat16)
+    up = (torch.randn((n, h), generator=gen(2)) * 0.05).cuda().to(torch.bfloat16)
+    idx = zipf_indices(t, k, n, 1.3, 7).cuda()
+    w = (torch.randn((t, k), generator=gen(3)) * 1.0).abs().cuda()
+    coef_hot, hot = _hot_run(x, up, w, idx, n, min_run)
+    coef_plain = _plain_coef(x, up, w, idx, n)
+    tau = min_run if min_run > 0 else max(512, t // 32)
+    counts = torch.bincount(idx.reshape(-1).long().cpu(), minlength=n)
+    assert hot == sorted(set(hot)), hot
+    assert all(int(counts[e]) >= tau for e in hot), [(e, int(counts[e])) for e in hot]
+    must = [e for e in range(n) if int(counts[e]) >= 2 * tau - 1]
+    assert len(hot) > 0 and (len(hot) == 64 or set(must) <= set(hot)), (hot, must)
+    assert_close(coef_hot, coef_plain, rtol=1e-4, atol=1e-5 * float(coef_plain.abs().max()) + 1e-6, what="hot vs gathered")
+    is_hot = torch.isin(idx.cpu(), torch.tensor(hot, dtype=torch.int32))
+    assert torch.equal(coef_hot.cpu()[~is_hot], coef_plain.cpu()[~is_hot]), "pairs on other experts take the same path as before"
+    sel = torch.arange(0, t, max(1, t // 64))
+    e_coef = orc.expert_coefficients(x[sel].float().cpu(), up.float().cpu(), w[sel].cpu(), idx[sel].cpu())
+    assert_close(coef_hot[sel], e_coef, rtol=1e-3, atol=1e-4, what="hot vs oracle")
+
+
+def test_hot_experts_none_found_is_the_plain_kernel_bit_for_bit():
+    """Uniform routing: no expert fills a window; the dense GEMM launch returns at once and nothing reads its output."""
+    t, h, n, k = 4096, 512, 65536, 8
+    x = (torch.randn((t, h), generator=gen(1)) * 1.0).cuda().to(torch.bfloat16)
+    up = (torch.randn((n, h), generator=gen(2)) * 0.05).cuda().to(torch.bfloat16)
+    idx = torch.randint(0, n, (t, k), generator=torch.Generator().manual_seed(5), dtype=torch.int32).cuda()
+    w = (torch.randn((t, k), generator=gen(3)) * 1.0).abs().cuda()
+    coef_hot, hot = _hot_run(x, up, w, idx, n, 0)
+    assert hot == []
+    assert torch.equal(coef_hot, _plain_coef(x, up, w, idx, n))
+
+
+def test_hot_experts_through_the_op_and_bad_indices_are_still_reported():
+    from omni_moe_b200.ops import expert_forward
+    t, h, n, k = 4096, 512, 4096, 8
+    x = (torch.randn((t, h), generator=gen(1)) * 1.0).cuda().to(torch.bfloat16)
+    up = (torch.randn((n, h), generator=gen(2)) * 0.05).cuda().to(torch.bfloat16)
+    dn = (torch.randn((n, h), generator=gen(4)) * 0.05).cuda().to(torch.bfloat16)
+    idx = zipf_indices(t, k, n, 1.3, 7).cuda()
+    w = (torch.randn((t, k), generator=gen(3)) * 1.0).abs().cuda()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y_hot = expert_forward(x, up, dn, w, idx, out_dtype=torch.float32, status=st, mode="scheduled", hot=True, hot_min_run=256)
+    y_plain = expert_forward(x, up, dn, w, idx, out_dtype=torch.float32, status=st, mode="scheduled", hot=False)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert_close(y_hot, y_plain, rtol=1e-4, atol=1e-5 * float(y_plain.abs().max()), what="hot vs gathered, output")
+    ey = orc.expert_forward(x[:64].float().cpu(), up.float().cpu(), dn.float().cpu(), w[:64].cpu(), idx[:64].cpu())
+    assert_close(y_hot[:64], ey, rtol=1e-3, atol=1e-4, what="hot path vs oracle")
+    bad = idx.clone()
+    bad[5, 1] = n + 3
+    expert_forward(x, up, dn, w, bad, out_dtype=torch.float32, status=st, mode="scheduled", hot=True, hot_min_run=256)
+    torch.cuda.synchronize()
+    assert int(st.item()) & 1  # OMNI_ST_BAD_EXPERT_INDEX: reported, nothing faults
