@@ -20,6 +20,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kRun = 16;  // sorted positions per warp in expert_coef_kernel
+constexpr int kCombineThreads = 128;
 constexpr int kHot = 64;  // experts whose products with every token come from a dense GEMM (omni_expert_coef_hot)
 
 __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc) {
@@ -113,18 +114,21 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     // computed, so a warp always has two gathers in flight.
     const int c0 = lane * 8;
     auto fetch_x = [&](int i, uint4 (&dst)[HV]) {
-      const int64_t t = __shfl_sync(FULL_MASK, my_t, i);
+      const int64_t t = __shfl_sync(FULL_MASK, my_t, i & 31);
+      // never predicated (a predicated load lands in a conditional block and is not in flight with its neighbours):
+      // a pair that is skipped reads row 0, a column past the end re-reads column 0 and meets a zero of the Up row
       const bool ok = t >= 0 && t < T && !((hot_mask >> i) & 1u);
+      const __nv_bfloat16* xr = x + (ok ? t : 0) * H;
 #pragma unroll
       for (int v = 0; v < HV; ++v) {
         const int c = c0 + v * 256;
-        dst[v] = (ok && c < H) ? ldg128_hint(x + t * H + c, pol_keep) : make_uint4(0, 0, 0, 0);
+        dst[v] = ldg128_hint(xr + (c < H ? c : 0), pol_keep);
       }
     };
     uint4 xcur[HV], xnext[HV];
     fetch_x(0, xcur);
     for (int i = 0; i < count; ++i) {
-      if (i + 1 < count) fetch_x(i + 1, xnext);
+      fetch_x(i + 1, xnext);  // past the end of the run: lane i + 1 carries no token, row 0 is read (an L1 hit) and dropped
       const int pair = __shfl_sync(FULL_MASK, my_pair, i);
       const int e = __shfl_sync(FULL_MASK, my_e, i);
       const float g = __shfl_sync(FULL_MASK, my_g, i);
@@ -244,102 +248,6 @@ __global__ void __launch_bounds__(kThreads) hot_rows_kernel(const int* __restric
   for (int c = tid; c < H / 8; c += kThreads) dst[c] = id == 0x7fffffff ? make_uint4(0, 0, 0, 0) : __ldg(src + c);
 }
 
-template <int HV, bool OUT_F32>
-__global__ void __launch_bounds__(kThreads) expert_combine_kernel(
-    const __nv_bfloat16* __restrict__ down, const float* __restrict__ coef, const int* __restrict__ indices,
-    int64_t T, int k, int H, int64_t N, int slabs, const void* residual, void* y, int* status) {
-  const int lane = lane_id();
-  const int64_t wid = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
-  const int64_t t = wid / slabs;
-  const int slab = static_cast<int>(wid - t * slabs);
-  if (t >= T) return;
-  const int c0 = slab * HV * 256 + lane * 8;
-  float acc[HV][8];
-#pragma unroll
-  for (int v = 0; v < HV; ++v)
-#pragma unroll
-    for (int q = 0; q < 8; ++q) acc[v][q] = 0.f;
-  bool bad = false;
-  for (int j0 = 0; j0 < k; j0 += 32) {
-    // lane l carries pair j0 + l of this token
-    int my_e = -1;
-    float my_c = 0.f;
-    if (j0 + lane < k) {
-      my_e = indices[t * k + j0 + lane];
-      my_c = coef[t * k + j0 + lane];
-      if (my_e < 0 || my_e >= N) { bad = true; my_e = -1; }
-    }
-    const int cnt = min(32, k - j0);
-    constexpr int UNR = HV >= 8 ? 2 : 4;  // rows in flight per step
-    for (int j = 0; j < cnt; j += UNR) {
-      uint4 dv[UNR][HV];
-      float c[UNR];
-#pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int e = __shfl_sync(FULL_MASK, my_e, (j + u) & 31);
-        c[u] = __shfl_sync(FULL_MASK, my_c, (j + u) & 31);
-        const bool on = (j + u < cnt) && e >= 0;
-        if (!on) c[u] = 0.f;
-#pragma unroll
-        for (int v = 0; v < HV; ++v) {
-          const int col = c0 + v * 256;
-          dv[u][v] = (on && col < H) ? ldg128(down + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < UNR; ++u)
-#pragma unroll
-        for (int v = 0; v < HV; ++v) {
-          const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv[u][v]);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 f = bf16x2_to_float2(pd[q]);
-            acc[v][2 * q] = __fmaf_rn(c[u], f.x, acc[v][2 * q]);
-            acc[v][2 * q + 1] = __fmaf_rn(c[u], f.y, acc[v][2 * q + 1]);
-          }
-        }
-    }
-  }
-#pragma unroll
-  for (int v = 0; v < HV; ++v) {
-    const int col = c0 + v * 256;
-    if (col >= H) continue;
-    const int64_t o = t * H + col;
-    if (OUT_F32) {
-      float4 a = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
-      float4 b = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
-      if (residual) {
-        // plain loads: residual may be the output buffer itself (in-place add)
-        const float4 ra = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o);
-        const float4 rb = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(residual) + o + 4);
-        a.x += ra.x, a.y += ra.y, a.z += ra.z, a.w += ra.w;
-        b.x += rb.x, b.y += rb.y, b.z += rb.z, b.w += rb.w;
-      }
-      float* yo = reinterpret_cast<float*>(y) + o;
-      *reinterpret_cast<float4*>(yo) = a;
-      *reinterpret_cast<float4*>(yo + 4) = b;
-    } else {
-      if (residual) {
-        const uint4 rv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(residual) + o);
-        const uint32_t* pr = reinterpret_cast<const uint32_t*>(&rv);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 f = bf16x2_to_float2(pr[q]);
-          acc[v][2 * q] += f.x;
-          acc[v][2 * q + 1] += f.y;
-        }
-      }
-      uint4 o4;
-      o4.x = float2_to_bf16x2(acc[v][0], acc[v][1]);
-      o4.y = float2_to_bf16x2(acc[v][2], acc[v][3]);
-      o4.z = float2_to_bf16x2(acc[v][4], acc[v][5]);
-      o4.w = float2_to_bf16x2(acc[v][6], acc[v][7]);
-      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(y) + o) = o4;
-    }
-  }
-  if (bad && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
-}
-
 // Token-centric fusion of the two kernels above for tables that stay resident in L2: a warp owns one
 // token, holds its x row in registers and walks its k pairs with the Up and the Down row of UNR
 // pairs in flight; dot, SiLU, weight and the accumulation of c * Down happen in registers, nothing
@@ -450,36 +358,41 @@ __device__ __forceinline__ void store_row(float (&acc)[HV][8], int64_t t, int c0
   }
 }
 
-// Token-centric combine over a pair list grouped by token (CSR): token t owns the pairs
-// [offsets[t], offsets[t+1]) of pair_experts / coef.  Used where the number of pairs per token varies:
-// on a GPU that holds a slice of the expert tables and received only the pairs routed to its rows.
+// Token-centric combine.  A warp owns (token, column slab of HV * 256 columns) and accumulates c * Down[e] over the
+// token's pairs in fp32 registers, four rows in flight per step, then writes the slab once.
+//   offsets == nullptr: the pairs of token t are entries [t * k, (t + 1) * k) of experts / coef (a [T, k] routing table);
+//   otherwise: entries [offsets[t], offsets[t + 1]) of a pair list grouped by token (a GPU that holds a slice of the
+//   tables and received only the pairs routed to its rows).
 template <int HV, bool OUT_F32>
-__global__ void __launch_bounds__(kThreads) expert_combine_segments_kernel(
-    const __nv_bfloat16* __restrict__ down, const float* __restrict__ coef, const int* __restrict__ pair_experts,
-    const int* __restrict__ offsets, int64_t T, int H, int64_t N, int slabs, const void* residual, void* y, int* status) {
+__global__ void __launch_bounds__(kCombineThreads) expert_combine_kernel(
+    const __nv_bfloat16* __restrict__ down, const float* __restrict__ coef, const int* __restrict__ experts,
+    const int* __restrict__ offsets, int64_t T, int k, int H, int64_t N, int slabs, const void* residual, void* y,
+    int* status) {
   const int lane = lane_id();
-  const int64_t wid = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  const int64_t wid = static_cast<int64_t>(blockIdx.x) * (kCombineThreads / 32) + (threadIdx.x >> 5);
   const int64_t t = wid / slabs;
   const int slab = static_cast<int>(wid - t * slabs);
   if (t >= T) return;
   const int c0 = slab * HV * 256 + lane * 8;
-  float acc[HV][8];
+  float2 acc[HV][4];
 #pragma unroll
   for (int v = 0; v < HV; ++v)
 #pragma unroll
-    for (int q = 0; q < 8; ++q) acc[v][q] = 0.f;
+    for (int q = 0; q < 4; ++q) acc[v][q] = make_float2(0.f, 0.f);
   bool bad = false;
-  const int lo = offsets[t], hi = offsets[t + 1];
-  constexpr int UNR = HV >= 8 ? 2 : 4;
-  for (int j0 = lo; j0 < hi; j0 += 32) {
+  const int64_t lo = offsets ? static_cast<int64_t>(offsets[t]) : t * k;
+  const int64_t hi = offsets ? static_cast<int64_t>(offsets[t + 1]) : lo + k;
+  for (int64_t j0 = lo; j0 < hi; j0 += 32) {
+    // lane l carries pair j0 + l of this token
     int my_e = -1;
     float my_c = 0.f;
     if (j0 + lane < hi) {
-      my_e = pair_experts[j0 + lane];
+      my_e = experts[j0 + lane];
       my_c = coef[j0 + lane];
       if (my_e < 0 || my_e >= N) { bad = true; my_e = -1; }
     }
-    const int cnt = min(32, hi - j0);
+    const int cnt = static_cast<int>(hi - j0 < 32 ? hi - j0 : 32);
+    constexpr int UNR = 4;  // rows in flight per step
     for (int j = 0; j < cnt; j += UNR) {
       uint4 dv[UNR][HV];
       float c[UNR];
@@ -489,24 +402,20 @@ __global__ void __launch_bounds__(kThreads) expert_combine_segments_kernel(
         c[u] = __shfl_sync(FULL_MASK, my_c, (j + u) & 31);
         const bool on = (j + u < cnt) && e >= 0;
         if (!on) c[u] = 0.f;
+        // never predicated: a pair that is absent or invalid reads row 0 with coefficient 0, a column past the row's
+        // end re-reads column 0 (its result is not stored).  Predicated loads here end up in conditional blocks, which
+        // keeps the rows of a step from being in flight together (8 rows per step ran 2.7 times slower than 4).
+        const __nv_bfloat16* rowp = down + static_cast<int64_t>(on ? e : 0) * H;
 #pragma unroll
         for (int v = 0; v < HV; ++v) {
           const int col = c0 + v * 256;
-          dv[u][v] = (on && col < H) ? ldg128(down + static_cast<int64_t>(e) * H + col) : make_uint4(0, 0, 0, 0);
+          dv[u][v] = ldg128(rowp + (col < H ? col : 0));
         }
       }
 #pragma unroll
       for (int u = 0; u < UNR; ++u)
 #pragma unroll
-        for (int v = 0; v < HV; ++v) {
-          const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dv[u][v]);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 f = bf16x2_to_float2(pd[q]);
-            acc[v][2 * q] = __fmaf_rn(c[u], f.x, acc[v][2 * q]);
-            acc[v][2 * q + 1] = __fmaf_rn(c[u], f.y, acc[v][2 * q + 1]);
-          }
-        }
+        for (int v = 0; v < HV; ++v) axpy8p(c[u], dv[u][v], acc[v]);
     }
   }
   store_row<HV, OUT_F32>(acc, t, c0, H, residual, y);
@@ -1044,6 +953,30 @@ extern "C" int omni_expert_coef_hot(const void* x, const void* up, const float* 
                             status, stream, hot_ids, hot_dots);
 }
 
+// Column slab of the combine by row length.  Four rows of a 1024-column slab in flight per warp at 127 registers keeps
+// 16 warps on an SM; wider slabs or more rows per step leave fewer warps and were slower at every measured shape.
+static int launch_combine(const __nv_bfloat16* db, const float* coef, const int32_t* experts, const int32_t* offsets,
+                          int64_t num_tokens, int k, int hidden, int64_t num_experts, const void* residual, void* y,
+                          int out_dtype, int32_t* status, cudaStream_t st) {
+  const int hv = hidden <= 256 ? 1 : hidden <= 512 ? 2 : 4;
+  const int slabs = ceil_div(hidden, hv * 256);
+  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens * slabs, kCombineThreads / 32));
+#define OMNI_COMB(HV)                                                                                                  \
+  do {                                                                                                                 \
+    if (out_dtype == OMNI_F32)                                                                                         \
+      expert_combine_kernel<HV, true><<<grid, kCombineThreads, 0, st>>>(db, coef, experts, offsets, num_tokens, k, hidden, \
+                                                                        num_experts, slabs, residual, y, status);      \
+    else                                                                                                               \
+      expert_combine_kernel<HV, false><<<grid, kCombineThreads, 0, st>>>(db, coef, experts, offsets, num_tokens, k, hidden, \
+                                                                         num_experts, slabs, residual, y, status);     \
+  } while (0)
+  if (hv == 1) OMNI_COMB(1);
+  else if (hv == 2) OMNI_COMB(2);
+  else OMNI_COMB(4);
+#undef OMNI_COMB
+  return check_launch("expert_combine_kernel");
+}
+
 extern "C" int omni_expert_combine(const void* down, const float* coef, const int32_t* indices, int64_t num_tokens,
                                    int k, int hidden, int64_t num_experts, const void* residual, void* y,
                                    int out_dtype, int32_t* status, void* stream) {
@@ -1055,24 +988,7 @@ extern "C" int omni_expert_combine(const void* down, const float* coef, const in
   OMNI_REQUIRE(aligned16(down) && aligned16(y) && aligned16(residual), "down, y and residual must be 16-byte aligned");
   const auto* db = static_cast<const __nv_bfloat16*>(down);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int hv = hidden <= 256 ? 1 : hidden <= 512 ? 2 : hidden <= 1024 ? 4 : 8;
-  const int slabs = ceil_div(hidden, hv * 256);
-  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens * slabs, kWarps));
-#define OMNI_COMB(HV)                                                                                              \
-  do {                                                                                                             \
-    if (out_dtype == OMNI_F32)                                                                                     \
-      expert_combine_kernel<HV, true><<<grid, kThreads, 0, st>>>(db, coef, indices, num_tokens, k, hidden, num_experts, \
-                                                                 slabs, residual, y, status);                        \
-    else                                                                                                           \
-      expert_combine_kernel<HV, false><<<grid, kThreads, 0, st>>>(db, coef, indices, num_tokens, k, hidden, num_experts, \
-                                                                  slabs, residual, y, status);                       \
-  } while (0)
-  if (hv == 1) OMNI_COMB(1);
-  else if (hv == 2) OMNI_COMB(2);
-  else if (hv == 4) OMNI_COMB(4);
-  else OMNI_COMB(8);
-#undef OMNI_COMB
-  return check_launch("expert_combine_kernel");
+  return launch_combine(db, coef, indices, nullptr, num_tokens, k, hidden, num_experts, residual, y, out_dtype, status, st);
 }
 
 extern "C" int omni_expert_fused(const void* x, const void* up, const void* down, const float* weights,
@@ -1250,26 +1166,8 @@ extern "C" int omni_expert_combine_segments(const void* down, const float* coef,
   OMNI_REQUIRE(aligned16(down) && aligned16(y) && aligned16(residual), "down, y and residual must be 16-byte aligned");
   const auto* db = static_cast<const __nv_bfloat16*>(down);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int hv = hidden <= 256 ? 1 : hidden <= 512 ? 2 : hidden <= 1024 ? 4 : 8;
-  const int slabs = ceil_div(hidden, hv * 256);
-  const unsigned grid = static_cast<unsigned>(ceil_div64(num_tokens * slabs, kWarps));
-#define OMNI_COMBS(HV)                                                                                                \
-  do {                                                                                                                \
-    if (out_dtype == OMNI_F32)                                                                                        \
-      expert_combine_segments_kernel<HV, true><<<grid, kThreads, 0, st>>>(db, coef, pair_experts, token_offsets,      \
-                                                                          num_tokens, hidden, num_experts, slabs,     \
-                                                                          residual, y, status);                       \
-    else                                                                                                              \
-      expert_combine_segments_kernel<HV, false><<<grid, kThreads, 0, st>>>(db, coef, pair_experts, token_offsets,     \
-                                                                           num_tokens, hidden, num_experts, slabs,    \
-                                                                           residual, y, status);                      \
-  } while (0)
-  if (hv == 1) OMNI_COMBS(1);
-  else if (hv == 2) OMNI_COMBS(2);
-  else if (hv == 4) OMNI_COMBS(4);
-  else OMNI_COMBS(8);
-#undef OMNI_COMBS
-  return check_launch("expert_combine_segments_kernel");
+  return launch_combine(db, coef, pair_experts, token_offsets, num_tokens, 0, hidden, num_experts, residual, y, out_dtype,
+                        status, st);
 }
 
 extern "C" int omni_expert_fused_f32(const float* x, const float* up, const float* down, const float* weights,
