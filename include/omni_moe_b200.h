@@ -192,6 +192,28 @@ OMNI_API int omni_expert_combine(const void *down, const float *coef, const int3
                         int32_t *status, void *stream);
 
 /*
+ * Dispatch planning for expert tables that are row-partitioned over `world` GPUs (rank r owns rows
+ * [r * rows_per_rank, (r + 1) * rows_per_rank)); the reference has no multi-GPU path, the tables being cut are
+ * up_embed / down_embed (omni_moe/modules/omni_moe.py:57-58).  A rank's tokens are cut into `chunks` equal ranges
+ * that are exchanged one after another.
+ *
+ * omni_partition_keys: keys[p] = chunk(p) * world + owner(indices[p]) for every pair p of the [T, k] routing table
+ *   and counts[key] = number of pairs with that key (cleared by the call): the split sizes of the exchange.
+ * omni_partition_records: records[i] = (token id of pair order[i] among its chunk's all-gathered rows
+ *   = token_base + token's offset inside its chunk, expert row inside the owner's slice, bits of the weight),
+ *   12 bytes each, for order = the stable sort of the pairs by key (omni_schedule over keys, num_experts =
+ *   chunks * world).
+ * An expert id outside the table is sent to the first or last rank with a row outside its slice; the expert kernels
+ * there report OMNI_ST_BAD_EXPERT_INDEX and skip the pair.
+ * Limits: num_tokens % chunks == 0, chunks * world <= 2048, num_tokens * k < 2^31.
+ */
+OMNI_API int omni_partition_keys(const int32_t *indices, int64_t num_tokens, int k, int64_t rows_per_rank,
+                        int world, int chunks, int32_t *keys, int32_t *counts, void *stream);
+OMNI_API int omni_partition_records(const int32_t *indices, const float *weights, const int32_t *order,
+                           int64_t num_tokens, int k, int64_t rows_per_rank, int world, int chunks,
+                           int64_t token_base, int32_t *records, void *stream);
+
+/*
  * The two routed-expert kernels for a GPU that holds only a slice of the expert tables (rows
  * [lo, hi) of Up / Down) and works on a list of (token, local expert, weight) pairs that other GPUs
  * dispatched to it, rather than on a [T, k] routing table.  The reference has no multi-GPU path;

@@ -11,7 +11,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libomni_moe_b200.so")
-SOURCES = ["capi.cu", "router_topk.cu", "schedule.cu", "expert.cu", "gemm_tcgen05.cu", "backward.cu", "elementwise.cu", "selftest.cu"]
+SOURCES = ["capi.cu", "router_topk.cu", "schedule.cu", "expert.cu", "gemm_tcgen05.cu", "backward.cu", "elementwise.cu", "selftest.cu", "partition.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

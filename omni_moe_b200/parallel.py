@@ -162,6 +162,45 @@ class ExchangePlan:
     recv_counts: list       # per chunk: list of `world` ints
 
 
+def _sorted_records(indices: torch.Tensor, weights: torch.Tensor, part: ExpertPartition, chunks: int):
+    """This rank's pairs as 12-byte records (token id among the chunk's all-gathered rows, expert row inside the
+    owner's slice, weight bits), grouped by key = chunk * world + owner in ascending pair order, and the number of
+    pairs per key as a ``[chunks, world]`` int64 tensor.  On CUDA: two kernels of the library around its radix
+    pass; elsewhere the same in torch operators."""
+    world, rank = part.world, part.rank
+    t_local, k = indices.shape
+    tc = t_local // chunks
+    if indices.is_cuda and k > 0:
+        from .ops.scheduler import schedule
+        dev = indices.device
+        idx = indices.to(torch.int32).contiguous()
+        w = weights.float().contiguous()
+        keys = torch.empty(t_local * k, device=dev, dtype=torch.int32)
+        counts = torch.empty(chunks * world, device=dev, dtype=torch.int32)
+        records = torch.empty((t_local * k, 3), device=dev, dtype=torch.int32)
+        lib = _lib.load()
+        with torch.cuda.device(dev):
+            st = _lib.stream_ptr()
+            _lib.check(lib.omni_partition_keys(idx.data_ptr(), t_local, k, part.rows_per_rank, world, chunks,
+                                               keys.data_ptr(), counts.data_ptr(), st))
+            order = schedule(keys.view(-1, 1), chunks * world, segments=False).sorted_pair_ids
+            _lib.check(lib.omni_partition_records(idx.data_ptr(), w.data_ptr(), order.data_ptr(), t_local, k,
+                                                  part.rows_per_rank, world, chunks, rank * tc, records.data_ptr(), st))
+        return records, counts.view(chunks, world).long()
+    flat_e = indices.reshape(-1).to(torch.int32)
+    owner = part.owner(flat_e).to(torch.int32)
+    pair = torch.arange(flat_e.numel(), device=flat_e.device, dtype=torch.int32)
+    token = torch.div(pair, max(k, 1), rounding_mode="floor")
+    chunk_of = torch.div(token, max(tc, 1), rounding_mode="floor") if chunks > 1 else torch.zeros_like(token)
+    key = chunk_of * world + owner
+    order = _stable_order_by_key(key, chunks * world)
+    counts = torch.bincount(key.long(), minlength=chunks * world).view(chunks, world)
+    tok_rec = (token[order] - chunk_of[order] * tc + rank * tc).to(torch.int32)
+    local_e = flat_e[order] - owner[order] * part.rows_per_rank
+    w_bits = weights.reshape(-1).float()[order].view(torch.int32)
+    return torch.stack([tok_rec, local_e, w_bits], dim=1).contiguous(), counts
+
+
 def plan_exchange(indices: torch.Tensor, weights: torch.Tensor, part: ExpertPartition, group=None,
                   chunks: int = 1, comm_stream=None) -> ExchangePlan:
     """Sorts this rank's pairs by (chunk, owning rank) and exchanges the counts.
@@ -175,14 +214,7 @@ def plan_exchange(indices: torch.Tensor, weights: torch.Tensor, part: ExpertPart
     if chunks < 1 or t_local % chunks:
         chunks = 1
     tc = t_local // chunks
-    flat_e = indices.reshape(-1).to(torch.int32)
-    owner = part.owner(flat_e).to(torch.int32)
-    pair = torch.arange(flat_e.numel(), device=flat_e.device, dtype=torch.int32)
-    token = torch.div(pair, max(k, 1), rounding_mode="floor")
-    chunk_of = torch.div(token, max(tc, 1), rounding_mode="floor") if chunks > 1 else torch.zeros_like(token)
-    key = chunk_of * world + owner
-    order = _stable_order_by_key(key, chunks * world)
-    counts = torch.bincount(key.long(), minlength=chunks * world).view(chunks, world)
+    records, counts = _sorted_records(indices, weights, part, chunks)
     shape_cols = [torch.full((world, 1), v, dtype=counts.dtype, device=counts.device) for v in (t_local, k, chunks)]
     hello = torch.cat([counts.t()] + shape_cols, dim=1).contiguous()
     got = torch.empty_like(hello)
@@ -209,11 +241,6 @@ def plan_exchange(indices: torch.Tensor, weights: torch.Tensor, part: ExpertPart
         for cnt in row[:chunks]:
             if cnt < 0 or cnt > tc * k:
                 raise ExchangeError("count exchange", f"rank {peer} announces {cnt} pairs, more than its {tc * k} per chunk")
-    # 12-byte records: token id among the chunk's all-gathered rows, expert row inside the owner's slice, weight bits
-    tok_rec = (token[order] - chunk_of[order] * tc + rank * tc).to(torch.int32)
-    local_e = flat_e[order] - owner[order] * part.rows_per_rank
-    w_bits = weights.reshape(-1).float()[order].view(torch.int32)
-    records = torch.stack([tok_rec, local_e, w_bits], dim=1).contiguous()
     starts = [0]
     for c in range(chunks):
         starts.append(starts[-1] + sum(send_host[c]))

@@ -167,3 +167,44 @@ def test_one_process_two_devices():
         m.check_status()
         outs.append(y.cpu())
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("t,k,n,world,chunks,rank", [(64, 8, 1000, 4, 2, 1), (4096, 64, 1 << 20, 8, 2, 5), (30, 3, 7, 3, 1, 2),
+                                                      (96, 16, 4096, 2, 4, 0), (2048, 32, 262144, 4, 2, 3)])
+def test_dispatch_records_from_the_planning_kernels_equal_the_torch_operators(t, k, n, world, chunks, rank):
+    """omni_partition_keys -> radix pass -> omni_partition_records against the same plan written in torch operators
+    (the path the gloo ranks of the CPU tests take): records and split sizes bit for bit."""
+    from omni_moe_b200.parallel import ExpertPartition, _sorted_records
+    part = ExpertPartition(n, world, rank)
+    g = gen(t * k + world)
+    idx = torch.randint(0, n, (t, k), generator=g, dtype=torch.int32)
+    w = torch.rand(t, k, generator=g)
+    rec_cpu, cnt_cpu = _sorted_records(idx, w, part, chunks)
+    rec_gpu, cnt_gpu = _sorted_records(idx.cuda(), w.cuda(), part, chunks)
+    torch.cuda.synchronize()
+    assert torch.equal(cnt_gpu.cpu(), cnt_cpu), (cnt_gpu, cnt_cpu)
+    assert torch.equal(rec_gpu.cpu(), rec_cpu)
+    assert int(cnt_cpu.sum()) == t * k
+
+
+def test_dispatch_records_send_an_expert_outside_the_table_to_an_end_rank():
+    """An id below 0 goes to rank 0, one past the table to the last rank, both with a row outside the slice (the expert
+    kernels of that rank report and skip it); every other record is unchanged."""
+    from omni_moe_b200.parallel import ExpertPartition, _sorted_records
+    t, k, n, world = 32, 4, 100, 4
+    part = ExpertPartition(n, world, 0)
+    idx = torch.randint(0, n, (t, k), generator=gen(3), dtype=torch.int32)
+    w = torch.rand(t, k, generator=gen(4))
+    good, cnt_good = _sorted_records(idx.cuda(), w.cuda(), part, 1)
+    bad = idx.clone()
+    bad[3, 1], bad[7, 2] = -5, n + 50
+    rec, cnt = _sorted_records(bad.cuda(), w.cuda(), part, 1)
+    torch.cuda.synchronize()
+    assert int(cnt.sum()) == t * k
+    rows = part.rows_per_rank
+    rec = rec.cpu()
+    starts = torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long), cnt.cpu().view(-1)]), 0)
+    owner_of_record = torch.bucketize(torch.arange(t * k), starts[1:], right=True)
+    outside = (rec[:, 1] < 0) | (rec[:, 1] >= rows)
+    assert int(outside.sum()) == 2
+    assert sorted(owner_of_record[outside].tolist()) == [0, world - 1]
