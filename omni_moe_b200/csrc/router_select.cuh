@@ -200,7 +200,11 @@ __device__ __forceinline__ void warp_select_sorted(const uint32_t (&key)[E], con
       int c = 0;
 #pragma unroll
       for (int e = 0; e < E; ++e) c += key[e] >= trial;
-      if (__reduce_add_sync(FULL_MASK, c) >= K) tau = trial;
+      c = __reduce_add_sync(FULL_MASK, c);
+      if (c >= K) tau = trial;
+      // exactly K keys reach the prefix found so far: they are the K winners whatever the lower bits of the K-th
+      // key are (tau is then a lower bound of it, not the key itself; the admission below only asks key >= tau)
+      if (c == K) break;
     }
   }
   int c_gt = 0, c_eq = 0;
