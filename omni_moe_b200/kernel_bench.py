@@ -273,6 +273,10 @@ def run_config(name: str, reps: int):
                                                     sorted_e.data_ptr(), None, None, None, None, meta.data_ptr(),
                                                     ws.data_ptr(), ws.numel(), s)), reps=reps)
     report("schedule_permutation", us, "hbm", 20.0 * P + 8.0 * N, "bytes per the full description (20 P + 8 N)")
+    # same-box bar: the library sort the reference's scheduler calls (torch.sort, stable, on the flat expert ids)
+    flat_ids = indices.view(-1)
+    us_t = time_graph(lambda s: torch.sort(flat_ids, stable=True), launches=1, reps=reps) if P else 0.0
+    report("schedule_bar_torch_stable_sort", us_t, "hbm", 20.0 * P + 8.0 * N, "torch.sort(stable=True) of the same keys, for comparison")
     # ---- routed experts (hbm): algorithmic bytes = x in, y out, each touched Up/Down row once, schedule arrays
     up = _randn_bf16((N, H), 0.02, dev, 3)
     down = _randn_bf16((N, H), 0.02, dev, 4)
