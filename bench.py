@@ -383,12 +383,16 @@ def _c5_parity(inner, tables, part, x_local, y_local, indices, rank, world, dist
             need = torch.empty(int(count.item()), dtype=torch.long, device=dev)
         dist.broadcast(need, 0)
     up_l, down_l = tables
+    by_columns = part is not None and hasattr(part, "width")
     lo, hi = (part.lo, part.hi) if part is not None else (0, inner.num_experts)
     mine = (need >= lo) & (need < hi)
     rows = []
     for tab in (up_l, down_l):
         r = torch.zeros((need.numel(), h), device=dev, dtype=torch.float32)
-        r[mine] = tab[need[mine] - lo].float()
+        if by_columns:
+            r[:, lo:hi] = tab[need].float()        # every rank holds its columns of every row
+        else:
+            r[mine] = tab[need[mine] - lo].float()
         if dist_on:
             dist.reduce(r, 0, op=dist.ReduceOp.SUM)
         rows.append(r)
@@ -457,6 +461,40 @@ def run_c5(world, rank, dev, dist_on, steps=5, warmup=2):
            "mode": f"expert tables row-partitioned over {world} GPUs, NCCL dispatch / combine" if dist_on else "whole layer on one GPU",
            "scaling": "strong", "ms_per_step": ms, "tokens_s": cfg["T"] / (ms * 1e-3), "steps": steps, "warmup": warmup,
            "tables_gib_per_gpu": 2 * tables[0].numel() * 2 / 2 ** 30, "phases_ms": phases, "parity": parity}
+    if dist_on and cfg["H"] % world == 0:
+        # the same tables cut by columns instead of rows (same memory per GPU): partial dot products all-reduced, state
+        # columns returned by an all-to-all, no host synchronisation in the step
+        from omni_moe_b200.parallel import ColumnPartitionedOmniMoE, columns_from_row_slices
+        up_cols = columns_from_row_slices(tables[0])
+        down_cols = columns_from_row_slices(tables[1])
+        del layer, tables
+        torch.cuda.empty_cache()
+        col = ColumnPartitionedOmniMoE(inner, None, table_slices=(up_cols, down_cols))
+        with torch.no_grad():
+            for _ in range(warmup):
+                y = col(x)
+            inner.check_status()
+            barrier(dist_on)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                y = col(x)
+            e1.record()
+            barrier(dist_on)
+            ms_c = max_over_ranks(e0.elapsed_time(e1) / steps, dist_on, dev)
+            col.record_phases = True
+            y = col(x)
+            phases_c = col.phases_ms()
+            col.record_phases = False
+            inner.check_status()
+            parity_c = _c5_parity(inner, (col.up_cols.data, col.down_cols.data), col.part, x.view(t_local, cfg["H"]), y,
+                                  inner.last_routing[1], rank, world, dist_on, dev)
+        out["column_partitioned"] = {
+            "mode": f"the same tables cut by columns over {world} GPUs: all-to-all of token / state columns, all-reduce of the dot products",
+            "ms_per_step": ms_c, "tokens_s": cfg["T"] / (ms_c * 1e-3), "tables_gib_per_gpu": 2 * up_cols.numel() * 2 / 2 ** 30,
+            "phases_ms": phases_c, "parity": parity_c}
+        del col, up_cols, down_cols
+        layer = tables = None
     del layer, inner, tables, x, y
     torch.cuda.empty_cache()
     return out

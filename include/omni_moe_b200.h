@@ -192,6 +192,18 @@ OMNI_API int omni_expert_combine(const void *down, const float *coef, const int3
                         int32_t *status, void *stream);
 
 /*
+ * The raw dot products of omni_expert_coef, dots[t, j] = x[t] . Up[e[t, j]] (no activation, no routing weight), for
+ * a GPU that holds a COLUMN slice of the expert tables (x [T, Hs] and up [N, Hs] are then the same Hs columns of the
+ * token rows and of the Up table): the partial products of all slices are added (an all-reduce of [T, k] floats)
+ * before w * silu(.) is applied, and omni_expert_combine over the matching Down columns gives the same columns of y.
+ * The reference has no multi-GPU path (the tables being cut are omni_moe/modules/omni_moe.py:57-58).
+ * Arguments and limits as omni_expert_coef (hidden = Hs).
+ */
+OMNI_API int omni_expert_dots(const void *x, const void *up, const int32_t *sorted_pair_ids,
+                     const int32_t *sorted_experts, int64_t num_tokens, int k, int hidden,
+                     int64_t num_experts, float *dots, int32_t *status, void *stream);
+
+/*
  * Dispatch planning for expert tables that are row-partitioned over `world` GPUs (rank r owns rows
  * [r * rows_per_rank, (r + 1) * rows_per_rank)); the reference has no multi-GPU path, the tables being cut are
  * up_embed / down_embed (omni_moe/modules/omni_moe.py:57-58).  A rank's tokens are cut into `chunks` equal ranges

@@ -41,6 +41,8 @@ SIGNATURES = {
                                      c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "omni_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p, c_void_p,
                                     c_int, c_void_p, c_void_p]),
+    "omni_expert_dots": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p, c_void_p,
+                                 c_void_p]),
     "omni_partition_keys": (c_int, [c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "omni_partition_records": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int, c_int64,
                                        c_void_p, c_void_p]),

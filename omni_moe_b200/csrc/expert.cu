@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     const int* __restrict__ perm, const int* __restrict__ sorted_experts, const int* __restrict__ pair_tokens,
     int64_t P, int64_t T, int k, int H, int64_t N, float* __restrict__ coef, int* status,
     const int* __restrict__ hot_ids, const float* __restrict__ hot_dots) {
+  // weights == nullptr: the raw dot products x . Up[e] are written instead of w * silu(x . Up[e]) (a GPU that holds a
+  // column slice of the tables: the partial products of all slices are added before the activation).
   // pair_tokens == nullptr: pairs come from a [T, k] routing table, pair p belongs to token p / k.
   // Otherwise pair p belongs to token pair_tokens[p] (pairs received from other GPUs).
   // hot_ids != nullptr: kHot ascending expert ids (padded with INT_MAX) followed by their count; the dot
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
     my_pair = perm[w0 + lane];
     my_e = sorted_experts[w0 + lane];
     if (my_pair >= 0 && my_pair < P) {
-      my_g = weights[my_pair];
+      my_g = weights ? weights[my_pair] : 1.f;
       my_t = pair_tokens ? pair_tokens[my_pair] : my_pair / k;
     }
   }
@@ -99,7 +101,10 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
         if (__ldg(hot_ids + lo + step - 1) < my_e) lo += step;
       if (__ldg(hot_ids + lo) == my_e) col = lo;
     }
-    if (col >= 0) coef[my_pair] = my_g * silu(__ldg(hot_dots + static_cast<int64_t>(my_t) * kHot + col));
+    if (col >= 0) {
+      const float d = __ldg(hot_dots + static_cast<int64_t>(my_t) * kHot + col);
+      coef[my_pair] = weights ? my_g * silu(d) : d;
+    }
     hot_mask = __ballot_sync(FULL_MASK, col >= 0);
     if (hot_mask == (count >= 32 ? FULL_MASK : ((1u << count) - 1u))) return;
   }
@@ -125,10 +130,8 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
         dst[v] = ldg128_hint(xr + (c < H ? c : 0), pol_keep);
       }
     };
-    uint4 xcur[HV], xnext[HV];
-    fetch_x(0, xcur);
-    for (int i = 0; i < count; ++i) {
-      fetch_x(i + 1, xnext);  // past the end of the run: lane i + 1 carries no token, row 0 is read (an L1 hit) and dropped
+    // one pair: the Up row of its expert (refetched only when the expert changes) against the token row xv
+    auto one_pair = [&](int i, const uint4 (&xv)[HV]) {
       const int pair = __shfl_sync(FULL_MASK, my_pair, i);
       const int e = __shfl_sync(FULL_MASK, my_e, i);
       const float g = __shfl_sync(FULL_MASK, my_g, i);
@@ -152,12 +155,20 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
         }
         float acc = 0.f;
 #pragma unroll
-        for (int v = 0; v < HV; ++v) acc = dot8(xcur[v], row[v], acc);
+        for (int v = 0; v < HV; ++v) acc = dot8(xv[v], row[v], acc);
         acc = warp_sum(acc);
-        if (lane == 0) coef[pair] = g * silu(acc);
+        if (lane == 0) coef[pair] = weights ? g * silu(acc) : acc;
       }
+    };
+    {
+      uint4 xcur[HV], xnext[HV];
+      fetch_x(0, xcur);
+      for (int i = 0; i < count; ++i) {
+        fetch_x(i + 1, xnext);  // past the end of the run: lane i + 1 carries no token, row 0 is read (an L1 hit) and dropped
+        one_pair(i, xcur);
 #pragma unroll
-      for (int v = 0; v < HV; ++v) xcur[v] = xnext[v];
+        for (int v = 0; v < HV; ++v) xcur[v] = xnext[v];
+      }
     }
   } else
   for (int i = 0; i < count; ++i) {
@@ -189,7 +200,7 @@ __global__ void __launch_bounds__(kThreads) expert_coef_kernel(
       for (int v = 0; v < HV; ++v) acc = dot8(xv[v], row[v], acc);
     }
     acc = warp_sum(acc);
-    if (lane == 0) coef[pair] = g * silu(acc);
+    if (lane == 0) coef[pair] = weights ? g * silu(acc) : acc;
   }
   if (bad_e && lane == 0) atomicOr(status, OMNI_ST_BAD_EXPERT_INDEX);
   if (bad_t && lane == 0) atomicOr(status, OMNI_ST_BAD_TOKEN_INDEX);
@@ -881,12 +892,12 @@ using namespace omni;
 static int launch_expert_coef(const void* x, const void* up, const float* weights, const int32_t* sorted_pair_ids,
                               const int32_t* sorted_experts, int64_t num_tokens, int k, int hidden,
                               int64_t num_experts, float* coef, int32_t* status, void* stream, const int* hot_ids,
-                              const float* hot_dots) {
+                              const float* hot_dots, bool raw = false) {
   OMNI_REQUIRE(num_tokens >= 0 && k >= 1 && hidden >= 8 && num_experts >= 1, "bad sizes");
   OMNI_REQUIRE(hidden % 8 == 0, "hidden must be a multiple of 8, got %d", hidden);
   const int64_t P = num_tokens * k;
   if (P == 0) return 0;
-  OMNI_REQUIRE(x && up && weights && sorted_pair_ids && sorted_experts && coef && status, "NULL argument");
+  OMNI_REQUIRE(x && up && (weights || raw) && sorted_pair_ids && sorted_experts && coef && status, "NULL argument");
   OMNI_REQUIRE(aligned16(x) && aligned16(up), "x and up must be 16-byte aligned");
   const auto* xb = static_cast<const __nv_bfloat16*>(x);
   const auto* ub = static_cast<const __nv_bfloat16*>(up);
@@ -902,6 +913,13 @@ static int launch_expert_coef(const void* x, const void* up, const float* weight
   else OMNI_COEF(16);
 #undef OMNI_COEF
   return check_launch("expert_coef_kernel");
+}
+
+extern "C" int omni_expert_dots(const void* x, const void* up, const int32_t* sorted_pair_ids, const int32_t* sorted_experts,
+                                int64_t num_tokens, int k, int hidden, int64_t num_experts, float* dots, int32_t* status,
+                                void* stream) {
+  return launch_expert_coef(x, up, nullptr, sorted_pair_ids, sorted_experts, num_tokens, k, hidden, num_experts, dots, status,
+                            stream, nullptr, nullptr, true);
 }
 
 extern "C" int omni_expert_coef(const void* x, const void* up, const float* weights, const int32_t* sorted_pair_ids,

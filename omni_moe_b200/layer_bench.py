@@ -10,7 +10,8 @@ Configurations: c2 (T 4096, H 1024, I 4096, 64x64 experts, k 16) and c5 (T 65536
 1024x1024 experts, k 64; 16 GiB of tables).  Synthetic data: x ~ N(0,1), all weights ~ N(0, 0.02) as the
 large-table configuration specifies, BatchNorm with default running statistics, eval mode.
 With --partitioned the T tokens are sharded evenly over the ranks (strong scaling: the job is the
-same T tokens at every N) and rank g holds rows [g N/G, (g+1) N/G) of the tables.
+same T tokens at every N) and rank g holds rows [g N/G, (g+1) N/G) of the tables (--columns: columns
+[g H/G, (g+1) H/G) of every row).
 Steps are timed with CUDA events between barriers; the maximum over ranks is reported by rank 0 as
 one JSON line.
 """
@@ -68,6 +69,7 @@ def main():
                     help="torch: the same layer written with PyTorch eager ops (gather / matmul experts, torch.topk "
                          "router) on the same GPU, as a same-box bar; c2 only (it materialises [T, k, H] gathers)")
     ap.add_argument("--chunks", type=int, default=2, help="token ranges pipelined through the exchange (--partitioned)")
+    ap.add_argument("--columns", action="store_true", help="with --partitioned: cut the tables by columns instead of rows")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -91,8 +93,14 @@ def main():
         part = ExpertPartition(cfg["N"], world, rank)
         inner = build_module(cfg, dev, table_rows=part.hi - part.lo, row_offset=part.lo)
         # the tables were built as slices in the first place: 16 GiB of rows never exist on one GPU
-        layer = PartitionedOmniMoE(inner, None, chunks=args.chunks,
-                                   table_slices=(inner.up_embed.weight.data, inner.down_embed.weight.data))
+        if args.columns:
+            from .parallel import ColumnPartitionedOmniMoE, columns_from_row_slices
+            up_cols = columns_from_row_slices(inner.up_embed.weight.data)
+            down_cols = columns_from_row_slices(inner.down_embed.weight.data)
+            layer = ColumnPartitionedOmniMoE(inner, None, table_slices=(up_cols, down_cols))
+        else:
+            layer = PartitionedOmniMoE(inner, None, chunks=args.chunks,
+                                       table_slices=(inner.up_embed.weight.data, inner.down_embed.weight.data))
         run = lambda: layer(x)
     elif args.impl == "torch":
         from .train_bench import torch_forward
@@ -126,15 +134,22 @@ def main():
         ms = float(t.item())
     inner.check_status()
     assert bool(torch.isfinite(y.float()).all())
+    phases = None
+    if args.partitioned:
+        with torch.no_grad():
+            layer.record_phases = True
+            run()
+            phases = layer.phases_ms()
+            layer.record_phases = False
     if rank == 0:
         tokens = cfg["T"] if args.partitioned else cfg["T"] * world
         print(json.dumps({
-            "config": args.config, "impl": args.impl, "mode": "tables row-partitioned" if args.partitioned else "replica",
+            "config": args.config, "impl": args.impl, "mode": ("tables column-partitioned" if args.columns else "tables row-partitioned") if args.partitioned else "replica",
             "n_gpus": world, "tokens_per_step": tokens, "ms_per_step": round(ms, 4),
             "tokens_per_s": round(tokens / (ms * 1e-3)), "steps": args.steps, "warmup": args.warmup,
             "scaling": "strong" if args.partitioned else "weak",
             "table_rows_per_gpu": (cfg["N"] + world - 1) // world if args.partitioned else cfg["N"],
-            "max_memory_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2)}), flush=True)
+            "max_memory_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2), "phases_ms": phases}), flush=True)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

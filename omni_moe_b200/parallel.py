@@ -588,3 +588,271 @@ class PartitionedOmniMoE(torch.nn.Module):
         m.last_routing = (scores, indices, weights)
         m.last_status = status
         return y.view(shape).to(hidden_states.dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Expert tables partitioned by COLUMNS
+# ---------------------------------------------------------------------------------------------------------------------
+# An expert of this layer is one Up row and one Down row, so the tables can just as well be cut along the hidden
+# dimension: rank g keeps columns [g * H / G, (g + 1) * H / G) of every row (the same memory per rank as a row
+# partition).  Then
+#   * x[t] . Up[e] is the sum of G partial dot products, one per rank: an all-reduce of [T_total, k] floats
+#     (4 bytes per pair instead of a hidden-sized partial state per token and rank);
+#   * sum_j c * Down[e] over a rank's columns gives those columns of the output for ALL tokens; an all-to-all returns
+#     them to the ranks that own the tokens (T_total * H / G values per rank, against T_total * H for a reduce-scatter
+#     of partial states), and the token rows reach the ranks the same way (instead of an all-gather);
+#   * every size is known in advance: no count exchange, no host synchronisation inside the step.
+# Every rank walks all pairs, but over H / G columns each, so the bytes it gathers are the same as with a row partition.
+
+
+@dataclass(frozen=True)
+class ColumnPartition:
+    """Contiguous column partition of ``[*, hidden]`` tables over ``world`` ranks (``hidden % world == 0``)."""
+    hidden: int
+    world: int
+    rank: int
+
+    @property
+    def width(self) -> int:
+        return self.hidden // self.world
+
+    @property
+    def lo(self) -> int:
+        return self.rank * self.width
+
+    @property
+    def hi(self) -> int:
+        return (self.rank + 1) * self.width
+
+    def slice_columns(self, table: torch.Tensor) -> torch.Tensor:
+        return table[:, self.lo:self.hi].contiguous()
+
+
+def exchange_token_columns(x: torch.Tensor, part: ColumnPartition, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``[T_local, H]`` per rank -> ``[world * T_local, H / world]``: this rank's columns of every rank's tokens,
+    ordered by source rank (= global token order when the tokens are sharded contiguously)."""
+    t, h = x.shape
+    send = x.view(t, part.world, part.width).transpose(0, 1).contiguous().view(part.world * t, part.width)
+    if out is None:
+        out = torch.empty_like(send)
+    _collective("token columns", dist.all_to_all_single, out, send, group=group)
+    return out
+
+
+def return_state_columns(y_cols: torch.Tensor, part: ColumnPartition, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Inverse of :func:`exchange_token_columns` for the results: ``[world * T_local, H / world]`` (this rank's
+    columns of all tokens) -> ``[world, T_local, H / world]`` (all column slices of this rank's tokens)."""
+    if out is None:
+        out = torch.empty_like(y_cols)
+    _collective("state columns", dist.all_to_all_single, out, y_cols.contiguous(), group=group)
+    return out.view(part.world, y_cols.size(0) // part.world, part.width)
+
+
+def gather_routing(indices: torch.Tensor, weights: torch.Tensor, group=None, out=None):
+    """The routing of all tokens on every rank: ``[T_local, k]`` -> ``[T_total, k]`` (expert ids int32, weights float32)."""
+    world = dist.get_world_size(group)
+    idx, w = indices.to(torch.int32).contiguous(), weights.float().contiguous()
+    idx_all, w_all = out if out is not None else (torch.empty((world * idx.size(0), idx.size(1)), device=idx.device, dtype=torch.int32),
+                                                  torch.empty((world * w.size(0), w.size(1)), device=w.device, dtype=torch.float32))
+    _collective("routing all-gather", dist.all_gather_into_tensor, idx_all, idx, group=group)
+    _collective("routing all-gather", dist.all_gather_into_tensor, w_all, w, group=group)
+    return idx_all, w_all
+
+
+def column_partial_dots(x_cols: torch.Tensor, idx_all: torch.Tensor, up_cols: torch.Tensor, status: torch.Tensor | None = None):
+    """This rank's part of ``x[t] . Up[e[t, j]]`` for all tokens, ``[T_total, k]`` float32 (CUDA kernels)."""
+    from .ops.scheduler import schedule
+    _lib.require_cuda(x_cols, idx_all, up_cols)
+    t, hs = x_cols.shape
+    k, n = idx_all.size(1), up_cols.size(0)
+    dots = torch.empty((t, k), device=x_cols.device, dtype=torch.float32)
+    if status is None:
+        status = _lib.device_status(x_cols.device)
+    with torch.cuda.device(x_cols.device):
+        sch = schedule(idx_all, n, segments=False)
+        _lib.check(_lib.load().omni_expert_dots(x_cols.data_ptr(), up_cols.data_ptr(), sch.sorted_pair_ids.data_ptr(),
+                                                sch.sorted_experts.data_ptr(), t, k, hs, n, dots.data_ptr(), status.data_ptr(),
+                                                _lib.stream_ptr()))
+    return dots
+
+
+def column_combine(coef: torch.Tensor, idx_all: torch.Tensor, down_cols: torch.Tensor, out_dtype=torch.bfloat16,
+                   status: torch.Tensor | None = None) -> torch.Tensor:
+    """This rank's columns of ``sum_j coef[t, j] * Down[e[t, j]]`` for all tokens (CUDA kernel)."""
+    _lib.require_cuda(coef, idx_all, down_cols)
+    t, k = idx_all.shape
+    n, hs = down_cols.shape
+    y = torch.empty((t, hs), device=coef.device, dtype=out_dtype)
+    if status is None:
+        status = _lib.device_status(coef.device)
+    with torch.cuda.device(coef.device):
+        _lib.check(_lib.load().omni_expert_combine(down_cols.data_ptr(), coef.data_ptr(), idx_all.data_ptr(), t, k, hs, n, None,
+                                                   y.data_ptr(), _lib.dtype_code(out_dtype), status.data_ptr(), _lib.stream_ptr()))
+    return y
+
+
+def column_expert_states(x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, up_cols: torch.Tensor,
+                         down_cols: torch.Tensor, part: ColumnPartition, group=None,
+                         dots_fn: Callable | None = None, combine_fn: Callable | None = None) -> torch.Tensor:
+    """Routed-expert states ``[T_local, H]`` of this rank's tokens with the tables partitioned by columns, one
+    collective after the other on the current stream (the plain form; :class:`ColumnPartitionedOmniMoE` overlaps
+    them with the kernels).  ``dots_fn(x_cols, idx_all, up_cols)`` and ``combine_fn(coef, idx_all, down_cols)``
+    replace the CUDA kernels (the CPU tests pass the oracle's arithmetic)."""
+    dots_fn = dots_fn or column_partial_dots
+    combine_fn = combine_fn or column_combine
+    x_cols = exchange_token_columns(x, part, group)
+    idx_all, w_all = gather_routing(indices, weights, group)
+    dots = dots_fn(x_cols, idx_all, up_cols).float().contiguous()
+    _collective("dot products", dist.all_reduce, dots, op=dist.ReduceOp.SUM, group=group)
+    coef = torch.nn.functional.silu(dots) * w_all
+    y_cols = combine_fn(coef, idx_all, down_cols)
+    mine = return_state_columns(y_cols, part, group)
+    return mine.transpose(0, 1).reshape(x.size(0), part.hidden)
+
+
+class ColumnPartitionedOmniMoE(torch.nn.Module):
+    """``OmniMoE`` with the expert tables partitioned by columns over the ranks of a process group.
+
+    Build it from a full module on every rank, or pass ``table_slices = (up_cols, down_cols)``, each ``[N, H / world]``,
+    when the tables are too large to exist whole.  Router and shared MLP are kept whole; the wrapped module is left
+    without tables and refuses to run on its own.  ``forward(hidden_states)`` takes this rank's tokens ``[B, S, H]``
+    (the same count on every rank, sharded contiguously in rank order) and returns their outputs.  Eval mode, bf16.
+
+    Compute stream: router, schedule of all pairs, partial dot products, their all-reduce, activation, combine over the
+    rank's columns, gate/up GEMM, down projection with the returned states added in its epilogue.  Communication
+    stream: the token columns (from the start, beside the router), the routing all-gather, the return of the state
+    columns (beside the gate/up GEMM).  Nothing on the host depends on device data: the whole step is enqueued ahead."""
+
+    def __init__(self, module, group=None, table_slices=None):
+        super().__init__()
+        from .modules.omni_moe import OmniMoE
+        assert isinstance(module, OmniMoE)
+        self.group = group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if module.hidden_size % world or (module.hidden_size // world) % 8:
+            raise ValueError(f"hidden size {module.hidden_size} cannot be cut into {world} column slices of a multiple of 8")
+        self.part = ColumnPartition(module.hidden_size, world, rank)
+        self.inner = module
+        if table_slices is None:
+            with torch.no_grad():
+                up = self.part.slice_columns(module.up_embed.weight.detach())
+                down = self.part.slice_columns(module.down_embed.weight.detach())
+        else:
+            up, down = table_slices
+        assert up.shape == down.shape == (module.num_experts, self.part.width)
+        self.up_cols = torch.nn.Parameter(up.to(torch.bfloat16).contiguous(), requires_grad=False)
+        self.down_cols = torch.nn.Parameter(down.to(torch.bfloat16).contiguous(), requires_grad=False)
+        empty = lambda: torch.nn.Parameter(torch.empty(0, module.hidden_size, dtype=up.dtype, device=up.device), requires_grad=False)
+        module.up_embed.weight, module.down_embed.weight = empty(), empty()
+        module._tables_partitioned = True
+        self.record_phases = False
+        self._clock = None
+        self._comm = None
+
+    def phases_ms(self) -> dict:
+        """Device time of the phases of the latest forward (``record_phases`` must be on): route, exchange (token
+        columns, routing, state columns; on the communication stream), local (schedule, dot products, combine),
+        reduce (the all-reduce of the dot products), mlp."""
+        if self._clock is None:
+            return {}
+        torch.cuda.synchronize()
+        return {k: round(v, 4) for k, v in self._clock.totals().items()}
+
+    @torch.no_grad()
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        from .ops.router import router_gate_topk
+        m, part = self.inner, self.part
+        if m.training:
+            raise RuntimeError("ColumnPartitionedOmniMoE runs in eval mode (batch statistics would need a cross-rank reduction)")
+        _lib.require_cuda(hidden_states)
+        shape = hidden_states.shape
+        x = hidden_states.detach().reshape(-1, m.hidden_size).to(torch.bfloat16).contiguous()
+        t, h, i, k = x.size(0), m.hidden_size, m.intermediate_size, m.top_k
+        world, hs = part.world, part.width
+        dev = x.device
+        wg, wu, wd, kx, ky = (m._bf16_weight(q.weight) for q in (m.gate_proj, m.up_proj, m.down_proj, m.router_gate_x, m.router_gate_y))
+        scale, shift = m._bn_fold_eval()
+        status = torch.zeros(1, device=dev, dtype=torch.int32)
+        lib = _lib.load()
+        clock = self._clock = _PhaseClock(self.record_phases)
+        with torch.cuda.device(dev):
+            if self._comm is None:
+                self._comm = torch.cuda.Stream(device=dev)
+            comm, main = self._comm, torch.cuda.current_stream()
+            # every buffer that the communication stream writes is allocated here, before the events it waits for
+            act = torch.empty((t, i), device=dev, dtype=torch.bfloat16)
+            y = torch.empty((t, h), device=dev, dtype=torch.bfloat16)
+            x_cols = torch.empty((world * t, hs), device=dev, dtype=torch.bfloat16)
+            idx_all = torch.empty((world * t, k), device=dev, dtype=torch.int32)
+            w_all = torch.empty((world * t, k), device=dev, dtype=torch.float32)
+            y_back = torch.empty((world * t, hs), device=dev, dtype=torch.bfloat16)
+            x_ready = torch.cuda.Event()
+            x_ready.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(x_ready)
+                tk = clock.start("exchange")
+                exchange_token_columns(x, part, self.group, out=x_cols)
+                clock.stop(tk)
+                ev_x = torch.cuda.Event()
+                ev_x.record(comm)
+            tk = clock.start("route")
+            scores, indices, weights = router_gate_topk(x, kx, ky, k, scale, shift, status=status)
+            clock.stop(tk)
+            ev_route = torch.cuda.Event()
+            ev_route.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev_route)
+                tk = clock.start("exchange")
+                gather_routing(indices, weights, self.group, out=(idx_all, w_all))
+                clock.stop(tk)
+                ev_r = torch.cuda.Event()
+                ev_r.record(comm)
+            main.wait_event(ev_r)
+            main.wait_event(ev_x)
+            tk = clock.start("local")
+            dots = column_partial_dots(x_cols, idx_all, self.up_cols, status)
+            clock.stop(tk)
+            tk = clock.start("reduce")
+            _collective("dot products", dist.all_reduce, dots, op=dist.ReduceOp.SUM, group=self.group)
+            clock.stop(tk)
+            tk = clock.start("local")
+            coef = torch.nn.functional.silu(dots).mul_(w_all)
+            y_cols = column_combine(coef, idx_all, self.down_cols, torch.bfloat16, status)
+            clock.stop(tk)
+            ev_comb = torch.cuda.Event()
+            ev_comb.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev_comb)
+                tk = clock.start("exchange")
+                mine = return_state_columns(y_cols, part, self.group, out=y_back)
+                clock.stop(tk)
+                ev_y = torch.cuda.Event()
+                ev_y.record(comm)
+            tk = clock.start("mlp")
+            _lib.check(lib.omni_mlp_gate_up(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), t, h, i, act.data_ptr(),
+                                            status.data_ptr(), main.cuda_stream))
+            clock.stop(tk)
+            main.wait_event(ev_y)
+            states = mine.transpose(0, 1).reshape(t, h).float()
+            tk = clock.start("mlp")
+            _lib.check(lib.omni_mlp_down(act.data_ptr(), wd.data_ptr(), t, h, i, states.data_ptr(), y.data_ptr(),
+                                         status.data_ptr(), main.cuda_stream))
+            clock.stop(tk)
+            for tns in (x, x_cols, indices, weights, idx_all, w_all, y_cols, y_back):
+                tns.record_stream(comm)
+        m.last_routing = (scores, indices, weights)
+        m.last_status = status
+        return y.view(shape).to(hidden_states.dtype)
+
+
+def columns_from_row_slices(rows_local: torch.Tensor, group=None) -> torch.Tensor:
+    """Re-partitions a table from rows to columns without ever holding it whole: every rank passes its contiguous
+    block of rows ``[N / world, H]`` (equal blocks, in rank order) and gets its column slice ``[N, H / world]``."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    r, h = rows_local.shape
+    assert h % world == 0, "the hidden size must be a multiple of the world size"
+    hs = h // world
+    send = rows_local.view(r, world, hs).transpose(0, 1).contiguous().view(world * r, hs)
+    out = torch.empty_like(send)
+    _collective("table columns", dist.all_to_all_single, out, send, group=group)
+    return out

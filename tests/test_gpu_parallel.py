@@ -208,3 +208,50 @@ def test_dispatch_records_send_an_expert_outside_the_table_to_an_end_rank():
     outside = (rec[:, 1] < 0) | (rec[:, 1] >= rows)
     assert int(outside.sum()) == 2
     assert sorted(owner_of_record[outside].tolist()) == [0, world - 1]
+
+
+@pytest.mark.parametrize("t,h,n,k,world", [(200, 256, 1000, 8, 4), (64, 4096, 300, 16, 2), (512, 1024, 4096, 32, 8),
+                                            (33, 96, 7, 4, 3)])
+def test_column_slices_sum_to_the_full_answer(t, h, n, k, world):
+    """Tables cut by columns, all ranks' shares computed in turn on one GPU: the partial dot products of the slices
+    (omni_expert_dots) add up to the full dot products, and the combine over a slice gives that slice of the output."""
+    from omni_moe_b200.parallel import ColumnPartition, column_combine, column_partial_dots
+    g = gen(t + n)
+    x = (torch.randn(t, h, generator=g) * 0.5).bfloat16()
+    up = (torch.randn(n, h, generator=g) * 0.1).bfloat16()
+    dn = (torch.randn(n, h, generator=g) * 0.1).bfloat16()
+    w = torch.rand(t, k, generator=g)
+    idx = torch.randint(0, n, (t, k), generator=g, dtype=torch.int32)
+    idx[:, 0] = idx[:, 1]
+    parts = [ColumnPartition(h, world, r) for r in range(world)]
+    xc, idxc, wc = x.cuda(), idx.cuda(), w.cuda()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dots = sum(column_partial_dots(p.slice_columns(xc), idxc, p.slice_columns(up.cuda()), st) for p in parts)
+    e_dots = (x.float()[:, None, :] * up.float()[idx.long()]).sum(-1)
+    assert_close(dots, e_dots, rtol=1e-4, atol=1e-4, what="summed partial dot products")
+    coef = torch.nn.functional.silu(dots) * wc
+    y = torch.cat([column_combine(coef, idxc, p.slice_columns(dn.cuda()), torch.float32, st) for p in parts], dim=1)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert_close(y, orc.expert_forward(x.float(), up.float(), dn.float(), w, idx), rtol=1e-3, atol=1e-4, what="column slices")
+
+
+_CHILD_COLUMNS = _CHILD.replace("import PartitionedOmniMoE, shard_tokens", "import ColumnPartitionedOmniMoE as PartitionedOmniMoE, shard_tokens") \
+                       .replace("assert m.up_local.shape[0] == 1024 // world and m.inner.up_embed.weight.shape[0] == 0",
+                                "assert m.up_cols.shape == (1024, 256 // world) and m.inner.up_embed.weight.shape[0] == 0")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_column_partitioned_layer_two_gpus_nccl(tmp_path):
+    assert "ColumnPartitionedOmniMoE" in _CHILD_COLUMNS and "up_cols" in _CHILD_COLUMNS
+    script = tmp_path / "child_columns.py"
+    script.write_text(_CHILD_COLUMNS)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, OMNI_ROOT=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout

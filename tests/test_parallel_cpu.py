@@ -222,3 +222,58 @@ def test_exchange_failures_surface_on_the_host(scenario):
     else:
         assert ret[1] == "left"
         assert "|" in ret[0] and ret[0].split("|")[0] in ("count exchange", "pair dispatch"), ret[0]
+
+
+# ---- tables partitioned by columns -------------------------------------------------------------------------------
+def _oracle_dots(x_cols, idx_all, up_cols):
+    return (x_cols.float()[:, None, :] * up_cols.float()[idx_all.long()]).sum(-1)
+
+
+def _oracle_combine(coef, idx_all, down_cols):
+    return (coef[:, :, None] * down_cols.float()[idx_all.long()]).sum(1)
+
+
+def _column_worker(rank, world, port, t_local, h, n, k, seed, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from omni_moe_b200.parallel import (ColumnPartition, column_expert_states, exchange_token_columns,
+                                            return_state_columns)
+        g = torch.Generator().manual_seed(seed)
+        t = t_local * world
+        x = torch.randn(t, h, generator=g)
+        up = torch.randn(n, h, generator=g) * 0.1
+        down = torch.randn(n, h, generator=g) * 0.1
+        idx = torch.randint(0, n, (t, k), generator=g, dtype=torch.int32)
+        idx[:, 0] = idx[:, 1]          # duplicates inside a token
+        w = torch.rand(t, k, generator=g)
+        part = ColumnPartition(h, world, rank)
+        sl = slice(rank * t_local, (rank + 1) * t_local)
+        # the two exchanges are inverse to each other and keep the global token order
+        cols = exchange_token_columns(x[sl], part)
+        assert torch.equal(cols, x[:, part.lo:part.hi])
+        back = return_state_columns(cols, part)
+        assert torch.equal(back.transpose(0, 1).reshape(t_local, h), x[sl])
+        got = column_expert_states(x[sl], idx[sl], w[sl], part.slice_columns(up), part.slice_columns(down), part,
+                                   dots_fn=_oracle_dots, combine_fn=_oracle_combine)
+        expect = orc.expert_forward(x, up, down, w, idx)[sl]
+        ret[rank] = float((got - expect).abs().max())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,t_local,h,n", [(2, 12, 16, 64), (3, 5, 24, 50), (4, 3, 32, 7)])
+def test_column_partitioned_exchange_gloo(world, t_local, h, n):
+    """Token columns out, routing gathered, partial dot products all-reduced, state columns back: the real exchange code
+    on gloo ranks with the oracle's arithmetic per rank equals the oracle's single-process answer."""
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_column_worker, args=(r, world, port, t_local, h, n, 6, 3, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)
