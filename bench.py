@@ -493,6 +493,9 @@ def run_c5(world, rank, dev, dist_on, steps=5, warmup=2):
             "mode": f"the same tables cut by columns over {world} GPUs: all-to-all of token / state columns, all-reduce of the dot products",
             "ms_per_step": ms_c, "tokens_s": cfg["T"] / (ms_c * 1e-3), "tables_gib_per_gpu": 2 * up_cols.numel() * 2 / 2 ** 30,
             "phases_ms": phases_c, "parity": parity_c}
+        out["best_mode"] = "column_partitioned" if ms_c < ms else "row_partitioned"
+        out["best_ms_per_step"] = min(ms, ms_c)
+        out["best_tokens_s"] = cfg["T"] / (min(ms, ms_c) * 1e-3)
         del col, up_cols, down_cols
         layer = tables = None
     del layer, inner, tables, x, y

@@ -833,7 +833,8 @@ class ColumnPartitionedOmniMoE(torch.nn.Module):
                                             status.data_ptr(), main.cuda_stream))
             clock.stop(tk)
             main.wait_event(ev_y)
-            states = mine.transpose(0, 1).reshape(t, h).float()
+            states = torch.empty((t, h), device=dev, dtype=torch.float32)   # [world, t, hs] bf16 -> [t, world * hs] fp32, one pass
+            states.view(t, world, hs).copy_(mine.transpose(0, 1))
             tk = clock.start("mlp")
             _lib.check(lib.omni_mlp_down(act.data_ptr(), wd.data_ptr(), t, h, i, states.data_ptr(), y.data_ptr(),
                                          status.data_ptr(), main.cuda_stream))
