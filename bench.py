@@ -257,7 +257,7 @@ def _workload_inputs():
     return torch.randn(1, CFG["tokens"], CFG["hidden"], generator=torch.Generator().manual_seed(100)).to(torch.bfloat16)
 
 
-def _cpu_forward_fn():
+def _cpu_forward_fn(dtype=torch.bfloat16):
     """A callable running one forward of the whole workload on the CPU, and what it is.
 
     First choice: the reference project's own PyTorch module (OmniMoE_Torch, omni_moe/modules/omni_moe.py:109-194),
@@ -273,8 +273,10 @@ def _cpu_forward_fn():
         ref_layer, ref_config = ref
         torch.manual_seed(0)
         m = ref_layer(ref_config(CFG["hidden"], CFG["intermediate"], "silu", CFG["experts"], CFG["top_k"]))
-        m = m.to(torch.bfloat16).eval()
-        return (lambda: m(x)), "reference", "bf16", cores, "OmniMoE_Torch of the reference project (unmodified file), module and tokens in bf16"
+        m = m.to(dtype).eval()
+        xd = x.to(dtype)
+        name = "bf16" if dtype == torch.bfloat16 else "f32"
+        return (lambda: m(xd)), "reference", name, cores, f"OmniMoE_Torch of the reference project (unmodified file), module and tokens in {name}"
     from oracle import omni_oracle as orc
     from omni_moe_b200.modules.omni_moe import OmniMoE, OmniMoEConfig
     torch.manual_seed(0)
@@ -297,8 +299,23 @@ def cpu_baseline_rate(seconds_budget: float = 12.0):
             el = time.perf_counter() - t0
             if el > seconds_budget or n >= 100:
                 break
-    return {"value": CFG["tokens"] * n / el, "unit": "tokens/s", "cores": cores, "kind": kind, "dtype": dtype,
-            "sample": f"{n} forwards of the whole workload ({CFG['tokens']} tokens each) in {el:.1f} s; {what}"}
+    out = {"value": CFG["tokens"] * n / el, "unit": "tokens/s", "cores": cores, "kind": kind, "dtype": dtype,
+           "sample": f"{n} forwards of the whole workload ({CFG['tokens']} tokens each) in {el:.1f} s; {what}"}
+    if kind == "reference":
+        # the same module in float32 (the precision the parity oracle computes in), a few forwards for the record
+        fwd32 = _cpu_forward_fn(torch.float32)[0]
+        with torch.no_grad():
+            fwd32()
+            n32, t0 = 0, time.perf_counter()
+            while n32 < 20:
+                fwd32()
+                n32 += 1
+                el32 = time.perf_counter() - t0
+                if el32 > 4.0:
+                    break
+        out["float32"] = {"value": CFG["tokens"] * n32 / el32, "unit": "tokens/s",
+                          "sample": f"{n32} forwards in {el32:.1f} s, module and tokens in float32"}
+    return out
 
 
 def run_reference(args, rank):
