@@ -406,7 +406,7 @@ def _plain_coef(x, up, w, idx, n):
 
 
 @pytest.mark.parametrize("t,h,n,k,min_run", [(4096, 512, 4096, 8, 512), (1000, 264, 300, 6, 64), (2048, 4096, 512, 4, 128),
-                                             (4099, 1024, 70000, 16, 0)])
+                                             (4099, 1024, 70000, 16, 0), (33, 264, 7, 4, 8), (129, 8, 3, 1, 16)])
 def test_hot_experts_take_the_dense_products_and_agree_with_the_gathered_ones(t, h, n, k, min_run):
     """Skewed routing: the experts that fill a whole window of min_run sorted positions are found (every expert with
     2 * min_run - 1 pairs must be among them unless 64 others come first, none with fewer than min_run pairs may be),
