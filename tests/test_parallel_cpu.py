@@ -277,3 +277,48 @@ def test_column_partitioned_exchange_gloo(world, t_local, h, n):
         p.join(120)
         assert p.exitcode == 0
     assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)
+
+
+def _column_wrapper_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from omni_moe_b200.modules.omni_moe import OmniMoE, OmniMoEConfig
+        from omni_moe_b200.parallel import ColumnPartitionedOmniMoE, columns_from_row_slices
+        torch.manual_seed(0)
+        full = OmniMoE(OmniMoEConfig(32, 64, "silu", 16, 2))
+        table = full.up_embed.weight.detach().clone()
+        m = ColumnPartitionedOmniMoE(full, None)
+        out = [m.up_cols.shape == (16, 16), torch.equal(m.up_cols.float(), table[:, rank * 16:(rank + 1) * 16].bfloat16().float()),
+               full.up_embed.weight.shape[0] == 0]
+        try:
+            full._operands()
+            out.append(False)
+        except RuntimeError:
+            out.append(True)
+        # rows -> columns without holding the table whole
+        cols = columns_from_row_slices(table[rank * 8:(rank + 1) * 8].contiguous())
+        out.append(torch.equal(cols, table[:, rank * 16:(rank + 1) * 16]))
+        # a hidden size that cannot be cut into slices of a multiple of 8 columns is refused
+        try:
+            ColumnPartitionedOmniMoE(OmniMoE(OmniMoEConfig(24, 64, "silu", 16, 2)), None)
+            out.append(False)
+        except ValueError:
+            out.append(True)
+        ret[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_partitioned_wrapper_keeps_the_slices_and_disarms_the_inner_module():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_column_wrapper_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert all(all(ret[r]) for r in range(world)), dict(ret)
