@@ -24,7 +24,10 @@ Printed JSON keys (one line, rank 0):
   partitioned_c5  the largest configuration (65536 tokens, hidden 4096, intermediate 11008, 1024 x 1024
              experts, top-k 64; strong scaling): on one GPU the whole layer, on N > 1 GPUs with the expert
              tables row-partitioned and dispatched / combined over NCCL; with the device time of its
-             phases and a parity check of sampled tokens against the CPU oracle
+             phases and a parity check of sampled tokens against the CPU oracle.  Its sub-record
+             column_partitioned is the same step with the same tables cut by columns instead (all-to-all of
+             token / state columns, all-reduce of the dot products, no host synchronisation), checked the
+             same way; best_mode / best_ms_per_step name the faster of the two
 Synthetic data: x ~ N(0,1), weights from the module's default initialisation under seed 0 (quick-start
 shape) or N(0, 0.02) (largest configuration).
 
