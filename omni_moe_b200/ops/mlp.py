@@ -66,8 +66,23 @@ def omni_mlp_func(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.T
     :param limit: optional clamp of gate and up before the activation (the ``limit`` of the reference's
         ``PrecisionConfig``, omni_moe/ops/triton/omni_mlp.py:27,54-61, which its public entry leaves unset)
     :return y: (num_tokens, hidden_size), dtype of ``x``
+
+    bf16 tensors (and fp16, rounded to bf16) run the two tcgen05 GEMMs of this library with fp32 accumulation; all-float32
+    tensors are computed in float32 by torch's matmuls (see below).
     """
     assert x.dim() == 2
+    if all(t.dtype == torch.float32 for t in (x, gate_weight, up_weight, down_weight)):
+        # float32 tensors get float32 arithmetic, as the reference gives them (its three projections are library GEMMs,
+        # omni_moe/ops/triton/interface.py:23-29): this one case does not run the kernels of this library but torch's
+        # float32 matmuls and elementwise operators, differentiable through autograd.  bf16 / fp16 tensors, and every
+        # path of the module's fused forward, use the tcgen05 kernels below.
+        _lib.require_cuda(x, gate_weight, up_weight, down_weight)
+        g = torch.nn.functional.linear(x, gate_weight)
+        u = torch.nn.functional.linear(x, up_weight)
+        if limit is not None:
+            assert limit > 0, "limit must be positive"
+            g, u = g.clamp(-limit, limit), u.clamp(-limit, limit)
+        return torch.nn.functional.linear(torch.nn.functional.silu(g) * u, down_weight)
     if x.size(1) % 8 or gate_weight.size(0) % 8:
         # hidden or intermediate size not a multiple of 8: zero padding leaves the result unchanged
         # (padded gate / up rows give silu(0) * 0 = 0 against zero columns of the down projection)
