@@ -14,7 +14,8 @@ Printed JSON keys (one line, rank 0):
              streams so that one step's kernel tails overlap the next step's heads), device-timed
   e2e        tokens/s through GraphedOmniMoE with HOST input and output buffers: every step copies
              its tokens from pinned host memory, runs the forward and copies the result back;
-             steps are pipelined over independent slots
+             steps are pipelined over independent slots; the leg runs untimed for --link-warmup seconds first
+             (the host link needs traffic to leave its low-power state)
   roofline   of the dominant kernel (gate/up GEMM with the SwiGLU epilogue), timed live here
   cpu_baseline  the reference's own PyTorch layer (OmniMoE_Torch) on the host cores, N = 1 only
   config     static description of the workload, identical in both arms
@@ -194,7 +195,7 @@ def time_resident(slots, steps, warmup, dist_on, dev, n_streams=RESIDENT_STREAMS
     return first_ms, later
 
 
-def time_e2e(slots, steps, warmup, dist_on, dev):
+def time_e2e(slots, steps, warmup, dist_on, dev, link_warmup_s=0.1):
     """Host buffers in and out every step; slot s runs on its own stream so that the copies of one
     step overlap the kernels of another."""
     def step(i):
@@ -204,6 +205,15 @@ def time_e2e(slots, steps, warmup, dist_on, dev):
             s["graph"].replay()
             s["y_host"].copy_(s["graph"].y, non_blocking=True)
 
+    # The host link idles while the resident legs run and needs some tens of milliseconds of traffic to leave its
+    # low-power state (a bare copy loop on these boxes: 36 GB/s over its first 100 copies of 8 MiB, 54 GB/s after).
+    # A serving process is in that steady state, so the same steps run untimed for LINK_WARMUP_S first.
+    link_steps, t0 = 0, time.perf_counter()
+    while link_warmup_s > 0 and time.perf_counter() - t0 < link_warmup_s:
+        for i in range(SLOTS):
+            step(i)
+        link_steps += SLOTS
+        slots[0]["stream"].synchronize()
     for i in range(warmup):
         step(i)
     barrier(dist_on)
@@ -218,7 +228,7 @@ def time_e2e(slots, steps, warmup, dist_on, dev):
         main.wait_stream(s["stream"])
     e1.record(main)
     barrier(dist_on)
-    return max_over_ranks(e0.elapsed_time(e1), dist_on, dev)
+    return max_over_ranks(e0.elapsed_time(e1), dist_on, dev), link_steps
 
 
 def time_gate_up(slots, reps):
@@ -529,6 +539,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--link-warmup", type=float, default=0.1,
+                    help="seconds of untimed end-to-end steps before the e2e leg's warm-up (0 = none)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-c5", action="store_true", help="skip the largest-configuration leg")
     ap.add_argument("--sustain", type=float, default=1.0, help="seconds of back-to-back blocks for the sustained figure")
@@ -562,7 +574,7 @@ def main():
     from omni_moe_b200.modules.omni_moe import OmniMoE
     ms, _ = time_resident(slots, args.steps, args.warmup, dist_on, dev)
     ms_serial, _ = time_resident(slots, args.steps, args.warmup, dist_on, dev, n_streams=1)   # one step at a time, for the record
-    ms_e2e = time_e2e(slots, args.steps, args.warmup, dist_on, dev)
+    ms_e2e, link_steps = time_e2e(slots, args.steps, args.warmup, dist_on, dev, args.link_warmup)
     # sustained: the same K-step block back to back for a second or more, clocks sampled meanwhile
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -608,6 +620,8 @@ def main():
             "e2e": {"value": tokens_total / (ms_e2e * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": CFG["tokens"] * CFG["hidden"] * 2, "d2h_bytes_per_step": CFG["tokens"] * CFG["hidden"] * 2,
                     "ms_per_step": ms_e2e / args.steps, "pipeline": f"{SLOTS} slots, one stream each",
+                    "link_warmup": f"{link_steps} untimed steps of the same pipeline ({args.link_warmup:.2f} s) before the {args.warmup} warm-up steps: "
+                                   "the host link needs traffic to leave its low-power state",
                     "host_placement": placement["reason"]},
             "gpu_launches": OmniMoE.kernels_per_forward(CFG["experts"], CFG["hidden"], 64, CFG["top_k"]) * args.steps,
             "clocks": clocks,
